@@ -1,0 +1,400 @@
+"""Benchmark of the Flash STU token loop on B200: standalone FlashSTUBlock (approx variant), bf16,
+B=8 sequences per GPU, L=8192, d_model=1024, K=24 -- the 8K-context block configuration.
+
+One step = one pass of the hot path over one batch of synthetic input:
+  prefill  the block forward over all L positions (fills the decode cache), then
+  decode   `--decode-steps` (512) cached single-token steps at positions L-512 .. L-1, teacher-forced from
+           the same inputs (so every decode row is checkable against the prefill rows).
+`value` is decode tokens/s summed over GPUs with inputs resident in HBM (CUDA events, max over ranks);
+`prefill` holds the prefill tokens/s of the same steps; `e2e` repeats the step through the public
+module API from pinned host buffers with the host<->device copies inside the timed region.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+Launch with torch.distributed.run for N > 1 (one rank per GPU, weak scaling: B=8 per GPU, no collective
+on the data path; NCCL only carries the max-over-ranks of the timings).
+`--impl reference` times the CPU restatement of the reference's path (oracle/) on the host cores.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+D_MODEL, NUM_FILTERS = 1024, 24
+L2_BYTES = 126e6
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--batch", type=int, default=8, help="sequences per GPU (default: the benchmark's 8)")
+    ap.add_argument("--seq-len", type=int, default=8192, help="context length (default: the benchmark's 8192)")
+    ap.add_argument("--decode-steps", type=int, default=512)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch decode steps eagerly instead of replaying a CUDA graph")
+    return ap.parse_args()
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for ln in self.lines:
+            f = [s.strip() for s in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def workload_name(a):
+    return (f"FlashSTUBlock(use_attention=False, approx) bf16 B={a.batch}/GPU L={a.seq_len} d_model={D_MODEL} "
+            f"K={NUM_FILTERS} mlp_scale=4: prefill over L positions + {a.decode_steps} cached decode steps")
+
+
+def filter_file(L):
+    p = os.path.join(ROOT, "flash_stu_2_b200", "data", f"phi_{L}_{NUM_FILTERS}.pt")
+    return p if os.path.exists(p) else None
+
+
+def make_state(L, seed=1):
+    """Random-init block parameters (seed 1, xavier for the STU projections, default Linear init)."""
+    import flash_stu_2_b200 as F
+    torch.manual_seed(seed)
+    fp = filter_file(L)
+    cfg = F.FlashSTUConfig(n_embd=D_MODEL, seq_len=L, num_eigh=NUM_FILTERS, use_attn=False, mlp_scale=4,
+                           torch_dtype=torch.bfloat16, n_layers=1, vocab_size=1, n_heads=D_MODEL // 64, filter_path=fp)
+    phi = None
+    if fp is not None:
+        phi = F.load_spectral_filters(fp, device="cpu", dtype=torch.bfloat16, verify_shape=(L, NUM_FILTERS))
+    blk = F.FlashSTUBlock(config=cfg, phi=phi)
+    for name, p in blk.named_parameters():
+        if ".stu.M_" in name:
+            torch.nn.init.xavier_normal_(p)
+    return blk
+
+
+# ----------------------------------------------------------------------------------------------- CPU arm
+def cpu_forward_seconds(blk_sd, n, x1, T):
+    from oracle import stu_oracle as O
+    lsd = {k[len("layer."):]: v for k, v in blk_sd.items() if k.startswith("layer.")}
+    t = time.perf_counter()
+    with torch.no_grad():
+        O.stu_layer(x1[:, :T], lsd, blk_sd["phi"], n, True)
+    return time.perf_counter() - t
+
+
+def cpu_baseline(a, blk, x_host):
+    """The reference's arithmetic for this block on the host cores (oracle port).  The reference has no
+    incremental STU decode, so one decode token costs a forward over the whole prefix."""
+    from oracle import stu_oracle as O
+    sd = {k: v.detach().clone() for k, v in blk.state_dict().items()}
+    n = O.fft_length(a.seq_len)
+    x1 = x_host[:1].clone()
+    t_dec = cpu_forward_seconds(sd, n, x1, a.seq_len - a.decode_steps // 2)
+    t_pre = cpu_forward_seconds(sd, n, x1, a.seq_len)
+    return {"value": 1.0 / t_dec, "unit": "decode tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "prefill_tokens_per_s": a.seq_len / t_pre,
+            "sample": f"1 of {a.batch} sequences: one decode position by full-prefix recompute "
+                      f"(T={a.seq_len - a.decode_steps // 2}) and one {a.seq_len}-token prefill forward, fp32 FFT path"}
+
+
+def run_reference(a):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import stu_oracle as O
+    blk = make_state(a.seq_len)
+    sd = {k: v.detach().clone() for k, v in blk.state_dict().items()}
+    n = O.fft_length(a.seq_len)
+    torch.manual_seed(1)
+    x1 = torch.randn(1, a.seq_len, D_MODEL).bfloat16()
+    first = a.seq_len - a.decode_steps
+    for i in range(a.warmup):
+        cpu_forward_seconds(sd, n, x1, first + i + 1)
+    t0 = time.perf_counter()
+    for i in range(a.steps):
+        cpu_forward_seconds(sd, n, x1, first + i + 1)   # one decode token of one sequence = one prefix forward
+    dt = time.perf_counter() - t0
+    val = a.steps / dt
+    cores = torch.get_num_threads()
+    sample = (f"each step = one decode token of one sequence at position {first}+i by full-prefix recompute "
+              f"(the reference keeps no STU cache), torch.fft fp32 path, {cores} threads")
+    print(json.dumps({
+        "impl": "reference", "metric": "decode tokens/s (aggregate over GPUs)", "value": val, "unit": "tokens/s",
+        "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup, "ms_per_step": dt / a.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": workload_name(a), "l2": "n/a (host run)"},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}))
+
+
+# ----------------------------------------------------------------------------------------------- GPU arm
+def run_b200(a):
+    import torch.distributed as dist
+    from flash_stu_2_b200 import ops
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py --impl b200 needs a CUDA device: the kernels have no CPU fallback")
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, L, d, S = a.batch, a.seq_len, D_MODEL, a.decode_steps
+    blk = make_state(L).to(dev).eval()
+    torch.manual_seed(1 + rank)
+    x_host = torch.randn(B, L, d).bfloat16().pin_memory()
+    x_dev = x_host.to(dev)
+    first = L - S
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    x_work = torch.empty_like(x_dev)
+    x_step = torch.empty(B, 1, d, dtype=torch.bfloat16, device=dev)
+    state = {"cache": None, "graph": None, "graph_launches": 0}
+
+    def prefill():
+        x_work.copy_(x_dev)
+        _, state["cache"] = blk(x_work, use_cache=True)
+
+    def rewind():
+        pos = state["cache"][1]
+        pos[:, 0] = first
+        pos._host_t = first
+
+    def eager_step():
+        _, state["cache"] = blk(x_step, past_key_value=state["cache"], use_cache=True)
+
+    def decode(n_steps=S):
+        pos = state["cache"][1]
+        for i in range(n_steps):
+            x_step.copy_(x_dev[:, first + i:first + i + 1])
+            if state["graph"] is not None:
+                state["graph"].replay()
+            else:
+                eager_step()
+        pos._host_t = first + n_steps
+
+    with torch.no_grad():
+        # first pass: eager, builds derived weights / scratch / status word before any capture
+        prefill(); rewind(); decode(2)
+        torch.cuda.synchronize()
+        if not a.no_graph:
+            rewind()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                eager_step()
+            torch.cuda.current_stream().wait_stream(side)
+            rewind()
+            g = torch.cuda.CUDAGraph()
+            n0 = ops.launch_count
+            with torch.cuda.graph(g):
+                eager_step()
+            state["graph_launches"] = ops.launch_count - n0
+            state["graph"] = g
+        for _ in range(a.warmup):
+            prefill(); rewind(); decode()
+        torch.cuda.synchronize()
+        ops.check_status()
+
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t_pre = t_dec = 0.0
+        n_launch0 = ops.launch_count
+        wall0 = time.perf_counter()
+        for _ in range(a.steps):
+            e0, e1, e2 = ev(), ev(), ev()
+            e0.record(); prefill(); e1.record(); rewind(); decode(); e2.record()
+            torch.cuda.synchronize()
+            t_pre += e0.elapsed_time(e1)
+            t_dec += e1.elapsed_time(e2)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - wall0
+        launches = ops.launch_count - n_launch0
+        if state["graph"] is not None:
+            launches += a.steps * S * state["graph_launches"]
+        clocks = sampler.stop() if rank == 0 else None
+        ops.check_status()
+        times = torch.tensor([t_pre, t_dec], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        t_pre, t_dec = (float(v) for v in times.tolist())   # ms, max over ranks, summed over steps
+
+        # ---- dominant kernel alone (fused decode kernel), CUDA events on the launching stream
+        layer = blk.layer
+        hist, pos = state["cache"]
+        MinT, taps = layer.stu.prepared()
+        x2 = x_step.view(B, d)
+        out2 = torch.empty_like(x2)
+        reps = min(256, S)
+        rewind()
+        for _ in range(3):
+            ops.decode_approx(x2, layer.stu_norm.weight, MinT, hist, taps, pos, out2)
+        rewind()
+        k0, k1 = ev(), ev()
+        k0.record()
+        for _ in range(reps):
+            ops.decode_approx(x2, layer.stu_norm.weight, MinT, hist, taps, pos, out2)
+        k1.record()
+        torch.cuda.synchronize()
+        kern_ms = k0.elapsed_time(k1) / reps
+        t_mid = first + reps / 2.0
+        # algorithmic bytes of one launch at position t: half the history (one parity) of every sequence,
+        # the even taps of every channel, M_inputs, and the token's row in and out
+        kern_bytes = B * d * (t_mid / 2) * 2 + d * (t_mid / 2 + 1) * 2 + d * d * 2 + 3 * B * d * 2
+
+        # ---- end to end through the module API from pinned host memory
+        y_host = torch.empty(B, 1, d, dtype=torch.bfloat16).pin_memory()
+        yp_host = torch.empty(B, L, d, dtype=torch.bfloat16).pin_memory()
+        e2e_steps = max(1, min(a.steps, 3))
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        w0 = time.perf_counter()
+        dec_s = 0.0
+        for _ in range(e2e_steps):
+            x_work.copy_(x_host, non_blocking=True)
+            _, state["cache"] = blk(x_work, use_cache=True)
+            yp_host.copy_(x_work, non_blocking=True)
+            torch.cuda.synchronize()
+            rewind()
+            d0 = time.perf_counter()
+            for i in range(S):
+                x_step.copy_(x_host[:, first + i:first + i + 1], non_blocking=True)
+                if state["graph"] is not None:
+                    state["graph"].replay()
+                else:
+                    eager_step()
+                y_host.copy_(x_step, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+            dec_s += time.perf_counter() - d0
+        e2e_wall = time.perf_counter() - w0
+        e2e = torch.tensor([dec_s, e2e_wall], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
+        dec_s, e2e_wall = (float(v) for v in e2e.tolist())
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    pk = peaks()
+    dec_tokens = world * B * S * a.steps
+    pre_tokens = world * B * L * a.steps
+    value = dec_tokens / (t_dec / 1e3)
+    achieved = kern_bytes / (kern_ms / 1e3) / 1e9
+    # prefill FLOPs per token: dense 2*(d^2 + 3*4*d^2) plus the FFT-as-GEMM form of one convolution per channel
+    n_fft = 1 << (2 * L - 2).bit_length()          # 2^ceil(log2(2L-1))
+    n1 = 1 << ((n_fft.bit_length() - 1) // 2)      # two-factor split n_fft = n1 * n2
+    n2 = n_fft // n1
+    flops_tok = 2 * 13 * d * d + d * 16 * n_fft * (n1 + n2) / L
+    pre_tflops = flops_tok * B * L / (t_pre / a.steps / 1e3) / 1e12
+    ws_mb = (B * d * L * 2 + d * L + 13 * d * d * 2) / 1e6
+    line = {
+        "metric": "decode tokens/s (aggregate over GPUs)", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": a.steps, "warmup": a.warmup, "ms_per_step": (t_pre + t_dec) / a.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": workload_name(a), "parallelism": f"dp{world} (independent sequences, no collective)",
+                   "l2": f"inputs larger than L2: decode working set {ws_mb:.0f} MB (history+taps+weights) and "
+                         f"prefill input {B * L * d * 2 / 1e6:.0f} MB vs 126 MB L2; no explicit flush",
+                   "decode_launch": "CUDA graph replay per step" if state["graph"] is not None else "eager launches"},
+        "decode_ms_per_token_step": t_dec / a.steps / S,
+        "prefill": {"value": pre_tokens / (t_pre / 1e3), "unit": "tokens/s", "ms": t_pre / a.steps,
+                    "tflops_algorithmic": pre_tflops,
+                    "frac_of_tensor_peak": pre_tflops / pk["bf16_tflops_sustained"],
+                    "peak_tflops": pk["bf16_tflops_sustained"], "peak_source": pk["source"] + " (sustained)"},
+        "roofline": {"bound": "hbm", "kernel": "stu_decode_kernel<bf16>", "achieved": achieved, "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "peak_source": pk["source"],
+                     "bytes_per_launch": kern_bytes, "us_per_launch": kern_ms * 1e3, "traffic": None},
+        "e2e": {"value": world * B * S * e2e_steps / dec_s, "unit": "tokens/s",
+                "h2d_bytes_per_step": B * L * d * 2 + S * B * d * 2, "d2h_bytes_per_step": B * L * d * 2 + S * B * d * 2,
+                "wall_s_per_step": e2e_wall / e2e_steps,
+                "note": "decode tokens/s with a pinned-host copy in and out around every token step; the prefill "
+                        "of each step also copies its 134 MB input in and its output back"},
+        "gpu_launches": launches, "wall_s_timed_region": wall, "clocks": clocks,
+    }
+    traffic_file = os.path.join(ROOT, "profiles", "decode_kernel_traffic.json")
+    if os.path.exists(traffic_file):
+        try:
+            line["roofline"]["traffic"] = json.load(open(traffic_file)).get("dram_bytes_per_launch_scaled")
+        except Exception:
+            pass
+    if world == 1 and not a.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(a, make_state(L), x_host)
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)

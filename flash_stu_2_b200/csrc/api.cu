@@ -1,0 +1,69 @@
+// C-ABI entry points that dispatch between the linear-layer kernels (see include/stu_b200.h).
+#include "common.cuh"
+#include "epilogue.cuh"
+
+extern "C" int stu_b200_version(void) { return 100; }
+
+enum { BACKEND_AUTO = 0, BACKEND_SIMT = 1, BACKEND_TCGEN05 = 2, BACKEND_SKINNY = 3 };
+
+// y = epilogue(x[M,K] @ W[N,K]^T).  element (n,k) of W at W[n*w_row_stride + k*w_k_stride].
+//   epilogue 0: y = acc                  1: y = resid + round(acc)
+//            2: y = round(gelu_tanh(round(x@W^T))) * round(x@W2^T)
+//            3: scatter into the parity-split history (y = hist base, hist_T tokens per sequence
+//               starting at time hist_t0, N channels, hist_Lh elements per parity row)
+// norm_w != NULL asks for x to be RMS-normalised (eps) on the way in; only the decode (skinny) path
+// fuses this, other shapes return STU_ERR_UNSUPPORTED so that the caller normalises separately.
+extern "C" int stu_linear(const void* x, long long x_row_stride, const void* W, long long w_row_stride,
+                          long long w_k_stride, const void* W2, const void* resid, long long resid_row_stride,
+                          void* y, long long y_row_stride, int M, int N, int K, int epilogue, int hist_T,
+                          int hist_t0, int hist_Lh, const void* norm_w, float eps, int dtype, int backend,
+                          void* stream) {
+  if (!x || !W || !y) return STU_ERR_NULL;
+  if (M < 0 || N <= 0 || K <= 0) return STU_ERR_SHAPE;
+  if (M == 0) return STU_OK;
+  if (epilogue < EPI_STORE || epilogue > EPI_HIST) return STU_ERR_UNSUPPORTED;
+  if (epilogue == EPI_GELU_MUL && !W2) return STU_ERR_NULL;
+  if (epilogue == EPI_RESID && !resid) return STU_ERR_NULL;
+  if (epilogue == EPI_HIST && (hist_T <= 0 || hist_Lh <= 0 || hist_t0 < 0 || (M % hist_T) != 0 ||
+                               hist_t0 + hist_T > 2 * hist_Lh))
+    return STU_ERR_SHAPE;
+  if (dtype != STU_F32 && dtype != STU_BF16) return STU_ERR_DTYPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  EpiArgsAny ep;
+  ep.y = y;
+  ep.ldy = (epilogue == EPI_HIST) ? (long long)N : y_row_stride;
+  ep.resid = resid;
+  ep.ldr = resid_row_stride;
+  ep.Tseq = hist_T;
+  ep.t0 = hist_t0;
+  ep.Lh = hist_Lh;
+
+  bool sk_ok = skinny_supported(x, x_row_stride, W, w_row_stride, w_k_stride, W2, M, N, K, epilogue, dtype);
+  if (norm_w) {
+    if (!sk_ok || dtype != STU_BF16 || (backend != BACKEND_AUTO && backend != BACKEND_SKINNY))
+      return STU_ERR_UNSUPPORTED;
+    return skinny_dispatch(x, x_row_stride, W, w_row_stride, W2, M, N, K, epilogue, ep, norm_w, eps, dtype, st);
+  }
+  bool tc_ok = gemm_tc_supported(x, x_row_stride, W, w_row_stride, w_k_stride, W2, M, N, K, epilogue, ep, dtype);
+  if (backend == BACKEND_AUTO) backend = sk_ok ? BACKEND_SKINNY : (tc_ok ? BACKEND_TCGEN05 : BACKEND_SIMT);
+  switch (backend) {
+    case BACKEND_SKINNY:
+      if (!sk_ok) return STU_ERR_UNSUPPORTED;
+      return skinny_dispatch(x, x_row_stride, W, w_row_stride, W2, M, N, K, epilogue, ep, nullptr, eps, dtype, st);
+    case BACKEND_TCGEN05:
+      if (!tc_ok) return STU_ERR_UNSUPPORTED;
+      return gemm_tc_dispatch(x, x_row_stride, W, w_row_stride, W2, M, N, K, epilogue, ep, st);
+    case BACKEND_SIMT:
+      return gemm_simt_dispatch(x, x_row_stride, W, w_row_stride, w_k_stride, W2, M, N, K, epilogue, ep, dtype, st);
+  }
+  return STU_ERR_UNSUPPORTED;
+}
+
+// 1 when stu_linear would fuse the RMSNorm for this shape (decode path), else 0.
+extern "C" int stu_linear_can_fuse_norm(int M, int N, int K, int epilogue, int dtype) {
+  (void)N;
+  if (dtype != STU_BF16 || M < 1 || M > 64 || K % 8 || epilogue == EPI_HIST) return 0;
+  int MT = (M + 15) / 16;
+  size_t smem = (size_t)MT * 16 * (K + 32) * 2 + (size_t)(epilogue == EPI_GELU_MUL ? 2 : 1) * 8 * MT * 4 * 32 * 4;
+  return smem <= 200 * 1024 ? 1 : 0;
+}

@@ -1,0 +1,88 @@
+// General tiled GEMM on CUDA cores with fp32 accumulation: the path for fp32 models (where the
+// 1e-3 / bit-exact-greedy bar rules out tf32 tensor cores) and for shapes the tcgen05 path does
+// not take (tiny K, unaligned strides).  y = epilogue(x @ W^T).
+#include "common.cuh"
+#include "epilogue.cuh"
+
+template <typename T, int EPI>
+__global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ A, long long lda,
+                                                        const T* __restrict__ B, long long ldb, long long skb,
+                                                        const T* __restrict__ B2, int M, int N, int K,
+                                                        EpiArgs<T> ep) {
+  constexpr int BM = 64, BN = 64, BK = 16;
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Bs[BK][BN + 4];
+  __shared__ float Bs2[EPI == EPI_GELU_MUL ? BK : 1][BN + 4];
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int tx = tid & 15, ty = tid >> 4;  // thread computes rows ty*4.., cols tx*4..
+  float acc[4][4] = {}, acc2[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    // 64x16 tile: 1024 elements, 4 per thread; consecutive threads walk k for coalescing
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      int e = tid + i * 256;
+      int r = e >> 4, kk = e & 15;
+      int m = m0 + r, k = k0 + kk;
+      As[kk][r] = (m < M && k < K) ? Elem<T>::to_f(A[(size_t)m * lda + k]) : 0.f;
+      int n = n0 + r;
+      bool ok = (n < N && k < K);
+      Bs[kk][r] = ok ? Elem<T>::to_f(B[(size_t)n * ldb + (size_t)k * skb]) : 0.f;
+      if (EPI == EPI_GELU_MUL) Bs2[kk][r] = ok ? Elem<T>::to_f(B2[(size_t)n * ldb + (size_t)k * skb]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; kk++) {
+      float a[4], b[4], b2[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; j++) b[j] = Bs[kk][tx * 4 + j];
+      if (EPI == EPI_GELU_MUL) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) b2[j] = Bs2[kk][tx * 4 + j];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+          if (EPI == EPI_GELU_MUL) acc2[i][j] = fmaf(a[i], b2[j], acc2[i][j]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+      if (m < M && n < N) epilogue_store<T, EPI>(ep, m, n, acc[i][j], acc2[i][j]);
+    }
+}
+
+template <typename T>
+static int launch_simt(const void* A, long long lda, const void* B, long long ldb, long long skb, const void* B2,
+                       int M, int N, int K, int epi, const EpiArgs<T>& ep, cudaStream_t st) {
+  dim3 grid((N + 63) / 64, (M + 63) / 64);
+#define LAUNCH(E)                                                                                          \
+  gemm_simt_kernel<T, E><<<grid, 256, 0, st>>>((const T*)A, lda, (const T*)B, ldb, skb, (const T*)B2, M, N, \
+                                               K, ep)
+  switch (epi) {
+    case EPI_STORE: LAUNCH(EPI_STORE); break;
+    case EPI_RESID: LAUNCH(EPI_RESID); break;
+    case EPI_GELU_MUL: LAUNCH(EPI_GELU_MUL); break;
+    case EPI_HIST: LAUNCH(EPI_HIST); break;
+    default: return STU_ERR_UNSUPPORTED;
+  }
+#undef LAUNCH
+  STU_CHECK_LAUNCH();
+  return STU_OK;
+}
+
+int gemm_simt_dispatch(const void* A, long long lda, const void* B, long long ldb, long long skb, const void* B2,
+                       int M, int N, int K, int epi, const EpiArgsAny& ep, int dtype, cudaStream_t st) {
+  if (dtype == STU_F32) return launch_simt<float>(A, lda, B, ldb, skb, B2, M, N, K, epi, ep.as<float>(), st);
+  if (dtype == STU_BF16) return launch_simt<bf16>(A, lda, B, ldb, skb, B2, M, N, K, epi, ep.as<bf16>(), st);
+  return STU_ERR_DTYPE;
+}

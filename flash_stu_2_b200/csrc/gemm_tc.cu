@@ -1,0 +1,402 @@
+// Prefill linear layers on the 5th-generation tensor cores: D[M,N] = A[M,K] . B[N,K]^T in bf16 with
+// fp32 accumulators held in tensor memory (TMEM).
+//
+// One CTA computes a 128 x 128 output tile.  Warp 0 is the TMA producer (cp.async.bulk.tensor, 128-byte
+// swizzled 128x64 operand tiles into a ring of shared-memory stages), warp 1 allocates TMEM and
+// issues tcgen05.mma from one thread, warps 2..5 drain the accumulator with tcgen05.ld and run the
+// fused epilogue (store / residual add / tanh-GELU gate * up / transposed scatter into the projected
+// history).  Two CTAs fit per SM for the single-accumulator epilogues, so one tile's epilogue
+// overlaps the other tile's main loop.  No cluster features and no multicast are used.
+//
+// Every wait on an mbarrier is bounded: on expiry the waiter raises the status word, the CTA drains
+// its outstanding bulk copies (bounded as well), frees its TMEM and returns.
+#include <cuda.h>
+#include <stdlib.h>
+
+#include "common.cuh"
+#include "epilogue.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BN * BK * 2;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+enum { EPI_HIST_T = 4 };  // internal: rows = channels, columns = tokens (operands swapped by the host)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after WAIT_LIMIT polls or two seconds of wall time, whichever comes first.
+// Returns false when the limit ran out or another role already gave up.
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  uint64_t start = 0;
+  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 255u) {
+      if (*abort_flag) return false;
+      uint64_t now = global_ns();
+      if (start == 0) start = now;
+      else if (now - start > 2000000000ull) break;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major bf16 tile stored as rows of 128 bytes with the
+// 128-byte swizzle (what the tensor maps below produce): 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;                 // leading byte offset (unused for swizzled K-major), encoded >> 4
+  d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                 // descriptor version for this architecture
+  d |= (uint64_t)2 << 61;                 // 128-byte swizzle
+  return d;
+}
+// Instruction descriptor: D fp32, A/B bf16, both K-major, M = 128, N = BN.
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(IDESC), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+      "%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
+template <int EPI, int STAGES>
+__global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                      const __grid_constant__ CUtensorMap tmB,
+                                                      const __grid_constant__ CUtensorMap tmB2, int M, int N, int K,
+                                                      int tiles_m, int tiles_n, int m_fast, EpiArgs<bf16> ep,
+                                                      int* status) {
+  constexpr bool DUAL = (EPI == EPI_GELU_MUL);
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES * (DUAL ? 2 : 1);
+  constexpr uint32_t TMEM_COLS = DUAL ? 256 : 128;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* issued_ctr = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));
+  int* consumed_ctr = issued_ctr + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bid = blockIdx.x;
+  const int tm = m_fast ? (bid % tiles_m) : (bid / tiles_n);
+  const int tn = m_fast ? (bid / tiles_m) : (bid % tiles_n);
+  const int m0 = tm * BM, n0 = tn * BN;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tmem_full, 1);
+    *abort_flag = 0;
+    *issued_ctr = 0;
+    *consumed_ctr = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer
+      for (int kb = 0; kb < num_kb; kb++) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) break;
+        unsigned char* sa = smem + s * STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        tma_load_2d(sa, &tmA, &full_bar[s], kb * BK, m0);
+        tma_load_2d(sa + A_BYTES, &tmB, &full_bar[s], kb * BK, n0);
+        if (DUAL) tma_load_2d(sa + A_BYTES + B_BYTES, &tmB2, &full_bar[s], kb * BK, n0);
+        *issued_ctr = kb + 1;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer
+      int kb = 0;
+      for (; kb < num_kb; kb++) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+        if (!mbar_wait(&full_bar[s], ph, abort_flag)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+        const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BK / 16; kk++) {
+          // advancing 16 bf16 = 32 bytes along K inside the swizzled row: +2 in the (>>4) address field
+          umma(tmem_base, da + 2 * kk, db + 2 * kk, (kb | kk) ? 1u : 0u);
+          if (DUAL) {
+            const uint64_t db2 = make_smem_desc(sa + A_BYTES + B_BYTES);
+            umma(tmem_base + BN, da + 2 * kk, db2 + 2 * kk, (kb | kk) ? 1u : 0u);
+          }
+        }
+        umma_commit(&empty_bar[s]);  // arrives when the MMAs above have finished reading this stage
+        *consumed_ctr = kb + 1;
+      }
+      if (kb == num_kb) umma_commit(tmem_full);
+    }
+  } else {
+    // ---------------- epilogue warps: TMEM lane quarter = warp % 4
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int m = m0 + row;
+    bool ok = mbar_wait(tmem_full, 0, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+#pragma unroll 1
+      for (int cch = 0; cch < BN / 32; cch++) {
+        uint32_t r[32], r2[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cch * 32);
+        tmem_ld32(taddr, r);
+        if (DUAL) tmem_ld32(taddr + BN, r2);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int nb = n0 + cch * 32;
+        if (m < M && nb < N) {
+          if (EPI == EPI_HIST_T) {
+            // row m = channel, columns = tokens nb..nb+31 of the flattened [B, T] batch
+            const int d = (int)ep.ldy;
+            const bool fast = (ep.Tseq % 32 == 0) && (ep.t0 % 16 == 0) && (nb + 32 <= N) && (ep.Lh % 8 == 0);
+            if (fast) {
+              const int b = nb / ep.Tseq, t = ep.t0 + (nb - b * ep.Tseq);  // t % 16 == 0
+              float ev[16], od[16];
+#pragma unroll
+              for (int j = 0; j < 16; j++) {
+                ev[j] = __uint_as_float(r[2 * j]);
+                od[j] = __uint_as_float(r[2 * j + 1]);
+              }
+              bf16* pe = ep.y + ((size_t)((size_t)b * d + m) * 2 + 0) * ep.Lh + (t >> 1);
+              bf16* po = ep.y + ((size_t)((size_t)b * d + m) * 2 + 1) * ep.Lh + (t >> 1);
+              store_vec(pe, ev);
+              store_vec(pe + 8, ev + 8);
+              store_vec(po, od);
+              store_vec(po + 8, od + 8);
+            } else {
+              for (int j = 0; j < 32; j++) {
+                int n = nb + j;
+                if (n < N) {
+                  int b = n / ep.Tseq, t = ep.t0 + (n - b * ep.Tseq);
+                  ep.y[hist_off(b, m, t, d, ep.Lh)] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                }
+              }
+            }
+          } else {
+            bf16* yrow = ep.y + (size_t)m * ep.ldy + nb;
+            const bf16* rrow = (EPI == EPI_RESID) ? ep.resid + (size_t)m * ep.ldr + nb : nullptr;
+            const bool vec = (nb + 32 <= N);
+#pragma unroll
+            for (int v8 = 0; v8 < 4; v8++) {
+              float o[8];
+              if (EPI == EPI_RESID) {
+                float rs[8];
+                if (vec) {
+                  load_vec(rrow + v8 * 8, rs);
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 8; j++) rs[j] = (nb + v8 * 8 + j < N) ? __bfloat162float(rrow[v8 * 8 + j]) : 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; j++) o[j] = rs[j] + round_to<bf16>(__uint_as_float(r[v8 * 8 + j]));
+              } else if (EPI == EPI_GELU_MUL) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                  float g = round_to<bf16>(gelu_tanh(round_to<bf16>(__uint_as_float(r[v8 * 8 + j]))));
+                  o[j] = g * round_to<bf16>(__uint_as_float(r2[v8 * 8 + j]));
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++) o[j] = __uint_as_float(r[v8 * 8 + j]);
+              }
+              if (vec) {
+                store_vec(yrow + v8 * 8, o);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                  if (nb + v8 * 8 + j < N) yrow[v8 * 8 + j] = __float2bfloat16_rn(o[j]);
+              }
+            }
+          }
+        }
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
+  __syncthreads();
+  if (*abort_flag) {
+    // A wait ran out.  Report it, then let copies that were issued but never consumed land (bounded)
+    // before shared memory is released.
+    if (threadIdx.x == 0) {
+      if (status) atomicExch(status, 3);
+      const int issued = *issued_ctr, consumed = *consumed_ctr;
+      for (int kb = consumed; kb < issued; kb++) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+        for (uint32_t it = 0; it < WAIT_LIMIT; ++it)
+          if (mbar_try_wait(&full_bar[s], ph)) break;
+      }
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// 2-D map over a row-major bf16 matrix [rows, cols] with row stride ld (elements); box 64 x 128, 128B swizzle.
+int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return STU_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? STU_OK : STU_ERR_UNSUPPORTED;
+}
+
+template <int EPI, int STAGES>
+int launch_tc(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& b2, int M, int N, int K, int m_fast,
+              const EpiArgs<bf16>& ep, int* status, cudaStream_t st) {
+  constexpr bool DUAL = (EPI == EPI_GELU_MUL);
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES * (DUAL ? 2 : 1);
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+  auto k = gemm_tc_kernel<EPI, STAGES>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  k<<<tiles_m * tiles_n, 192, smem, st>>>(a, b, b2, M, N, K, tiles_m, tiles_n, m_fast, ep, status);
+  STU_CHECK_LAUNCH();
+  return STU_OK;
+}
+
+int* g_status_word = nullptr;  // optional device status word registered by the host wrapper
+
+}  // namespace
+
+extern "C" int stu_set_status_word(int* device_status) {
+  g_status_word = device_status;
+  return STU_OK;
+}
+
+bool gemm_tc_supported(const void* A, long long lda, const void* B, long long ldb, long long skb, const void* B2,
+                       int M, int N, int K, int epi, const EpiArgsAny& ep, int dtype) {
+  if (dtype != STU_BF16 || skb != 1) return false;
+  static const bool disabled = getenv("STU_B200_DISABLE_TCGEN05") != nullptr;  // debugging aid: CUDA-core GEMM instead
+  if (disabled) return false;
+  if (lda % 8 || ldb % 8 || K % 8 || !aligned16(A) || !aligned16(B) || (B2 && !aligned16(B2))) return false;
+  if (M < 1 || N < 1 || K < 8) return false;
+  if (epi == EPI_HIST) return aligned16(ep.y) && get_encode_fn() != nullptr;
+  if (ep.ldy % 8 || !aligned16(ep.y)) return false;
+  if (epi == EPI_RESID && (ep.ldr % 8 || !aligned16(ep.resid))) return false;
+  return get_encode_fn() != nullptr;
+}
+
+int gemm_tc_dispatch(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N,
+                     int K, int epi, const EpiArgsAny& epa, cudaStream_t st) {
+  CUtensorMap ma, mb, mb2;
+  EpiArgs<bf16> ep = epa.as<bf16>();
+  int rc;
+  if (epi == EPI_HIST) {
+    // swap operands: rows = channels (the weight), columns = tokens, so that each epilogue thread owns
+    // one channel row of the history and writes whole 16-byte runs per parity
+    if ((rc = make_map(&ma, B, N, K, ldb)) != STU_OK) return rc;
+    if ((rc = make_map(&mb, A, M, K, lda)) != STU_OK) return rc;
+    ep.ldy = N;  // channel count
+    return launch_tc<EPI_HIST_T, 3>(ma, mb, mb, N, M, K, /*m_fast=*/1, ep, g_status_word, st);
+  }
+  if ((rc = make_map(&ma, A, M, K, lda)) != STU_OK) return rc;
+  if ((rc = make_map(&mb, B, N, K, ldb)) != STU_OK) return rc;
+  mb2 = mb;
+  if (epi == EPI_GELU_MUL && (rc = make_map(&mb2, B2, N, K, ldb)) != STU_OK) return rc;
+  switch (epi) {
+    case EPI_STORE: return launch_tc<EPI_STORE, 3>(ma, mb, mb2, M, N, K, 0, ep, g_status_word, st);
+    case EPI_RESID: return launch_tc<EPI_RESID, 3>(ma, mb, mb2, M, N, K, 0, ep, g_status_word, st);
+    case EPI_GELU_MUL: return launch_tc<EPI_GELU_MUL, 4>(ma, mb, mb2, M, N, K, 0, ep, g_status_word, st);
+  }
+  return STU_ERR_UNSUPPORTED;
+}

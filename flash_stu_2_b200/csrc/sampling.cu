@@ -1,0 +1,255 @@
+// Next-token selection from the last-position logits (reference flash_stu/model.py:268-299):
+//   z = clamp(logits / temperature, -1e4, 1e4)  (division rounded to the logits dtype)
+//   top-k: keep z >= k-th largest (ties kept); top-p: sort kept descending (ties by index), drop an
+//   entry when the probability mass ranked before it exceeds top_p; then argmax (greedy) or a draw.
+// The reference draws with torch.multinomial; here one uniform u in [0,1) per sequence selects the
+// first kept vocabulary index whose running sum of exp(z - max) (vocabulary order) exceeds u * total,
+// which is reproducible across devices.
+// One CTA of 1024 threads per sequence.  top-k uses a 4-pass radix select over order-preserving keys;
+// when top-k is given the (<= 1024) survivors are gathered, bitonic-sorted in shared memory and the
+// nucleus cut and the draw are made on that list, otherwise the draw scans the whole vocabulary.
+#include "common.cuh"
+
+constexpr int SP_T = 1024;
+constexpr int SP_CAND = 1024;
+
+__device__ __forceinline__ uint32_t ord_key(float f) {
+  uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+template <typename T> __device__ __forceinline__ float scaled_logit(const T* row, int i, float temperature) {
+  float z = round_to<T>(__fdiv_rn(Elem<T>::to_f(row[i]), temperature));
+  return fminf(fmaxf(z, -1e4f), 1e4f);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logits, long long ld, int V,
+                                                      float temperature, int top_k, float top_p, int do_sample,
+                                                      const float* __restrict__ uniforms, long long* __restrict__ out,
+                                                      long long out_stride, int* __restrict__ status) {
+  __shared__ float s_val[SP_CAND];
+  __shared__ int s_idx[SP_CAND];
+  __shared__ unsigned int s_hist[256];
+  __shared__ float s_red[32];
+  __shared__ int s_redi[32];
+  __shared__ unsigned int s_prefix, s_need, s_count;
+  __shared__ int s_choice;
+  const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const T* row = logits + (size_t)b * ld;
+
+  // ---- argmax (lowest index among ties); also the fallback result
+  float best = -INFINITY;
+  int besti = V;
+  for (int i = tid; i < V; i += SP_T) {
+    float z = scaled_logit(row, i, temperature);
+    if (z > best || (z == best && i < besti)) { best = z; besti = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+    if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
+  }
+  if (lane == 0) { s_red[warp] = best; s_redi[warp] = besti; }
+  __syncthreads();
+  if (warp == 0) {
+    best = s_red[lane]; besti = s_redi[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+      if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
+    }
+    if (lane == 0) { s_red[0] = best; s_redi[0] = besti; }
+  }
+  __syncthreads();
+  const float zmax = s_red[0];
+  const int imax = s_redi[0];
+  if (!do_sample) {
+    if (tid == 0) out[(size_t)b * out_stride] = imax < V ? imax : 0;
+    return;
+  }
+  const float u = uniforms[b];
+
+  if (top_k > 0 && top_k < V) {
+    // ---- radix select: key of the k-th largest
+    if (tid == 0) { s_prefix = 0; s_need = (unsigned)top_k; }
+    for (int pass = 0; pass < 4; pass++) {
+      const int shift = 24 - 8 * pass;
+      if (tid < 256) s_hist[tid] = 0;
+      __syncthreads();
+      const unsigned prefix = s_prefix;
+      const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+      for (int i = tid; i < V; i += SP_T) {
+        unsigned key = ord_key(scaled_logit(row, i, temperature));
+        if ((key & mask) == prefix) atomicAdd(&s_hist[(key >> shift) & 255u], 1u);
+      }
+      __syncthreads();
+      if (tid == 0) {
+        unsigned need = s_need, cum = 0;
+        int bin = 255;
+        for (; bin > 0; bin--) {
+          if (cum + s_hist[bin] >= need) break;
+          cum += s_hist[bin];
+        }
+        s_need = need - cum;
+        s_prefix = prefix | ((unsigned)bin << shift);
+      }
+      __syncthreads();
+    }
+    const unsigned kth_key = s_prefix;
+    // ---- gather survivors (key >= kth_key)
+    if (tid == 0) s_count = 0;
+    __syncthreads();
+    for (int i = tid; i < V; i += SP_T) {
+      float z = scaled_logit(row, i, temperature);
+      if (ord_key(z) >= kth_key) {
+        unsigned slot = atomicAdd(&s_count, 1u);
+        if (slot < SP_CAND) { s_val[slot] = z; s_idx[slot] = i; }
+      }
+    }
+    __syncthreads();
+    const int C = (int)s_count;
+    if (C > SP_CAND) {  // more ties than the candidate list holds: report and return the argmax
+      if (tid == 0) {
+        if (status) atomicExch(status, 4);
+        out[(size_t)b * out_stride] = imax;
+      }
+      return;
+    }
+    if (tid >= C) { s_val[tid] = -INFINITY; s_idx[tid] = 0x7fffffff; }
+    __syncthreads();
+    // ---- bitonic sort by (value descending, index ascending)
+    for (int k = 2; k <= SP_CAND; k <<= 1)
+      for (int j = k >> 1; j > 0; j >>= 1) {
+        int ixj = tid ^ j;
+        if (ixj > tid) {
+          float va = s_val[tid], vb = s_val[ixj];
+          int ia = s_idx[tid], ib = s_idx[ixj];
+          bool a_first = (va > vb) || (va == vb && ia < ib);  // a ranks before b
+          bool up = ((tid & k) == 0);
+          if (up ? !a_first : a_first) {
+            s_val[tid] = vb; s_val[ixj] = va; s_idx[tid] = ib; s_idx[ixj] = ia;
+          }
+        }
+        __syncthreads();
+      }
+    // ---- nucleus cut and draw (sequential over <= 1024 entries, fp32, deterministic)
+    if (tid == 0) {
+      int keep = C;
+      if (top_p > 0.f && top_p < 1.f) {
+        float tot = 0.f;
+        for (int r = 0; r < C; r++) tot += __expf(s_val[r] - zmax);
+        float cum = 0.f;
+        keep = 0;
+        for (int r = 0; r < C; r++) {
+          if (r > 0 && cum > top_p) break;
+          keep = r + 1;
+          cum += __expf(s_val[r] - zmax) / tot;
+        }
+      }
+      s_choice = keep;
+    }
+    __syncthreads();
+    const int keep = s_choice;
+    // re-sort the kept entries by index ascending for the vocabulary-order running sum
+    if (tid >= keep) s_idx[tid] = 0x7fffffff;
+    __syncthreads();
+    for (int k = 2; k <= SP_CAND; k <<= 1)
+      for (int j = k >> 1; j > 0; j >>= 1) {
+        int ixj = tid ^ j;
+        if (ixj > tid) {
+          int ia = s_idx[tid], ib = s_idx[ixj];
+          bool up = ((tid & k) == 0);
+          if (up ? (ia > ib) : (ia < ib)) {
+            float va = s_val[tid];
+            s_val[tid] = s_val[ixj]; s_val[ixj] = va; s_idx[tid] = ib; s_idx[ixj] = ia;
+          }
+        }
+        __syncthreads();
+      }
+    if (tid == 0) {
+      float tot = 0.f;
+      for (int r = 0; r < keep; r++) tot += __expf(s_val[r] - zmax);
+      const float target = u * tot;
+      float cum = 0.f;
+      int choice = s_idx[keep - 1];
+      for (int r = 0; r < keep; r++) {
+        cum += __expf(s_val[r] - zmax);
+        if (cum > target) { choice = s_idx[r]; break; }
+      }
+      out[(size_t)b * out_stride] = choice;
+    }
+    return;
+  }
+  if (top_p > 0.f && top_p < 1.f) {  // nucleus filtering without top-k is not implemented on the device
+    if (tid == 0) {
+      if (status) atomicExch(status, 5);
+      out[(size_t)b * out_stride] = imax;
+    }
+    return;
+  }
+  // ---- plain temperature sampling over the whole vocabulary: chunked running sum in index order
+  const int chunk = (V + SP_T - 1) / SP_T;
+  const int lo = tid * chunk, hi = min(V, lo + chunk);
+  float part = 0.f;
+  for (int i = lo; i < hi; i++) part += __expf(scaled_logit(row, i, temperature) - zmax);
+  // block exclusive scan of the 1024 partial sums
+  float incl = part;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    float n = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += n;
+  }
+  if (lane == 31) s_red[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    float w = s_red[lane], wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      float n = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += n;
+    }
+    s_red[lane] = wi - w;  // exclusive prefix of warp totals
+    if (lane == 31) s_hist[0] = __float_as_uint(wi);
+  }
+  if (tid == 0) s_choice = 0x7fffffff;
+  __syncthreads();
+  const float tot = __uint_as_float(s_hist[0]);
+  const float target = u * tot;
+  const float excl = s_red[warp] + incl - part;
+  if (lo < hi && excl <= target && target < excl + part) {
+    float cum = excl;
+    int choice = hi - 1;
+    for (int i = lo; i < hi; i++) {
+      cum += __expf(scaled_logit(row, i, temperature) - zmax);
+      if (cum > target) { choice = i; break; }
+    }
+    atomicMin(&s_choice, choice);
+  }
+  __syncthreads();
+  if (tid == 0) out[(size_t)b * out_stride] = (s_choice == 0x7fffffff) ? imax : s_choice;
+}
+
+// logits [B, V] (row stride ld); uniforms [B] fp32 on the device (read only when do_sample);
+// out[b * out_stride] receives the token id (int64).  top_k <= 0 and top_p outside (0,1) disable the filters.
+extern "C" int stu_sample(const void* logits, long long ld, int B, int V, float temperature, int top_k, float top_p,
+                          int do_sample, const float* uniforms, long long* out, long long out_stride, int* status,
+                          int dtype, void* stream) {
+  if (!logits || !out) return STU_ERR_NULL;
+  if (do_sample && !uniforms) return STU_ERR_NULL;
+  if (B <= 0 || V <= 0 || !(temperature > 0.f)) return STU_ERR_SHAPE;
+  if (top_k > SP_CAND) return STU_ERR_UNSUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == STU_F32)
+    sample_kernel<float><<<B, SP_T, 0, st>>>((const float*)logits, ld, V, temperature, top_k, top_p, do_sample,
+                                             uniforms, out, out_stride, status);
+  else if (dtype == STU_BF16)
+    sample_kernel<bf16><<<B, SP_T, 0, st>>>((const bf16*)logits, ld, V, temperature, top_k, top_p, do_sample,
+                                            uniforms, out, out_stride, status);
+  else
+    return STU_ERR_DTYPE;
+  STU_CHECK_LAUNCH();
+  return STU_OK;
+}

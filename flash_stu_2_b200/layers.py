@@ -1,0 +1,86 @@
+"""Residual layers (flash_stu/layers/stu_layer.py:28-119, flash_stu/layers/attention_layer.py:29-87):
+x += op(norm(x)); x += mlp(norm(x)), in place on the caller's tensor as in the reference."""
+import torch
+import torch.nn as nn
+
+from . import ops
+from .modules import MLP, STU, Attention, RMSNorm
+
+
+def _inplace_target(x: torch.Tensor):
+    """The kernels write a contiguous [B,T,d] buffer; a strided caller tensor is copied back at the end."""
+    return x if x.is_contiguous() else x.contiguous()
+
+
+class STULayer(nn.Module):
+    def __init__(self, config, phi, n):
+        super().__init__()
+        self.config = config
+        if config.stu_enable_mlp_sandwich:
+            raise NotImplementedError("stu_enable_mlp_sandwich has no kernel here")
+        self.stu_norm = RMSNorm(config.n_embd, dtype=config.torch_dtype)
+        self.stu_mlp_enabled = False
+        self.stu = STU(config, phi, n)
+        self.mlp_norm = RMSNorm(config.n_embd, dtype=config.torch_dtype)
+        self.mlp = MLP(config, dtype=config.torch_dtype)
+        self._scratch = {}
+
+    def _decode(self, x, entry):
+        B, _, d = x.shape
+        key = (B, x.device, x.dtype)
+        if key not in self._scratch:
+            self._scratch = {key: torch.empty(B, d, dtype=x.dtype, device=x.device)}
+        mid = self._scratch[key]
+        x2 = x.view(B, d)
+        entry = self.stu.decode_step(x2, self.stu_norm.weight, self.stu_norm.eps, entry, mid)
+        inter = self.mlp.intermediate_size
+        if ops.can_fuse_norm(B, inter, d, ops.EPI_GELU_MUL, x.dtype):
+            self.mlp.apply_residual(mid, mid, x2, norm_w=self.mlp_norm.weight, eps=self.mlp_norm.eps)
+        else:
+            self.mlp.apply_residual(ops.rmsnorm(mid, self.mlp_norm.weight, self.mlp_norm.eps), mid, x2)
+        return entry
+
+    def forward(self, x: torch.Tensor, past_key_value=None, use_cache=False):
+        xc = _inplace_target(x)
+        B, T, d = xc.shape
+        if T == 1 and past_key_value is not None:
+            entry = self._decode(xc, past_key_value)
+        else:
+            xn = ops.rmsnorm(xc, self.stu_norm.weight, self.stu_norm.eps)
+            entry = self.stu.add_to_residual(xn, xc, past_key_value, use_cache)
+            x2 = xc.view(B * T, d)
+            xn2 = ops.rmsnorm(x2, self.mlp_norm.weight, self.mlp_norm.eps)
+            self.mlp.apply_residual(xn2, x2, x2)
+        if xc is not x:
+            x.copy_(xc)
+        if use_cache:
+            return x, entry
+        return x
+
+
+class AttentionLayer(nn.Module):
+    def __init__(self, config) -> None:
+        super().__init__()
+        self.config = config
+        self.attn_norm = RMSNorm(config.n_embd, dtype=config.torch_dtype)
+        self.attn = Attention(config)
+        self.mlp_norm = RMSNorm(config.n_embd, dtype=config.torch_dtype)
+        self.mlp = MLP(config, dtype=config.torch_dtype)
+
+    def forward(self, x: torch.Tensor, past_key_value=None, use_cache=True):
+        xc = _inplace_target(x)
+        B, T, d = xc.shape
+        x2 = xc.view(B * T, d)
+        xn = ops.rmsnorm(xc, self.attn_norm.weight, self.attn_norm.eps)
+        y, entry = self.attn.attend(xn, past_key_value, use_cache)
+        ops.linear(y.view(B * T, d), self.attn.c_proj.weight, resid=x2, out=x2, epilogue=ops.EPI_RESID)
+        inter = self.mlp.intermediate_size
+        if T == 1 and ops.can_fuse_norm(B, inter, d, ops.EPI_GELU_MUL, x.dtype):
+            self.mlp.apply_residual(x2, x2, x2, norm_w=self.mlp_norm.weight, eps=self.mlp_norm.eps)
+        else:
+            self.mlp.apply_residual(ops.rmsnorm(x2, self.mlp_norm.weight, self.mlp_norm.eps), x2, x2)
+        if xc is not x:
+            x.copy_(xc)
+        if use_cache:
+            return x, entry
+        return x

@@ -1,0 +1,204 @@
+"""FlashSTU language model and its token loop (flash_stu/model.py:26-304) on the CUDA kernels.
+
+Same constructor, forward() and generate() signatures as the reference.  Differences that a caller
+can observe, all forced by the reference's own gaps:
+  * STU layers keep a decode cache (the reference's return None, so its cached generate() feeds a
+    length-1 sequence to the convolution); one cached step here equals the full-prefix forward row;
+  * inside generate() only the last position goes through the LM head;
+  * sampling draws by inverse CDF from one uniform per sequence (optionally passed as
+    `uniforms=[steps,B]` or drawn from `generator=`) instead of torch.multinomial.
+"""
+from typing import Any, Dict, Optional, Tuple
+
+import torch
+import torch.nn as nn
+from transformers import PreTrainedModel
+from transformers.modeling_outputs import CausalLMOutputWithPast
+
+from . import ops
+from .config import FlashSTUConfig
+from .filters import get_spectral_filters, nearest_power_of_two
+from .layers import AttentionLayer, STULayer
+from .modules import STU, Attention, RMSNorm
+
+
+class FlashSTU(PreTrainedModel):
+    config_class = FlashSTUConfig
+    _tied_weights_keys = ["lm_head.weight"]
+
+    def __init__(self, config: FlashSTUConfig) -> None:
+        super().__init__(config)
+        self.config = config
+        self.n_layers = config.n_layers
+        self.n = nearest_power_of_two(config.seq_len * 2 - 1, round_up=True)
+        self.use_approx = config.use_approx
+        self.use_hankel_L = config.use_hankel_L
+        phi = get_spectral_filters(config.seq_len, config.num_eigh, use_hankel_L=config.use_hankel_L,
+                                   dtype=config.torch_dtype, load_from=config.filter_path)
+        self.register_buffer("phi", phi, persistent=True)
+        self.tok_emb = nn.Embedding(config.vocab_size, config.n_embd, dtype=config.torch_dtype)
+        self.dropout = nn.Dropout(config.dropout)
+        self.layers = nn.ModuleList()
+        for idx in range(self.n_layers):
+            if idx % 2 == 1 and config.use_attn:
+                self.layers.append(AttentionLayer(config))
+            else:
+                self.layers.append(STULayer(config, self.phi, self.n))
+        self.norm = RMSNorm(config.n_embd, dtype=config.torch_dtype)
+        if config.bias:
+            raise NotImplementedError("bias=True has no kernel here (the reference default is bias=False)")
+        self.lm_head = nn.Linear(config.n_embd, config.vocab_size, bias=False, dtype=config.torch_dtype)
+        self.tok_emb.weight = self.lm_head.weight
+        self.std = config.n_embd ** -0.5
+        self.apply(self._init_weights)
+
+    # ------------------------------------------------------------------ backbone
+    def _backbone(self, input_ids, past_key_values, use_cache: bool, collect_hidden: bool = False):
+        if not input_ids.is_cuda:
+            raise RuntimeError("flash_stu_2_b200 has no CPU path: move the model and input_ids to a CUDA device")
+        if self.training and self.config.dropout > 0:
+            raise NotImplementedError("dropout > 0 in training mode has no kernel here (inference path only)")
+        x = ops.embed(input_ids, self.tok_emb.weight)
+        hidden = (x.clone(),) if collect_hidden else None
+        cache = () if use_cache else None
+        for idx, layer in enumerate(self.layers):
+            past = past_key_values[idx] if past_key_values is not None else None
+            if use_cache:
+                x, present = layer(x, past_key_value=past, use_cache=True)
+                cache = cache + (present,)
+            else:
+                x = layer(x, past_key_value=past, use_cache=False)
+            if collect_hidden:
+                hidden = hidden + (x.clone(),)
+        return x, cache, hidden
+
+    def forward(
+        self,
+        input_ids: Optional[torch.LongTensor] = None,
+        attention_mask: Optional[torch.Tensor] = None,
+        past_key_values: Optional[Tuple[Tuple[torch.Tensor]]] = None,
+        labels: Optional[torch.LongTensor] = None,
+        use_cache: Optional[bool] = None,
+        output_hidden_states: Optional[bool] = None,
+        return_dict: Optional[bool] = None,
+        **kwargs,
+    ):
+        if input_ids is None:
+            raise ValueError("input_ids must be provided")
+        if labels is not None:
+            raise NotImplementedError("the loss/labels path is training code and is not part of this implementation")
+        return_dict = True if return_dict is None else return_dict
+        use_cache = use_cache if use_cache is not None else bool(getattr(self.config, "use_cache", False))
+        x, cache, hidden = self._backbone(input_ids, past_key_values, use_cache, bool(output_hidden_states))
+        B, T, d = x.shape
+        xn = ops.rmsnorm(x, self.norm.weight, self.norm.eps)
+        logits = ops.linear(xn.view(B * T, d), self.lm_head.weight).view(B, T, -1)
+        if not return_dict:
+            out = (logits,)
+            if use_cache:
+                out = out + (cache,)
+            if output_hidden_states:
+                out = out + (hidden,)
+            return out
+        return CausalLMOutputWithPast(loss=None, logits=logits, past_key_values=cache,
+                                      hidden_states=hidden if output_hidden_states else None)
+
+    def last_logits(self, input_ids, past_key_values=None, use_cache: bool = True):
+        """Logits of the last position only, [B,V], plus the cache (what the token loop needs)."""
+        x, cache, _ = self._backbone(input_ids, past_key_values, use_cache)
+        last = x[:, -1]
+        V = self.lm_head.weight.shape[0]
+        B = last.shape[0]
+        if ops.can_fuse_norm(B, V, last.shape[1], ops.EPI_STORE, last.dtype) and last.stride(1) == 1:
+            logits = ops.linear(last, self.lm_head.weight, norm_w=self.norm.weight, eps=self.norm.eps)
+        else:
+            logits = ops.linear(ops.rmsnorm(last.contiguous(), self.norm.weight, self.norm.eps), self.lm_head.weight)
+        return logits, cache
+
+    # ------------------------------------------------------------------ token loop
+    @torch.no_grad()
+    def generate(
+        self,
+        input_ids: torch.LongTensor,
+        max_length: int = 100,
+        temperature: float = 1.0,
+        top_k: Optional[int] = None,
+        top_p: Optional[float] = None,
+        do_sample: bool = True,
+        use_cache: bool = True,
+        **kwargs,
+    ) -> torch.LongTensor:
+        uniforms = kwargs.get("uniforms")
+        generator = kwargs.get("generator")
+        return_logits = kwargs.get("return_logits", False)
+        B, T0 = input_ids.shape
+        steps = max_length - T0
+        if steps <= 0:
+            return input_ids
+        if do_sample and top_p is not None and top_k is None:
+            raise NotImplementedError("top_p without top_k has no kernel here")
+        dev = input_ids.device
+        generated = torch.empty(B, max_length, dtype=torch.int64, device=dev)
+        generated[:, :T0] = input_ids
+        all_logits = []
+        past = None
+        for step in range(steps):
+            cur = T0 + step
+            if use_cache and past is not None:
+                inp = generated[:, cur - 1:cur]
+            else:
+                inp = generated[:, max(0, cur - self.config.seq_len):cur]
+                past = None
+            logits, past = self.last_logits(inp, past, use_cache)
+            if return_logits:
+                all_logits.append(logits)
+            u = None
+            if do_sample:
+                u = uniforms[step].to(device=dev, dtype=torch.float32).contiguous() if uniforms is not None else \
+                    torch.rand(B, device=dev, generator=generator)
+            ops.sample(logits, temperature, top_k, top_p, do_sample, u, generated[:, cur:], out_stride=max_length)
+        if return_logits:
+            return generated, torch.stack(all_logits, dim=1)
+        return generated
+
+    def prepare_inputs_for_generation(self, input_ids, past_key_values=None, attention_mask=None, use_cache=None,
+                                      **kwargs) -> Dict[str, Any]:
+        if past_key_values is not None:
+            input_ids = input_ids[:, -1:]
+        return {"input_ids": input_ids, "past_key_values": past_key_values, "use_cache": use_cache,
+                "attention_mask": attention_mask}
+
+    @staticmethod
+    def _reorder_cache(past_key_values, beam_idx: torch.Tensor):
+        out = ()
+        for layer_past in past_key_values:
+            if layer_past is None:
+                out += (None,)
+            else:
+                out += (tuple(t.index_select(0, beam_idx.to(t.device)) for t in layer_past),)
+        return out
+
+    def get_num_params(self, non_embedding: bool = False) -> int:
+        n = sum(p.numel() for p in self.parameters())
+        if non_embedding:
+            n -= self.tok_emb.weight.numel()
+        return n
+
+    def _get_num_params(self):
+        return self.get_num_params(non_embedding=False)
+
+    def _init_weights(self, module):
+        # same initialisers and the same running `std` rescale on SCALE_INIT modules as
+        # flash_stu/model.py:428-452
+        if isinstance(module, nn.Linear):
+            if hasattr(module, "SCALE_INIT"):
+                self.std *= (2 * self.n_layers) ** -0.5
+            torch.nn.init.normal_(module.weight, mean=0.0, std=self.std)
+        elif isinstance(module, nn.Embedding):
+            torch.nn.init.normal_(module.weight, mean=0.0, std=self.std)
+        elif isinstance(module, STU):
+            torch.nn.init.xavier_normal_(module.M_inputs)
+            torch.nn.init.xavier_normal_(module.M_filters)
+        elif isinstance(module, Attention):
+            torch.nn.init.xavier_normal_(module.c_attn.weight)
+            torch.nn.init.xavier_normal_(module.c_proj.weight)

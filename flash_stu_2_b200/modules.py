@@ -1,0 +1,249 @@
+"""Operators of the token loop with the reference's class names, constructor signatures and
+state-dict keys (flash_stu/modules/{stu,attention,swiglu}.py), running on the CUDA kernels.
+
+Cache entries are tuples of tensors with the batch on dim 0 (so FlashSTU._reorder_cache keeps
+working): STU layers hold the projected input history, attention layers a ring of the last
+window+1 keys/values.  The reference's STU layers hold no cache at all (layers/stu_layer.py:99-119);
+the cached decode defined here equals the reference's full-prefix forward row by row.
+"""
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import ops
+from .filters import nearest_power_of_two
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+def new_pos(batch: int, device) -> torch.Tensor:
+    """[B,2] int32: column 0 = tokens cached so far, column 1 (row 0) = arrival counter used by kernels."""
+    p = torch.zeros(batch, 2, dtype=torch.int32, device=device)
+    p._host_t = 0
+    return p
+
+
+def host_pos(pos: torch.Tensor) -> int:
+    """Host-side mirror of pos[0,0]; falls back to a device read when the tensor was re-created."""
+    t = getattr(pos, "_host_t", None)
+    if t is None:
+        t = int(pos[0, 0].item())
+        pos._host_t = t
+    return t
+
+
+class RMSNorm(nn.Module):
+    """torch.nn.RMSNorm(dim, dtype) arithmetic (the reference's non-Triton branch,
+    flash_stu/layers/stu_layer.py:17-36): fp32 statistics, eps = finfo(float32).eps."""
+
+    def __init__(self, dim: int, eps: Optional[float] = None, dtype=None):
+        super().__init__()
+        self.eps = ops.RMS_EPS if eps is None else eps
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype))
+
+    def forward(self, x):
+        return ops.rmsnorm(x, self.weight, self.eps)
+
+
+class MLP(nn.Module):
+    """Gated tanh-GELU MLP, down(gelu_tanh(gate(x)) * up(x)) (flash_stu/modules/swiglu.py:4-29)."""
+
+    def __init__(self, config, dtype=None):
+        super().__init__()
+        dtype = dtype if dtype is not None else config.torch_dtype
+        if config.bias:
+            raise NotImplementedError("bias=True has no kernel here (the reference default is bias=False)")
+        self.hidden_size = config.n_embd
+        self.intermediate_size = config.n_embd * config.mlp_scale
+        self.gate_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False, dtype=dtype)
+        self.up_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False, dtype=dtype)
+        self.down_proj = nn.Linear(self.intermediate_size, self.hidden_size, bias=False, dtype=dtype)
+        self.dropout = nn.Dropout(config.dropout)
+
+    def apply_residual(self, xn2d: torch.Tensor, resid2d: torch.Tensor, out2d: torch.Tensor,
+                       norm_w: Optional[torch.Tensor] = None, eps: float = ops.RMS_EPS):
+        """out = resid + down(gelu(gate(xn)) * up(xn)); with norm_w, xn is RMS-normalised inside the kernel."""
+        h = ops.linear(xn2d, self.gate_proj.weight, W2=self.up_proj.weight, epilogue=ops.EPI_GELU_MUL,
+                       norm_w=norm_w, eps=eps)
+        return ops.linear(h, self.down_proj.weight, resid=resid2d, out=out2d, epilogue=ops.EPI_RESID)
+
+    def forward(self, x):
+        x2 = x.reshape(-1, x.shape[-1])
+        h = ops.linear(x2, self.gate_proj.weight, W2=self.up_proj.weight, epilogue=ops.EPI_GELU_MUL)
+        return ops.linear(h, self.down_proj.weight).reshape(x.shape)
+
+
+class STU(nn.Module):
+    """Spectral transform unit (flash_stu/modules/stu.py:12-120), approx variant on CUDA kernels.
+
+    forward(x) returns the operator output like the reference.  Layers call `add_to_residual`,
+    which also maintains the decode cache: entry = (hist [B,d,2,Lh], pos [B,2])."""
+
+    def __init__(self, config, phi, n, feature_dim=None) -> None:
+        super().__init__()
+        self.config = config
+        self.register_buffer("phi", phi, persistent=False)
+        self.n = n
+        self.K = config.num_eigh
+        self.d_in = feature_dim if feature_dim is not None else config.n_embd
+        self.d_out = self.d_in
+        self.use_hankel_L = config.use_hankel_L
+        self.use_approx = config.use_approx
+        if config.d_in_tile is not None or config.d_out_tile is not None:
+            raise NotImplementedError("d_in_tile/d_out_tile (block-diagonal tiling) has no kernel here")
+        if self.use_hankel_L:
+            raise NotImplementedError("use_hankel_L=True (single branch) has no kernel here yet")
+        if not self.use_approx:
+            raise NotImplementedError("use_approx=False (full M_phi+- contraction) has no kernel here yet")
+        dt = config.torch_dtype
+        self.M_inputs = nn.Parameter(torch.empty(self.d_in, self.d_out, dtype=dt))
+        self.M_filters = nn.Parameter(torch.empty(self.K, self.d_in, dtype=dt))
+        self._prep_key = None
+        self._prep = None
+
+    # ---- derived, cached per parameter version: M_inputs^T (K-major rows) and the even-tap table
+    @property
+    def seq_len(self) -> int:
+        return self.phi.shape[0]
+
+    @property
+    def Lh(self) -> int:
+        return _round_up((self.seq_len + 1) // 2, 8)
+
+    def prepared(self):
+        key = (self.M_inputs._version, self.M_filters._version, self.phi._version, self.M_inputs.data_ptr(),
+               self.M_filters.data_ptr(), self.phi.data_ptr())
+        if self._prep_key != key:
+            with torch.no_grad():
+                phi = self.phi.to(self.M_filters.dtype).contiguous()
+                MinT = self.M_inputs.detach().t().contiguous()
+                # fp = phi @ M_filters, rounded to the model dtype as in the reference (stu.py:88)
+                fp = ops.linear(phi, self.M_filters.detach(), transposed_weight=True, backend=ops.BACKEND_SIMT)
+                taps = ops.taps_even(fp, self.Lh)
+            self._prep, self._prep_key = (MinT, taps), key
+        return self._prep
+
+    def new_cache(self, batch: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+        hist = torch.zeros(batch, self.d_in, 2, self.Lh, dtype=self.M_inputs.dtype, device=device)
+        return hist, new_pos(batch, device)
+
+    def add_to_residual(self, xn: torch.Tensor, x: torch.Tensor, entry=None, use_cache: bool = False):
+        """x += STU(xn) for xn, x [B,T,d] (x contiguous).  Returns the cache entry when use_cache."""
+        B, T, d = xn.shape
+        MinT, taps = self.prepared()
+        t0 = 0
+        if entry is not None:
+            hist, pos = entry
+            t0 = host_pos(pos)
+        elif use_cache:
+            hist, pos = self.new_cache(B, xn.device)
+        else:
+            pos = None
+            hist = torch.empty(B, d, 2, self.Lh, dtype=xn.dtype, device=xn.device)
+        if t0 + T > self.seq_len:
+            raise ValueError(f"sequence position {t0 + T} exceeds seq_len={self.seq_len} (the filters have seq_len taps)")
+        Lh = hist.shape[3]
+        ops.linear(xn.reshape(B * T, d), MinT, out=hist, epilogue=ops.EPI_HIST, hist_T=T, hist_t0=t0, hist_Lh=Lh)
+        yT = torch.empty(B, d, 2, _round_up((t0 + T + 1) // 2, 8), dtype=xn.dtype, device=xn.device)
+        ops.conv_prefill_approx(hist, taps, yT, x, t0, t0 + T, use_tensor_cores=(xn.dtype == torch.bfloat16 and
+                                                                              STU.tensor_core_conv))
+        if pos is not None:
+            pos[:, 0] += T
+            pos._host_t = t0 + T
+            return hist, pos
+        return None
+
+    tensor_core_conv = True  # class switch used by tests to compare the two convolution kernels
+
+    def decode_step(self, x2d: torch.Tensor, norm_w: torch.Tensor, eps: float, entry, out2d: torch.Tensor):
+        """out = x + STU(rmsnorm(x)) for one new token per sequence; appends to the cache."""
+        hist, pos = entry
+        MinT, taps = self.prepared()
+        t = host_pos(pos)
+        if t + 1 > self.seq_len:
+            raise ValueError(f"sequence position {t + 1} exceeds seq_len={self.seq_len}")
+        ops.decode_approx(x2d, norm_w, MinT, hist, taps, pos, out2d, eps)
+        pos._host_t = t + 1
+        return hist, pos
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = torch.zeros_like(x, memory_format=torch.contiguous_format)
+        self.add_to_residual(x.contiguous(), y)
+        return y
+
+
+class Attention(nn.Module):
+    """Causal sliding-window multi-head attention with ALiBi slopes (x0.25) and tanh soft-capping
+    (flash_stu/modules/attention.py:16-105).  Cache entry = (k_ring [B,W,d], v_ring [B,W,d], pos [B,2])
+    with W = window+1 slots, exact because older keys can never be attended."""
+
+    def __init__(self, config):
+        super().__init__()
+        assert config.n_embd % config.n_heads == 0
+        if config.bias:
+            raise NotImplementedError("bias=True has no kernel here (the reference default is bias=False)")
+        self.n_heads = config.n_heads
+        self.head_dim = config.n_embd // config.n_heads
+        if self.head_dim > 128:
+            raise NotImplementedError("head_dim > 128 has no kernel here")
+        self.bsz = config.bsz
+        self.c_attn = nn.Linear(config.n_embd, 3 * config.n_embd, bias=False, dtype=config.torch_dtype)
+        self.c_proj = nn.Linear(config.n_embd, config.n_embd, bias=False, dtype=config.torch_dtype)
+        self.c_proj.SCALE_INIT = 1
+        self.dropout = config.dropout
+        self.resid_dropout = nn.Dropout(self.dropout)
+        self.register_buffer("alibi_slopes", self._get_alibi_slopes(self.n_heads), persistent=False)
+        ws = config.window_size
+        self.window_size = ws
+        self.window = int(ws[0] if isinstance(ws, (tuple, list)) else ws)
+        self.softcap = config.softcap
+
+    @staticmethod
+    def _generate_slopes(n: int):
+        start = 2 ** (-(2 ** -(math.log2(n) - 3)))
+        return [start * (start ** i) for i in range(n)]
+
+    def _get_alibi_slopes(self, n_heads: int, interpolation_factor: float = 0.25):
+        if math.log2(n_heads).is_integer():
+            slopes = self._generate_slopes(n_heads)
+        else:
+            n = nearest_power_of_two(n_heads, round_up=False)
+            slopes = self._generate_slopes(n) + self._generate_slopes(2 * n)[0::2][: n_heads - n]
+        return torch.tensor(slopes, dtype=torch.float32) * interpolation_factor
+
+    def new_cache(self, batch: int, device):
+        d = self.n_heads * self.head_dim
+        W = self.window + 1
+        dt = self.c_attn.weight.dtype
+        return (torch.zeros(batch, W, d, dtype=dt, device=device), torch.zeros(batch, W, d, dtype=dt, device=device),
+                new_pos(batch, device))
+
+    def attend(self, xn: torch.Tensor, entry=None, use_cache: bool = False):
+        """Heads merged, before c_proj: returns (y [B,T,d], entry)."""
+        B, T, d = xn.shape
+        qkv = ops.linear(xn.reshape(B * T, d), self.c_attn.weight).view(B, T, 3 * d)
+        if entry is None and use_cache:
+            entry = self.new_cache(B, xn.device)
+        if entry is not None:
+            k_ring, v_ring, pos = entry
+            t0 = host_pos(pos)
+            y = ops.swa_forward(qkv, k_ring, v_ring, pos, self.alibi_slopes, self.n_heads, self.window, self.softcap,
+                                update_cache=True)
+            pos._host_t = t0 + T
+            return y, entry
+        dummy = torch.zeros(1, 1, 1, dtype=xn.dtype, device=xn.device)
+        y = ops.swa_forward(qkv, dummy, dummy, new_pos(B, xn.device), self.alibi_slopes, self.n_heads, self.window,
+                            self.softcap, update_cache=False)
+        return y, None
+
+    def forward(self, x, past_key_value=None, use_cache=True):
+        B, T, d = x.shape
+        y, entry = self.attend(x.contiguous(), past_key_value, use_cache)
+        y = ops.linear(y.reshape(B * T, d), self.c_proj.weight).view(B, T, d)
+        if use_cache:
+            return y, entry
+        return y

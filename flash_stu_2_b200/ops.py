@@ -1,0 +1,210 @@
+"""Tensor-level wrappers around the C-ABI: torch supplies device memory and streams, nothing else.
+
+Every function takes CUDA tensors, launches on torch's current stream and returns without
+synchronising.  Device-side problems (bounded waits that ran out, out-of-range token ids or
+positions) are recorded in a per-process status word; `check_status()` reads it (one sync).
+"""
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+EPI_STORE, EPI_RESID, EPI_GELU_MUL, EPI_HIST = 0, 1, 2, 3
+BACKEND_AUTO, BACKEND_SIMT, BACKEND_TCGEN05, BACKEND_SKINNY = 0, 1, 2, 3
+RMS_EPS = float(torch.finfo(torch.float32).eps)  # what torch.nn.RMSNorm(eps=None) resolves to
+
+_status = {}
+launch_count = 0  # kernels launched through this module (bench.py reports it)
+
+
+def _count(n=1):
+    global launch_count
+    launch_count += n
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise TypeError(f"flash_stu_2_b200 kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("flash_stu_2_b200 has no CPU path: tensors must live on a CUDA device")
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def status_word(device) -> torch.Tensor:
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _status:
+        w = torch.zeros(1, dtype=torch.int32, device=dev)
+        _status[key] = w
+        _lib.check(_lib.load().stu_set_status_word(w.data_ptr()), "stu_set_status_word")
+    return _status[key]
+
+
+STATUS_TEXT = {1: "token id outside the vocabulary", 2: "position outside the cache capacity (seq_len)",
+               3: "a bounded mbarrier wait ran out inside the tcgen05 GEMM", 4: "more top-k ties than the candidate list holds",
+               5: "top_p without top_k is not implemented on the device"}
+
+
+def check_status(device=None):
+    """Raise if any kernel flagged a device-side problem since the last check (synchronises)."""
+    for key, w in _status.items():
+        v = int(w.item())
+        if v:
+            w.zero_()
+            raise RuntimeError(f"flash_stu_2_b200 device status {v}: {STATUS_TEXT.get(v, 'unknown')}")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = RMS_EPS, out: Optional[torch.Tensor] = None):
+    _cuda(x, weight)
+    d = x.shape[-1]
+    x2 = x.reshape(-1, d)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    if out is None:
+        out = torch.empty(x2.shape, dtype=x.dtype, device=x.device)
+    o2 = out.reshape(-1, d)
+    rc = _lib.load().stu_rmsnorm(x2.data_ptr(), weight.data_ptr(), o2.data_ptr(), x2.shape[0], d, x2.stride(0),
+                                 o2.stride(0), eps, _dt(x), _stream())
+    _lib.check(rc, "stu_rmsnorm")
+    _count()
+    return out.reshape(x.shape)
+
+
+def embed(ids: torch.Tensor, table: torch.Tensor):
+    _cuda(ids, table)
+    ids = ids.contiguous().to(torch.int64)
+    out = torch.empty(*ids.shape, table.shape[1], dtype=table.dtype, device=table.device)
+    rc = _lib.load().stu_embed(ids.data_ptr(), table.data_ptr(), out.data_ptr(), ids.numel(), table.shape[1],
+                               table.shape[0], status_word(table.device).data_ptr(), _dt(table), _stream())
+    _lib.check(rc, "stu_embed")
+    _count()
+    return out
+
+
+def can_fuse_norm(M: int, N: int, K: int, epilogue: int, dtype: torch.dtype) -> bool:
+    code = 1 if dtype == torch.bfloat16 else 0
+    return bool(_lib.load().stu_linear_can_fuse_norm(M, N, K, epilogue, code))
+
+
+def linear(x: torch.Tensor, W: torch.Tensor, *, W2: Optional[torch.Tensor] = None,
+           resid: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, epilogue: int = EPI_STORE,
+           norm_w: Optional[torch.Tensor] = None, eps: float = RMS_EPS, backend: int = BACKEND_AUTO,
+           transposed_weight: bool = False, hist_T: int = 0, hist_t0: int = 0, hist_Lh: int = 0):
+    """y = epilogue(x @ W^T) for x [M,K] and W [N,K] (or W [K,N] with transposed_weight=True)."""
+    _cuda(x, W, W2, resid, out, norm_w)
+    assert x.dim() == 2 and W.dim() == 2 and x.stride(1) == 1
+    M, K = x.shape
+    if transposed_weight:
+        assert W.shape[0] == K
+        N, w_rs, w_ks = W.shape[1], W.stride(1), W.stride(0)
+    else:
+        assert W.shape[1] == K, (W.shape, K)
+        N, w_rs, w_ks = W.shape[0], W.stride(0), W.stride(1)
+    if W2 is not None:
+        assert W2.shape == W.shape and W2.stride() == W.stride()
+    if epilogue == EPI_HIST:
+        assert out is not None
+        y_rs = 0
+    else:
+        if out is None:
+            out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+        assert out.shape == (M, N) and out.stride(1) == 1
+        y_rs = out.stride(0)
+    r_rs = 0
+    if resid is not None:
+        assert resid.shape == (M, N) and resid.stride(1) == 1
+        r_rs = resid.stride(0)
+    rc = _lib.load().stu_linear(x.data_ptr(), x.stride(0), W.data_ptr(), w_rs, w_ks, _p(W2), _p(resid), r_rs,
+                                out.data_ptr(), y_rs, M, N, K, epilogue, hist_T, hist_t0, hist_Lh, _p(norm_w), eps,
+                                _dt(x), backend, _stream())
+    _lib.check(rc, "stu_linear")
+    _count()
+    return out
+
+
+def taps_even(fp: torch.Tensor, Lh: int):
+    """fp [L, d] (phi @ M_filters in the model dtype) -> even taps, channel-major [d, Lh]."""
+    _cuda(fp)
+    fp = fp.contiguous()
+    L, d = fp.shape
+    taps = torch.zeros(d, Lh, dtype=fp.dtype, device=fp.device)
+    rc = _lib.load().stu_taps_even(fp.data_ptr(), taps.data_ptr(), L, d, Lh, _dt(fp), _stream())
+    _lib.check(rc, "stu_taps_even")
+    _count()
+    return taps
+
+
+def conv_prefill_approx(hist, taps, yT, x, t0: int, t_end: int, use_tensor_cores: bool):
+    """x[b, t-t0, c] += 2 * sum_{j even} fp[j,c] * hist[b,c,t-j] for t in [t0, t_end)."""
+    _cuda(hist, taps, yT, x)
+    B, d, _, Lh = hist.shape
+    assert hist.is_contiguous() and yT.is_contiguous() and taps.shape == (d, Lh) and taps.is_contiguous()
+    assert x.shape == (B, t_end - t0, d) and x.stride(2) == 1
+    rc = _lib.load().stu_conv_prefill_approx(hist.data_ptr(), taps.data_ptr(), yT.data_ptr(), x.data_ptr(),
+                                             x.stride(0), x.stride(1), B, d, Lh, yT.shape[3], t0, t_end, _dt(x),
+                                             int(use_tensor_cores), _stream())
+    _lib.check(rc, "stu_conv_prefill_approx")
+    _count(2)
+    return x
+
+
+def decode_approx(x, norm_w, MinT, hist, taps, pos, out, eps: float = RMS_EPS):
+    """One fused decode step of an approx STU layer (norm, projection, cache append, taps, residual)."""
+    _cuda(x, norm_w, MinT, hist, taps, pos, out)
+    B, d, _, Lh = hist.shape
+    assert x.shape == (B, d) and out.shape == (B, d) and x.stride(1) == 1 and out.stride(1) == 1
+    assert pos.dtype == torch.int32 and pos.shape == (B, 2) and pos.is_contiguous()
+    assert x.data_ptr() != out.data_ptr()
+    rc = _lib.load().stu_decode_approx(x.data_ptr(), x.stride(0), norm_w.data_ptr(), MinT.data_ptr(), hist.data_ptr(),
+                                       taps.data_ptr(), pos.data_ptr(), out.data_ptr(), out.stride(0), B, d, Lh, eps,
+                                       status_word(x.device).data_ptr(), _dt(x), _stream())
+    _lib.check(rc, "stu_decode_approx")
+    _count()
+    return out
+
+
+def swa_forward(qkv, k_ring, v_ring, pos, slopes, H: int, window: int, softcap: float, update_cache: bool):
+    """Sliding-window attention for the Tn tokens in qkv [B,Tn,3d] against the ring cache; returns [B,Tn,d]."""
+    _cuda(qkv, k_ring, v_ring, pos, slopes)
+    B, Tn, d3 = qkv.shape
+    d = d3 // 3
+    assert qkv.is_contiguous() and slopes.dtype == torch.float32 and pos.dtype == torch.int32
+    W = max(int(k_ring.shape[1]), window + 1)  # an uncached call passes a dummy ring that is never read
+    assert not update_cache or (k_ring.shape == (B, W, d) and k_ring.is_contiguous() and v_ring.is_contiguous())
+    out = torch.empty(B, Tn, d, dtype=qkv.dtype, device=qkv.device)
+    rc = _lib.load().stu_swa_forward(qkv.data_ptr(), k_ring.data_ptr(), v_ring.data_ptr(), pos.data_ptr(),
+                                     slopes.data_ptr(), out.data_ptr(), B, Tn, H, d // H, W, window, float(softcap or 0.0),
+                                     int(update_cache), _dt(qkv), _stream())
+    _lib.check(rc, "stu_swa_forward")
+    _count(2 if update_cache else 1)
+    return out
+
+
+def sample(logits, temperature: float, top_k: Optional[int], top_p: Optional[float], do_sample: bool,
+           uniforms: Optional[torch.Tensor], out: torch.Tensor, out_stride: int = 1):
+    """Pick one token per row of logits [B,V]; writes int64 ids to out[b*out_stride]."""
+    _cuda(logits, uniforms, out)
+    B, V = logits.shape
+    assert logits.stride(1) == 1 and out.dtype == torch.int64
+    rc = _lib.load().stu_sample(logits.data_ptr(), logits.stride(0), B, V, float(temperature), int(top_k or 0),
+                                float(top_p if top_p is not None else -1.0), int(do_sample), _p(uniforms),
+                                out.data_ptr(), out_stride, status_word(logits.device).data_ptr(), _dt(logits),
+                                _stream())
+    _lib.check(rc, "stu_sample")
+    _count()
+    return out

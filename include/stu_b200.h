@@ -1,0 +1,106 @@
+/* libstu_b200.so -- C ABI of the B200 (sm_100a) kernels for the Flash STU token loop.
+ *
+ * The reference (hazan-lab/flash-stu-2) is pure PyTorch and has no FFI layer; its operator boundary is
+ * the set of Python modules cited beside each entry point below (paths inside the reference
+ * repository).  A host binding calls these functions with DEVICE pointers (e.g. tensor.data_ptr()),
+ * plain sizes/strides in ELEMENTS, and the CUDA stream to launch on.
+ *
+ * Conventions
+ *   dtype      0 = float32, 1 = bfloat16 (storage and rounding points; accumulation is fp32)
+ *   stream     a cudaStream_t passed as void*
+ *   return     0 = ok; <0 = argument error detected on the host before any launch
+ *              (-1 dtype, -2 shape, -3 alignment, -4 unsupported configuration, -5 null pointer);
+ *              >0 = cudaError_t from the launch.  Nothing throws, aborts or traps.
+ *   ownership  the caller allocates every input, output, cache and scratch buffer; the library keeps no
+ *              pointer after a call returns (except the status word registered below) and never
+ *              allocates or synchronises.
+ *   status     device-side problems (bounded waits that expired, ids/positions out of range) are written
+ *              to the int registered with stu_set_status_word(); 0 means none.
+ *   pos        int32 [B][2] device array: pos[2*b] = tokens of sequence b already cached,
+ *              pos[1] = arrival counter (must be 0 between calls).  Kernels that append to a cache
+ *              advance it themselves, so a captured CUDA graph can be replayed without new arguments.
+ *   history    projected STU inputs, [B][d][2][Lh]: element (b, c, t) at ((b*d + c)*2 + (t&1))*Lh + (t>>1)
+ */
+#ifndef STU_B200_H
+#define STU_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int stu_b200_version(void);
+
+/* Registers the device int that kernels set on a device-side problem (NULL to unregister). */
+int stu_set_status_word(int* device_status);
+
+/* y[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps) * w.
+ * Replaces torch.nn.RMSNorm / LigerRMSNorm as used in flash_stu/layers/stu_layer.py:32-36,67-71,
+ * flash_stu/layers/attention_layer.py:33-43 and flash_stu/model.py:90-96,173. */
+int stu_rmsnorm(const void* x, const void* w, void* y, int rows, int d, long long x_row_stride,
+                long long y_row_stride, float eps, int dtype, void* stream);
+
+/* out[r,:] = table[ids[r],:] (int64 ids).  Replaces nn.Embedding at flash_stu/model.py:152. */
+int stu_embed(const long long* ids, const void* table, void* out, int rows, int d, int vocab, int* status,
+              int dtype, void* stream);
+
+/* y = epilogue(x[M,K] @ W[N,K]^T); element (n,k) of W at W[n*w_row_stride + k*w_k_stride].
+ *   epilogue 0  y = acc                       nn.Linear: attention.py:74,101; model.py:176; `x @ M_inputs` stu.py:87
+ *            1  y = resid + round(acc)        the x.add_(...) of stu_layer.py:93,96 / attention_layer.py:56,62
+ *            2  y = round(gelu_tanh(round(x@W^T))) * round(x@W2^T)     swiglu.py:22-28
+ *            3  scatter round(acc) into the history `y` (N channels, hist_T tokens per sequence starting at
+ *               time hist_t0, hist_Lh elements per parity row): the projected input `x @ M_inputs`
+ *   norm_w     when non-NULL, x is RMS-normalised with this weight (eps) inside the kernel; only fused for
+ *              decode shapes (see stu_linear_can_fuse_norm), otherwise -4.
+ *   backend    0 auto (M<=64: weight-streaming mma.sync/FMA kernel; bf16 aligned: tcgen05+TMA GEMM; else
+ *              CUDA-core GEMM), 1 CUDA-core, 2 tcgen05, 3 decode kernel. */
+int stu_linear(const void* x, long long x_row_stride, const void* W, long long w_row_stride, long long w_k_stride,
+               const void* W2, const void* resid, long long resid_row_stride, void* y, long long y_row_stride,
+               int M, int N, int K, int epilogue, int hist_T, int hist_t0, int hist_Lh, const void* norm_w,
+               float eps, int dtype, int backend, void* stream);
+int stu_linear_can_fuse_norm(int M, int N, int K, int epilogue, int dtype);
+
+/* taps[c][j] = fp[2j][c] for fp = phi @ M_filters ([L,d], model dtype): the even taps that survive when the
+ * plus and minus branches of flash_stu/utils/stu_utils.py:223-227 are added (flash_stu/modules/stu.py:88,120). */
+int stu_taps_even(const void* fp, void* taps, int L, int d, int Lh, int dtype, void* stream);
+
+/* Prefill convolution of the approx STU variant: for t in [t0, t_end)
+ *   x[b, t-t0, c] += round(2 * sum_{j even, j<=t} fp[j,c] * hist(b,c,t-j))
+ * i.e. spectral_plus + spectral_minus of flash_stu/modules/stu.py:95-98,120 (torch.fft path
+ * flash_stu/utils/stu_utils.py:208-228), added to the residual stream.  hist must already hold the
+ * projected inputs of times [0, t_end).  yT is scratch with the history layout and y_Lh elements per
+ * parity row (y_Lh >= ceil(t_end/2)).  use_tensor_cores=1 (bf16 only) runs the Toeplitz product on
+ * mma.sync tensor cores, 0 the fp32 CUDA-core kernel. */
+int stu_conv_prefill_approx(const void* hist, const void* taps, void* yT, void* x, long long x_bstride,
+                            long long x_tstride, int B, int d, int Lh, int y_Lh, int t0, int t_end, int dtype,
+                            int use_tensor_cores, void* stream);
+
+/* One cached decode step of an approx STU layer, fused:
+ *   out[b,:] = x[b,:] + STU(rmsnorm(x[b,:]) * norm_w)   at time t = pos[2*b]; appends to hist, advances pos.
+ * MinT is M_inputs transposed ([d_out][d_in]).  The reference has no such step (its STU layers keep no
+ * cache, flash_stu/layers/stu_layer.py:99-119); the result equals row t of the full-prefix forward of
+ * flash_stu/layers/stu_layer.py:78-93.  out must not alias x. */
+int stu_decode_approx(const void* x, long long x_row_stride, const void* norm_w, const void* MinT, void* hist,
+                      const void* taps, int* pos, void* out, long long out_row_stride, int B, int d, int Lh,
+                      float eps, int* status, int dtype, void* stream);
+
+/* Sliding-window attention for the Tn new tokens in qkv [B,Tn,3*H*hd] (c_attn output) against a ring
+ * cache of W >= window+1 slots ([B][W][H*hd] each; token t in slot t % W), ALiBi slopes [H] (fp32) and tanh
+ * soft-capping; out [B,Tn,H*hd] (heads merged, before c_proj).  update_cache=1 stores the new keys/values
+ * and advances pos by Tn.  Replaces flash_attn_func as called at flash_stu/modules/attention.py:90-99 and
+ * the torch.cat cache of attention.py:82-88. */
+int stu_swa_forward(const void* qkv, void* k_ring, void* v_ring, int* pos, const float* slopes, void* out, int B,
+                    int Tn, int H, int hd, int W, int window, float softcap, int update_cache, int dtype,
+                    void* stream);
+
+/* Next token from last-position logits [B,V]: temperature, clamp(+-1e4), top-k, top-p, then argmax or an
+ * inverse-CDF draw from uniforms[b]; writes int64 ids to out[b*out_stride].  Replaces
+ * flash_stu/model.py:268-299 (torch.multinomial is replaced by the reproducible draw).
+ * top_k <= 0 and top_p outside (0,1) disable the filters; top_p needs top_k (<= 1024). */
+int stu_sample(const void* logits, long long ld, int B, int V, float temperature, int top_k, float top_p,
+               int do_sample, const float* uniforms, long long* out, long long out_stride, int* status, int dtype,
+               void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* STU_B200_H */

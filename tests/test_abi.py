@@ -1,0 +1,47 @@
+"""The C-ABI library builds, loads without a GPU and exports every symbol include/stu_b200.h declares."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "stu_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(?:int)\s+(stu_\w+)\s*\(", text)))
+
+
+def test_header_declares_entry_points():
+    names = declared_symbols()
+    assert "stu_linear" in names and "stu_decode_approx" in names and len(names) >= 10
+
+
+def test_library_exports_every_declared_symbol():
+    from flash_stu_2_b200 import _lib
+    lib = _lib.load()
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for name in declared_symbols():
+        assert hasattr(raw, name), f"{name} declared in include/stu_b200.h but not exported"
+    # the Python binding covers exactly the declared set
+    assert sorted(_lib.exported_symbols()) == declared_symbols()
+    assert lib.stu_b200_version() >= 100
+
+
+def test_argument_errors_are_reported_without_a_gpu():
+    from flash_stu_2_b200 import _lib
+    lib = _lib.load()
+    # null pointers / bad shapes are rejected on the host before any CUDA call
+    assert lib.stu_rmsnorm(None, None, None, 1, 8, 8, 8, 1e-6, 1, None) == -5
+    assert lib.stu_linear_can_fuse_norm(8, 4096, 1024, 2, 1) == 1
+    assert lib.stu_linear_can_fuse_norm(8, 4096, 1024, 2, 0) == 0
+    assert lib.stu_linear_can_fuse_norm(128, 4096, 1024, 2, 1) == 0
+
+
+def test_ops_refuse_cpu_tensors():
+    import torch
+    from flash_stu_2_b200 import ops
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.rmsnorm(torch.randn(2, 8), torch.ones(8))

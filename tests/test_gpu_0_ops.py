@@ -1,0 +1,229 @@
+"""Kernel-level parity on a B200: every C-ABI op against the CPU oracle / an fp32 torch statement of the op.
+Tolerances: fp32 1e-3 relative (observed far below), bf16 2e-2 relative, as the parity bar states."""
+import math
+
+import pytest
+import torch
+
+from oracle import stu_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 1e-3, torch.bfloat16: 2e-2}
+
+
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    return torch.device("cuda:0")
+
+
+def rel(a, b):
+    return O.rel_err(a.detach().cpu(), b.detach().cpu())
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(5, 32), (3, 7, 1024), (2, 50)])
+def test_rmsnorm(dt, shape):
+    from flash_stu_2_b200 import ops
+    torch.manual_seed(0)
+    x = (torch.randn(*shape) * 3).to(dt)
+    w = torch.randn(shape[-1]).to(dt)
+    y = ops.rmsnorm(x.to(dev()), w.to(dev()))
+    ref = O.rmsnorm(x, w)
+    assert rel(y, ref) <= (1e-6 if dt == torch.float32 else 2 ** -7)
+
+
+def _lin_ref(x, W, W2, resid, epi, dt):
+    acc = x.double() @ W.double().t()
+    if epi == 0:
+        return acc.to(dt)
+    if epi == 1:
+        return (resid.float() + acc.to(dt).float()).to(dt)
+    g = torch.nn.functional.gelu(acc.to(dt).float(), approximate="tanh").to(dt)
+    return (g.float() * (x.double() @ W2.double().t()).to(dt).float()).to(dt)
+
+
+@pytest.mark.parametrize("backend", [1, 2, 3])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("epi", [0, 1, 2])
+def test_linear_backends(backend, dt, epi):
+    from flash_stu_2_b200 import ops
+    if backend == 2 and dt != torch.bfloat16:
+        pytest.skip("tcgen05 path is bf16 only")
+    torch.manual_seed(1)
+    shapes = [(300, 200, 136), (128, 128, 64), (257, 520, 1032)] if backend != 3 else [(8, 200, 136), (33, 72, 1024), (2, 50, 64)]
+    for (M, N, K) in shapes:
+        x = torch.randn(M, K).to(dt)
+        W = (torch.randn(N, K) / math.sqrt(K)).to(dt)
+        W2 = (torch.randn(N, K) / math.sqrt(K)).to(dt)
+        resid = torch.randn(M, N).to(dt)
+        ref = _lin_ref(x, W, W2, resid, epi, dt)
+        y = ops.linear(x.to(dev()), W.to(dev()), W2=W2.to(dev()) if epi == 2 else None,
+                       resid=resid.to(dev()) if epi == 1 else None, epilogue=epi, backend=backend)
+        ops.check_status()
+        assert rel(y, ref) <= TOL[dt] / 2, (M, N, K, rel(y, ref))
+
+
+def test_linear_fused_norm_decode():
+    from flash_stu_2_b200 import ops
+    torch.manual_seed(2)
+    for (M, N, K, epi) in [(8, 4096, 1024, 2), (32, 1536, 1536, 0), (5, 104, 64, 1)]:
+        dt = torch.bfloat16
+        x = torch.randn(M, K).to(dt)
+        nw = torch.randn(K).to(dt)
+        W = (torch.randn(N, K) / math.sqrt(K)).to(dt)
+        W2 = (torch.randn(N, K) / math.sqrt(K)).to(dt)
+        resid = torch.randn(M, N).to(dt)
+        ref = _lin_ref(O.rmsnorm(x, nw), W, W2, resid, epi, dt)
+        y = ops.linear(x.to(dev()), W.to(dev()), W2=W2.to(dev()) if epi == 2 else None,
+                       resid=resid.to(dev()) if epi == 1 else None, epilogue=epi, norm_w=nw.to(dev()))
+        assert rel(y, ref) <= 1e-2, rel(y, ref)
+
+
+def test_linear_transposed_small_k():
+    """phi @ M_filters: K = num_eigh = 24 inner dimension, weight given as [K, N]."""
+    from flash_stu_2_b200 import ops
+    torch.manual_seed(3)
+    for dt in (torch.float32, torch.bfloat16):
+        phi = torch.randn(130, 24).to(dt)
+        Mf = torch.randn(24, 72).to(dt)
+        y = ops.linear(phi.to(dev()), Mf.to(dev()), transposed_weight=True, backend=1)
+        assert rel(y, (phi.double() @ Mf.double()).to(dt)) <= TOL[dt] / 4
+
+
+def _hist_from(xp, Lh):
+    B, T, d = xp.shape
+    h = torch.zeros(B, d, 2, Lh, dtype=xp.dtype)
+    for p in range(2):
+        n = (T - p + 1) // 2
+        h[:, :, p, :n] = xp[:, p::2].transpose(1, 2)
+    return h
+
+
+@pytest.mark.parametrize("dt,tc", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
+@pytest.mark.parametrize("shape", [(2, 64, 16, 0), (3, 300, 40, 0), (9, 1100, 8, 0), (2, 1301, 8, 655)])
+def test_conv_prefill_matches_fft_oracle(dt, tc, shape):
+    """x += conv_plus + conv_minus of the reference (FFT, fp32) == 2 * even-tap direct sum."""
+    from flash_stu_2_b200 import ops
+    B, T, d, t0 = shape
+    torch.manual_seed(4)
+    L = T + 3
+    Lh = ((L + 1) // 2 + 7) // 8 * 8
+    xp = torch.randn(B, T, d).to(dt)
+    fp = (torch.randn(L, d) / math.sqrt(L)).to(dt)
+    x0 = torch.randn(B, T, d).to(dt)
+    n = O.fft_length(L)
+    plus, minus = O.convolve(xp, fp, n, True, True)
+    ref = (x0.float() + (plus + minus).float()).to(dt)
+    hist = _hist_from(xp, Lh).to(dev())
+    taps = ops.taps_even(fp.to(dev()), Lh)
+    yT = torch.full((B, d, 2, ((T + 1) // 2 + 7) // 8 * 8), float("nan"), dtype=dt, device=dev())
+    x = x0[:, t0:].contiguous().to(dev())
+    ops.conv_prefill_approx(hist, taps, yT, x, t0, T, use_tensor_cores=tc)
+    # bf16: the reference rounds each branch before the add, the kernel rounds the folded sum once
+    assert rel(x, ref[:, t0:]) <= (2e-5 if dt == torch.float32 else 1.5e-2), rel(x, ref[:, t0:])
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_history_scatter_epilogue(dt):
+    from flash_stu_2_b200 import ops
+    torch.manual_seed(5)
+    for backend, (B, T, d, t0) in [(1, (2, 37, 24, 5)), (0, (2, 256, 128, 32)), (0, (3, 100, 64, 7))]:
+        Lh = ((t0 + T + 1) // 2 + 7) // 8 * 8
+        x = torch.randn(B, T, d).to(dt)
+        Mi = (torch.randn(d, d) / math.sqrt(d)).to(dt)
+        xp = (x.double() @ Mi.double()).to(dt)
+        hist = torch.zeros(B, d, 2, Lh, dtype=dt, device=dev())
+        ops.linear(x.reshape(B * T, d).to(dev()), Mi.t().contiguous().to(dev()), out=hist, epilogue=3, hist_T=T,
+                   hist_t0=t0, hist_Lh=Lh, backend=backend)
+        ops.check_status()
+        full = torch.zeros(B, t0 + T, d, dtype=dt)
+        full[:, t0:] = xp
+        assert rel(hist, _hist_from(full, Lh)) <= TOL[dt] / 2
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_decode_step_equals_prefill_row(dt):
+    """S3: the fused decode kernel at time t reproduces row t of the full-prefix layer half."""
+    from flash_stu_2_b200 import ops
+    torch.manual_seed(6)
+    B, T, d, L = 3, 45, 64, 64
+    Lh = 32
+    x = torch.randn(B, T, d).to(dt)
+    nw = (1 + 0.1 * torch.randn(d)).to(dt)
+    Mi = (torch.randn(d, d) / math.sqrt(d)).to(dt)
+    fp = (torch.randn(L, d) / 8).to(dt)
+    xn = O.rmsnorm(x, nw)
+    xp = xn @ Mi
+    plus, minus = O.convolve(xp, fp, O.fft_length(L), True, True)
+    ref = x + (plus + minus)
+    hist = torch.zeros(B, d, 2, Lh, dtype=dt, device=dev())
+    pos = torch.zeros(B, 2, dtype=torch.int32, device=dev())
+    taps = ops.taps_even(fp.to(dev()), Lh)
+    MinT = Mi.t().contiguous().to(dev())
+    outs = []
+    for t in range(T):
+        out = torch.empty(B, d, dtype=dt, device=dev())
+        ops.decode_approx(x[:, t].contiguous().to(dev()), nw.to(dev()), MinT, hist, taps, pos, out)
+        outs.append(out.cpu())
+    ops.check_status()
+    got = torch.stack(outs, 1)
+    assert pos[:, 0].tolist() == [T] * B and int(pos[0, 1]) == 0
+    assert rel(got, ref) <= (1e-5 if dt == torch.float32 else 1.5e-2), rel(got, ref)
+    assert rel(hist, _hist_from(xp, Lh)) <= (1e-5 if dt == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("cfg", [(2, 40, 4, 8, 8), (1, 70, 2, 64, 16), (2, 33, 3, 128, 100)])
+def test_attention_prefill_and_cached_decode(dt, cfg):
+    from flash_stu_2_b200 import ops
+    B, T, H, hd, w = cfg
+    d = H * hd
+    torch.manual_seed(7)
+    x = torch.randn(B, T, d).to(dt)
+    p = {"attn.c_attn.weight": (torch.randn(3 * d, d) / math.sqrt(d)).to(dt),
+         "attn.c_proj.weight": torch.eye(d).to(dt)}
+    ref, _ = O.attention(x, p, H, w, 50.0)
+    qkv = (x @ p["attn.c_attn.weight"].t()).to(dev())
+    slopes = O.alibi_slopes(H).float().to(dev())
+    W = w + 1
+    kr = torch.zeros(B, W, d, dtype=dt, device=dev())
+    vr = torch.zeros_like(kr)
+    pos = torch.zeros(B, 2, dtype=torch.int32, device=dev())
+    T1 = T - 5
+    y1 = ops.swa_forward(qkv[:, :T1].contiguous(), kr, vr, pos, slopes, H, w, 50.0, update_cache=True)
+    ys = [y1]
+    for t in range(T1, T):
+        ys.append(ops.swa_forward(qkv[:, t:t + 1].contiguous(), kr, vr, pos, slopes, H, w, 50.0, update_cache=True))
+    got = torch.cat(ys, 1)
+    assert pos[:, 0].tolist() == [T] * B
+    assert rel(got, ref) <= (1e-4 if dt == torch.float32 else 1.5e-2), rel(got, ref)
+    # uncached call over the whole sequence
+    dummy = torch.zeros(1, 1, 1, dtype=dt, device=dev())
+    y = ops.swa_forward(qkv, dummy, dummy, torch.zeros(B, 2, dtype=torch.int32, device=dev()), slopes, H, w, 50.0,
+                        update_cache=False)
+    assert rel(y, ref) <= (1e-4 if dt == torch.float32 else 1.5e-2)
+
+
+def test_sampling_matches_oracle():
+    from flash_stu_2_b200 import ops
+    torch.manual_seed(8)
+    B, V = 6, 50257
+    for dt in (torch.float32, torch.bfloat16):
+        logits = (torch.randn(B, V) * 3).to(dt)
+        out = torch.zeros(B, dtype=torch.int64, device=dev())
+        ops.sample(logits.to(dev()), 1.0, None, None, False, None, out)
+        assert torch.equal(out.cpu(), logits.float().argmax(-1))
+        for (temp, k, p) in [(0.8, 40, None), (0.8, 5, 0.9), (1.3, 1, None), (1.0, None, None)]:
+            u = torch.rand(B)
+            z = O.filter_logits(logits, temp, k, p)
+            want = O.pick_token(z, True, u).view(-1)
+            ops.sample(logits.to(dev()), temp, k, p, True, u.to(dev()), out)
+            ops.check_status()
+            got = out.cpu()
+            # the draw may differ only where u lands within rounding of a CDF boundary; require the
+            # chosen token to be inside the filtered support and almost all draws identical
+            assert all(torch.isfinite(z[b, got[b]]) for b in range(B))
+            if dt == torch.float32:
+                assert (got == want).float().mean() >= 0.8, (got, want)

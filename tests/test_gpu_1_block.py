@@ -1,0 +1,110 @@
+"""FlashSTUBlock on a B200 against the reference's own outputs (tests/golden/blocks.pt) and the
+size-independent properties of the cached token loop."""
+import pytest
+import torch
+
+from oracle import stu_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    return torch.device("cuda:0")
+
+
+def make_block(r, dt, approx=True):
+    import flash_stu_2_b200 as F
+    cfg = F.FlashSTUConfig(n_embd=r["d"], seq_len=r["L"], num_eigh=r["K"], use_approx=approx, use_attn=False,
+                           mlp_scale=4, torch_dtype=dt, n_layers=1, vocab_size=1, n_heads=1)
+    blk = F.FlashSTUBlock(config=cfg, phi=r["sd"]["phi"].clone(), n=r["n"])
+    blk.load_state_dict(r["sd"])
+    return blk.to(dev()).eval()
+
+
+@pytest.mark.parametrize("name,tol", [("approx_float32", 1e-3), ("approx_bfloat16", 2e-2)])
+def test_block_forward_matches_reference_golden(golden, name, tol):
+    from flash_stu_2_b200 import ops
+    r = golden("blocks")[name]
+    dt = r["x"].dtype
+    blk = make_block(r, dt)
+    x = r["x"].clone().to(dev())
+    with torch.no_grad():
+        y = blk(x)
+    ops.check_status()
+    assert y.data_ptr() == x.data_ptr()  # in place on the caller's tensor, like the reference
+    err = O.rel_err(y.cpu(), r["y"])
+    assert err <= tol, err
+
+
+@pytest.mark.parametrize("name,tol", [("approx_float32", 1e-3), ("approx_bfloat16", 2e-2)])
+def test_block_cached_decode_equals_prefill_rows(golden, name, tol):
+    """prefill T1 tokens with a cache, then single-token steps: every row equals the full forward."""
+    from flash_stu_2_b200 import ops
+    r = golden("blocks")[name]
+    dt = r["x"].dtype
+    blk = make_block(r, dt)
+    x = r["x"].to(dev())
+    T = x.shape[1]
+    T1 = T - 17
+    with torch.no_grad():
+        y1, cache = blk(x[:, :T1].clone(), use_cache=True)
+        rows = [y1]
+        for t in range(T1, T):
+            yt, cache = blk(x[:, t:t + 1].clone(), past_key_value=cache, use_cache=True)
+            rows.append(yt)
+    ops.check_status()
+    got = torch.cat(rows, 1).cpu()
+    assert int(cache[1][0, 0]) == T
+    err = O.rel_err(got, r["y"])
+    assert err <= tol, err
+
+
+def test_block_tensor_core_and_cuda_core_convolutions_agree(golden):
+    import flash_stu_2_b200 as F
+    r = golden("blocks")["approx_bfloat16"]
+    blk = make_block(r, torch.bfloat16)
+    x = r["x"].to(dev())
+    with torch.no_grad():
+        a = blk(x.clone())
+        F.STU.tensor_core_conv = False
+        try:
+            b = blk(x.clone())
+        finally:
+            F.STU.tensor_core_conv = True
+    assert O.rel_err(a.cpu(), b.cpu()) <= 4e-3
+
+
+def test_block_properties_at_benchmark_width():
+    """d_model=1024, K=24 as in the benchmark block, shorter context (L=2048, B=2): prefix consistency,
+    causality and chunked prefill == one-shot prefill, checked against the oracle on one sequence."""
+    import flash_stu_2_b200 as F
+    from flash_stu_2_b200 import ops
+    torch.manual_seed(1)
+    L, K, d, B = 2048, 24, 1024, 2
+    dt = torch.bfloat16
+    phi = O.spectral_filters(L, K, dtype=dt)
+    cfg = F.FlashSTUConfig(n_embd=d, seq_len=L, num_eigh=K, use_attn=False, mlp_scale=4, torch_dtype=dt, n_layers=1,
+                           vocab_size=1, n_heads=1)
+    blk = F.FlashSTUBlock(config=cfg, phi=phi, n=O.fft_length(L))
+    for n_, p in blk.named_parameters():
+        if ".stu.M_" in n_:
+            torch.nn.init.xavier_normal_(p)
+    sd = {k: v.clone() for k, v in blk.state_dict().items()}
+    blk = blk.to(dev()).eval()
+    x = torch.randn(B, L, d).to(dt)
+    with torch.no_grad():
+        full = blk(x.clone().to(dev())).cpu()
+        T = 1000
+        short = blk(x[:, :T].clone().to(dev())).cpu()
+        y1, cache = blk(x[:, :768].clone().to(dev()), use_cache=True)
+        y2, cache = blk(x[:, 768:1500].clone().to(dev()), past_key_value=cache, use_cache=True)
+        y3, cache = blk(x[:, 1500:1501].clone().to(dev()), past_key_value=cache, use_cache=True)
+    ops.check_status()
+    assert O.rel_err(short, full[:, :T]) <= 1e-6          # prefix consistency (same kernels, same order)
+    chunked = torch.cat([y1.cpu(), y2.cpu(), y3.cpu()], 1)
+    assert O.rel_err(chunked, full[:, :1501]) <= 2e-2
+    lsd = {k[len("layer."):]: v for k, v in sd.items() if k.startswith("layer.")}
+    ref = O.stu_layer(x[:1], lsd, sd["phi"], O.fft_length(L), True)
+    assert O.rel_err(full[:1], ref) <= 2e-2

@@ -1,0 +1,76 @@
+"""Host-side mirror of the reference API: construction, state-dict keys, filters, cache plumbing."""
+import os
+
+import pytest
+import torch
+
+import flash_stu_2_b200 as F
+from oracle import stu_oracle as O
+
+
+def _cfg(tmp_path, **kw):
+    L, K = kw.pop("seq_len", 64), kw.pop("num_eigh", 8)
+    phi = F.get_spectral_filters(L, K, dtype=torch.float32, device="cpu")
+    fp = os.path.join(tmp_path, "phi.pt")
+    F.save_spectral_filters(phi, fp, metadata={"seq_len": L, "K": K})
+    base = dict(n_embd=32, n_layers=4, n_heads=4, seq_len=L, window_size=8, vocab_size=97, mlp_scale=4, num_eigh=K,
+                torch_dtype=torch.float32, filter_path=fp)
+    base.update(kw)
+    return F.FlashSTUConfig(**base)
+
+
+def test_filters_match_oracle_and_roundtrip(tmp_path):
+    phi = F.get_spectral_filters(64, 8, dtype=torch.float32, device="cpu")
+    ref = O.spectral_filters(64, 8)
+    assert torch.allclose(phi, ref, rtol=0, atol=0)
+    p = os.path.join(tmp_path, "sub", "f")
+    F.save_spectral_filters(phi, p)
+    back = F.load_spectral_filters(p + ".pt", device="cpu", dtype=torch.bfloat16, verify_shape=(64, 8))
+    assert back.dtype == torch.bfloat16 and torch.equal(back, phi.bfloat16())
+    with pytest.raises(ValueError):
+        F.load_spectral_filters(p + ".pt", device="cpu", verify_shape=(64, 9))
+    assert F.nearest_power_of_two(2 * 8192 - 1, round_up=True) == 16384
+
+
+def test_state_dict_keys_match_reference(tmp_path, golden):
+    g = golden("models")
+    for name in ("stu_only_approx_fp32", "hybrid_approx_fp32"):
+        r = g[name]
+        m = F.FlashSTU(_cfg(str(tmp_path), use_attn=r["cfg"]["use_attn"]))
+        assert set(m.state_dict().keys()) == set(r["sd"].keys())
+        m.load_state_dict(r["sd"])
+        assert m.tok_emb.weight is m.lm_head.weight
+    blk = F.FlashSTUBlock(d_model=64, sequence_length=128, num_filters=8, torch_dtype=torch.float32)
+    assert set(blk.state_dict().keys()) == set(golden("blocks")["approx_float32"]["sd"].keys())
+    assert not blk.is_attention_block and blk.get_num_params() > 0
+
+
+def test_layer_alternation_and_alibi(tmp_path, golden):
+    m = F.FlashSTU(_cfg(str(tmp_path)))
+    kinds = [type(l).__name__ for l in m.layers]
+    assert kinds == ["STULayer", "AttentionLayer", "STULayer", "AttentionLayer"]
+    m2 = F.FlashSTU(_cfg(str(tmp_path), use_attn=False))
+    assert all(type(l).__name__ == "STULayer" for l in m2.layers)
+    for H, s in golden("alibi_slopes").items():
+        cfg = _cfg(str(tmp_path), n_embd=8 * H, n_heads=H)
+        assert torch.allclose(F.Attention(cfg).alibi_slopes.double(), s.double(), rtol=1e-6, atol=0)
+
+
+def test_unsupported_switches_fail_loudly(tmp_path):
+    for kw in (dict(use_approx=False), dict(use_hankel_L=True), dict(d_in_tile=16), dict(stu_enable_mlp_sandwich=True),
+               dict(bias=True)):
+        with pytest.raises(NotImplementedError):
+            F.FlashSTU(_cfg(str(tmp_path), use_attn=False, **kw))
+
+
+def test_model_refuses_cpu(tmp_path):
+    m = F.FlashSTU(_cfg(str(tmp_path)))
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        m(torch.zeros(1, 4, dtype=torch.long))
+
+
+def test_reorder_cache_keeps_structure():
+    hist, pos = torch.arange(24.).view(3, 2, 2, 2), torch.tensor([[5, 0]] * 3, dtype=torch.int32)
+    kv = (torch.arange(12.).view(3, 2, 2), torch.arange(12.).view(3, 2, 2), pos.clone())
+    out = F.FlashSTU._reorder_cache(((hist, pos), kv, None), torch.tensor([2, 0, 0]))
+    assert out[2] is None and torch.equal(out[0][0][0], hist[2]) and out[1][2].shape == (3, 2)
