@@ -213,8 +213,14 @@ def run_b200(a):
     state = {"cache": None, "graph": None, "graph_launches": 0}
 
     def prefill():
+        # the cache buffers are allocated once and reused (a captured decode graph holds their addresses):
+        # rewinding the position to 0 makes the call a prefill from the start of the sequence
         x_work.copy_(x_dev)
-        _, state["cache"] = blk(x_work, use_cache=True)
+        if state["cache"] is not None:
+            pos = state["cache"][1]
+            pos[:, 0] = 0
+            pos._host_t = 0
+        _, state["cache"] = blk(x_work, past_key_value=state["cache"], use_cache=True)
 
     def rewind():
         pos = state["cache"][1]
@@ -320,7 +326,10 @@ def run_b200(a):
         dec_s = 0.0
         for _ in range(e2e_steps):
             x_work.copy_(x_host, non_blocking=True)
-            _, state["cache"] = blk(x_work, use_cache=True)
+            pos = state["cache"][1]
+            pos[:, 0] = 0
+            pos._host_t = 0
+            _, state["cache"] = blk(x_work, past_key_value=state["cache"], use_cache=True)
             yp_host.copy_(x_work, non_blocking=True)
             torch.cuda.synchronize()
             rewind()
