@@ -17,6 +17,7 @@ ERRORS = {
     -4: "configuration not supported by the CUDA kernels",
     -5: "null pointer",
     -6: "device status word set",
+    -7: "the call needs more scratch than the library's built-in 32 MiB array",
 }
 
 _lib = None
@@ -34,6 +35,8 @@ _SIGNATURES = {
     "stu_taps_even": ([_P, _P, c_int, c_int, c_int, c_int, _P], c_int),
     "stu_conv_prefill_approx": ([_P, _P, _P, _P, _LL, _LL, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  _P], c_int),
+    "stu_conv_prefill_approx_static": ([_P, _P, _P, _LL, _LL, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+                                       c_int),
     "stu_decode_approx": ([_P, _LL, _P, _P, _P, _P, _P, _P, _LL, c_int, c_int, c_int, c_float, _P, c_int, _P], c_int),
     "stu_swa_forward": ([_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                          _P], c_int),

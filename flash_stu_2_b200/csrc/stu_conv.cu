@@ -473,3 +473,63 @@ extern "C" int stu_decode_approx(const void* x, long long x_row_stride, const vo
   STU_CHECK_LAUNCH();
   return STU_OK;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Prefill convolution for callers that cannot allocate device memory.
+//
+// stu_conv_prefill_approx needs a scratch buffer (yT) that the caller normally allocates.  Some hosts
+// cannot do that at the point where they call in: a serving process that handed the whole HBM to its
+// own arena at start-up (so a later cudaMalloc fails), or a steady-state loop that runs under a
+// "no allocation" rule because cudaMalloc/cudaFree synchronise the device and stall every stream.
+// For them the scratch lives in the library image itself: a fixed 32 MiB array in device global
+// memory that every GPU holding a context with this library loaded keeps until the process exits.
+//
+// Host code must not hand the array's name to a kernel: on the host the symbol is only a stand-in, and
+// a kernel given it would fault or quietly use unrelated memory.  The device address is fetched with
+// cudaGetSymbolAddress once per device, with that device current, and cached.
+constexpr size_t STATIC_SCRATCH_BYTES = (size_t)32 << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+
+#define STU_ERR_SCRATCH_TOO_SMALL (-7)
+
+#include <mutex>
+static std::mutex g_static_scratch_mutex;
+static void* g_static_scratch_ptr[64] = {nullptr};
+
+// Same computation and arguments as stu_conv_prefill_approx, minus yT / y_Lh.
+//   * Limit: B * d * 2 * roundup8(ceil(t_end / 2)) elements of the dtype must fit in 32 MiB
+//     (e.g. bf16: B*d*t_end <= 16 Mi elements); larger calls return -7 before anything is launched.
+//   * The first call on each device looks up the array's device address (no allocation, but a
+//     runtime call that is not a kernel launch): make that first call outside any stream capture.
+//   * All calls on a device share the one array.  Nothing in it has to start at zero (the convolution
+//     writes every element the residual add reads), so it is never cleared and simply keeps the last
+//     call's values; two calls that overlap in time on the same GPU (different streams) race on it.
+//   * No cudaMalloc / cudaFree / allocating library routine is called on any path.
+extern "C" int stu_conv_prefill_approx_static(const void* hist, const void* taps, void* x, long long x_bstride,
+                                              long long x_tstride, int B, int d, int Lh, int t0, int t_end,
+                                              int dtype, int use_tensor_cores, void* stream) {
+  if (!hist || !taps || !x) return STU_ERR_NULL;
+  if (B <= 0 || d <= 0 || Lh <= 0 || t0 < 0 || t_end <= t0 || t_end > 2 * Lh) return STU_ERR_SHAPE;
+  if (dtype != STU_F32 && dtype != STU_BF16) return STU_ERR_DTYPE;
+  const int y_Lh = (((t_end + 1) / 2) + 7) / 8 * 8;
+  const size_t elem = dtype == STU_F32 ? 4 : 2;
+  const size_t need = (size_t)B * (size_t)d * 2 * (size_t)y_Lh * elem;
+  if (need > STATIC_SCRATCH_BYTES) return STU_ERR_SCRATCH_TOO_SMALL;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return STU_ERR_UNSUPPORTED;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (!g_static_scratch_ptr[dev]) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_static_scratch);
+      if (e != cudaSuccess) return (int)e;
+      g_static_scratch_ptr[dev] = p;
+    }
+    scratch = g_static_scratch_ptr[dev];
+  }
+  return stu_conv_prefill_approx(hist, taps, scratch, x, x_bstride, x_tstride, B, d, Lh, y_Lh, t0, t_end, dtype,
+                                 use_tensor_cores, stream);
+}

@@ -163,6 +163,22 @@ def conv_prefill_approx(hist, taps, yT, x, t0: int, t_end: int, use_tensor_cores
     return x
 
 
+def conv_prefill_approx_static(hist, taps, x, t0: int, t_end: int, use_tensor_cores: bool):
+    """conv_prefill_approx without a caller-provided scratch tensor: for hosts that cannot allocate device
+    memory when they call (all HBM already owned by their own pool, or a no-allocation steady state).
+    The scratch is a 32 MiB array built into the library; larger problems raise."""
+    _cuda(hist, taps, x)
+    B, d, _, Lh = hist.shape
+    assert hist.is_contiguous() and taps.shape == (d, Lh) and taps.is_contiguous()
+    assert x.shape == (B, t_end - t0, d) and x.stride(2) == 1
+    rc = _lib.load().stu_conv_prefill_approx_static(hist.data_ptr(), taps.data_ptr(), x.data_ptr(), x.stride(0),
+                                                    x.stride(1), B, d, Lh, t0, t_end, _dt(x), int(use_tensor_cores),
+                                                    _stream())
+    _lib.check(rc, "stu_conv_prefill_approx_static")
+    _count(2)
+    return x
+
+
 def decode_approx(x, norm_w, MinT, hist, taps, pos, out, eps: float = RMS_EPS):
     """One fused decode step of an approx STU layer (norm, projection, cache append, taps, residual)."""
     _cuda(x, norm_w, MinT, hist, taps, pos, out)

@@ -9,7 +9,8 @@
  *   dtype      0 = float32, 1 = bfloat16 (storage and rounding points; accumulation is fp32)
  *   stream     a cudaStream_t passed as void*
  *   return     0 = ok; <0 = argument error detected on the host before any launch
- *              (-1 dtype, -2 shape, -3 alignment, -4 unsupported configuration, -5 null pointer);
+ *              (-1 dtype, -2 shape, -3 alignment, -4 unsupported configuration, -5 null pointer,
+ *              -7 built-in scratch too small);
  *              >0 = cudaError_t from the launch.  Nothing throws, aborts or traps.
  *   ownership  the caller allocates every input, output, cache and scratch buffer; the library keeps no
  *              pointer after a call returns (except the status word registered below) and never
@@ -73,6 +74,17 @@ int stu_taps_even(const void* fp, void* taps, int L, int d, int Lh, int dtype, v
 int stu_conv_prefill_approx(const void* hist, const void* taps, void* yT, void* x, long long x_bstride,
                             long long x_tstride, int B, int d, int Lh, int y_Lh, int t0, int t_end, int dtype,
                             int use_tensor_cores, void* stream);
+
+/* The same prefill convolution for callers that cannot allocate device memory (a server whose own arena
+ * already owns all of HBM, or a steady-state loop under a no-allocation rule): the scratch is a fixed
+ * 32 MiB array inside the library image instead of the caller's yT.  This entry point has no counterpart
+ * in the reference.  Returns -7 when B*d*2*roundup8(ceil(t_end/2)) elements exceed 32 MiB.  The first
+ * call on a device resolves the array's address (make it outside stream capture); all calls on a device
+ * share the array, which keeps the previous call's contents and needs no clearing; calls overlapping on
+ * one GPU race.  Never calls cudaMalloc/cudaFree. */
+int stu_conv_prefill_approx_static(const void* hist, const void* taps, void* x, long long x_bstride,
+                                   long long x_tstride, int B, int d, int Lh, int t0, int t_end, int dtype,
+                                   int use_tensor_cores, void* stream);
 
 /* One cached decode step of an approx STU layer, fused:
  *   out[b,:] = x[b,:] + STU(rmsnorm(x[b,:]) * norm_w)   at time t = pos[2*b]; appends to hist, advances pos.
