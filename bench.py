@@ -30,13 +30,15 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 D_MODEL, NUM_FILTERS = 1024, 24
-L2_BYTES = 126e6
+# dram__bytes_read.sum + dram__bytes_write.sum of one stu_decode_kernel launch at B=8, L=8192, t~7690, from the
+# ncu capture summarised in profiles/stu_decode_kernel_block_8k.md (algorithmic bytes there: 73.0 MB)
+DECODE_KERNEL_DRAM_BYTES = 79.5e6
 
 
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=8, help="sequences per GPU (default: the benchmark's 8)")
@@ -68,7 +70,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -190,7 +192,7 @@ def run_reference(a):
 # ----------------------------------------------------------------------------------------------- GPU arm
 def run_b200(a):
     import torch.distributed as dist
-    from flash_stu_2_b200 import ops
+    from flash_stu_2_b200 import ops, parallel
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -287,26 +289,23 @@ def run_b200(a):
             launches += a.steps * S * state["graph_launches"]
         clocks = sampler.stop() if rank == 0 else None
         ops.check_status()
-        times = torch.tensor([t_pre, t_dec], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(times, op=dist.ReduceOp.MAX)
-        t_pre, t_dec = (float(v) for v in times.tolist())   # ms, max over ranks, summed over steps
+        t_pre, t_dec = parallel.max_over_ranks([t_pre, t_dec], device=dev)   # ms, summed over steps
 
         # ---- dominant kernel alone (fused decode kernel), CUDA events on the launching stream
         layer = blk.layer
         hist, pos = state["cache"]
-        MinT, taps = layer.stu.prepared()
+        MinT, taps, taps8 = layer.stu.prepared()
         x2 = x_step.view(B, d)
         out2 = torch.empty_like(x2)
         reps = min(256, S)
         rewind()
         for _ in range(3):
-            ops.decode_approx(x2, layer.stu_norm.weight, MinT, hist, taps, pos, out2)
+            ops.decode_approx(x2, layer.stu_norm.weight, MinT, hist, taps, pos, out2, taps8=taps8)
         rewind()
         k0, k1 = ev(), ev()
         k0.record()
         for _ in range(reps):
-            ops.decode_approx(x2, layer.stu_norm.weight, MinT, hist, taps, pos, out2)
+            ops.decode_approx(x2, layer.stu_norm.weight, MinT, hist, taps, pos, out2, taps8=taps8)
         k1.record()
         torch.cuda.synchronize()
         kern_ms = k0.elapsed_time(k1) / reps
@@ -344,10 +343,7 @@ def run_b200(a):
                 torch.cuda.current_stream().synchronize()
             dec_s += time.perf_counter() - d0
         e2e_wall = time.perf_counter() - w0
-        e2e = torch.tensor([dec_s, e2e_wall], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
-        dec_s, e2e_wall = (float(v) for v in e2e.tolist())
+        dec_s, e2e_wall = parallel.max_over_ranks([dec_s, e2e_wall], device=dev)
 
     if rank != 0:
         if world > 1:
@@ -378,7 +374,7 @@ def run_b200(a):
                     "tflops_algorithmic": pre_tflops,
                     "frac_of_tensor_peak": pre_tflops / pk["bf16_tflops_sustained"],
                     "peak_tflops": pk["bf16_tflops_sustained"], "peak_source": pk["source"] + " (sustained)"},
-        "roofline": {"bound": "hbm", "kernel": "stu_decode_kernel<bf16>", "achieved": achieved, "peak": pk["hbm_gbs"],
+        "roofline": {"bound": "hbm", "kernel": "stu_decode_mma_kernel", "achieved": achieved, "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "peak_source": pk["source"],
                      "bytes_per_launch": kern_bytes, "us_per_launch": kern_ms * 1e3, "traffic": None},
         "e2e": {"value": world * B * S * e2e_steps / dec_s, "unit": "tokens/s",
@@ -388,12 +384,8 @@ def run_b200(a):
                         "of each step also copies its 134 MB input in and its output back"},
         "gpu_launches": launches, "wall_s_timed_region": wall, "clocks": clocks,
     }
-    traffic_file = os.path.join(ROOT, "profiles", "decode_kernel_traffic.json")
-    if os.path.exists(traffic_file):
-        try:
-            line["roofline"]["traffic"] = json.load(open(traffic_file)).get("dram_bytes_per_launch_scaled")
-        except Exception:
-            pass
+    if (B, L, d) == (8, 8192, 1024):
+        line["roofline"]["traffic"] = DECODE_KERNEL_DRAM_BYTES
     if world == 1 and not a.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(a, make_state(L), x_host)
     print(json.dumps(line))

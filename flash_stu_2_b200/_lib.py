@@ -37,7 +37,9 @@ _SIGNATURES = {
                                  _P], c_int),
     "stu_conv_prefill_approx_static": ([_P, _P, _P, _LL, _LL, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
                                        c_int),
-    "stu_decode_approx": ([_P, _LL, _P, _P, _P, _P, _P, _P, _LL, c_int, c_int, c_int, c_float, _P, c_int, _P], c_int),
+    "stu_taps_rev8": ([_P, _P, c_int, c_int, c_int, _P], c_int),
+    "stu_decode_approx": ([_P, _LL, _P, _P, _P, _P, _P, _P, _P, _LL, c_int, c_int, c_int, c_float, _P, c_int, _P],
+                          c_int),
     "stu_swa_forward": ([_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                          _P], c_int),
     "stu_sample": ([_P, _LL, c_int, c_int, c_float, c_int, c_float, c_int, _P, _P, _LL, _P, c_int, _P], c_int),

@@ -5,8 +5,9 @@
 // swizzled 128x64 operand tiles into a ring of shared-memory stages), warp 1 allocates TMEM and
 // issues tcgen05.mma from one thread, warps 2..5 drain the accumulator with tcgen05.ld and run the
 // fused epilogue (store / residual add / tanh-GELU gate * up / transposed scatter into the projected
-// history).  Two CTAs fit per SM for the single-accumulator epilogues, so one tile's epilogue
-// overlaps the other tile's main loop.  No cluster features and no multicast are used.
+// history).  The kernel is persistent (one CTA per SM walks the tile list) and the accumulator is
+// double-buffered in TMEM, so one tile's epilogue overlaps the next tile's main loop.  No cluster
+// features and no multicast are used.
 //
 // Every wait on an mbarrier is bounded: on expiry the waiter raises the status word, the CTA drains
 // its outstanding bulk copies (bounded as well), frees its TMEM and returns.
@@ -111,30 +112,43 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
       : "r"(taddr));
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// tanh-GELU with the hardware tanh approximation (relative error ~2^-11, below the bf16 rounding that follows)
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+  const float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(inner));
+  return 0.5f * x * (1.0f + t);
+}
+
+// Persistent kernel: CTA i handles tiles i, i + gridDim.x, ...  The accumulator is double-buffered in TMEM
+// (2 x 128 columns, or 2 x 256 for the gate/up epilogue), so the MMA warp starts the next tile while
+// the epilogue warps drain the previous one.
 template <int EPI, int STAGES>
-__global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,
-                                                      const __grid_constant__ CUtensorMap tmB,
-                                                      const __grid_constant__ CUtensorMap tmB2, int M, int N, int K,
-                                                      int tiles_m, int tiles_n, int m_fast, EpiArgs<bf16> ep,
-                                                      int* status) {
+__global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                         const __grid_constant__ CUtensorMap tmB,
+                                                         const __grid_constant__ CUtensorMap tmB2, int M, int N,
+                                                         int K, int tiles_m, int tiles_n, int m_fast,
+                                                         EpiArgs<bf16> ep, int* status) {
   constexpr bool DUAL = (EPI == EPI_GELU_MUL);
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES * (DUAL ? 2 : 1);
-  constexpr uint32_t TMEM_COLS = DUAL ? 256 : 128;
+  constexpr uint32_t ACC_COLS = DUAL ? 256 : 128;
+  constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* tmem_full = empty_bar + STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+  uint64_t* tmem_full = empty_bar + STAGES;   // [2]
+  uint64_t* tmem_empty = tmem_full + 2;       // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* issued_ctr = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));
   int* consumed_ctr = issued_ctr + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int bid = blockIdx.x;
-  const int tm = m_fast ? (bid % tiles_m) : (bid / tiles_n);
-  const int tn = m_fast ? (bid / tiles_m) : (bid % tiles_n);
-  const int m0 = tm * BM, n0 = tn * BN;
+  const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -142,7 +156,10 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(tmem_full, 1);
+    for (int i = 0; i < 2; i++) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 128);
+    }
     *abort_flag = 0;
     *issued_ctr = 0;
     *consumed_ctr = 0;
@@ -161,56 +178,77 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
   if (warp == 0) {
     if (lane == 0) {
       // ---------------- TMA producer
-      for (int kb = 0; kb < num_kb; kb++) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) break;
-        unsigned char* sa = smem + s * STAGE_BYTES;
-        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-        tma_load_2d(sa, &tmA, &full_bar[s], kb * BK, m0);
-        tma_load_2d(sa + A_BYTES, &tmB, &full_bar[s], kb * BK, n0);
-        if (DUAL) tma_load_2d(sa + A_BYTES + B_BYTES, &tmB2, &full_bar[s], kb * BK, n0);
-        *issued_ctr = kb + 1;
+      int g = 0;  // k-blocks issued so far (ring position)
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const int tm = m_fast ? (tile % tiles_m) : (tile / tiles_n);
+        const int tn = m_fast ? (tile / tiles_m) : (tile % tiles_n);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; kb++, g++) {
+          const int s = g % STAGES;
+          const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+          unsigned char* sa = smem + s * STAGE_BYTES;
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          tma_load_2d(sa, &tmA, &full_bar[s], kb * BK, m0);
+          tma_load_2d(sa + A_BYTES, &tmB, &full_bar[s], kb * BK, n0);
+          if (DUAL) tma_load_2d(sa + A_BYTES + B_BYTES, &tmB2, &full_bar[s], kb * BK, n0);
+          *issued_ctr = g + 1;
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // ---------------- MMA issuer
-      int kb = 0;
-      for (; kb < num_kb; kb++) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        if (!mbar_wait(&full_bar[s], ph, abort_flag)) break;
+      int g = 0, it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, it++) {
+        const int buf = it & 1;
+        const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS;
+        if (!mbar_wait(&tmem_empty[buf], (((uint32_t)it >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-        const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
+        for (int kb = 0; kb < num_kb; kb++, g++) {
+          const int s = g % STAGES;
+          const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < BK / 16; kk++) {
-          // advancing 16 bf16 = 32 bytes along K inside the swizzled row: +2 in the (>>4) address field
-          umma(tmem_base, da + 2 * kk, db + 2 * kk, (kb | kk) ? 1u : 0u);
-          if (DUAL) {
-            const uint64_t db2 = make_smem_desc(sa + A_BYTES + B_BYTES);
-            umma(tmem_base + BN, da + 2 * kk, db2 + 2 * kk, (kb | kk) ? 1u : 0u);
+          for (int kk = 0; kk < BK / 16; kk++) {
+            // advancing 16 bf16 = 32 bytes along K inside the swizzled row: +2 in the (>>4) address field
+            umma(acc_addr, da + 2 * kk, db + 2 * kk, (kb | kk) ? 1u : 0u);
+            if (DUAL) {
+              const uint64_t db2 = make_smem_desc(sa + A_BYTES + B_BYTES);
+              umma(acc_addr + BN, da + 2 * kk, db2 + 2 * kk, (kb | kk) ? 1u : 0u);
+            }
           }
+          umma_commit(&empty_bar[s]);  // arrives when the MMAs above have finished reading this stage
+          *consumed_ctr = g + 1;
         }
-        umma_commit(&empty_bar[s]);  // arrives when the MMAs above have finished reading this stage
-        *consumed_ctr = kb + 1;
+        if (ok) umma_commit(&tmem_full[buf]);
       }
-      if (kb == num_kb) umma_commit(tmem_full);
     }
   } else {
     // ---------------- epilogue warps: TMEM lane quarter = warp % 4
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
-    const int m = m0 + row;
-    bool ok = mbar_wait(tmem_full, 0, abort_flag);
-    ok = __all_sync(0xffffffffu, ok);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, it++) {
+      const int tm = m_fast ? (tile % tiles_m) : (tile / tiles_n);
+      const int tn = m_fast ? (tile / tiles_m) : (tile % tiles_n);
+      const int m0 = tm * BM, n0 = tn * BN;
+      const int m = m0 + row;
+      const int buf = it & 1;
+      const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS;
+      bool ok = mbar_wait(&tmem_full[buf], ((uint32_t)it >> 1) & 1u, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
       for (int cch = 0; cch < BN / 32; cch++) {
         uint32_t r[32], r2[32];
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cch * 32);
+        const uint32_t taddr = acc_addr + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cch * 32);
         tmem_ld32(taddr, r);
         if (DUAL) tmem_ld32(taddr + BN, r2);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -263,8 +301,8 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
               } else if (EPI == EPI_GELU_MUL) {
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
-                  float g = round_to<bf16>(gelu_tanh(round_to<bf16>(__uint_as_float(r[v8 * 8 + j]))));
-                  o[j] = g * round_to<bf16>(__uint_as_float(r2[v8 * 8 + j]));
+                  float gte = round_to<bf16>(gelu_tanh_fast(round_to<bf16>(__uint_as_float(r[v8 * 8 + j]))));
+                  o[j] = gte * round_to<bf16>(__uint_as_float(r2[v8 * 8 + j]));
                 }
               } else {
 #pragma unroll
@@ -281,6 +319,9 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
           }
         }
       }
+      // this thread's TMEM reads of the buffer are complete (wait::ld above): hand it back to the MMA warp
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(&tmem_empty[buf]);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   }
@@ -291,10 +332,10 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     if (threadIdx.x == 0) {
       if (status) atomicExch(status, 3);
       const int issued = *issued_ctr, consumed = *consumed_ctr;
-      for (int kb = consumed; kb < issued; kb++) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        for (uint32_t it = 0; it < WAIT_LIMIT; ++it)
+      for (int g = consumed; g < issued; g++) {
+        const int s = g % STAGES;
+        const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+        for (uint32_t w = 0; w < WAIT_LIMIT; ++w)
           if (mbar_try_wait(&full_bar[s], ph)) break;
       }
     }
@@ -349,7 +390,16 @@ int launch_tc(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& b2,
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-  k<<<tiles_m * tiles_n, 192, smem, st>>>(a, b, b2, M, N, K, tiles_m, tiles_n, m_fast, ep, status);
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
+      sm_count = 148;
+  }
+  const int tiles = tiles_m * tiles_n;
+  const int grid = tiles < sm_count ? tiles : sm_count;  // one persistent CTA per SM
+  k<<<grid, 192, smem, st>>>(a, b, b2, M, N, K, tiles_m, tiles_n, m_fast, ep, status);
   STU_CHECK_LAUNCH();
   return STU_OK;
 }
@@ -387,15 +437,15 @@ int gemm_tc_dispatch(const void* A, long long lda, const void* B, long long ldb,
     if ((rc = make_map(&ma, B, N, K, ldb)) != STU_OK) return rc;
     if ((rc = make_map(&mb, A, M, K, lda)) != STU_OK) return rc;
     ep.ldy = N;  // channel count
-    return launch_tc<EPI_HIST_T, 3>(ma, mb, mb, N, M, K, /*m_fast=*/1, ep, g_status_word, st);
+    return launch_tc<EPI_HIST_T, 6>(ma, mb, mb, N, M, K, /*m_fast=*/1, ep, g_status_word, st);
   }
   if ((rc = make_map(&ma, A, M, K, lda)) != STU_OK) return rc;
   if ((rc = make_map(&mb, B, N, K, ldb)) != STU_OK) return rc;
   mb2 = mb;
   if (epi == EPI_GELU_MUL && (rc = make_map(&mb2, B2, N, K, ldb)) != STU_OK) return rc;
   switch (epi) {
-    case EPI_STORE: return launch_tc<EPI_STORE, 3>(ma, mb, mb2, M, N, K, 0, ep, g_status_word, st);
-    case EPI_RESID: return launch_tc<EPI_RESID, 3>(ma, mb, mb2, M, N, K, 0, ep, g_status_word, st);
+    case EPI_STORE: return launch_tc<EPI_STORE, 6>(ma, mb, mb2, M, N, K, 0, ep, g_status_word, st);
+    case EPI_RESID: return launch_tc<EPI_RESID, 6>(ma, mb, mb2, M, N, K, 0, ep, g_status_word, st);
     case EPI_GELU_MUL: return launch_tc<EPI_GELU_MUL, 4>(ma, mb, mb2, M, N, K, 0, ep, g_status_word, st);
   }
   return STU_ERR_UNSUPPORTED;

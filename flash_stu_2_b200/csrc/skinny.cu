@@ -24,62 +24,45 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, uint32_t a0, uint32_t a
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-constexpr int SK_PAD = 32;  // activation row padding (elements) that spreads rows over distinct banks
-
-// Stage x[M,K] (bf16) into shared memory rows of K+SK_PAD elements; rows M..MT*16-1 are zero.
-// With NORM each row is replaced by rmsnorm(x)*w rounded to bf16 (the tensor the reference feeds
-// its nn.Linear).
-template <bool NORM>
-__device__ void stage_rows_bf16(bf16* xs, const bf16* __restrict__ x, long long lda, int M, int MT, int K,
-                                const bf16* __restrict__ nw, float eps) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  const int ld = K + SK_PAD;
-  for (int m = warp; m < MT * 16; m += nwarps) {
-    bf16* dst = xs + (size_t)m * ld;
-    if (m >= M) {
-      for (int k = lane * 8; k < K; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
-      continue;
-    }
-    const bf16* src = x + (size_t)m * lda;
-    if (!NORM) {
-      for (int k = lane * 8; k < K; k += 256)
-        *reinterpret_cast<uint4*>(dst + k) = *reinterpret_cast<const uint4*>(src + k);
-    } else {
-      float ss = 0.f;
-      for (int k = lane * 8; k < K; k += 256) {
-        float v[8];
-        load_vec(src + k, v);
+// Normalise eight activation values the way the reference's RMSNorm output tensor holds them
+// (x * r * w rounded to bf16) and pack them as four bf16x2 words.
+__device__ __forceinline__ uint4 norm_pack(const uint4& raw, float r, const uint4& nraw) {
+  float xv[8], wv[8];
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  const uint32_t n[4] = {nraw.x, nraw.y, nraw.z, nraw.w};
 #pragma unroll
-        for (int j = 0; j < 8; j++) ss += v[j] * v[j];
-      }
-      ss = warp_sum(ss);
-      float r = rsqrtf(ss / (float)K + eps);
-      for (int k = lane * 8; k < K; k += 256) {
-        float v[8], g[8];
-        load_vec(src + k, v);
-        load_vec(nw + k, g);
-#pragma unroll
-        for (int j = 0; j < 8; j++) v[j] = v[j] * r * g[j];
-        store_vec(dst + k, v);
-      }
-    }
+  for (int i = 0; i < 4; i++) {
+    xv[2 * i] = __uint_as_float(w[i] << 16);
+    xv[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    wv[2 * i] = __uint_as_float(n[i] << 16);
+    wv[2 * i + 1] = __uint_as_float(n[i] & 0xffff0000u);
   }
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(xv[2 * i] * r * wv[2 * i], xv[2 * i + 1] * r * wv[2 * i + 1]);
+    o[i] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-template <int EPI, int MT, bool NORM>
-__global__ void __launch_bounds__(256) skinny_bf16_kernel(const bf16* __restrict__ x, long long lda,
-                                                          const bf16* __restrict__ W, long long ldb,
-                                                          const bf16* __restrict__ W2, int M, int N, int K,
-                                                          EpiArgs<bf16> ep, const bf16* __restrict__ nw, float eps) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* xs = reinterpret_cast<bf16*>(smem_raw);
-  const int ld = K + SK_PAD;
-  float* red = reinterpret_cast<float*>(smem_raw + (size_t)MT * 16 * ld * sizeof(bf16));
+// One CTA = eight output features; its NW warps split K in interleaved 32-element chunks.  Every lane
+// loads 16 bytes of its weight row and 16 bytes of its activation row(s) per chunk straight from global
+// memory (the activations are L2-resident) and feeds them to mma.sync with the k-order permuted so that
+// no shuffle or shared-memory staging is needed.  All loads of a round (U chunks) are issued before any
+// is used; with NORM the row statistics are computed while they are in flight.
+//   MT   16-row activation tiles (M <= 16*MT);  LOW8: M <= 8, the upper half-tile is implicit zeros
+template <int EPI, int MT, bool LOW8, bool NORM, int U, int NW>
+__global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __restrict__ x, long long lda,
+                                                              const bf16* __restrict__ W, long long ldb,
+                                                              const bf16* __restrict__ W2, int M, int N, int K,
+                                                              EpiArgs<bf16> ep, const bf16* __restrict__ nw,
+                                                              float eps) {
   constexpr bool DUAL = (EPI == EPI_GELU_MUL);
   constexpr int NACC = DUAL ? 2 : 1;
-
-  stage_rows_bf16<NORM>(xs, x, lda, M, MT, K, nw, eps);
-  __syncthreads();
+  constexpr int NH = LOW8 ? 1 : 2;  // activation half-tiles (rows g and g+8) per m-tile
+  __shared__ float s_r[MT * 16];
+  __shared__ float red[NACC * NW * MT * 4 * 32];
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, q = lane & 3;
@@ -88,6 +71,49 @@ __global__ void __launch_bounds__(256) skinny_bf16_kernel(const bf16* __restrict
   const bool nvalid = n < N;
   const bf16* wrow = W + (size_t)(nvalid ? n : 0) * ldb;
   const bf16* wrow2 = DUAL ? (W2 + (size_t)(nvalid ? n : 0) * ldb) : nullptr;
+  const int nchunks = (K + 31) >> 5;
+
+  uint4 wv[U], wv2[DUAL ? U : 1], xv[U][MT][NH], nwv[NORM ? U : 1];
+  auto issue = [&](int c0) {
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int ch = c0 + NW * u;
+      const int k = (ch << 5) + q * 8;
+      const bool kok = ch < nchunks && (k + 8) <= K;
+      wv[u] = (kok && nvalid) ? ldg_stream(wrow + k) : make_uint4(0, 0, 0, 0);
+      if (DUAL) wv2[u] = (kok && nvalid) ? ldg_stream(wrow2 + k) : make_uint4(0, 0, 0, 0);
+      if (NORM) nwv[u] = kok ? *reinterpret_cast<const uint4*>(nw + k) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int t = 0; t < MT; t++)
+#pragma unroll
+        for (int h = 0; h < NH; h++) {
+          const int m = t * 16 + h * 8 + g;
+          xv[u][t][h] = (kok && m < M) ? *reinterpret_cast<const uint4*>(x + (size_t)m * lda + k)
+                                       : make_uint4(0, 0, 0, 0);
+        }
+    }
+  };
+  issue(warp);
+
+  if (NORM) {
+    for (int m = warp; m < MT * 16; m += NW) {
+      float r = 0.f;
+      if (m < M) {
+        const bf16* src = x + (size_t)m * lda;
+        float ss = 0.f;
+        for (int k = lane * 8; k < K; k += 256) {
+          float v[8];
+          load_vec(src + k, v);
+#pragma unroll
+          for (int j = 0; j < 8; j++) ss += v[j] * v[j];
+        }
+        ss = warp_sum(ss);
+        r = rsqrtf(ss / (float)K + eps);
+      }
+      if (lane == 0) s_r[m] = r;
+    }
+    __syncthreads();
+  }
 
   float acc[NACC][MT][4];
 #pragma unroll
@@ -97,34 +123,29 @@ __global__ void __launch_bounds__(256) skinny_bf16_kernel(const bf16* __restrict
 #pragma unroll
       for (int i = 0; i < 4; i++) acc[a][t][i] = 0.f;
 
-  const int nchunks = (K + 31) >> 5;
-  constexpr int U = 4;
-  for (int c0 = warp; c0 < nchunks; c0 += 8 * U) {
-    uint4 wv[U], wv2[U];
+  for (int c0 = warp; c0 < nchunks; c0 += NW * U) {
+    if (c0 != warp) issue(c0);
 #pragma unroll
     for (int u = 0; u < U; u++) {
-      int k = ((c0 + 8 * u) << 5) + q * 8;
-      bool ok = nvalid && (c0 + 8 * u) < nchunks && (k + 8) <= K;
-      wv[u] = ok ? ldg_stream(wrow + k) : make_uint4(0, 0, 0, 0);
-      if (DUAL) wv2[u] = ok ? ldg_stream(wrow2 + k) : make_uint4(0, 0, 0, 0);
-    }
+      const int ch = c0 + NW * u;
+      const int k = (ch << 5) + q * 8;
+      // ch is the same for the whole warp: mma.sync must be reached by all 32 lanes, so a lane whose k falls
+      // past the end of a partial chunk takes part with zero operands (its loads above were predicated off)
+      if (ch < nchunks) {
 #pragma unroll
-    for (int u = 0; u < U; u++) {
-      int k = ((c0 + 8 * u) << 5) + q * 8;
-      if ((c0 + 8 * u) >= nchunks) break;
-      bool kok = (k + 8) <= K;
-#pragma unroll
-      for (int t = 0; t < MT; t++) {
-        uint4 xa = make_uint4(0, 0, 0, 0), xb = make_uint4(0, 0, 0, 0);
-        if (kok) {
-          xa = *reinterpret_cast<const uint4*>(xs + (size_t)(t * 16 + g) * ld + k);
-          xb = *reinterpret_cast<const uint4*>(xs + (size_t)(t * 16 + g + 8) * ld + k);
-        }
-        mma_bf16_16816(acc[0][t], xa.x, xb.x, xa.y, xb.y, wv[u].x, wv[u].y);
-        mma_bf16_16816(acc[0][t], xa.z, xb.z, xa.w, xb.w, wv[u].z, wv[u].w);
-        if (DUAL) {
-          mma_bf16_16816(acc[1][t], xa.x, xb.x, xa.y, xb.y, wv2[u].x, wv2[u].y);
-          mma_bf16_16816(acc[1][t], xa.z, xb.z, xa.w, xb.w, wv2[u].z, wv2[u].w);
+        for (int t = 0; t < MT; t++) {
+          uint4 xa = xv[u][t][0];
+          uint4 xb = LOW8 ? make_uint4(0, 0, 0, 0) : xv[u][t][NH - 1];
+          if (NORM) {  // zero activations (k past the row end) stay zero
+            xa = norm_pack(xa, s_r[t * 16 + g], nwv[u]);
+            if (!LOW8) xb = norm_pack(xb, s_r[t * 16 + 8 + g], nwv[u]);
+          }
+          mma_bf16_16816(acc[0][t], xa.x, xb.x, xa.y, xb.y, wv[u].x, wv[u].y);
+          mma_bf16_16816(acc[0][t], xa.z, xb.z, xa.w, xb.w, wv[u].z, wv[u].w);
+          if (DUAL) {
+            mma_bf16_16816(acc[1][t], xa.x, xb.x, xa.y, xb.y, wv2[u].x, wv2[u].y);
+            mma_bf16_16816(acc[1][t], xa.z, xb.z, xa.w, xb.w, wv2[u].z, wv2[u].w);
+          }
         }
       }
     }
@@ -135,17 +156,17 @@ __global__ void __launch_bounds__(256) skinny_bf16_kernel(const bf16* __restrict
 #pragma unroll
     for (int t = 0; t < MT; t++)
 #pragma unroll
-      for (int i = 0; i < 4; i++) red[(((a * 8 + warp) * MT + t) * 4 + i) * 32 + lane] = acc[a][t][i];
+      for (int i = 0; i < 4; i++) red[(((a * NW + warp) * MT + t) * 4 + i) * 32 + lane] = acc[a][t][i];
   __syncthreads();
   // element (row, col) of m-tile t lives in lane (row%8)*4 + col/2, register (row/8)*2 + col%2
-  for (int e = threadIdx.x; e < MT * 128; e += 256) {
+  for (int e = threadIdx.x; e < MT * 128; e += NW * 32) {
     int t = e >> 7, r = (e >> 3) & 15, cidx = e & 7;
     int src_lane = (r & 7) * 4 + (cidx >> 1), reg = (r >> 3) * 2 + (cidx & 1);
     float s = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; w++) {
-      s += red[(((0 * 8 + w) * MT + t) * 4 + reg) * 32 + src_lane];
-      if (DUAL) s2 += red[(((1 * 8 + w) * MT + t) * 4 + reg) * 32 + src_lane];
+    for (int w = 0; w < NW; w++) {
+      s += red[(((0 * NW + w) * MT + t) * 4 + reg) * 32 + src_lane];
+      if (DUAL) s2 += red[(((1 * NW + w) * MT + t) * 4 + reg) * 32 + src_lane];
     }
     int m = t * 16 + r, nn = n0 + cidx;
     if (m < M && nn < N) epilogue_store<bf16, EPI>(ep, m, nn, s, s2);
@@ -187,55 +208,59 @@ __global__ void __launch_bounds__(256) skinny_f32_kernel(const float* __restrict
   }
 }
 
-static size_t skinny_smem_bytes(int MT, int K, bool dual) {
-  return (size_t)MT * 16 * (K + SK_PAD) * sizeof(bf16) + (size_t)(dual ? 2 : 1) * 8 * MT * 4 * 32 * sizeof(float);
-}
-
 bool skinny_supported(const void* A, long long lda, const void* B, long long ldb, long long skb, const void* B2,
                       int M, int N, int K, int epi, int dtype) {
   if (M < 1 || M > 64 || skb != 1 || epi == EPI_HIST) return false;
-  if (dtype == STU_BF16) {
-    if (K % 8 || lda % 8 || ldb % 8 || !aligned16(A) || !aligned16(B) || (B2 && !aligned16(B2))) return false;
-    int MT = (M + 15) / 16;
-    return skinny_smem_bytes(MT, K, epi == EPI_GELU_MUL) <= 200 * 1024;
-  }
+  if (dtype == STU_BF16)
+    return !(K % 8 || lda % 8 || ldb % 8 || !aligned16(A) || !aligned16(B) || (B2 && !aligned16(B2)));
   if (dtype == STU_F32)
     return !(K % 4 || lda % 4 || ldb % 4 || !aligned16(A) || !aligned16(B) || (B2 && !aligned16(B2)));
   return false;
 }
 
-template <int EPI, int MT>
-static int launch_skinny_bf16(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M,
-                              int N, int K, const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st) {
-  size_t smem = skinny_smem_bytes(MT, K, EPI == EPI_GELU_MUL);
+template <int EPI, int MT, bool LOW8, int U, int NW>
+static int launch_skinny_cfg(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N,
+                             int K, const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st) {
   dim3 grid((N + 7) / 8);
-  cudaError_t e;
-  if (nw) {
-    auto k = skinny_bf16_kernel<EPI, MT, true>;
-    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    k<<<grid, 256, smem, st>>>((const bf16*)A, lda, (const bf16*)B, ldb, (const bf16*)B2, M, N, K, ep,
-                               (const bf16*)nw, eps);
-  } else {
-    auto k = skinny_bf16_kernel<EPI, MT, false>;
-    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    k<<<grid, 256, smem, st>>>((const bf16*)A, lda, (const bf16*)B, ldb, (const bf16*)B2, M, N, K, ep, nullptr,
-                               eps);
-  }
+  if (nw)
+    skinny_bf16_kernel<EPI, MT, LOW8, true, U, NW><<<grid, NW * 32, 0, st>>>(
+        (const bf16*)A, lda, (const bf16*)B, ldb, (const bf16*)B2, M, N, K, ep, (const bf16*)nw, eps);
+  else
+    skinny_bf16_kernel<EPI, MT, LOW8, false, U, NW><<<grid, NW * 32, 0, st>>>(
+        (const bf16*)A, lda, (const bf16*)B, ldb, (const bf16*)B2, M, N, K, ep, nullptr, eps);
   STU_CHECK_LAUNCH();
   return STU_OK;
+}
+
+// Register budget: a round keeps U weight vectors (2U for gate/up) and U*MT*(1 or 2) activation vectors
+// per lane.  Long K rows use 16 warps so that one or two rounds cover the row.
+template <int EPI, int MT, bool LOW8>
+static int launch_skinny_shape(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M,
+                               int N, int K, const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st) {
+  constexpr bool light = (EPI != EPI_GELU_MUL) && (MT == 1);  // few registers per chunk: deeper rounds fit
+  const int chunks = (K + 31) / 32;
+  const int per8 = (chunks + 7) / 8;
+  if constexpr (light) {
+    if (per8 <= 4) return launch_skinny_cfg<EPI, MT, LOW8, 4, 8>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+    if (per8 <= 8) return launch_skinny_cfg<EPI, MT, LOW8, 8, 8>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+    return launch_skinny_cfg<EPI, MT, LOW8, 8, 16>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+  } else if constexpr (MT <= 2) {
+    return launch_skinny_cfg<EPI, MT, LOW8, 4, 8>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+  } else {
+    return launch_skinny_cfg<EPI, MT, LOW8, 2, 8>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+  }
 }
 
 template <int EPI>
 static int launch_skinny_bf16_mt(int MT, const void* A, long long lda, const void* B, long long ldb, const void* B2,
                                  int M, int N, int K, const EpiArgs<bf16>& ep, const void* nw, float eps,
                                  cudaStream_t st) {
+  if (M <= 8) return launch_skinny_shape<EPI, 1, true>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
   switch (MT) {
-    case 1: return launch_skinny_bf16<EPI, 1>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
-    case 2: return launch_skinny_bf16<EPI, 2>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
-    case 3: return launch_skinny_bf16<EPI, 3>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
-    case 4: return launch_skinny_bf16<EPI, 4>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+    case 1: return launch_skinny_shape<EPI, 1, false>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+    case 2: return launch_skinny_shape<EPI, 2, false>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+    case 3: return launch_skinny_shape<EPI, 3, false>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+    case 4: return launch_skinny_shape<EPI, 4, false>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
   }
   return STU_ERR_SHAPE;
 }

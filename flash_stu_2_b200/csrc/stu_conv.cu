@@ -247,28 +247,50 @@ __global__ void __launch_bounds__(256) conv_mma_kernel(const bf16* __restrict__ 
 }
 
 // ------------------------------------------------------------------------------------------------
-// x[b, t - t0, c] = round(x + yT[b][c][t&1][t>>1]) for t in [t0, t_end); 64 times x 32 channels per CTA.
+// x[b, t - t0, c] = round(x + yT[b][c][t&1][t>>1]) for t in [t0, t_end).  One CTA moves 128 times x 8*V
+// channels: 16-byte loads along time from the two parity rows of each channel into a padded shared
+// tile, then 16-byte read-modify-writes along channels of the token-major residual stream.
 template <typename T>
 __global__ void __launch_bounds__(256) transpose_add_kernel(T* __restrict__ x, long long x_bstride,
                                                             long long x_tstride, const T* __restrict__ yT, int d,
                                                             int Lh, int t0, int t_end) {
-  __shared__ float tile[32][65];
-  const int b = blockIdx.z, c0 = blockIdx.y * 32, tb = (t0 & ~1) + blockIdx.x * 64;  // tb even
-  // read: for channel row r, 32 elements of each parity
-  for (int e = threadIdx.x; e < 32 * 64; e += 256) {
-    int r = e >> 6, i = e & 63, p = i >> 5, s = (tb >> 1) + (i & 31);
-    int c = c0 + r, t = 2 * s + p;
-    float v = 0.f;
-    if (c < d && t >= t0 && t < t_end) v = Elem<T>::to_f(yT[((size_t)((size_t)b * d + c) * 2 + p) * Lh + s]);
-    tile[r][2 * (i & 31) + p] = v;
+  constexpr int V = Elem<T>::VEC;           // elements per 16 bytes
+  constexpr int TC = 8 * V;                 // channels per CTA (64 bf16 / 32 fp32)
+  constexpr int TS = 64;                    // time indices per parity per CTA
+  constexpr int SROW = (sizeof(T) == 2) ? 66 : 65;  // row pitch in elements: odd number of 32-bit words
+  __shared__ __align__(16) T tile[2][TC][SROW];
+  // tile origin: the first time is rounded down to a multiple of 2V so that sb is a multiple of V and the
+  // 16-byte loads along a parity row stay aligned for any t0
+  const int b = blockIdx.z, c0 = blockIdx.y * TC, tb = (t0 - t0 % (2 * V)) + blockIdx.x * (2 * TS);
+  const int sb = tb >> 1;
+  constexpr int NV = TS / V;
+  for (int item = threadIdx.x; item < 2 * TC * NV; item += 256) {
+    const int p = item / (TC * NV), c = (item / NV) % TC, v = item % NV;
+    const int s = sb + v * V;
+    float val[V];
+#pragma unroll
+    for (int j = 0; j < V; j++) val[j] = 0.f;
+    if (c0 + c < d && s + V <= Lh) load_vec(yT + ((size_t)((size_t)b * d + c0 + c) * 2 + p) * Lh + s, val);
+#pragma unroll
+    for (int j = 0; j < V; j++) tile[p][c][v * V + j] = Elem<T>::from_f(val[j]);
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < 64 * 32; e += 256) {
-    int tt = e >> 5, r = e & 31;
-    int t = tb + tt, c = c0 + r;
-    if (c < d && t >= t0 && t < t_end) {
+  for (int item = threadIdx.x; item < 2 * TS * 8; item += 256) {
+    const int tl = item >> 3, cg = item & 7;
+    const int t = tb + tl, c = c0 + cg * V;
+    if (t >= t0 && t < t_end && c < d) {
       T* px = x + (size_t)b * x_bstride + (size_t)(t - t0) * x_tstride + c;
-      *px = Elem<T>::from_f(Elem<T>::to_f(*px) + tile[r][tt]);
+      const int p = tl & 1, si = tl >> 1;
+      if (c + V <= d && ((reinterpret_cast<uintptr_t>(px) & 15u) == 0)) {
+        float xv[V];
+        load_vec(px, xv);
+#pragma unroll
+        for (int j = 0; j < V; j++) xv[j] += Elem<T>::to_f(tile[p][cg * V + j][si]);
+        store_vec(px, xv);
+      } else {
+        for (int j = 0; j < V && c + j < d; j++)
+          px[j] = Elem<T>::from_f(Elem<T>::to_f(px[j]) + Elem<T>::to_f(tile[p][cg * V + j][si]));
+      }
     }
   }
 }
@@ -311,8 +333,10 @@ extern "C" int stu_conv_prefill_approx(const void* hist, const void* taps, void*
     }
   }
   STU_CHECK_LAUNCH();
-  int tb = t0 & ~1;
-  dim3 g2((t_end - tb + 63) / 64, (d + 31) / 32, B);
+  const int v2 = (dtype == STU_F32) ? 8 : 16;  // 2V: the kernel aligns its first tile to this
+  int tb = t0 - t0 % v2;
+  const int tc = (dtype == STU_F32) ? 32 : 64;
+  dim3 g2((t_end - tb + 127) / 128, (d + tc - 1) / tc, B);
   if (dtype == STU_F32)
     transpose_add_kernel<float><<<g2, 256, 0, st>>>((float*)x, x_bstride, x_tstride, (const float*)yT, d, y_Lh, t0,
                                                     t_end);
@@ -334,6 +358,32 @@ extern "C" int stu_conv_prefill_approx(const void* hist, const void* taps, void*
 // with t = pos[2*b].  The taps are staged reversed in shared memory so that both operands of the
 // dot product are ascending 128-bit vectors.  The last CTA to finish advances every pos[2*b] by one
 // (pos[1] is the arrival counter), so a captured graph can be replayed without host-side arguments.
+__device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void unpack_vec(const uint4& v, float (&out)[8], bf16) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    out[2 * i] = __uint_as_float(w[i] << 16);
+    out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ void unpack_vec(const uint4& v, float (&out)[4], float) {
+  out[0] = __uint_as_float(v.x); out[1] = __uint_as_float(v.y);
+  out[2] = __uint_as_float(v.z); out[3] = __uint_as_float(v.w);
+}
+
+// The kernel is latency-bound unless many loads are in flight, so the order of work is: read the
+// positions, issue the first DEC_U 16-byte history loads of the warp's run and the CTA's tap loads,
+// then do the RMSNorm / projection (whose own loads overlap the ones in flight), then reverse the taps
+// into shared memory, then consume.
+constexpr int DEC_U = 8;
+
 template <typename T>
 __global__ void __launch_bounds__(256) stu_decode_kernel(const T* __restrict__ x, long long x_rstride,
                                                          const T* __restrict__ norm_w, const T* __restrict__ MinT,
@@ -344,30 +394,50 @@ __global__ void __launch_bounds__(256) stu_decode_kernel(const T* __restrict__ x
   constexpr int V = Elem<T>::VEC;
   extern __shared__ __align__(16) unsigned char smraw[];
   T* tr = reinterpret_cast<T*>(smraw);  // tr[i] = taps[c][smax - i], i = 0..smax, zero padded to a vector
-  __shared__ int s_smax;
   const int c = blockIdx.x, b0 = blockIdx.y * 8;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int b = b0 + warp;
   const bool active = b < B;
-  int t = active ? pos[2 * b] : 0;
-  bool bad = active && (t < 0 || t >= 2 * Lh);
-  if (bad) {
-    if (lane == 0 && status) atomicExch(status, 2);
-    t = 0;
+  // positions of the (up to eight) sequences of this CTA; every thread derives smax without a barrier
+  int smax = 0, t = 0;
+  bool bad = false;
+#pragma unroll
+  for (int w = 0; w < 8; w++) {
+    if (b0 + w < B) {
+      int tw = pos[2 * (b0 + w)];
+      bool badw = (tw < 0 || tw >= 2 * Lh);
+      if (badw) tw = 0;
+      smax = max(smax, tw >> 1);
+      if (w == warp) { t = tw; bad = badw; }
+    }
   }
+  if (bad && lane == 0 && status) atomicExch(status, 2);
   const int p = t & 1, s = t >> 1;
-  if (threadIdx.x == 0) s_smax = 0;
-  __syncthreads();
-  if (lane == 0 && active) atomicMax(&s_smax, s);
-  __syncthreads();
-  const int smax = s_smax;
-  const int ntr = (smax + 1 + V - 1) / V * V;
-  for (int i = threadIdx.x; i < ntr; i += 256)
-    tr[i] = (i <= smax) ? taps[(size_t)c * Lh + (smax - i)] : Elem<T>::from_f(0.f);
-  __syncthreads();
-
-  if (active && !bad) {
-    // --- RMSNorm statistic of row b, then the projection onto channel c
+  const bool run = active && !bad;
+  T* hrow = hist + ((size_t)((size_t)(run ? b : 0) * d + c) * 2 + p) * Lh;
+  const int sh = smax - s;                 // offset of this row into the reversed taps
+  const bool fast = run && (sh % V) == 0;  // uniform positions: vector path
+  const int svec = (s / V) * V;
+  // ---- 1. history prefetch (first DEC_U vectors per lane)
+  uint4 hraw[DEC_U];
+#pragma unroll
+  for (int u = 0; u < DEC_U; u++) {
+    const int i = (u * 32 + lane) * V;
+    hraw[u] = (fast && i < svec) ? ldg_nc_v4(hrow + i) : make_uint4(0, 0, 0, 0);
+  }
+  // ---- 2. tap loads (forward order, reversed when written to shared memory below)
+  const int ntaps = smax + 1;
+  const int nvec = (ntaps + V - 1) / V;  // Lh % V == 0, so a partial last vector stays inside the row
+  const T* trow = taps + (size_t)c * Lh;
+  uint4 traw[2];
+#pragma unroll
+  for (int u = 0; u < 2; u++) {
+    const int v = threadIdx.x + u * 256;
+    traw[u] = (v < nvec) ? ldg_nc_v4(trow + v * V) : make_uint4(0, 0, 0, 0);
+  }
+  // ---- 3. RMSNorm statistic of row b and the projection onto channel c
+  float xp = 0.f, xc = 0.f;
+  if (run) {
     const T* xr = x + (size_t)b * x_rstride;
     float ss = 0.f;
     for (int k = lane * V; k < d; k += 32 * V) {
@@ -389,22 +459,74 @@ __global__ void __launch_bounds__(256) stu_decode_kernel(const T* __restrict__ x
       for (int j = 0; j < V; j++) dot = fmaf(round_to<T>(v[j] * r * g[j]), m[j], dot);
     }
     dot = warp_sum(dot);
-    const float xp = round_to<T>(dot);
-    T* hrow = hist + ((size_t)((size_t)b * d + c) * 2 + p) * Lh;
+    xp = round_to<T>(dot);
+    xc = Elem<T>::to_f(xr[c]);
     if (lane == 0) hrow[s] = Elem<T>::from_f(xp);
-    // --- tap dot product over the stored history [0, s); the new element pairs with tap 0 = tr[smax]
-    const int sh = smax - s;  // this row's offset into the reversed taps (0 when positions are uniform)
-    float acc0 = 0.f, acc1 = 0.f;
-    const int svec = (s / V) * V;
-    if ((sh % V) == 0) {
-      for (int i = lane * V; i < svec; i += 32 * V) {
-        float hv[V], tv[V];
-        load_vec(hrow + i, hv);
-        load_vec(tr + sh + i, tv);
+  }
+  // ---- 4. reversed taps into shared memory
+  const int ntr = nvec * V;
 #pragma unroll
-        for (int j = 0; j < V; j += 2) {
-          acc0 = fmaf(hv[j], tv[j], acc0);
-          acc1 = fmaf(hv[j + 1], tv[j + 1], acc1);
+  for (int u = 0; u < 2; u++) {
+    const int v = threadIdx.x + u * 256;
+    if (v < nvec) {
+      float tv[V];
+      unpack_vec(traw[u], tv, T());
+#pragma unroll
+      for (int j = 0; j < V; j++) {
+        const int tap = v * V + j;            // tap index; destination smax - tap (>= 0 only for real taps)
+        if (tap <= smax) tr[smax - tap] = Elem<T>::from_f(tv[j]);
+      }
+    }
+  }
+  for (int v = threadIdx.x + 512; v < nvec; v += 256) {  // rows longer than 512 vectors (Lh > 4096 for bf16)
+    float tv[V];
+    load_vec(trow + v * V, tv);
+#pragma unroll
+    for (int j = 0; j < V; j++) {
+      const int tap = v * V + j;
+      if (tap <= smax) tr[smax - tap] = Elem<T>::from_f(tv[j]);
+    }
+  }
+  for (int i = ntaps + threadIdx.x; i < ntr; i += 256) tr[i] = Elem<T>::from_f(0.f);
+  __syncthreads();
+  // ---- 5. tap dot product over the stored history [0, s); the new element pairs with tap 0 = tr[smax]
+  if (run) {
+    float acc0 = 0.f, acc1 = 0.f;
+    if (fast) {
+#pragma unroll
+      for (int u = 0; u < DEC_U; u++) {
+        const int i = (u * 32 + lane) * V;
+        if (i < svec) {
+          float hv[V], tv[V];
+          unpack_vec(hraw[u], hv, T());
+          load_vec(tr + sh + i, tv);
+#pragma unroll
+          for (int j = 0; j < V; j += 2) {
+            acc0 = fmaf(hv[j], tv[j], acc0);
+            acc1 = fmaf(hv[j + 1], tv[j + 1], acc1);
+          }
+        }
+      }
+      for (int base = DEC_U * 32 * V; base < svec; base += DEC_U * 32 * V) {
+        uint4 raw[DEC_U];
+#pragma unroll
+        for (int u = 0; u < DEC_U; u++) {
+          const int i = base + (u * 32 + lane) * V;
+          raw[u] = (i < svec) ? ldg_nc_v4(hrow + i) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < DEC_U; u++) {
+          const int i = base + (u * 32 + lane) * V;
+          if (i < svec) {
+            float hv[V], tv[V];
+            unpack_vec(raw[u], hv, T());
+            load_vec(tr + sh + i, tv);
+#pragma unroll
+            for (int j = 0; j < V; j += 2) {
+              acc0 = fmaf(hv[j], tv[j], acc0);
+              acc1 = fmaf(hv[j + 1], tv[j + 1], acc1);
+            }
+          }
         }
       }
     } else {
@@ -414,11 +536,11 @@ __global__ void __launch_bounds__(256) stu_decode_kernel(const T* __restrict__ x
     float acc = warp_sum(acc0 + acc1);
     if (lane == 0) {
       acc = fmaf(xp, Elem<T>::to_f(tr[smax]), acc);
-      float y = round_to<T>(2.f * acc);
-      out[(size_t)b * out_rstride + c] = Elem<T>::from_f(Elem<T>::to_f(xr[c]) + y);
+      const float y = round_to<T>(2.f * acc);
+      out[(size_t)b * out_rstride + c] = Elem<T>::from_f(xc + y);
     }
   }
-  // --- arrival counter: the last CTA advances the positions
+  // ---- arrival counter: the last CTA advances the positions
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
@@ -435,13 +557,291 @@ __global__ void __launch_bounds__(256) stu_decode_kernel(const T* __restrict__ x
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Tensor-core form of the fused decode step (bf16).  The CUDA-core kernel above spends ~26 instructions
+// per 16 bytes of history (unpack, convert, FMA) and is issue-bound at a third of the HBM rate.  Here the
+// tap dot products of the eight sequences of a group are one skinny matrix product per channel,
+//   y[b] = sum_i H[b][i] * tap[s - i],   A = H (8 rows x k), B = the taps broadcast to all 8 columns,
+// issued as mma.sync m16n8k16: a lane feeds each 16-byte history load straight into two MMAs.  The taps
+// come from a table that is stored reversed and in all eight 16-byte alignments (taps8[e][c][Lh+8],
+// taps8[e][c][u] = tap[Lh-1-(u+e)]), so the B fragments are aligned 16-byte pieces as well.  Both streams
+// go through a 12-deep per-lane cp.async ring.  The RMSNorm + M_inputs projection of the new token is a
+// second small MMA.
+// One CTA = 4 channels x 8 sequences; warps (2c, 2c+1) split the time range of channel c.
+// Positions that differ inside a group of 8 sequences take a scalar path (same results, slower).
+constexpr int DM_CPB = 4;
+constexpr int DM_NS = 12;  // depth of the per-lane cp.async ring (16-byte history + 16-byte tap vector per slot)
+
+// Each lane streams exactly the 16-byte pieces its own MMA fragments need, so the ring lives in shared
+// memory as private per-lane slots filled by cp.async: no registers are tied up by loads in flight, no
+// scoreboard serialises them, and completion is tracked per lane with cp.async.wait_group.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
+               "l"(gmem_src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__global__ void __launch_bounds__(256) stu_decode_mma_kernel(const bf16* __restrict__ x, long long x_rstride,
+                                                             const bf16* __restrict__ norm_w,
+                                                             const bf16* __restrict__ MinT, bf16* __restrict__ hist,
+                                                             const bf16* __restrict__ taps8, int* __restrict__ pos,
+                                                             bf16* __restrict__ out, long long out_rstride, int B,
+                                                             int d, int Lh, float eps, int* __restrict__ status) {
+  __shared__ float s_r[8];
+  __shared__ float s_proj[8][8][DM_CPB];
+  __shared__ float s_xp[8][DM_CPB];
+  __shared__ float s_acc[8][8];
+  extern __shared__ __align__(16) uint4 dm_ring[];  // [warp][slot][2][lane]
+  const int c0 = blockIdx.x * DM_CPB, b0 = blockIdx.y * 8;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, q = lane & 3;
+  const int LP = Lh + 8;  // row pitch of taps8
+  uint4* ring = dm_ring + (size_t)warp * DM_NS * 64 + lane;
+  // ---- positions of the group; uniform groups take the tensor-core path
+  const int tg = pos[2 * b0];
+  bool uniform = true, bad = false;
+#pragma unroll
+  for (int w = 0; w < 8; w++) {
+    if (b0 + w < B) {
+      const int tw = pos[2 * (b0 + w)];
+      uniform = uniform && (tw == tg);
+      bad = bad || (tw < 0 || tw >= 2 * Lh);
+    }
+  }
+  if (bad) {
+    if (threadIdx.x == 0 && status) atomicExch(status, 2);
+  } else {
+    // ---- row statistics (warp w -> sequence b0 + w), shared through s_r
+    {
+      const int b = b0 + warp;
+      float r = 0.f;
+      if (b < B) {
+        const bf16* xr = x + (size_t)b * x_rstride;
+        float ss = 0.f;
+        for (int k = lane * 8; k < d; k += 256) {
+          float v[8];
+          load_vec(xr + k, v);
+#pragma unroll
+          for (int j = 0; j < 8; j++) ss += v[j] * v[j];
+        }
+        ss = warp_sum(ss);
+        r = rsqrtf(ss / (float)d + eps);
+      }
+      if (lane == 0) s_r[warp] = r;
+    }
+    const int cc = warp >> 1, half = warp & 1;
+    const int c = c0 + cc;
+    const int brow = b0 + g;
+    const bool rowvalid = brow < B;
+    // uniform path state
+    const int p = tg & 1, s = tg >> 1;
+    const int o = Lh - 1 - s, e = o & 7;
+    const bf16* hrow = hist + ((size_t)((size_t)(rowvalid ? brow : b0) * d + c) * 2 + p) * Lh;
+    const bf16* tbase = taps8 + ((size_t)e * d + c) * LP + (o - e);
+    // chunks of 32 history elements that lie entirely before the new element are split between the two warps of
+    // the channel and streamed through the cp.async ring; one group is committed per chunk slot (empty once
+    // the range is exhausted) so that wait_group<DM_NS-1> always means "the oldest slot has landed".  The (at
+    // most one) partial chunk is handled after the loop with element masks.
+    const int nfull = s >> 5;
+    const int hmid = (nfull + 1) >> 1;
+    const int cb0 = half ? hmid : 0;
+    const int nmine = (half ? nfull : hmid) - cb0;
+    const bf16* hp = hrow + ((size_t)cb0 << 5) + 8 * q;
+    const bf16* tp = tbase + ((size_t)cb0 << 5) + 8 * q;
+    if (uniform) {
+#pragma unroll
+      for (int u = 0; u < DM_NS - 1; u++) {
+        if (u < nmine) {
+          cp_async16(ring + u * 64, hp + 32 * u);
+          cp_async16(ring + u * 64 + 32, tp + 32 * u);
+        }
+        cp_async_commit();
+      }
+    }
+    __syncthreads();
+    // ---- projection of the new token: xp[b][cc] = round(sum_k round(x*r*w)[b][k] * MinT[c0+cc][k]) as MMAs,
+    //      K split over the eight warps
+    {
+      float accp[4] = {0.f, 0.f, 0.f, 0.f};
+      const float rg = s_r[g];
+      const bf16* xr = x + (size_t)(rowvalid ? brow : b0) * x_rstride;
+      const bf16* mr = MinT + (size_t)((g < DM_CPB && c0 + g < d) ? c0 + g : c0) * d;
+      const bool mvalid = (g < DM_CPB) && (c0 + g < d);
+      for (int k0 = warp * 32; k0 < d; k0 += 256) {  // k0 is warp-uniform: every lane reaches the MMAs
+        const int k = k0 + 8 * q;
+        const bool kok = (k + 8 <= d);  // lanes past the end of a partial chunk contribute zeros
+        uint32_t a[4] = {0u, 0u, 0u, 0u};
+        uint4 mv = make_uint4(0, 0, 0, 0);
+        if (kok) {
+          float xv[8], wv[8];
+          load_vec(xr + k, xv);
+          load_vec(norm_w + k, wv);
+          if (mvalid) mv = *reinterpret_cast<const uint4*>(mr + k);
+          if (rowvalid) {
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+              a[j] = pack_bf16x2(xv[2 * j] * rg * wv[2 * j], xv[2 * j + 1] * rg * wv[2 * j + 1]);
+          }
+        }
+        mma_bf16(accp, a[0], 0u, a[1], 0u, mv.x, mv.y);
+        mma_bf16(accp, a[2], 0u, a[3], 0u, mv.z, mv.w);
+      }
+      if (q < 2) {  // columns 2q, 2q+1 are channels c0+2q, c0+2q+1
+        s_proj[warp][g][2 * q] = accp[0];
+        s_proj[warp][g][2 * q + 1] = accp[1];
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      const int row = threadIdx.x >> 2, ch = threadIdx.x & 3;
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; w++) sum += s_proj[w][row][ch];
+      const float xpv = round_to<bf16>(sum);
+      s_xp[row][ch] = xpv;
+      const int b = b0 + row;
+      if (b < B && c0 + ch < d) {
+        const int tb = pos[2 * b];
+        hist[((size_t)((size_t)b * d + c0 + ch) * 2 + (tb & 1)) * Lh + (tb >> 1)] = __float2bfloat16_rn(xpv);
+      }
+    }
+    // ---- tap dot products over the stored history [0, s)
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (uniform) {
+      for (int j = 0; j < nmine; j++) {
+        const int jn = j + DM_NS - 1;
+        if (jn < nmine) {
+          const int slot = jn % DM_NS;
+          cp_async16(ring + slot * 64, hp + 32 * jn);
+          cp_async16(ring + slot * 64 + 32, tp + 32 * jn);
+        }
+        cp_async_commit();
+        cp_async_wait<DM_NS - 1>();
+        const int slot = j % DM_NS;
+        const uint4 a = ring[slot * 64], t = ring[slot * 64 + 32];
+        // rows past the batch read a valid row's data; their accumulator rows are never stored
+        mma_bf16(acc, a.x, 0u, a.y, 0u, t.x, t.y);
+        mma_bf16(acc, a.z, 0u, a.w, 0u, t.z, t.w);
+      }
+      cp_async_wait<0>();
+      if (half == 1 && (s & 31)) {  // partial chunk: elements [32*nfull, s)
+        const int iv = (nfull << 5) + 8 * q;
+        uint32_t a[4] = {0u, 0u, 0u, 0u};
+        uint4 t = make_uint4(0, 0, 0, 0);
+        if (iv < s) {
+          const uint4 raw = ldg_nc_v4(hrow + iv);
+          t = ldg_nc_v4(tbase + iv);
+          a[0] = raw.x; a[1] = raw.y; a[2] = raw.z; a[3] = raw.w;
+          const int keep = s - iv;  // elements of this vector that lie before the new one
+          if (keep < 8) {
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++) {
+              if (2 * jj + 1 >= keep) a[jj] = (2 * jj < keep) ? (a[jj] & 0x0000ffffu) : 0u;
+            }
+          }
+        }
+        mma_bf16(acc, a[0], 0u, a[1], 0u, t.x, t.y);
+        mma_bf16(acc, a[2], 0u, a[3], 0u, t.z, t.w);
+      }
+      if (q == 0) s_acc[warp][g] = acc[0];
+    } else {
+      // scalar path: each warp pair still owns channel c; lanes stride over the history of each row
+      for (int row = half; row < 8; row += 2) {
+        const int b = b0 + row;
+        float a = 0.f;
+        if (b < B) {
+          const int tb = pos[2 * b], pb = tb & 1, sb = tb >> 1;
+          const bf16* hr = hist + ((size_t)((size_t)b * d + c) * 2 + pb) * Lh;
+          const bf16* t0p = taps8 + (size_t)c * LP;  // alignment 0: taps8[0][c][u] = tap[Lh-1-u]
+          for (int i = lane; i < sb; i += 32)
+            a = fmaf(__bfloat162float(hr[i]), __bfloat162float(t0p[Lh - 1 - (sb - i)]), a);
+          a = warp_sum(a);
+        }
+        if (lane == 0) s_acc[2 * cc][row] = a, s_acc[2 * cc + 1][row] = 0.f;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      const int row = threadIdx.x >> 2, ch = threadIdx.x & 3;
+      const int b = b0 + row, cch = c0 + ch;
+      if (b < B && cch < d) {
+        const float tap0 = __bfloat162float(taps8[(size_t)cch * LP + (Lh - 1)]);
+        const float sum = s_acc[2 * ch][row] + s_acc[2 * ch + 1][row] + s_xp[row][ch] * tap0;
+        const float y = round_to<bf16>(2.f * sum);
+        const float xv = __bfloat162float(x[(size_t)b * x_rstride + cch]);
+        out[(size_t)b * out_rstride + cch] = __float2bfloat16_rn(xv + y);
+      }
+    }
+  }
+  // ---- arrival counter: the last CTA advances the positions
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int total = gridDim.x * gridDim.y;
+    if (atomicAdd(&pos[1], 1) == total - 1) {
+      pos[1] = 0;
+      for (int i = 0; i < B; i++) {
+        const int tv2 = pos[2 * i];
+        if (tv2 >= 0 && tv2 < 2 * Lh) pos[2 * i] = tv2 + 1;
+      }
+      __threadfence();
+    }
+  }
+}
+
+// taps8[e][c][u] = taps[c][Lh-1-(u+e)] for u + e < Lh, else 0; row pitch Lh + 8.
+__global__ void taps_rev8_kernel(const bf16* __restrict__ taps, bf16* __restrict__ taps8, int d, int Lh) {
+  const int LP = Lh + 8;
+  const size_t total = (size_t)8 * d * LP;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int u = (int)(idx % LP);
+    const int c = (int)((idx / LP) % d);
+    const int e = (int)(idx / ((size_t)LP * d));
+    const int j = Lh - 1 - (u + e);
+    taps8[idx] = (j >= 0) ? taps[(size_t)c * Lh + j] : __float2bfloat16_rn(0.f);
+  }
+}
+
+extern "C" int stu_taps_rev8(const void* taps, void* taps8, int d, int Lh, int dtype, void* stream) {
+  if (!taps || !taps8) return STU_ERR_NULL;
+  if (d <= 0 || Lh <= 0 || Lh % 8) return STU_ERR_SHAPE;
+  if (dtype != STU_BF16) return STU_ERR_DTYPE;
+  taps_rev8_kernel<<<1024, 256, 0, (cudaStream_t)stream>>>((const bf16*)taps, (bf16*)taps8, d, Lh);
+  STU_CHECK_LAUNCH();
+  return STU_OK;
+}
+
 extern "C" int stu_decode_approx(const void* x, long long x_row_stride, const void* norm_w, const void* MinT,
-                                 void* hist, const void* taps, int* pos, void* out, long long out_row_stride,
-                                 int B, int d, int Lh, float eps, int* status, int dtype, void* stream) {
+                                 void* hist, const void* taps, const void* taps8, int* pos, void* out,
+                                 long long out_row_stride, int B, int d, int Lh, float eps, int* status, int dtype,
+                                 void* stream) {
   if (!x || !norm_w || !MinT || !hist || !taps || !pos || !out) return STU_ERR_NULL;
   if (B <= 0 || d <= 0 || Lh <= 0) return STU_ERR_SHAPE;
-  if (B < 1) return STU_ERR_SHAPE;
   cudaStream_t st = (cudaStream_t)stream;
+  if (taps8 && dtype == STU_BF16) {
+    // tensor-core kernel: needs the reversed 8-alignment tap table
+    if (d % 8 || Lh % 8 || x_row_stride % 8 || !aligned16(x) || !aligned16(MinT) || !aligned16(hist) ||
+        !aligned16(norm_w) || !aligned16(taps8))
+      return STU_ERR_ALIGN;
+    dim3 gm((d + DM_CPB - 1) / DM_CPB, (B + 7) / 8);
+    const size_t ring_bytes = (size_t)8 * DM_NS * 64 * sizeof(uint4);
+    cudaError_t ea = cudaFuncSetAttribute(stu_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)ring_bytes);
+    if (ea != cudaSuccess) return (int)ea;
+    stu_decode_mma_kernel<<<gm, 256, ring_bytes, st>>>((const bf16*)x, x_row_stride, (const bf16*)norm_w, (const bf16*)MinT,
+                                              (bf16*)hist, (const bf16*)taps8, pos, (bf16*)out, out_row_stride, B,
+                                              d, Lh, eps, status);
+    STU_CHECK_LAUNCH();
+    return STU_OK;
+  }
   dim3 grid(d, (B + 7) / 8);
   if (dtype == STU_F32) {
     if (d % 4 || Lh % 4 || x_row_stride % 4 || !aligned16(x) || !aligned16(MinT) || !aligned16(hist) ||

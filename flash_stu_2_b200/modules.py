@@ -124,7 +124,8 @@ class STU(nn.Module):
                 # fp = phi @ M_filters, rounded to the model dtype as in the reference (stu.py:88)
                 fp = ops.linear(phi, self.M_filters.detach(), transposed_weight=True, backend=ops.BACKEND_SIMT)
                 taps = ops.taps_even(fp, self.Lh)
-            self._prep, self._prep_key = (MinT, taps), key
+                taps8 = ops.taps_rev8(taps) if taps.dtype == torch.bfloat16 else None
+            self._prep, self._prep_key = (MinT, taps, taps8), key
         return self._prep
 
     def new_cache(self, batch: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -134,7 +135,7 @@ class STU(nn.Module):
     def add_to_residual(self, xn: torch.Tensor, x: torch.Tensor, entry=None, use_cache: bool = False):
         """x += STU(xn) for xn, x [B,T,d] (x contiguous).  Returns the cache entry when use_cache."""
         B, T, d = xn.shape
-        MinT, taps = self.prepared()
+        MinT, taps, _ = self.prepared()
         t0 = 0
         if entry is not None:
             hist, pos = entry
@@ -157,16 +158,17 @@ class STU(nn.Module):
             return hist, pos
         return None
 
-    tensor_core_conv = True  # class switch used by tests to compare the two convolution kernels
+    tensor_core_conv = True    # class switches used by tests to compare the tensor-core and CUDA-core kernels
+    tensor_core_decode = True
 
     def decode_step(self, x2d: torch.Tensor, norm_w: torch.Tensor, eps: float, entry, out2d: torch.Tensor):
         """out = x + STU(rmsnorm(x)) for one new token per sequence; appends to the cache."""
         hist, pos = entry
-        MinT, taps = self.prepared()
+        MinT, taps, taps8 = self.prepared()
         t = host_pos(pos)
         if t + 1 > self.seq_len:
             raise ValueError(f"sequence position {t + 1} exceeds seq_len={self.seq_len}")
-        ops.decode_approx(x2d, norm_w, MinT, hist, taps, pos, out2d, eps)
+        ops.decode_approx(x2d, norm_w, MinT, hist, taps, pos, out2d, eps, taps8=taps8 if STU.tensor_core_decode else None)
         pos._host_t = t + 1
         return hist, pos
 

@@ -149,6 +149,17 @@ def taps_even(fp: torch.Tensor, Lh: int):
     return taps
 
 
+def taps_rev8(taps: torch.Tensor):
+    """Reversed tap table in all eight 16-byte alignments, [8, d, Lh+8] (bf16; feeds the tensor-core decode kernel)."""
+    _cuda(taps)
+    d, Lh = taps.shape
+    out = torch.empty(8, d, Lh + 8, dtype=taps.dtype, device=taps.device)
+    rc = _lib.load().stu_taps_rev8(taps.data_ptr(), out.data_ptr(), d, Lh, _dt(taps), _stream())
+    _lib.check(rc, "stu_taps_rev8")
+    _count()
+    return out
+
+
 def conv_prefill_approx(hist, taps, yT, x, t0: int, t_end: int, use_tensor_cores: bool):
     """x[b, t-t0, c] += 2 * sum_{j even} fp[j,c] * hist[b,c,t-j] for t in [t0, t_end)."""
     _cuda(hist, taps, yT, x)
@@ -179,15 +190,17 @@ def conv_prefill_approx_static(hist, taps, x, t0: int, t_end: int, use_tensor_co
     return x
 
 
-def decode_approx(x, norm_w, MinT, hist, taps, pos, out, eps: float = RMS_EPS):
-    """One fused decode step of an approx STU layer (norm, projection, cache append, taps, residual)."""
-    _cuda(x, norm_w, MinT, hist, taps, pos, out)
+def decode_approx(x, norm_w, MinT, hist, taps, pos, out, eps: float = RMS_EPS, taps8=None):
+    """One fused decode step of an approx STU layer (norm, projection, cache append, taps, residual).
+    With taps8 (bf16) the tensor-core kernel runs, otherwise the CUDA-core one."""
+    _cuda(x, norm_w, MinT, hist, taps, pos, out, taps8)
     B, d, _, Lh = hist.shape
     assert x.shape == (B, d) and out.shape == (B, d) and x.stride(1) == 1 and out.stride(1) == 1
     assert pos.dtype == torch.int32 and pos.shape == (B, 2) and pos.is_contiguous()
     assert x.data_ptr() != out.data_ptr()
     rc = _lib.load().stu_decode_approx(x.data_ptr(), x.stride(0), norm_w.data_ptr(), MinT.data_ptr(), hist.data_ptr(),
-                                       taps.data_ptr(), pos.data_ptr(), out.data_ptr(), out.stride(0), B, d, Lh, eps,
+                                       taps.data_ptr(), _p(taps8), pos.data_ptr(), out.data_ptr(), out.stride(0), B, d,
+                                       Lh, eps,
                                        status_word(x.device).data_ptr(), _dt(x), _stream())
     _lib.check(rc, "stu_decode_approx")
     _count()

@@ -90,10 +90,17 @@ int stu_conv_prefill_approx_static(const void* hist, const void* taps, void* x, 
  *   out[b,:] = x[b,:] + STU(rmsnorm(x[b,:]) * norm_w)   at time t = pos[2*b]; appends to hist, advances pos.
  * MinT is M_inputs transposed ([d_out][d_in]).  The reference has no such step (its STU layers keep no
  * cache, flash_stu/layers/stu_layer.py:99-119); the result equals row t of the full-prefix forward of
- * flash_stu/layers/stu_layer.py:78-93.  out must not alias x. */
+ * flash_stu/layers/stu_layer.py:78-93.  out must not alias x.
+ * taps8 (bf16 only, may be NULL) is the table made by stu_taps_rev8; with it the step runs on mma.sync tensor
+ * cores (8 sequences x 4 channels per CTA), without it on CUDA cores (one warp per sequence and channel). */
 int stu_decode_approx(const void* x, long long x_row_stride, const void* norm_w, const void* MinT, void* hist,
-                      const void* taps, int* pos, void* out, long long out_row_stride, int B, int d, int Lh,
-                      float eps, int* status, int dtype, void* stream);
+                      const void* taps, const void* taps8, int* pos, void* out, long long out_row_stride, int B,
+                      int d, int Lh, float eps, int* status, int dtype, void* stream);
+
+/* taps8[e][c][u] = taps[c][Lh-1-(u+e)] (0 past the end), e = 0..7, row pitch Lh+8: the even-tap table reversed
+ * and stored in all eight 16-byte alignments, so that the decode kernel's tap operand is an aligned
+ * 16-byte load at every position.  bf16, Lh % 8 == 0.  Derived data, no counterpart in the reference. */
+int stu_taps_rev8(const void* taps, void* taps8, int d, int Lh, int dtype, void* stream);
 
 /* Sliding-window attention for the Tn new tokens in qkv [B,Tn,3*H*hd] (c_attn output) against a ring
  * cache of W >= window+1 slots ([B][W][H*hd] each; token t in slot t % W), ALiBi slopes [H] (fp32) and tanh

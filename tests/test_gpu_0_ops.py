@@ -143,35 +143,73 @@ def test_history_scatter_epilogue(dt):
         assert rel(hist, _hist_from(full, Lh)) <= TOL[dt] / 2
 
 
-@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
-def test_decode_step_equals_prefill_row(dt):
-    """S3: the fused decode kernel at time t reproduces row t of the full-prefix layer half."""
-    from flash_stu_2_b200 import ops
-    torch.manual_seed(6)
-    B, T, d, L = 3, 45, 64, 64
-    Lh = 32
+def _decode_fixture(dt, B, T, d, L, seed=6):
+    import math as _m
+    torch.manual_seed(seed)
     x = torch.randn(B, T, d).to(dt)
     nw = (1 + 0.1 * torch.randn(d)).to(dt)
-    Mi = (torch.randn(d, d) / math.sqrt(d)).to(dt)
+    Mi = (torch.randn(d, d) / _m.sqrt(d)).to(dt)
     fp = (torch.randn(L, d) / 8).to(dt)
     xn = O.rmsnorm(x, nw)
     xp = xn @ Mi
     plus, minus = O.convolve(xp, fp, O.fft_length(L), True, True)
-    ref = x + (plus + minus)
+    return x, nw, Mi, fp, xp, x + (plus + minus)
+
+
+@pytest.mark.parametrize("dt,tc", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
+@pytest.mark.parametrize("shape", [(3, 45, 64, 64), (9, 70, 40, 160)])
+def test_decode_step_equals_prefill_row(dt, tc, shape):
+    """S3: the fused decode kernel at time t reproduces row t of the full-prefix layer half
+    (CUDA-core kernel and, for bf16, the tensor-core kernel fed by the reversed tap table)."""
+    from flash_stu_2_b200 import ops
+    B, T, d, L = shape
+    Lh = ((L + 1) // 2 + 7) // 8 * 8
+    x, nw, Mi, fp, xp, ref = _decode_fixture(dt, B, T, d, L)
     hist = torch.zeros(B, d, 2, Lh, dtype=dt, device=dev())
     pos = torch.zeros(B, 2, dtype=torch.int32, device=dev())
     taps = ops.taps_even(fp.to(dev()), Lh)
+    taps8 = ops.taps_rev8(taps) if tc else None
     MinT = Mi.t().contiguous().to(dev())
     outs = []
     for t in range(T):
         out = torch.empty(B, d, dtype=dt, device=dev())
-        ops.decode_approx(x[:, t].contiguous().to(dev()), nw.to(dev()), MinT, hist, taps, pos, out)
+        ops.decode_approx(x[:, t].contiguous().to(dev()), nw.to(dev()), MinT, hist, taps, pos, out, taps8=taps8)
         outs.append(out.cpu())
     ops.check_status()
     got = torch.stack(outs, 1)
     assert pos[:, 0].tolist() == [T] * B and int(pos[0, 1]) == 0
     assert rel(got, ref) <= (1e-5 if dt == torch.float32 else 1.5e-2), rel(got, ref)
     assert rel(hist, _hist_from(xp, Lh)) <= (1e-5 if dt == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("tc", [False, True])
+def test_decode_step_with_ragged_positions(tc):
+    """Sequences of one batch at different positions (what _reorder_cache / ragged prompts produce)."""
+    from flash_stu_2_b200 import ops
+    dt = torch.bfloat16
+    B, T, d, L = 5, 50, 32, 64
+    Lh = 32
+    x, nw, Mi, fp, xp, ref = _decode_fixture(dt, B, T, d, L, seed=9)
+    where = [7, 30, 30, 1, 49]
+    hist_full = _hist_from(xp, Lh)
+    hist = torch.zeros_like(hist_full)
+    for b, t in enumerate(where):  # rows hold only the first t projected inputs
+        for p in range(2):
+            n = (t - p + 1) // 2
+            hist[b, :, p, :n] = hist_full[b, :, p, :n]
+    hist = hist.to(dev())
+    pos = torch.zeros(B, 2, dtype=torch.int32)
+    pos[:, 0] = torch.tensor(where, dtype=torch.int32)
+    pos = pos.to(dev())
+    taps = ops.taps_even(fp.to(dev()), Lh)
+    taps8 = ops.taps_rev8(taps) if tc else None
+    xin = torch.stack([x[b, t] for b, t in enumerate(where)]).to(dev())
+    out = torch.empty(B, d, dtype=dt, device=dev())
+    ops.decode_approx(xin, nw.to(dev()), Mi.t().contiguous().to(dev()), hist, taps, pos, out, taps8=taps8)
+    ops.check_status()
+    want = torch.stack([ref[b, t] for b, t in enumerate(where)])
+    assert pos[:, 0].tolist() == [t + 1 for t in where]
+    assert rel(out, want) <= 1.5e-2, rel(out, want)
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
