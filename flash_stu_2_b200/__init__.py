@@ -10,7 +10,8 @@ from .modules import MLP, STU, Attention, RMSNorm
 from .layers import AttentionLayer, STULayer
 from .block import FlashSTUBlock
 from .model import FlashSTU
+from .mini_stu import MiniSTU
 
-__all__ = ["FlashSTU", "FlashSTUConfig", "FlashSTUBlock", "STU", "Attention", "MLP", "RMSNorm", "STULayer",
+__all__ = ["FlashSTU", "MiniSTU", "FlashSTUConfig", "FlashSTUBlock", "STU", "Attention", "MLP", "RMSNorm", "STULayer",
            "AttentionLayer", "get_spectral_filters", "get_hankel", "save_spectral_filters", "load_spectral_filters",
            "nearest_power_of_two"]

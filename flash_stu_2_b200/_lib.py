@@ -40,6 +40,11 @@ _SIGNATURES = {
     "stu_taps_rev8": ([_P, _P, c_int, c_int, c_int, _P], c_int),
     "stu_decode_approx": ([_P, _LL, _P, _P, _P, _P, _P, _P, _P, _LL, c_int, c_int, c_int, c_float, _P, c_int, _P],
                           c_int),
+    "stu_to_history": ([_P, _LL, _LL, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P], c_int),
+    "stu_toeplitz": ([_P, _LL, c_int, _P, c_int, _LL, c_int, _P], c_int),
+    "stu_full_combine": ([_P, _P, _LL, _P, _LL, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P], c_int),
+    "stu_full_decode_prepare": ([_P, _LL, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P], c_int),
+    "stu_full_decode_combine": ([_P, _LL, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P], c_int),
     "stu_swa_forward": ([_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                          _P], c_int),
     "stu_sample": ([_P, _LL, c_int, c_int, c_float, c_int, c_float, c_int, _P, _P, _LL, _P, c_int, _P], c_int),

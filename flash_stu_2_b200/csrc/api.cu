@@ -9,6 +9,7 @@ enum { BACKEND_AUTO = 0, BACKEND_SIMT = 1, BACKEND_TCGEN05 = 2, BACKEND_SKINNY =
 // y = epilogue(x[M,K] @ W[N,K]^T).  element (n,k) of W at W[n*w_row_stride + k*w_k_stride].
 //   epilogue 0: y = acc                  1: y = resid + round(acc)
 //            2: y = round(gelu_tanh(round(x@W^T))) * round(x@W2^T)
+//            +0x100: W is lower triangular (zero for k > n); the tcgen05 path skips those k-blocks
 //            3: scatter into the parity-split history (y = hist base, hist_T tokens per sequence
 //               starting at time hist_t0, N channels, hist_Lh elements per parity row)
 // norm_w != NULL asks for x to be RMS-normalised (eps) on the way in; only the decode (skinny) path
@@ -21,6 +22,8 @@ extern "C" int stu_linear(const void* x, long long x_row_stride, const void* W, 
   if (!x || !W || !y) return STU_ERR_NULL;
   if (M < 0 || N <= 0 || K <= 0) return STU_ERR_SHAPE;
   if (M == 0) return STU_OK;
+  const int causal = (epilogue & EPI_FLAG_CAUSAL) ? 1 : 0;
+  epilogue &= ~EPI_FLAG_CAUSAL;
   if (epilogue < EPI_STORE || epilogue > EPI_HIST) return STU_ERR_UNSUPPORTED;
   if (epilogue == EPI_GELU_MUL && !W2) return STU_ERR_NULL;
   if (epilogue == EPI_RESID && !resid) return STU_ERR_NULL;
@@ -52,7 +55,7 @@ extern "C" int stu_linear(const void* x, long long x_row_stride, const void* W, 
       return skinny_dispatch(x, x_row_stride, W, w_row_stride, W2, M, N, K, epilogue, ep, nullptr, eps, dtype, st);
     case BACKEND_TCGEN05:
       if (!tc_ok) return STU_ERR_UNSUPPORTED;
-      return gemm_tc_dispatch(x, x_row_stride, W, w_row_stride, W2, M, N, K, epilogue, ep, st);
+      return gemm_tc_dispatch(x, x_row_stride, W, w_row_stride, W2, M, N, K, epilogue, causal, ep, st);
     case BACKEND_SIMT:
       return gemm_simt_dispatch(x, x_row_stride, W, w_row_stride, w_k_stride, W2, M, N, K, epilogue, ep, dtype, st);
   }

@@ -9,6 +9,8 @@ enum {
   EPI_GELU_MUL = 2,  // y = round(gelu_tanh(round(acc))) * round(acc2)   flash_stu/modules/swiglu.py:22-28
   EPI_HIST = 3,      // scatter acc into the parity-split channel-major history [B][N][2][Lh]
 };
+// OR-ed into the epilogue code: W is lower triangular (W[n][k] = 0 for k > n); kernels may skip those blocks
+#define EPI_FLAG_CAUSAL 0x100
 
 template <typename T> struct EpiArgs {
   T* y;
@@ -52,7 +54,7 @@ __device__ __forceinline__ void epilogue_store(const EpiArgs<T>& ep, int m, int 
 int gemm_simt_dispatch(const void* A, long long lda, const void* B, long long ldb, long long skb, const void* B2,
                        int M, int N, int K, int epi, const EpiArgsAny& ep, int dtype, cudaStream_t st);
 int gemm_tc_dispatch(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N,
-                     int K, int epi, const EpiArgsAny& ep, cudaStream_t st);
+                     int K, int epi, int causal, const EpiArgsAny& ep, cudaStream_t st);
 bool gemm_tc_supported(const void* A, long long lda, const void* B, long long ldb, long long skb, const void* B2,
                        int M, int N, int K, int epi, const EpiArgsAny& ep, int dtype);
 int skinny_dispatch(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N, int K,

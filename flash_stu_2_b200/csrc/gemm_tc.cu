@@ -123,6 +123,14 @@ __device__ __forceinline__ float gelu_tanh_fast(float x) {
   return 0.5f * x * (1.0f + t);
 }
 
+// With `causal` the B operand is lower triangular (B[n][k] = 0 for k > n, the Toeplitz matrices of the STU
+// full variant): k-blocks that lie entirely above the diagonal of the tile's last column are skipped.
+__device__ __forceinline__ int tile_kb(int num_kb, int n0, int causal) {
+  if (!causal) return num_kb;
+  const int need = (n0 + BN + BK - 1) / BK;
+  return need < num_kb ? need : num_kb;
+}
+
 // Persistent kernel: CTA i handles tiles i, i + gridDim.x, ...  The accumulator is double-buffered in TMEM
 // (2 x 128 columns, or 2 x 256 for the gate/up epilogue), so the MMA warp starts the next tile while
 // the epilogue warps drain the previous one.
@@ -131,7 +139,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
                                                          const __grid_constant__ CUtensorMap tmB,
                                                          const __grid_constant__ CUtensorMap tmB2, int M, int N,
                                                          int K, int tiles_m, int tiles_n, int m_fast,
-                                                         EpiArgs<bf16> ep, int* status) {
+                                                         int causal, EpiArgs<bf16> ep, int* status) {
   constexpr bool DUAL = (EPI == EPI_GELU_MUL);
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES * (DUAL ? 2 : 1);
   constexpr uint32_t ACC_COLS = DUAL ? 256 : 128;
@@ -184,7 +192,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         const int tm = m_fast ? (tile % tiles_m) : (tile / tiles_n);
         const int tn = m_fast ? (tile / tiles_m) : (tile % tiles_n);
         const int m0 = tm * BM, n0 = tn * BN;
-        for (int kb = 0; kb < num_kb; kb++, g++) {
+        const int kb_end = tile_kb(num_kb, n0, causal);
+        for (int kb = 0; kb < kb_end; kb++, g++) {
           const int s = g % STAGES;
           const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
           if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
@@ -205,9 +214,11 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, it++) {
         const int buf = it & 1;
         const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS;
+        const int tn_ = m_fast ? (tile / tiles_m) : (tile % tiles_n);
+        const int kb_end = tile_kb(num_kb, tn_ * BN, causal);
         if (!mbar_wait(&tmem_empty[buf], (((uint32_t)it >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        for (int kb = 0; kb < num_kb; kb++, g++) {
+        for (int kb = 0; kb < kb_end; kb++, g++) {
           const int s = g % STAGES;
           const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
           if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
@@ -382,7 +393,7 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
 
 template <int EPI, int STAGES>
 int launch_tc(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& b2, int M, int N, int K, int m_fast,
-              const EpiArgs<bf16>& ep, int* status, cudaStream_t st) {
+              int causal, const EpiArgs<bf16>& ep, int* status, cudaStream_t st) {
   constexpr bool DUAL = (EPI == EPI_GELU_MUL);
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES * (DUAL ? 2 : 1);
   const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
@@ -399,7 +410,7 @@ int launch_tc(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& b2,
   }
   const int tiles = tiles_m * tiles_n;
   const int grid = tiles < sm_count ? tiles : sm_count;  // one persistent CTA per SM
-  k<<<grid, 192, smem, st>>>(a, b, b2, M, N, K, tiles_m, tiles_n, m_fast, ep, status);
+  k<<<grid, 192, smem, st>>>(a, b, b2, M, N, K, tiles_m, tiles_n, m_fast, causal, ep, status);
   STU_CHECK_LAUNCH();
   return STU_OK;
 }
@@ -427,7 +438,7 @@ bool gemm_tc_supported(const void* A, long long lda, const void* B, long long ld
 }
 
 int gemm_tc_dispatch(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N,
-                     int K, int epi, const EpiArgsAny& epa, cudaStream_t st) {
+                     int K, int epi, int causal, const EpiArgsAny& epa, cudaStream_t st) {
   CUtensorMap ma, mb, mb2;
   EpiArgs<bf16> ep = epa.as<bf16>();
   int rc;
@@ -437,16 +448,16 @@ int gemm_tc_dispatch(const void* A, long long lda, const void* B, long long ldb,
     if ((rc = make_map(&ma, B, N, K, ldb)) != STU_OK) return rc;
     if ((rc = make_map(&mb, A, M, K, lda)) != STU_OK) return rc;
     ep.ldy = N;  // channel count
-    return launch_tc<EPI_HIST_T, 6>(ma, mb, mb, N, M, K, /*m_fast=*/1, ep, g_status_word, st);
+    return launch_tc<EPI_HIST_T, 6>(ma, mb, mb, N, M, K, /*m_fast=*/1, 0, ep, g_status_word, st);
   }
   if ((rc = make_map(&ma, A, M, K, lda)) != STU_OK) return rc;
   if ((rc = make_map(&mb, B, N, K, ldb)) != STU_OK) return rc;
   mb2 = mb;
   if (epi == EPI_GELU_MUL && (rc = make_map(&mb2, B2, N, K, ldb)) != STU_OK) return rc;
   switch (epi) {
-    case EPI_STORE: return launch_tc<EPI_STORE, 6>(ma, mb, mb2, M, N, K, 0, ep, g_status_word, st);
-    case EPI_RESID: return launch_tc<EPI_RESID, 6>(ma, mb, mb2, M, N, K, 0, ep, g_status_word, st);
-    case EPI_GELU_MUL: return launch_tc<EPI_GELU_MUL, 4>(ma, mb, mb2, M, N, K, 0, ep, g_status_word, st);
+    case EPI_STORE: return launch_tc<EPI_STORE, 6>(ma, mb, mb2, M, N, K, 0, causal, ep, g_status_word, st);
+    case EPI_RESID: return launch_tc<EPI_RESID, 6>(ma, mb, mb2, M, N, K, 0, causal, ep, g_status_word, st);
+    case EPI_GELU_MUL: return launch_tc<EPI_GELU_MUL, 4>(ma, mb, mb2, M, N, K, 0, 0, ep, g_status_word, st);
   }
   return STU_ERR_UNSUPPORTED;
 }

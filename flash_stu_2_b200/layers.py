@@ -32,7 +32,11 @@ class STULayer(nn.Module):
             self._scratch = {key: torch.empty(B, d, dtype=x.dtype, device=x.device)}
         mid = self._scratch[key]
         x2 = x.view(B, d)
-        entry = self.stu.decode_step(x2, self.stu_norm.weight, self.stu_norm.eps, entry, mid)
+        if self.stu.use_approx:
+            entry = self.stu.decode_step(x2, self.stu_norm.weight, self.stu_norm.eps, entry, mid)
+        else:
+            xn = ops.rmsnorm(x2, self.stu_norm.weight, self.stu_norm.eps)
+            entry = self.stu.full_decode_step(xn, x2, mid, entry)
         inter = self.mlp.intermediate_size
         if ops.can_fuse_norm(B, inter, d, ops.EPI_GELU_MUL, x.dtype):
             self.mlp.apply_residual(mid, mid, x2, norm_w=self.mlp_norm.weight, eps=self.mlp_norm.eps)

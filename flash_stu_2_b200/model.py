@@ -197,8 +197,13 @@ class FlashSTU(PreTrainedModel):
         elif isinstance(module, nn.Embedding):
             torch.nn.init.normal_(module.weight, mean=0.0, std=self.std)
         elif isinstance(module, STU):
-            torch.nn.init.xavier_normal_(module.M_inputs)
-            torch.nn.init.xavier_normal_(module.M_filters)
+            if module.use_approx:
+                torch.nn.init.xavier_normal_(module.M_inputs)
+                torch.nn.init.xavier_normal_(module.M_filters)
+            else:
+                torch.nn.init.xavier_normal_(module.M_phi_plus)
+                if not module.use_hankel_L:
+                    torch.nn.init.xavier_normal_(module.M_phi_minus)
         elif isinstance(module, Attention):
             torch.nn.init.xavier_normal_(module.c_attn.weight)
             torch.nn.init.xavier_normal_(module.c_proj.weight)

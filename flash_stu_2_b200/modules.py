@@ -78,7 +78,7 @@ class MLP(nn.Module):
 
 
 class STU(nn.Module):
-    """Spectral transform unit (flash_stu/modules/stu.py:12-120), approx variant on CUDA kernels.
+    """Spectral transform unit (flash_stu/modules/stu.py:12-120), approx and full variants on CUDA kernels.
 
     forward(x) returns the operator output like the reference.  Layers call `add_to_residual`,
     which also maintains the decode cache: entry = (hist [B,d,2,Lh], pos [B,2])."""
@@ -95,13 +95,16 @@ class STU(nn.Module):
         self.use_approx = config.use_approx
         if config.d_in_tile is not None or config.d_out_tile is not None:
             raise NotImplementedError("d_in_tile/d_out_tile (block-diagonal tiling) has no kernel here")
-        if self.use_hankel_L:
-            raise NotImplementedError("use_hankel_L=True (single branch) has no kernel here yet")
-        if not self.use_approx:
-            raise NotImplementedError("use_approx=False (full M_phi+- contraction) has no kernel here yet")
         dt = config.torch_dtype
-        self.M_inputs = nn.Parameter(torch.empty(self.d_in, self.d_out, dtype=dt))
-        self.M_filters = nn.Parameter(torch.empty(self.K, self.d_in, dtype=dt))
+        if self.use_approx:
+            if self.use_hankel_L:
+                raise NotImplementedError("use_hankel_L=True with use_approx=True (single branch) has no kernel here yet")
+            self.M_inputs = nn.Parameter(torch.empty(self.d_in, self.d_out, dtype=dt))
+            self.M_filters = nn.Parameter(torch.empty(self.K, self.d_in, dtype=dt))
+        else:
+            self.M_phi_plus = nn.Parameter(torch.empty(self.K, self.d_in, self.d_out, dtype=dt))
+            if not self.use_hankel_L:
+                self.M_phi_minus = nn.Parameter(torch.empty(self.K, self.d_in, self.d_out, dtype=dt))
         self._prep_key = None
         self._prep = None
 
@@ -115,6 +118,8 @@ class STU(nn.Module):
         return _round_up((self.seq_len + 1) // 2, 8)
 
     def prepared(self):
+        if not self.use_approx:
+            return self.prepared_full()
         key = (self.M_inputs._version, self.M_filters._version, self.phi._version, self.M_inputs.data_ptr(),
                self.M_filters.data_ptr(), self.phi.data_ptr())
         if self._prep_key != key:
@@ -128,12 +133,100 @@ class STU(nn.Module):
             self._prep, self._prep_key = (MinT, taps, taps8), key
         return self._prep
 
+    def prepared_full(self):
+        """(phi [L,K] contiguous in the model dtype, Mcat [d_out, nsign*K*d_in]): the two M_phi tensors as one
+        K-major weight whose column order (sign, k, i) matches the U operand the kernels build."""
+        mats = [self.M_phi_plus] + ([] if self.use_hankel_L else [self.M_phi_minus])
+        key = tuple(m._version for m in mats) + tuple(m.data_ptr() for m in mats) + (self.phi._version, self.phi.data_ptr())
+        if self._prep_key != key:
+            with torch.no_grad():
+                phi = self.phi.to(self.M_phi_plus.dtype).contiguous()
+                Mcat = torch.cat([m.detach().reshape(self.K * self.d_in, self.d_out) for m in mats], dim=0).t().contiguous()
+            self._prep, self._prep_key = (phi, Mcat), key
+        return self._prep
+
+    @property
+    def param_dtype(self):
+        return (self.M_inputs if self.use_approx else self.M_phi_plus).dtype
+
     def new_cache(self, batch: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
-        hist = torch.zeros(batch, self.d_in, 2, self.Lh, dtype=self.M_inputs.dtype, device=device)
+        hist = torch.zeros(batch, self.d_in, 2, self.Lh, dtype=self.param_dtype, device=device)
         return hist, new_pos(batch, device)
+
+    # ------------------------------------------------------------------ full variant
+    def full_forward(self, xn: torch.Tensor, resid: Optional[torch.Tensor], out: torch.Tensor, entry=None,
+                     use_cache: bool = False):
+        """out[B,T,d_out] = (resid +) sum_k U+[..,k,:] @ M_phi_plus[k] + U-[..,k,:] @ M_phi_minus[k] for the T new
+        positions of xn [B,T,d_in]; the cache holds the history of xn."""
+        B, T, d = xn.shape
+        phi, Mcat = self.prepared_full()
+        K, nsign = self.K, (1 if self.use_hankel_L else 2)
+        t0 = 0
+        if entry is not None:
+            hist, pos = entry
+            t0 = host_pos(pos)
+        elif use_cache:
+            hist, pos = self.new_cache(B, xn.device)
+        else:
+            pos = None
+            hist = torch.zeros(B, d, 2, _round_up((T + 1) // 2, 8), dtype=xn.dtype, device=xn.device)
+        if t0 + T > self.seq_len:
+            raise ValueError(f"sequence position {t0 + T} exceeds seq_len={self.seq_len} (the filters have seq_len taps)")
+        Lh = hist.shape[3]
+        ops.to_history(xn, hist, t0)
+        S = _round_up((t0 + T + 1) // 2, 8)
+        rows = hist.view(B * d * 2, Lh)[:, :S]
+        even_in = hist.view(B * d, 2, Lh)[:, 0, :S]
+        odd_in = hist.view(B * d, 2, Lh)[:, 1, :S]
+        Tz = torch.empty(3, S, S, dtype=xn.dtype, device=xn.device)
+        E = torch.empty(B * d * 2, S, dtype=xn.dtype, device=xn.device)
+        Q = torch.empty(B * d * 2, S, dtype=xn.dtype, device=xn.device)
+        U = torch.empty(B * T, nsign * K * d, dtype=xn.dtype, device=xn.device)
+        causal = ops.EPI_STORE | ops.EPI_FLAG_CAUSAL
+        for k in range(K):
+            ops.toeplitz(phi, k, Tz)
+            ops.linear(rows, Tz[0], out=E, epilogue=causal)
+            ops.linear(even_in, Tz[1], out=Q.view(B * d, 2, S)[:, 1], epilogue=causal)  # parity-1 outputs
+            ops.linear(odd_in, Tz[2], out=Q.view(B * d, 2, S)[:, 0], epilogue=causal)   # parity-0 outputs
+            ops.full_combine(E, Q, U, B, d, K, k, nsign == 2, t0, t0 + T)
+        o2 = out.view(B * T, self.d_out)
+        if resid is not None:
+            ops.linear(U, Mcat, resid=resid.view(B * T, self.d_out), out=o2, epilogue=ops.EPI_RESID)
+        else:
+            ops.linear(U, Mcat, out=o2)
+        if pos is not None:
+            pos[:, 0] += T
+            pos._host_t = t0 + T
+            return hist, pos
+        return None
+
+    def full_decode_step(self, xn2d: torch.Tensor, resid2d: torch.Tensor, out2d: torch.Tensor, entry):
+        """One cached token of the full variant: out = resid + STU(xn) at the cached position."""
+        hist, pos = entry
+        phi, Mcat = self.prepared_full()
+        B, d, _, Lh = hist.shape
+        K, nsign = self.K, (1 if self.use_hankel_L else 2)
+        t = host_pos(pos)
+        if t + 1 > self.seq_len:
+            raise ValueError(f"sequence position {t + 1} exceeds seq_len={self.seq_len}")
+        key = (B, xn2d.device, xn2d.dtype)
+        if getattr(self, "_dec_scratch_key", None) != key:
+            self._dec_scratch = (torch.zeros(2 * K, Lh, dtype=xn2d.dtype, device=xn2d.device),
+                                 torch.empty(B * d * 2, 2 * K, dtype=xn2d.dtype, device=xn2d.device),
+                                 torch.empty(B, nsign * K * d, dtype=xn2d.dtype, device=xn2d.device))
+            self._dec_scratch_key = key
+        PhiT, G, U = self._dec_scratch
+        ops.full_decode_prepare(xn2d, hist, phi, pos, PhiT)
+        ops.linear(hist.view(B * d * 2, Lh), PhiT, out=G)
+        ops.full_decode_combine(G, pos, U, B, d, K, nsign == 2, Lh, advance=True)
+        ops.linear(U, Mcat, resid=resid2d, out=out2d, epilogue=ops.EPI_RESID)
+        pos._host_t = t + 1
+        return hist, pos
 
     def add_to_residual(self, xn: torch.Tensor, x: torch.Tensor, entry=None, use_cache: bool = False):
         """x += STU(xn) for xn, x [B,T,d] (x contiguous).  Returns the cache entry when use_cache."""
+        if not self.use_approx:
+            return self.full_forward(xn, x, x, entry, use_cache)
         B, T, d = xn.shape
         MinT, taps, _ = self.prepared()
         t0 = 0
@@ -173,6 +266,10 @@ class STU(nn.Module):
         return hist, pos
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if not self.use_approx:
+            y = torch.empty(*x.shape[:2], self.d_out, dtype=x.dtype, device=x.device)
+            self.full_forward(x.contiguous(), None, y)
+            return y
         y = torch.zeros_like(x, memory_format=torch.contiguous_format)
         self.add_to_residual(x.contiguous(), y)
         return y

@@ -11,6 +11,7 @@ import torch
 from . import _lib
 
 EPI_STORE, EPI_RESID, EPI_GELU_MUL, EPI_HIST = 0, 1, 2, 3
+EPI_FLAG_CAUSAL = 0x100  # OR-ed into the epilogue: the weight is lower triangular
 BACKEND_AUTO, BACKEND_SIMT, BACKEND_TCGEN05, BACKEND_SKINNY = 0, 1, 2, 3
 RMS_EPS = float(torch.finfo(torch.float32).eps)  # what torch.nn.RMSNorm(eps=None) resolves to
 
@@ -117,7 +118,7 @@ def linear(x: torch.Tensor, W: torch.Tensor, *, W2: Optional[torch.Tensor] = Non
         N, w_rs, w_ks = W.shape[0], W.stride(0), W.stride(1)
     if W2 is not None:
         assert W2.shape == W.shape and W2.stride() == W.stride()
-    if epilogue == EPI_HIST:
+    if (epilogue & 0xff) == EPI_HIST:
         assert out is not None
         y_rs = 0
     else:
@@ -205,6 +206,58 @@ def decode_approx(x, norm_w, MinT, hist, taps, pos, out, eps: float = RMS_EPS, t
     _lib.check(rc, "stu_decode_approx")
     _count()
     return out
+
+
+def to_history(x, hist, t0: int):
+    """x [B,T,d] -> hist[b][c][t&1][t>>1] for t in [t0, t0+T)."""
+    _cuda(x, hist)
+    B, T, d = x.shape
+    assert hist.is_contiguous() and hist.shape[:3] == (B, d, 2) and x.stride(2) == 1
+    rc = _lib.load().stu_to_history(x.data_ptr(), x.stride(0), x.stride(1), hist.data_ptr(), B, d, hist.shape[3], t0,
+                                    t0 + T, _dt(x), _stream())
+    _lib.check(rc, "stu_to_history")
+    _count()
+
+
+def toeplitz(phi, k: int, out):
+    """out [3,S,S] <- the three Toeplitz matrices (even / odd->parity 1 / odd->parity 0) of filter column k."""
+    _cuda(phi, out)
+    L, K = phi.shape
+    assert phi.is_contiguous() and out.is_contiguous() and out.shape[0] == 3 and out.shape[1] == out.shape[2]
+    col = phi[:, k]
+    rc = _lib.load().stu_toeplitz(col.data_ptr(), K, L, out.data_ptr(), out.shape[1], out.shape[2], _dt(phi), _stream())
+    _lib.check(rc, "stu_toeplitz")
+    _count()
+
+
+def full_combine(E, Q, U, B: int, d: int, K: int, k: int, both_signs: bool, t0: int, t_end: int):
+    _cuda(E, Q, U)
+    assert E.shape == Q.shape and E.is_contiguous() and Q.is_contiguous() and U.stride(1) == 1
+    rc = _lib.load().stu_full_combine(E.data_ptr(), Q.data_ptr(), E.shape[1], U.data_ptr(), U.stride(0), B, d, K, k,
+                                      int(both_signs), t0, t_end, _dt(E), _stream())
+    _lib.check(rc, "stu_full_combine")
+    _count()
+
+
+def full_decode_prepare(x2d, hist, phi, pos, PhiT):
+    _cuda(x2d, hist, phi, pos, PhiT)
+    B, d, _, Lh = hist.shape
+    L, K = phi.shape
+    assert PhiT.shape == (2 * K, Lh) and PhiT.is_contiguous() and phi.is_contiguous() and x2d.stride(1) == 1
+    rc = _lib.load().stu_full_decode_prepare(x2d.data_ptr(), x2d.stride(0), hist.data_ptr(), phi.data_ptr(),
+                                             pos.data_ptr(), PhiT.data_ptr(), B, d, K, L, Lh,
+                                             status_word(x2d.device).data_ptr(), _dt(x2d), _stream())
+    _lib.check(rc, "stu_full_decode_prepare")
+    _count()
+
+
+def full_decode_combine(G, pos, U, B: int, d: int, K: int, both_signs: bool, Lh: int, advance: bool = True):
+    _cuda(G, pos, U)
+    assert G.stride(1) == 1 and U.is_contiguous()
+    rc = _lib.load().stu_full_decode_combine(G.data_ptr(), G.stride(0), pos.data_ptr(), U.data_ptr(), B, d, K,
+                                             int(both_signs), Lh, int(advance), _dt(G), _stream())
+    _lib.check(rc, "stu_full_decode_combine")
+    _count(2 if advance else 1)
 
 
 def swa_forward(qkv, k_ring, v_ring, pos, slopes, H: int, window: int, softcap: float, update_cache: bool):

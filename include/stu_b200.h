@@ -102,6 +102,34 @@ int stu_decode_approx(const void* x, long long x_row_stride, const void* norm_w,
  * 16-byte load at every position.  bf16, Lh % 8 == 0.  Derived data, no counterpart in the reference. */
 int stu_taps_rev8(const void* taps, void* taps8, int d, int Lh, int dtype, void* stream);
 
+/* ---- full STU variant (flash_stu/modules/stu.py:100-118, mini_stu/stu.py:240-269): U+-[b,t,k,i] =
+ * sum_j (+-1)^j phi[j,k] x[b,t-j,i] contracted with M_phi_plus / M_phi_minus.  The filters are shared by all
+ * channels, so per filter the convolution is three GEMMs (stu_linear with epilogue | 0x100 = lower-triangular
+ * weight) of history rows with Toeplitz matrices, combined into the token-major operand of the contraction. */
+
+/* x [B, t_end-t0, d] (token-major) -> history layout, times [t0, t_end). */
+int stu_to_history(const void* x, long long x_bstride, long long x_tstride, void* hist, int B, int d, int Lh, int t0,
+                   int t_end, int dtype, void* stream);
+
+/* out[kind][m][s], kind 0..2, S x S each with row pitch ld, from one filter column f[j*f_stride], j < L:
+ * kind 0: f[2(m-s)] (even taps); kind 1: f[2(m-s)+1] (odd taps feeding parity-1 outputs from parity-0 inputs);
+ * kind 2: f[2(m-s)-1] (odd taps feeding parity-0 outputs from parity-1 inputs); zero above the diagonal. */
+int stu_toeplitz(const void* f, long long f_stride, int L, void* out, int S, long long ld, int dtype, void* stream);
+
+/* U[(b,t-t0)][k*d+i] = E+Q and, with both_signs, U[..][(K+k)*d+i] = E-Q, for E,Q [B*d*2][ldE] in history row
+ * order (the even-tap and odd-tap products of filter k). */
+int stu_full_combine(const void* E, const void* Q, long long ldE, void* U, long long ldU, int B, int d, int K, int k,
+                     int both_signs, int t0, int t_end, int dtype, void* stream);
+
+/* One cached decode step of the full variant, around one GEMM G = hist_rows @ PhiT^T (stu_linear, M = B*d*2,
+ * N = 2K, K = Lh): prepare appends x_t at time pos[0] and rebuilds PhiT [2K][Lh] (time-reversed even / odd
+ * taps for that position); combine forms U+- [B][2*K*d] from G and (advance != 0) moves every position on.
+ * The reference has no cached STU step (flash_stu/layers/stu_layer.py:99-119). */
+int stu_full_decode_prepare(const void* x, long long x_row_stride, void* hist, const void* phi, const int* pos,
+                            void* PhiT, int B, int d, int K, int L, int Lh, int* status, int dtype, void* stream);
+int stu_full_decode_combine(const void* G, long long ldG, int* pos, void* U, int B, int d, int K, int both_signs,
+                            int Lh, int advance, int dtype, void* stream);
+
 /* Sliding-window attention for the Tn new tokens in qkv [B,Tn,3*H*hd] (c_attn output) against a ring
  * cache of W >= window+1 slots ([B][W][H*hd] each; token t in slot t % W), ALiBi slopes [H] (fp32) and tanh
  * soft-capping; out [B,Tn,H*hd] (heads merged, before c_proj).  update_cache=1 stores the new keys/values

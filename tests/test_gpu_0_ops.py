@@ -265,3 +265,88 @@ def test_sampling_matches_oracle():
             assert all(torch.isfinite(z[b, got[b]]) for b in range(B))
             if dt == torch.float32:
                 assert (got == want).float().mean() >= 0.8, (got, want)
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_full_variant_building_blocks(dt):
+    """to_history, the three Toeplitz matrices, the causal GEMM flag and the combine step against plain torch."""
+    from flash_stu_2_b200 import ops
+    torch.manual_seed(12)
+    B, T, d, K, L, t0 = 2, 301, 40, 5, 320, 0
+    S = ((T + 1) // 2 + 7) // 8 * 8
+    x = torch.randn(B, T, d).to(dt)
+    phi = (torch.randn(L, K) / 4).to(dt)
+    hist = torch.zeros(B, d, 2, S, dtype=dt, device=dev())
+    ops.to_history(x.to(dev()), hist, t0)
+    assert torch.equal(hist.cpu(), _hist_from(x, S))
+    Tz = torch.empty(3, S, S, dtype=dt, device=dev())
+    ops.toeplitz(phi.to(dev()), 3, Tz)
+    m = torch.arange(S)[:, None]
+    s_ = torch.arange(S)[None, :]
+    for kind, off in ((0, 0), (1, 1), (2, -1)):
+        j = 2 * (m - s_) + off
+        ok = (m >= s_) & (j >= 0) & (j < L)
+        want = torch.where(ok, phi[:, 3][j.clamp(0, L - 1)], torch.zeros((), dtype=dt))
+        assert torch.equal(Tz[kind].cpu(), want), kind
+    rows = hist.view(B * d * 2, S)
+    dense = ops.linear(rows, Tz[0], backend=0)
+    causal = ops.linear(rows, Tz[0], epilogue=ops.EPI_STORE | ops.EPI_FLAG_CAUSAL, backend=0)
+    ops.check_status()
+    assert rel(causal, dense) <= 1e-6
+    ref = (rows.cpu().double() @ Tz[0].cpu().double().t()).to(dt)
+    assert rel(causal, ref) <= TOL[dt] / 2
+    # E, Q -> U for one filter
+    E = torch.randn(B * d * 2, S).to(dt)
+    Q = torch.randn(B * d * 2, S).to(dt)
+    U = torch.zeros(B * T, 2 * K * d, dtype=dt, device=dev())
+    ops.full_combine(E.to(dev()), Q.to(dev()), U, B, d, K, 3, True, t0, T)
+    Ev = E.view(B, d, 2, S)
+    Qv = Q.view(B, d, 2, S)
+    want = torch.zeros(B, T, 2, K, d, dtype=dt)
+    for p in range(2):
+        n = (T - p + 1) // 2
+        want[:, p::2, 0, 3] = (Ev[:, :, p, :n].float() + Qv[:, :, p, :n].float()).to(dt).transpose(1, 2)
+        want[:, p::2, 1, 3] = (Ev[:, :, p, :n].float() - Qv[:, :, p, :n].float()).to(dt).transpose(1, 2)
+    assert torch.equal(U.cpu().view(B, T, 2, K, d), want)
+
+
+@pytest.mark.parametrize("name,tol", [("std_full_float32", 1e-3), ("std_full_bfloat16", 2e-2),
+                                       ("hankelL_full_float32", 1e-3), ("std_approx_float32", 1e-3),
+                                       ("std_approx_bfloat16", 2e-2)])
+def test_stu_operator_matches_reference_golden(golden, name, tol):
+    """STU.forward (operator output, no residual) against the reference module's own outputs."""
+    import flash_stu_2_b200 as F
+    from flash_stu_2_b200 import ops
+    r = golden("stu_modules")[name]
+    dt = r["x"].dtype
+    L, K = r["phi"].shape
+    d = r["x"].shape[2]
+    cfg = F.FlashSTUConfig(n_embd=d, seq_len=L, num_eigh=K, use_approx="_approx_" in name,
+                           use_hankel_L=name.startswith("hankelL"), torch_dtype=dt, n_layers=1, vocab_size=1)
+    m = F.STU(cfg, r["phi"].clone(), r["n"])
+    with torch.no_grad():
+        for k, v in r["params"].items():
+            getattr(m, k).copy_(v)
+    m = m.to(dev())
+    with torch.no_grad():
+        y = m(r["x"].to(dev()))
+        T = r["T_short"]
+        ys = m(r["x"][:, :T].contiguous().to(dev()))
+    ops.check_status()
+    assert rel(y, r["y_full"]) <= tol, rel(y, r["y_full"])
+    assert rel(ys, r["y_short"]) <= tol, rel(ys, r["y_short"])
+
+
+def test_mini_stu_spectral_matches_reference_golden(golden):
+    import flash_stu_2_b200 as F
+    from flash_stu_2_b200 import ops
+    r = golden("mini_stu")["spectral_fp32"]
+    L, K = r["phi"].shape
+    m = F.MiniSTU(seq_len=L, num_filters=K, input_dim=r["x"].shape[2], output_dim=r["y"].shape[2],
+                  precomputed_filters=r["phi"])
+    m.load_state_dict(r["params"])
+    m = m.to(dev())
+    with torch.no_grad():
+        y = m(r["x"].to(dev()))
+    ops.check_status()
+    assert rel(y, r["y"]) <= 1e-3, rel(y, r["y"])

@@ -15,6 +15,7 @@ def dev():
 
 
 def make_block(r, dt, approx=True):
+    approx = approx and not r.get("_full", False)
     import flash_stu_2_b200 as F
     cfg = F.FlashSTUConfig(n_embd=r["d"], seq_len=r["L"], num_eigh=r["K"], use_approx=approx, use_attn=False,
                            mlp_scale=4, torch_dtype=dt, n_layers=1, vocab_size=1, n_heads=1)
@@ -23,10 +24,13 @@ def make_block(r, dt, approx=True):
     return blk.to(dev()).eval()
 
 
-@pytest.mark.parametrize("name,tol", [("approx_float32", 1e-3), ("approx_bfloat16", 2e-2)])
+ALL_BLOCKS = [("approx_float32", 1e-3), ("approx_bfloat16", 2e-2), ("full_float32", 1e-3), ("full_bfloat16", 2e-2)]
+
+
+@pytest.mark.parametrize("name,tol", ALL_BLOCKS)
 def test_block_forward_matches_reference_golden(golden, name, tol):
     from flash_stu_2_b200 import ops
-    r = golden("blocks")[name]
+    r = dict(golden("blocks")[name], _full=name.startswith("full"))
     dt = r["x"].dtype
     blk = make_block(r, dt)
     x = r["x"].clone().to(dev())
@@ -38,11 +42,11 @@ def test_block_forward_matches_reference_golden(golden, name, tol):
     assert err <= tol, err
 
 
-@pytest.mark.parametrize("name,tol", [("approx_float32", 1e-3), ("approx_bfloat16", 2e-2)])
+@pytest.mark.parametrize("name,tol", ALL_BLOCKS)
 def test_block_cached_decode_equals_prefill_rows(golden, name, tol):
     """prefill T1 tokens with a cache, then single-token steps: every row equals the full forward."""
     from flash_stu_2_b200 import ops
-    r = golden("blocks")[name]
+    r = dict(golden("blocks")[name], _full=name.startswith("full"))
     dt = r["x"].dtype
     blk = make_block(r, dt)
     x = r["x"].to(dev())

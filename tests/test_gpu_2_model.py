@@ -27,7 +27,7 @@ def build(r, tmp_path):
     return m.to(dev()).eval()
 
 
-@pytest.mark.parametrize("name", ["stu_only_approx_fp32", "hybrid_approx_fp32", "hybrid_approx_bf16"])
+@pytest.mark.parametrize("name", ["stu_only_approx_fp32", "stu_only_full_fp32", "hybrid_approx_fp32", "hybrid_approx_bf16"])
 def test_logits_match_reference(golden, tmp_path, name):
     from flash_stu_2_b200 import ops
     r = golden("models")[name]
@@ -42,7 +42,7 @@ def test_logits_match_reference(golden, tmp_path, name):
     assert O.rel_err(short, r["logits_short"]) <= tol
 
 
-@pytest.mark.parametrize("name", ["stu_only_approx_fp32", "hybrid_approx_fp32"])
+@pytest.mark.parametrize("name", ["stu_only_approx_fp32", "stu_only_full_fp32", "hybrid_approx_fp32"])
 def test_greedy_generate_is_token_exact(golden, tmp_path, name):
     """fp32 greedy decoding with the cache reproduces the reference's no-cache loop token for token."""
     from flash_stu_2_b200 import ops

@@ -34,9 +34,9 @@ def test_filters_match_oracle_and_roundtrip(tmp_path):
 
 def test_state_dict_keys_match_reference(tmp_path, golden):
     g = golden("models")
-    for name in ("stu_only_approx_fp32", "hybrid_approx_fp32"):
+    for name in ("stu_only_approx_fp32", "hybrid_approx_fp32", "stu_only_full_fp32"):
         r = g[name]
-        m = F.FlashSTU(_cfg(str(tmp_path), use_attn=r["cfg"]["use_attn"]))
+        m = F.FlashSTU(_cfg(str(tmp_path), use_attn=r["cfg"]["use_attn"], use_approx=r["cfg"]["use_approx"]))
         assert set(m.state_dict().keys()) == set(r["sd"].keys())
         m.load_state_dict(r["sd"])
         assert m.tok_emb.weight is m.lm_head.weight
@@ -57,8 +57,7 @@ def test_layer_alternation_and_alibi(tmp_path, golden):
 
 
 def test_unsupported_switches_fail_loudly(tmp_path):
-    for kw in (dict(use_approx=False), dict(use_hankel_L=True), dict(d_in_tile=16), dict(stu_enable_mlp_sandwich=True),
-               dict(bias=True)):
+    for kw in (dict(use_hankel_L=True), dict(d_in_tile=16), dict(stu_enable_mlp_sandwich=True), dict(bias=True)):
         with pytest.raises(NotImplementedError):
             F.FlashSTU(_cfg(str(tmp_path), use_attn=False, **kw))
 
