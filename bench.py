@@ -374,7 +374,7 @@ def run_b200(a):
                     "tflops_algorithmic": pre_tflops,
                     "frac_of_tensor_peak": pre_tflops / pk["bf16_tflops_sustained"],
                     "peak_tflops": pk["bf16_tflops_sustained"], "peak_source": pk["source"] + " (sustained)"},
-        "roofline": {"bound": "hbm", "kernel": "stu_decode_mma_kernel", "achieved": achieved, "peak": pk["hbm_gbs"],
+        "roofline": {"bound": "hbm", "kernel": "stu_decode_diag_kernel", "achieved": achieved, "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "peak_source": pk["source"],
                      "bytes_per_launch": kern_bytes, "us_per_launch": kern_ms * 1e3, "traffic": None},
         "e2e": {"value": world * B * S * e2e_steps / dec_s, "unit": "tokens/s",

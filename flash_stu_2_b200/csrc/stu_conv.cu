@@ -15,6 +15,8 @@
 //   transpose_add_kernel x[b,t,c] += yT[b][c][t&1][t>>1]   (residual add, back to token-major)
 //   stu_decode_kernel    one fused decode step: RMSNorm + M_inputs row + history append + tap dot +
 //                        residual, one warp per (sequence, channel)
+#include <stdlib.h>
+
 #include "common.cuh"
 
 // ------------------------------------------------------------------------------------------------
@@ -558,227 +560,118 @@ __global__ void __launch_bounds__(256) stu_decode_kernel(const T* __restrict__ x
 }
 
 // ------------------------------------------------------------------------------------------------
-// Tensor-core form of the fused decode step (bf16).  The CUDA-core kernel above spends ~26 instructions
-// per 16 bytes of history (unpack, convert, FMA) and is issue-bound at a third of the HBM rate.  Here the
-// tap dot products of the eight sequences of a group are one skinny matrix product per channel,
-//   y[b] = sum_i H[b][i] * tap[s - i],   A = H (8 rows x k), B = the taps broadcast to all 8 columns,
-// issued as mma.sync m16n8k16: a lane feeds each 16-byte history load straight into two MMAs.  The taps
-// come from a table that is stored reversed and in all eight 16-byte alignments (taps8[e][c][Lh+8],
-// taps8[e][c][u] = tap[Lh-1-(u+e)]), so the B fragments are aligned 16-byte pieces as well.  Both streams
-// go through a 12-deep per-lane cp.async ring.  The RMSNorm + M_inputs projection of the new token is a
-// second small MMA.
-// One CTA = 4 channels x 8 sequences; warps (2c, 2c+1) split the time range of channel c.
-// Positions that differ inside a group of 8 sequences take a scalar path (same results, slower).
-constexpr int DM_CPB = 4;
-constexpr int DM_NS = 12;  // depth of the per-lane cp.async ring (16-byte history + 16-byte tap vector per slot)
+// Tensor-core form of the fused decode step (bf16).  The CUDA-core kernel above spends ~26 instructions per 16
+// bytes of history (unpack, convert, FMA) and is issue-bound.  Here one warp owns one (sequence, channel) and
+// streams that row's history and the channel's reversed taps as whole 512-byte runs (16 bytes per lane per
+// instruction, full cache lines).  The dot product of a 256-element run is taken on the tensor cores as the
+// DIAGONAL of a 16x16 product: the lane's four history words are the A fragment of mma.sync m16n8k16 (any
+// fixed assignment of memory positions to (row, k) slots will do, as long as the taps use the same one), the
+// taps words 0/2 and 1/3 are the B fragments of the two n-tiles, and sum_r D[r][r] is the dot product.  That is
+// two MMAs per 16-byte load, with the access pattern of the CUDA-core kernel (one contiguous run per warp).
+// The taps come from a table stored reversed and in all eight 16-byte alignments (taps8[e][c][Lh+8],
+// taps8[e][c][u] = tap[Lh-1-(u+e)]), so the tap operand is an aligned 16-byte load at every position.
+// Ragged positions need no special case: every warp has its own position and tap alignment.
+constexpr int DD_U = 4;  // 512-byte runs of history (and of taps) a warp keeps in flight
 
-// Each lane streams exactly the 16-byte pieces its own MMA fragments need, so the ring lives in shared
-// memory as private per-lane slots filled by cp.async: no registers are tied up by loads in flight, no
-// scoreboard serialises them, and completion is tracked per lane with cp.async.wait_group.
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
-               "l"(gmem_src)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-
-__global__ void __launch_bounds__(256) stu_decode_mma_kernel(const bf16* __restrict__ x, long long x_rstride,
-                                                             const bf16* __restrict__ norm_w,
-                                                             const bf16* __restrict__ MinT, bf16* __restrict__ hist,
-                                                             const bf16* __restrict__ taps8, int* __restrict__ pos,
-                                                             bf16* __restrict__ out, long long out_rstride, int B,
-                                                             int d, int Lh, float eps, int* __restrict__ status) {
-  __shared__ float s_r[8];
-  __shared__ float s_proj[8][8][DM_CPB];
-  __shared__ float s_xp[8][DM_CPB];
-  __shared__ float s_acc[8][8];
-  extern __shared__ __align__(16) uint4 dm_ring[];  // [warp][slot][2][lane]
-  const int c0 = blockIdx.x * DM_CPB, b0 = blockIdx.y * 8;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, q = lane & 3;
-  const int LP = Lh + 8;  // row pitch of taps8
-  uint4* ring = dm_ring + (size_t)warp * DM_NS * 64 + lane;
-  // ---- positions of the group; uniform groups take the tensor-core path
-  const int tg = pos[2 * b0];
-  bool uniform = true, bad = false;
-#pragma unroll
-  for (int w = 0; w < 8; w++) {
-    if (b0 + w < B) {
-      const int tw = pos[2 * (b0 + w)];
-      uniform = uniform && (tw == tg);
-      bad = bad || (tw < 0 || tw >= 2 * Lh);
-    }
+__global__ void __launch_bounds__(256, 4) stu_decode_diag_kernel(const bf16* __restrict__ x, long long x_rstride,
+                                                              const bf16* __restrict__ norm_w,
+                                                              const bf16* __restrict__ MinT, bf16* __restrict__ hist,
+                                                              const bf16* __restrict__ taps8, int* __restrict__ pos,
+                                                              bf16* __restrict__ out, long long out_rstride, int B,
+                                                              int d, int Lh, float eps, int* __restrict__ status) {
+  const int c = blockIdx.x, b = blockIdx.y * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+  const int LP = Lh + 8;
+  bool run = b < B;
+  int t = run ? pos[2 * b] : 0;
+  if (run && (t < 0 || t >= 2 * Lh)) {
+    if (lane == 0 && status) atomicExch(status, 2);
+    run = false;
   }
-  if (bad) {
-    if (threadIdx.x == 0 && status) atomicExch(status, 2);
-  } else {
-    // ---- row statistics (warp w -> sequence b0 + w), shared through s_r
-    {
-      const int b = b0 + warp;
-      float r = 0.f;
-      if (b < B) {
-        const bf16* xr = x + (size_t)b * x_rstride;
-        float ss = 0.f;
-        for (int k = lane * 8; k < d; k += 256) {
-          float v[8];
-          load_vec(xr + k, v);
-#pragma unroll
-          for (int j = 0; j < 8; j++) ss += v[j] * v[j];
-        }
-        ss = warp_sum(ss);
-        r = rsqrtf(ss / (float)d + eps);
-      }
-      if (lane == 0) s_r[warp] = r;
-    }
-    const int cc = warp >> 1, half = warp & 1;
-    const int c = c0 + cc;
-    const int brow = b0 + g;
-    const bool rowvalid = brow < B;
-    // uniform path state
-    const int p = tg & 1, s = tg >> 1;
+  if (run) {
+    const int p = t & 1, s = t >> 1;
+    bf16* hrow = hist + ((size_t)((size_t)b * d + c) * 2 + p) * Lh;
     const int o = Lh - 1 - s, e = o & 7;
-    const bf16* hrow = hist + ((size_t)((size_t)(rowvalid ? brow : b0) * d + c) * 2 + p) * Lh;
-    const bf16* tbase = taps8 + ((size_t)e * d + c) * LP + (o - e);
-    // chunks of 32 history elements that lie entirely before the new element are split between the two warps of
-    // the channel and streamed through the cp.async ring; one group is committed per chunk slot (empty once
-    // the range is exhausted) so that wait_group<DM_NS-1> always means "the oldest slot has landed".  The (at
-    // most one) partial chunk is handled after the loop with element masks.
-    const int nfull = s >> 5;
-    const int hmid = (nfull + 1) >> 1;
-    const int cb0 = half ? hmid : 0;
-    const int nmine = (half ? nfull : hmid) - cb0;
-    const bf16* hp = hrow + ((size_t)cb0 << 5) + 8 * q;
-    const bf16* tp = tbase + ((size_t)cb0 << 5) + 8 * q;
-    if (uniform) {
+    const bf16* trow = taps8 + ((size_t)e * d + c) * LP + (o - e);  // trow[i] = tap[s - i], 16-byte aligned
+    const int nfull = s >> 8;                                        // complete 256-element runs before s
+    uint4 hv[DD_U], tv[DD_U];
 #pragma unroll
-      for (int u = 0; u < DM_NS - 1; u++) {
-        if (u < nmine) {
-          cp_async16(ring + u * 64, hp + 32 * u);
-          cp_async16(ring + u * 64 + 32, tp + 32 * u);
-        }
-        cp_async_commit();
+    for (int u = 0; u < DD_U; u++) {
+      if (u < nfull) {
+        hv[u] = ldg_nc_v4(hrow + (u << 8) + 8 * lane);
+        tv[u] = ldg_nc_v4(trow + (u << 8) + 8 * lane);
       }
     }
-    __syncthreads();
-    // ---- projection of the new token: xp[b][cc] = round(sum_k round(x*r*w)[b][k] * MinT[c0+cc][k]) as MMAs,
-    //      K split over the eight warps
-    {
-      float accp[4] = {0.f, 0.f, 0.f, 0.f};
-      const float rg = s_r[g];
-      const bf16* xr = x + (size_t)(rowvalid ? brow : b0) * x_rstride;
-      const bf16* mr = MinT + (size_t)((g < DM_CPB && c0 + g < d) ? c0 + g : c0) * d;
-      const bool mvalid = (g < DM_CPB) && (c0 + g < d);
-      for (int k0 = warp * 32; k0 < d; k0 += 256) {  // k0 is warp-uniform: every lane reaches the MMAs
-        const int k = k0 + 8 * q;
-        const bool kok = (k + 8 <= d);  // lanes past the end of a partial chunk contribute zeros
-        uint32_t a[4] = {0u, 0u, 0u, 0u};
-        uint4 mv = make_uint4(0, 0, 0, 0);
-        if (kok) {
-          float xv[8], wv[8];
-          load_vec(xr + k, xv);
-          load_vec(norm_w + k, wv);
-          if (mvalid) mv = *reinterpret_cast<const uint4*>(mr + k);
-          if (rowvalid) {
+    // ---- RMSNorm statistic of row b and the projection onto channel c (overlaps the loads above)
+    const bf16* xr = x + (size_t)b * x_rstride;
+    float ss = 0.f;
+    for (int k = lane * 8; k < d; k += 256) {
+      float v[8];
+      load_vec(xr + k, v);
 #pragma unroll
-            for (int j = 0; j < 4; j++)
-              a[j] = pack_bf16x2(xv[2 * j] * rg * wv[2 * j], xv[2 * j + 1] * rg * wv[2 * j + 1]);
+      for (int j = 0; j < 8; j++) ss += v[j] * v[j];
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / (float)d + eps);
+    const bf16* mrow = MinT + (size_t)c * d;
+    float dot = 0.f;
+    for (int k = lane * 8; k < d; k += 256) {
+      float v[8], gw[8], m[8];
+      load_vec(xr + k, v);
+      load_vec(norm_w + k, gw);
+      load_vec(mrow + k, m);
+#pragma unroll
+      for (int j = 0; j < 8; j++) dot = fmaf(round_to<bf16>(v[j] * r * gw[j]), m[j], dot);
+    }
+    dot = warp_sum(dot);
+    const float xp = round_to<bf16>(dot);
+    if (lane == 0) hrow[s] = __float2bfloat16_rn(xp);
+    // ---- tap dot product over the stored history [0, s)
+    float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int j0 = 0; j0 < nfull; j0 += DD_U) {
+      if (j0) {
+#pragma unroll
+        for (int u = 0; u < DD_U; u++) {
+          if (j0 + u < nfull) {
+            hv[u] = ldg_nc_v4(hrow + ((j0 + u) << 8) + 8 * lane);
+            tv[u] = ldg_nc_v4(trow + ((j0 + u) << 8) + 8 * lane);
           }
         }
-        mma_bf16(accp, a[0], 0u, a[1], 0u, mv.x, mv.y);
-        mma_bf16(accp, a[2], 0u, a[3], 0u, mv.z, mv.w);
       }
-      if (q < 2) {  // columns 2q, 2q+1 are channels c0+2q, c0+2q+1
-        s_proj[warp][g][2 * q] = accp[0];
-        s_proj[warp][g][2 * q + 1] = accp[1];
-      }
-    }
-    __syncthreads();
-    if (threadIdx.x < 32) {
-      const int row = threadIdx.x >> 2, ch = threadIdx.x & 3;
-      float sum = 0.f;
 #pragma unroll
-      for (int w = 0; w < 8; w++) sum += s_proj[w][row][ch];
-      const float xpv = round_to<bf16>(sum);
-      s_xp[row][ch] = xpv;
-      const int b = b0 + row;
-      if (b < B && c0 + ch < d) {
-        const int tb = pos[2 * b];
-        hist[((size_t)((size_t)b * d + c0 + ch) * 2 + (tb & 1)) * Lh + (tb >> 1)] = __float2bfloat16_rn(xpv);
-      }
-    }
-    // ---- tap dot products over the stored history [0, s)
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    if (uniform) {
-      for (int j = 0; j < nmine; j++) {
-        const int jn = j + DM_NS - 1;
-        if (jn < nmine) {
-          const int slot = jn % DM_NS;
-          cp_async16(ring + slot * 64, hp + 32 * jn);
-          cp_async16(ring + slot * 64 + 32, tp + 32 * jn);
+      for (int u = 0; u < DD_U; u++) {
+        if (j0 + u < nfull) {  // warp-uniform
+          mma_bf16(acc0, hv[u].x, hv[u].y, hv[u].z, hv[u].w, tv[u].x, tv[u].z);
+          mma_bf16(acc1, hv[u].x, hv[u].y, hv[u].z, hv[u].w, tv[u].y, tv[u].w);
         }
-        cp_async_commit();
-        cp_async_wait<DM_NS - 1>();
-        const int slot = j % DM_NS;
-        const uint4 a = ring[slot * 64], t = ring[slot * 64 + 32];
-        // rows past the batch read a valid row's data; their accumulator rows are never stored
-        mma_bf16(acc, a.x, 0u, a.y, 0u, t.x, t.y);
-        mma_bf16(acc, a.z, 0u, a.w, 0u, t.z, t.w);
       }
-      cp_async_wait<0>();
-      if (half == 1 && (s & 31)) {  // partial chunk: elements [32*nfull, s)
-        const int iv = (nfull << 5) + 8 * q;
-        uint32_t a[4] = {0u, 0u, 0u, 0u};
-        uint4 t = make_uint4(0, 0, 0, 0);
-        if (iv < s) {
-          const uint4 raw = ldg_nc_v4(hrow + iv);
-          t = ldg_nc_v4(tbase + iv);
-          a[0] = raw.x; a[1] = raw.y; a[2] = raw.z; a[3] = raw.w;
-          const int keep = s - iv;  // elements of this vector that lie before the new one
-          if (keep < 8) {
+    }
+    if (s & 255) {  // last, partial run: elements [256*nfull, s)
+      const int i0 = (nfull << 8) + 8 * lane;
+      const int keep = s - i0;
+      uint32_t a[4] = {0u, 0u, 0u, 0u};
+      uint4 tt = make_uint4(0, 0, 0, 0);
+      if (keep > 0) {
+        const uint4 raw = ldg_nc_v4(hrow + i0);
+        tt = ldg_nc_v4(trow + i0);
+        a[0] = raw.x; a[1] = raw.y; a[2] = raw.z; a[3] = raw.w;
+        if (keep < 8) {
 #pragma unroll
-            for (int jj = 0; jj < 4; jj++) {
-              if (2 * jj + 1 >= keep) a[jj] = (2 * jj < keep) ? (a[jj] & 0x0000ffffu) : 0u;
-            }
+          for (int jj = 0; jj < 4; jj++) {
+            if (2 * jj + 1 >= keep) a[jj] = (2 * jj < keep) ? (a[jj] & 0x0000ffffu) : 0u;
           }
         }
-        mma_bf16(acc, a[0], 0u, a[1], 0u, t.x, t.y);
-        mma_bf16(acc, a[2], 0u, a[3], 0u, t.z, t.w);
       }
-      if (q == 0) s_acc[warp][g] = acc[0];
-    } else {
-      // scalar path: each warp pair still owns channel c; lanes stride over the history of each row
-      for (int row = half; row < 8; row += 2) {
-        const int b = b0 + row;
-        float a = 0.f;
-        if (b < B) {
-          const int tb = pos[2 * b], pb = tb & 1, sb = tb >> 1;
-          const bf16* hr = hist + ((size_t)((size_t)b * d + c) * 2 + pb) * Lh;
-          const bf16* t0p = taps8 + (size_t)c * LP;  // alignment 0: taps8[0][c][u] = tap[Lh-1-u]
-          for (int i = lane; i < sb; i += 32)
-            a = fmaf(__bfloat162float(hr[i]), __bfloat162float(t0p[Lh - 1 - (sb - i)]), a);
-          a = warp_sum(a);
-        }
-        if (lane == 0) s_acc[2 * cc][row] = a, s_acc[2 * cc + 1][row] = 0.f;
-      }
+      mma_bf16(acc0, a[0], a[1], a[2], a[3], tt.x, tt.z);
+      mma_bf16(acc1, a[0], a[1], a[2], a[3], tt.y, tt.w);
     }
-    __syncthreads();
-    if (threadIdx.x < 32) {
-      const int row = threadIdx.x >> 2, ch = threadIdx.x & 3;
-      const int b = b0 + row, cch = c0 + ch;
-      if (b < B && cch < d) {
-        const float tap0 = __bfloat162float(taps8[(size_t)cch * LP + (Lh - 1)]);
-        const float sum = s_acc[2 * ch][row] + s_acc[2 * ch + 1][row] + s_xp[row][ch] * tap0;
-        const float y = round_to<bf16>(2.f * sum);
-        const float xv = __bfloat162float(x[(size_t)b * x_rstride + cch]);
-        out[(size_t)b * out_rstride + cch] = __float2bfloat16_rn(xv + y);
-      }
+    // diagonal: D0[g][g] sits in lane (g, q = g/2) register g&1; D1[g+8][g] in the same lane, register 2+(g&1)
+    float part = (q == (g >> 1)) ? ((g & 1) ? (acc0[1] + acc1[3]) : (acc0[0] + acc1[2])) : 0.f;
+    part = warp_sum(part);
+    if (lane == 0) {
+      const float tap0 = __bfloat162float(taps8[(size_t)c * LP + (Lh - 1)]);
+      const float y = round_to<bf16>(2.f * fmaf(xp, tap0, part));
+      out[(size_t)b * out_rstride + c] = __float2bfloat16_rn(__bfloat162float(xr[c]) + y);
     }
   }
   // ---- arrival counter: the last CTA advances the positions
@@ -831,14 +724,10 @@ extern "C" int stu_decode_approx(const void* x, long long x_row_stride, const vo
     if (d % 8 || Lh % 8 || x_row_stride % 8 || !aligned16(x) || !aligned16(MinT) || !aligned16(hist) ||
         !aligned16(norm_w) || !aligned16(taps8))
       return STU_ERR_ALIGN;
-    dim3 gm((d + DM_CPB - 1) / DM_CPB, (B + 7) / 8);
-    const size_t ring_bytes = (size_t)8 * DM_NS * 64 * sizeof(uint4);
-    cudaError_t ea = cudaFuncSetAttribute(stu_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)ring_bytes);
-    if (ea != cudaSuccess) return (int)ea;
-    stu_decode_mma_kernel<<<gm, 256, ring_bytes, st>>>((const bf16*)x, x_row_stride, (const bf16*)norm_w, (const bf16*)MinT,
-                                              (bf16*)hist, (const bf16*)taps8, pos, (bf16*)out, out_row_stride, B,
-                                              d, Lh, eps, status);
+    dim3 gd(d, (B + 7) / 8);
+    stu_decode_diag_kernel<<<gd, 256, 0, st>>>((const bf16*)x, x_row_stride, (const bf16*)norm_w, (const bf16*)MinT,
+                                               (bf16*)hist, (const bf16*)taps8, pos, (bf16*)out, out_row_stride, B, d,
+                                               Lh, eps, status);
     STU_CHECK_LAUNCH();
     return STU_OK;
   }

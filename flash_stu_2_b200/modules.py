@@ -24,16 +24,24 @@ def new_pos(batch: int, device) -> torch.Tensor:
     """[B,2] int32: column 0 = tokens cached so far, column 1 (row 0) = arrival counter used by kernels."""
     p = torch.zeros(batch, 2, dtype=torch.int32, device=device)
     p._host_t = 0
+    p._uniform = True
     return p
 
 
 def host_pos(pos: torch.Tensor) -> int:
-    """Host-side mirror of pos[0,0]; falls back to a device read when the tensor was re-created."""
+    """Host-side mirror of pos[0,0]; falls back to a device read when the tensor was re-created
+    (e.g. by _reorder_cache), which also re-checks whether all sequences share one position."""
     t = getattr(pos, "_host_t", None)
     if t is None:
-        t = int(pos[0, 0].item())
+        col = pos[:, 0].tolist()
+        t = int(col[0])
         pos._host_t = t
+        pos._uniform = all(v == t for v in col)
     return t
+
+
+def uniform_pos(pos: torch.Tensor) -> bool:
+    return getattr(pos, "_uniform", False)
 
 
 class RMSNorm(nn.Module):
@@ -261,7 +269,8 @@ class STU(nn.Module):
         t = host_pos(pos)
         if t + 1 > self.seq_len:
             raise ValueError(f"sequence position {t + 1} exceeds seq_len={self.seq_len}")
-        ops.decode_approx(x2d, norm_w, MinT, hist, taps, pos, out2d, eps, taps8=taps8 if STU.tensor_core_decode else None)
+        ops.decode_approx(x2d, norm_w, MinT, hist, taps, pos, out2d, eps,
+                          taps8=taps8 if STU.tensor_core_decode else None)
         pos._host_t = t + 1
         return hist, pos
 

@@ -92,7 +92,8 @@ int stu_conv_prefill_approx_static(const void* hist, const void* taps, void* x, 
  * cache, flash_stu/layers/stu_layer.py:99-119); the result equals row t of the full-prefix forward of
  * flash_stu/layers/stu_layer.py:78-93.  out must not alias x.
  * taps8 (bf16 only, may be NULL) is the table made by stu_taps_rev8; with it the step runs on mma.sync tensor
- * cores (8 sequences x 4 channels per CTA), without it on CUDA cores (one warp per sequence and channel). */
+ * cores, without it on CUDA cores (one warp per sequence and channel).
+ */
 int stu_decode_approx(const void* x, long long x_row_stride, const void* norm_w, const void* MinT, void* hist,
                       const void* taps, const void* taps8, int* pos, void* out, long long out_row_stride, int B,
                       int d, int Lh, float eps, int* status, int dtype, void* stream);

@@ -157,7 +157,7 @@ def _decode_fixture(dt, B, T, d, L, seed=6):
 
 
 @pytest.mark.parametrize("dt,tc", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
-@pytest.mark.parametrize("shape", [(3, 45, 64, 64), (9, 70, 40, 160)])
+@pytest.mark.parametrize("shape", [(3, 45, 64, 64), (9, 70, 40, 160), (10, 300, 256, 600)])
 def test_decode_step_equals_prefill_row(dt, tc, shape):
     """S3: the fused decode kernel at time t reproduces row t of the full-prefix layer half
     (CUDA-core kernel and, for bf16, the tensor-core kernel fed by the reversed tap table)."""
