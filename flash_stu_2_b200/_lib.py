@@ -45,6 +45,8 @@ _SIGNATURES = {
     "stu_full_combine": ([_P, _P, _LL, _P, _LL, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P], c_int),
     "stu_full_decode_prepare": ([_P, _LL, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P], c_int),
     "stu_full_decode_combine": ([_P, _LL, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P], c_int),
+    "stu_lds_final_state": ([_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P], c_int),
+    "stu_lds_decode_features": ([_P, _LL, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P], c_int),
     "stu_swa_forward": ([_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                          _P], c_int),
     "stu_sample": ([_P, _LL, c_int, c_int, c_float, c_int, c_float, c_int, _P, _P, _LL, _P, c_int, _P], c_int),

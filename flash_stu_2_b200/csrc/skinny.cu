@@ -52,10 +52,8 @@ __device__ __forceinline__ uint4 norm_pack(const uint4& raw, float r, const uint
 // no shuffle or shared-memory staging is needed.  All loads of a round (U chunks) are issued before any
 // is used; with NORM the row statistics are computed while they are in flight.
 //   MT   16-row activation tiles (M <= 16*MT);  LOW8: M <= 8, the upper half-tile is implicit zeros
-// For the up-to-8-row shapes the register cap buys a single wave of CTAs (e.g. 512 CTAs of 256 threads at
-// 4 per SM), which matters more for these few-microsecond kernels than a handful of spilled values.
 template <int EPI, int MT, bool LOW8, bool NORM, int U, int NW>
-__global__ void __launch_bounds__(NW * 32, (LOW8 && MT == 1) ? (NW == 8 ? 4 : 2) : 1) skinny_bf16_kernel(const bf16* __restrict__ x, long long lda,
+__global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __restrict__ x, long long lda,
                                                               const bf16* __restrict__ W, long long ldb,
                                                               const bf16* __restrict__ W2, int M, int N, int K,
                                                               EpiArgs<bf16> ep, const bf16* __restrict__ nw,

@@ -1,15 +1,45 @@
 """MiniSTU (mini_stu/stu.py:12-275): the bare full-variant spectral transform with its own input and
 output widths, same constructor signature and parameter names (M_phi_plus, M_phi_minus) as the reference.
-The spectral backend runs on the kernels of the full STU variant; the distilled-LDS backend and the
-optional post-MLP are not built here yet and raise."""
+The spectral backend runs on the kernels of the full STU variant.  The distilled-LDS backend
+(mini_stu/stu_lds.py:213-394) produces prefill outputs through the same kernels, as the causal convolution with
+the LDS impulse responses, and decodes with a recurrent float64 state; forward() takes the optional
+`past_key_value` / `use_cache` pair for that (the reference has no cached call).  The optional post-MLP is not
+part of this implementation and raises."""
+import os
 from types import SimpleNamespace
 from typing import Optional
 
 import torch
 import torch.nn as nn
 
+from . import ops
 from .filters import get_spectral_filters, nearest_power_of_two
-from .modules import STU
+from .modules import STU, new_pos, host_pos
+
+LDS_PARAMS = os.path.join(os.path.dirname(os.path.abspath(__file__)), "data", "lds_params.pt")
+
+
+class FixedDiagonalLDS(nn.Module):
+    """Buffers of the distilled diagonal LDS (mini_stu/stu_lds.py:213-252): A, B_vec, h0 float64, C model dtype."""
+
+    def __init__(self, A, B_vec, C, h0):
+        super().__init__()
+        self.register_buffer("A", A.detach().clone())
+        self.register_buffer("B_vec", B_vec.detach().clone())
+        self.register_buffer("C", C.detach().clone())
+        self.register_buffer("h0", h0.detach().clone())
+
+
+class DistillSTUFast(nn.Module):
+    """Holder of the learned contraction M [n_filters, d_in, d_out] (mini_stu/stu_lds.py:344-377)."""
+
+    def __init__(self, lds, K, d_in, d_out, dtype):
+        super().__init__()
+        self.lds = lds
+        self.K, self.d_in, self.d_out = K, d_in, d_out
+        self.n_filters = 2 * K
+        self.M = nn.Parameter(torch.randn(self.n_filters, d_in, d_out, dtype=dtype, device=lds.A.device)
+                              / (self.n_filters * d_in) ** 0.5)
 
 
 class MiniSTU(nn.Module):
@@ -32,14 +62,30 @@ class MiniSTU(nn.Module):
         backend: str = "spectral",
     ):
         super().__init__()
-        if backend != "spectral":
-            raise NotImplementedError("MiniSTU(backend='lds') has no kernel here yet")
+        if backend not in ("spectral", "lds"):
+            raise ValueError(f"unknown backend {backend!r}")
         if use_mlp:
             raise NotImplementedError("MiniSTU(use_mlp=True) (plain post-MLP) is not part of this implementation")
         self.seq_len, self.num_filters = seq_len, num_filters
         self.input_dim, self.output_dim = input_dim, output_dim
         self.use_hankel_L, self.use_mlp, self.dtype, self.backend = use_hankel_L, use_mlp, dtype, backend
         self.device = device or torch.device("cpu")
+        if backend == "lds":
+            assert not use_hankel_L, "LDS backend requires use_hankel_L=False"
+            assert num_filters == 24, "LDS backend requires num_filters=24"
+            raw = torch.load(os.environ.get("STU_B200_LDS_PARAMS", LDS_PARAMS), map_location="cpu", weights_only=False)
+            raw = raw.get("model_state_dict", raw)
+            A = raw["A"].to(dtype=torch.float64, device=self.device)
+            Bv = raw["B"].to(dtype=torch.float64, device=self.device).flatten()
+            C = raw["C"].to(dtype=dtype, device=self.device)
+            h0 = raw["h0"].to(dtype=torch.float64, device=self.device)
+            self.lds_module = FixedDiagonalLDS(A, Bv, C, h0)
+            self.distill_stu = DistillSTUFast(self.lds_module, num_filters, input_dim, output_dim, dtype)
+            self.n = nearest_power_of_two(seq_len * 2 - 1, round_up=True)
+            self.mlp = None
+            self._lds_key = None
+            object.__setattr__(self, "_op", None)
+            return
         if precomputed_filters is not None:
             phi = precomputed_filters.to(self.device, dtype)
         else:
@@ -65,10 +111,65 @@ class MiniSTU(nn.Module):
             inner.M_phi_minus = self.M_phi_minus
         object.__setattr__(self, "_op", inner)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    # ------------------------------------------------------------------ LDS backend
+    def _lds_prepared(self):
+        """Impulse responses G[j,f] = sum_n C[n,f] B[n] A[n]^j (float64 on the host, rounded once to the model
+        dtype), wrapped as the filters of a single-branch full-variant operator whose M_phi is `distill_stu.M`."""
+        lds, M = self.lds_module, self.distill_stu.M
+        key = (lds.A._version, lds.B_vec._version, lds.C._version, lds.h0._version, M.data_ptr(), lds.C.data_ptr())
+        if self._lds_key != key:
+            if float(lds.h0.abs().max()) != 0.0:
+                raise NotImplementedError("a non-zero initial LDS state h0 has no kernel here")
+            A, Bv, C = lds.A.double().cpu(), lds.B_vec.double().cpu(), lds.C.double().cpu()
+            j = torch.arange(self.seq_len, dtype=torch.float64)
+            G = ((A[None, :] ** j[:, None]) * Bv[None, :]) @ C          # [L, F]
+            F_ = C.shape[1]
+            cfg = SimpleNamespace(num_eigh=F_, n_embd=self.input_dim, use_hankel_L=True, use_approx=False,
+                                  torch_dtype=self.dtype, d_in_tile=None, d_out_tile=None)
+            op = STU(cfg, G.to(device=M.device, dtype=self.dtype), self.n)
+            op.d_out = self.output_dim
+            del op.M_phi_plus
+            op.M_phi_plus = M
+            object.__setattr__(self, "_op", op)
+            self._lds_f32 = (lds.A.to(M.device, torch.float64).contiguous(), lds.B_vec.to(M.device, torch.float64).contiguous(),
+                             lds.C.to(M.device, self.dtype).contiguous())
+            self._lds_key = key
+        return self._op
+
+    def _forward_lds(self, x, past_key_value=None, use_cache=False):
+        op = self._lds_prepared()
+        A32, B32, Cm = self._lds_f32
+        B, T, d = x.shape
+        D, F_ = Cm.shape
+        x = x.contiguous()
+        if past_key_value is not None:
+            if T != 1:
+                raise NotImplementedError("the LDS backend continues a cache one token at a time")
+            h, pos = past_key_value
+            t = host_pos(pos)
+            U = torch.empty(B, F_ * d, dtype=x.dtype, device=x.device)
+            ops.lds_decode_features(x.view(B, d), h, A32, B32, Cm, U)
+            _, Mcat = op.prepared_full()
+            y = ops.linear(U, Mcat).view(B, 1, self.output_dim)
+            pos[:, 0] += 1
+            pos._host_t = t + 1
+            return (y, (h, pos)) if use_cache else y
+        y = torch.empty(B, T, self.output_dim, dtype=x.dtype, device=x.device)
+        if not use_cache:
+            op.full_forward(x, None, y)
+            return y
+        hist, pos = op.new_cache(B, x.device)
+        op.full_forward(x, None, y, (hist, pos), True)
+        h = torch.empty(B, d, D, dtype=torch.float64, device=x.device)
+        ops.lds_final_state(hist, h, A32, B32, T)
+        return y, (h, pos)
+
+    def forward(self, x: torch.Tensor, past_key_value=None, use_cache: bool = False) -> torch.Tensor:
         if x.dim() == 2:
             x = x.unsqueeze(0)
         assert x.dim() == 3, f"Expected x with shape [B, L, I] or [L, I]; got {tuple(x.shape)}"
+        if self.backend == "lds":
+            return self._forward_lds(x.to(self.dtype), past_key_value, use_cache)
         x = x.to(self.M_phi_plus.dtype)
         op = self._op
         if op.phi.device != self.phi.device:

@@ -260,6 +260,30 @@ def full_decode_combine(G, pos, U, B: int, d: int, K: int, both_signs: bool, Lh:
     _count(2 if advance else 1)
 
 
+def lds_final_state(hist, h, A32, B32, T: int):
+    """h[b,i,:] <- LDS state after the T inputs stored in hist [B,d,2,Lh] (float64 state [B,d,D])."""
+    _cuda(hist, h, A32, B32)
+    B, d, _, Lh = hist.shape
+    assert hist.is_contiguous() and h.is_contiguous() and h.dtype == torch.float64 and A32.dtype == torch.float64
+    rc = _lib.load().stu_lds_final_state(hist.data_ptr(), h.data_ptr(), A32.data_ptr(), B32.data_ptr(), B, d, Lh, T,
+                                         h.shape[2], _dt(hist), _stream())
+    _lib.check(rc, "stu_lds_final_state")
+    _count()
+
+
+def lds_decode_features(x2d, h, A32, B32, C, U):
+    """One recurrent LDS step for every channel: h <- A*h + B*x; U[b, f*d+i] = (h @ C)[f]."""
+    _cuda(x2d, h, A32, B32, C, U)
+    B, d = x2d.shape
+    D, F = C.shape
+    assert h.shape == (B, d, D) and h.is_contiguous() and h.dtype == torch.float64 and A32.dtype == torch.float64
+    assert C.is_contiguous() and U.is_contiguous() and x2d.stride(1) == 1
+    rc = _lib.load().stu_lds_decode_features(x2d.data_ptr(), x2d.stride(0), h.data_ptr(), A32.data_ptr(), B32.data_ptr(),
+                                             C.data_ptr(), U.data_ptr(), B, d, D, F, _dt(x2d), _stream())
+    _lib.check(rc, "stu_lds_decode_features")
+    _count()
+
+
 def swa_forward(qkv, k_ring, v_ring, pos, slopes, H: int, window: int, softcap: float, update_cache: bool):
     """Sliding-window attention for the Tn tokens in qkv [B,Tn,3d] against the ring cache; returns [B,Tn,d]."""
     _cuda(qkv, k_ring, v_ring, pos, slopes)

@@ -131,6 +131,19 @@ int stu_full_decode_prepare(const void* x, long long x_row_stride, void* hist, c
 int stu_full_decode_combine(const void* G, long long ldG, int* pos, void* U, int B, int d, int K, int both_signs,
                             int Lh, int advance, int dtype, void* stream);
 
+/* ---- distilled-LDS variant (mini_stu/stu_lds.py:213-394): per channel h_t = A*h_{t-1} + B*x_t (D modes, float64),
+ * U[f] = sum_n h[n] C[n,f], y = sum_{f,i} U[f,i] M[f,i,o].  Prefill outputs go through the full-variant entry
+ * points above with the impulse responses G[j,f] = sum_n C[n,f] B[n] A[n]^j as filters. */
+
+/* h [B*d][D] (float64) <- state after the Tn inputs held in hist; replaces the scan of mini_stu/stu_lds.py:17-99 for
+ * the purpose of seeding the decode. */
+int stu_lds_final_state(const void* hist, double* h, const double* A, const double* Bv, int B, int d, int Lh, int Tn,
+                        int D, int dtype, void* stream);
+
+/* One recurrent step (mini_stu/lds.py:95-101): h updated in place, U [B][F*d] = features in the row order of M. */
+int stu_lds_decode_features(const void* x, long long x_row_stride, double* h, const double* A, const double* Bv,
+                            const void* C, void* U, int B, int d, int D, int F, int dtype, void* stream);
+
 /* Sliding-window attention for the Tn new tokens in qkv [B,Tn,3*H*hd] (c_attn output) against a ring
  * cache of W >= window+1 slots ([B][W][H*hd] each; token t in slot t % W), ALiBi slopes [H] (fp32) and tanh
  * soft-capping; out [B,Tn,H*hd] (heads merged, before c_proj).  update_cache=1 stores the new keys/values

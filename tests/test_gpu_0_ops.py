@@ -350,3 +350,43 @@ def test_mini_stu_spectral_matches_reference_golden(golden):
         y = m(r["x"].to(dev()))
     ops.check_status()
     assert rel(y, r["y"]) <= 1e-3, rel(y, r["y"])
+
+
+@pytest.mark.parametrize("dt,tol", [(torch.float32, 1e-3), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("shape", [(2, 48, 6, 10), (3, 200, 64, 32)])
+def test_mini_stu_lds_prefill_and_recurrent_decode(golden, dt, tol, shape):
+    """MiniSTU(backend='lds'): prefill (convolution with the LDS impulse responses) and the recurrent decode
+    steps against the float64 recurrence of the reference (mini_stu/stu_lds.py) on the same rounded inputs."""
+    import flash_stu_2_b200 as F
+    from flash_stu_2_b200 import ops
+    B, T, din, dout = shape
+    g = golden("mini_stu")["lds_fp64"]
+    torch.manual_seed(13)
+    m = F.MiniSTU(seq_len=T, num_filters=24, input_dim=din, output_dim=dout, backend="lds", dtype=dt)
+    x = torch.randn(B, T, din).to(dt)
+    Mr = m.distill_stu.M.detach().clone()
+    Cr = m.lds_module.C.detach().clone()
+    assert torch.equal(m.lds_module.A, g["A"]) and torch.equal(Cr, g["C"].to(dt))
+    want = O.lds_forward(x.double(), g["A"], g["B_vec"], Cr.double(), g["h0"], Mr.double())
+    m = m.to(dev())
+    T1 = T - 9
+    with torch.no_grad():
+        y_all = m(x.to(dev()))
+        y1, cache = m(x[:, :T1].to(dev()), use_cache=True)
+        rows = [y1]
+        for t in range(T1, T):
+            yt, cache = m(x[:, t:t + 1].to(dev()), past_key_value=cache, use_cache=True)
+            rows.append(yt)
+    ops.check_status()
+    assert rel(y_all, want) <= tol, rel(y_all, want)
+    got = torch.cat(rows, 1)
+    assert rel(got, want) <= tol, rel(got, want)
+    if shape == (2, 48, 6, 10) and dt == torch.float32:
+        # the reference module's own output (float64 run of MiniSTU(backend='lds')) with its M
+        m2 = F.MiniSTU(seq_len=T, num_filters=24, input_dim=din, output_dim=dout, backend="lds", dtype=dt)
+        with torch.no_grad():
+            m2.distill_stu.M.copy_(g["M"].to(dt))
+        m2 = m2.to(dev())
+        with torch.no_grad():
+            y2 = m2(g["x"].to(dt).to(dev()))
+        assert rel(y2, g["y"]) <= 1e-3, rel(y2, g["y"])
