@@ -45,6 +45,8 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=8192, help="context length (default: the benchmark's 8192)")
     ap.add_argument("--decode-steps", type=int, default=512)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="plain stream-ordered launches for the decode kernels (no programmatic dependent launch)")
     ap.add_argument("--no-graph", action="store_true", help="launch decode steps eagerly instead of replaying a CUDA graph")
     return ap.parse_args()
 
@@ -147,6 +149,7 @@ def cpu_baseline(a, blk, x_host):
     """The reference's arithmetic for this block on the host cores (oracle port).  The reference has no
     incremental STU decode, so one decode token costs a forward over the whole prefix."""
     from oracle import stu_oracle as O
+    torch.set_num_threads(len(os.sched_getaffinity(0)))
     sd = {k: v.detach().clone() for k, v in blk.state_dict().items()}
     n = O.fft_length(a.seq_len)
     x1 = x_host[:1].clone()
@@ -163,6 +166,8 @@ def run_reference(a):
     if rank != 0:
         return
     from oracle import stu_oracle as O
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; the host arm uses every core this process may run on
+    torch.set_num_threads(len(os.sched_getaffinity(0)))
     blk = make_state(a.seq_len)
     sd = {k: v.detach().clone() for k, v in blk.state_dict().items()}
     n = O.fft_length(a.seq_len)
@@ -203,6 +208,8 @@ def run_b200(a):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     B, L, d, S = a.batch, a.seq_len, D_MODEL, a.decode_steps
+    if a.no_overlap:
+        ops.overlap_decode = False
     blk = make_state(L).to(dev).eval()
     torch.manual_seed(1 + rank)
     x_host = torch.randn(B, L, d).bfloat16().pin_memory()
@@ -211,8 +218,9 @@ def run_b200(a):
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
     x_work = torch.empty_like(x_dev)
-    x_step = torch.empty(B, 1, d, dtype=torch.bfloat16, device=dev)
-    state = {"cache": None, "graph": None, "graph_launches": 0}
+    x_step = torch.empty(B, 1, d, dtype=torch.bfloat16, device=dev)       # token buffer of the end-to-end loop
+    x_steps = torch.zeros(S, B, 1, d, dtype=torch.bfloat16, device=dev)   # teacher-forced inputs, overwritten in
+    state = {"cache": None, "graph": None, "graph1": None, "graph_launches": 0}   # place by the block's outputs
 
     def prefill():
         # the cache buffers are allocated once and reused (a captured decode graph holds their addresses):
@@ -229,37 +237,40 @@ def run_b200(a):
         pos[:, 0] = first
         pos._host_t = first
 
-    def eager_step():
-        _, state["cache"] = blk(x_step, past_key_value=state["cache"], use_cache=True)
+    def eager_step(buf):
+        _, state["cache"] = blk(buf, past_key_value=state["cache"], use_cache=True)
 
-    def decode(n_steps=S):
-        pos = state["cache"][1]
-        for i in range(n_steps):
-            x_step.copy_(x_dev[:, first + i:first + i + 1])
-            if state["graph"] is not None:
-                state["graph"].replay()
-            else:
-                eager_step()
-        pos._host_t = first + n_steps
+    def eager_steps():
+        for i in range(S):
+            eager_step(x_steps[i])
+
+    def decode():
+        # the block works in place (as the reference's layers do), so the S input rows are laid out token-major
+        # once per pass; every token step then reads its row and leaves its output there
+        x_steps.copy_(x_dev[:, first:].transpose(0, 1).unsqueeze(2))
+        if state["graph"] is not None:
+            state["graph"].replay()
+        else:
+            eager_steps()
+        state["cache"][1]._host_t = first + S
+
+    def capture(fn):
+        rewind()
+        g = torch.cuda.CUDAGraph()
+        n0 = ops.launch_count
+        with torch.cuda.graph(g):
+            fn()
+        return g, ops.launch_count - n0
 
     with torch.no_grad():
         # first pass: eager, builds derived weights / scratch / status word before any capture
-        prefill(); rewind(); decode(2)
+        prefill(); rewind(); eager_step(x_steps[0]); eager_step(x_step)
         torch.cuda.synchronize()
         if not a.no_graph:
-            rewind()
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                eager_step()
-            torch.cuda.current_stream().wait_stream(side)
-            rewind()
-            g = torch.cuda.CUDAGraph()
-            n0 = ops.launch_count
-            with torch.cuda.graph(g):
-                eager_step()
-            state["graph_launches"] = ops.launch_count - n0
-            state["graph"] = g
+            # all S token steps in one graph (positions are read from device memory, so the same graph serves every
+            # pass); a one-step graph on its own token buffer serves the end-to-end loop
+            state["graph"], state["graph_launches"] = capture(eager_steps)
+            state["graph1"], _ = capture(lambda: eager_step(x_step))
         for _ in range(a.warmup):
             prefill(); rewind(); decode()
         torch.cuda.synchronize()
@@ -286,7 +297,7 @@ def run_b200(a):
         wall = time.perf_counter() - wall0
         launches = ops.launch_count - n_launch0
         if state["graph"] is not None:
-            launches += a.steps * S * state["graph_launches"]
+            launches += a.steps * state["graph_launches"]
         clocks = sampler.stop() if rank == 0 else None
         ops.check_status()
         t_pre, t_dec = parallel.max_over_ranks([t_pre, t_dec], device=dev)   # ms, summed over steps
@@ -298,14 +309,28 @@ def run_b200(a):
         x2 = x_step.view(B, d)
         out2 = torch.empty_like(x2)
         reps = min(256, S)
+
+        def kernel_only():
+            ops.decode_approx(x2, layer.stu_norm.weight, MinT, hist, taps, pos, out2, taps8=taps8,
+                              flags=ops.FLAG_UNIFORM_POS)
+
         rewind()
         for _ in range(3):
-            ops.decode_approx(x2, layer.stu_norm.weight, MinT, hist, taps, pos, out2, taps8=taps8)
+            kernel_only()
+        # the launches are replayed from a graph: issued one by one from Python they would be paced by the host
+        # (the kernel is shorter than a ctypes call), and the figure would be the interpreter's, not the GPU's
+        kg = None
+        if not a.no_graph:
+            kg, _ = capture(lambda: [kernel_only() for _ in range(reps)])
         rewind()
+        torch.cuda.synchronize()
         k0, k1 = ev(), ev()
         k0.record()
-        for _ in range(reps):
-            ops.decode_approx(x2, layer.stu_norm.weight, MinT, hist, taps, pos, out2, taps8=taps8)
+        if kg is not None:
+            kg.replay()
+        else:
+            for _ in range(reps):
+                kernel_only()
         k1.record()
         torch.cuda.synchronize()
         kern_ms = k0.elapsed_time(k1) / reps
@@ -335,10 +360,10 @@ def run_b200(a):
             d0 = time.perf_counter()
             for i in range(S):
                 x_step.copy_(x_host[:, first + i:first + i + 1], non_blocking=True)
-                if state["graph"] is not None:
-                    state["graph"].replay()
+                if state["graph1"] is not None:
+                    state["graph1"].replay()
                 else:
-                    eager_step()
+                    eager_step(x_step)
                 y_host.copy_(x_step, non_blocking=True)
                 torch.cuda.current_stream().synchronize()
             dec_s += time.perf_counter() - d0
@@ -368,13 +393,14 @@ def run_b200(a):
         "config": {"workload": workload_name(a), "parallelism": f"dp{world} (independent sequences, no collective)",
                    "l2": f"inputs larger than L2: decode working set {ws_mb:.0f} MB (history+taps+weights) and "
                          f"prefill input {B * L * d * 2 / 1e6:.0f} MB vs 126 MB L2; no explicit flush",
-                   "decode_launch": "CUDA graph replay per step" if state["graph"] is not None else "eager launches"},
+                   "decode_launch": (f"one CUDA graph of all {S} token steps (device-resident positions)"
+                                     if state["graph"] is not None else "eager launches")},
         "decode_ms_per_token_step": t_dec / a.steps / S,
         "prefill": {"value": pre_tokens / (t_pre / 1e3), "unit": "tokens/s", "ms": t_pre / a.steps,
                     "tflops_algorithmic": pre_tflops,
                     "frac_of_tensor_peak": pre_tflops / pk["bf16_tflops_sustained"],
                     "peak_tflops": pk["bf16_tflops_sustained"], "peak_source": pk["source"] + " (sustained)"},
-        "roofline": {"bound": "hbm", "kernel": "stu_decode_diag_kernel", "achieved": achieved, "peak": pk["hbm_gbs"],
+        "roofline": {"bound": "hbm", "kernel": "stu_decode_rows8_kernel", "achieved": achieved, "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "peak_source": pk["source"],
                      "bytes_per_launch": kern_bytes, "us_per_launch": kern_ms * 1e3, "traffic": None},
         "e2e": {"value": world * B * S * e2e_steps / dec_s, "unit": "tokens/s",

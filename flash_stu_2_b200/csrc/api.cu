@@ -14,6 +14,11 @@ enum { BACKEND_AUTO = 0, BACKEND_SIMT = 1, BACKEND_TCGEN05 = 2, BACKEND_SKINNY =
 //               starting at time hist_t0, N channels, hist_Lh elements per parity row)
 // norm_w != NULL asks for x to be RMS-normalised (eps) on the way in; only the decode (skinny) path
 // fuses this, other shapes return STU_ERR_UNSUPPORTED so that the caller normalises separately.
+bool pdl_enabled() {
+  static const bool off = getenv("STU_B200_DISABLE_PDL") != nullptr;
+  return !off;
+}
+
 extern "C" int stu_linear(const void* x, long long x_row_stride, const void* W, long long w_row_stride,
                           long long w_k_stride, const void* W2, const void* resid, long long resid_row_stride,
                           void* y, long long y_row_stride, int M, int N, int K, int epilogue, int hist_T,
@@ -23,7 +28,8 @@ extern "C" int stu_linear(const void* x, long long x_row_stride, const void* W, 
   if (M < 0 || N <= 0 || K <= 0) return STU_ERR_SHAPE;
   if (M == 0) return STU_OK;
   const int causal = (epilogue & EPI_FLAG_CAUSAL) ? 1 : 0;
-  epilogue &= ~EPI_FLAG_CAUSAL;
+  const int pdl = epilogue & (STU_FLAG_OVERLAP | STU_FLAG_EARLY_TRIGGER);  // honoured by the skinny kernels only
+  epilogue &= ~(EPI_FLAG_CAUSAL | STU_FLAG_OVERLAP | STU_FLAG_EARLY_TRIGGER);
   if (epilogue < EPI_STORE || epilogue > EPI_HIST) return STU_ERR_UNSUPPORTED;
   if (epilogue == EPI_GELU_MUL && !W2) return STU_ERR_NULL;
   if (epilogue == EPI_RESID && !resid) return STU_ERR_NULL;
@@ -45,14 +51,14 @@ extern "C" int stu_linear(const void* x, long long x_row_stride, const void* W, 
   if (norm_w) {
     if (!sk_ok || dtype != STU_BF16 || (backend != BACKEND_AUTO && backend != BACKEND_SKINNY))
       return STU_ERR_UNSUPPORTED;
-    return skinny_dispatch(x, x_row_stride, W, w_row_stride, W2, M, N, K, epilogue, ep, norm_w, eps, dtype, st);
+    return skinny_dispatch(x, x_row_stride, W, w_row_stride, W2, M, N, K, epilogue, ep, norm_w, eps, dtype, pdl, st);
   }
   bool tc_ok = gemm_tc_supported(x, x_row_stride, W, w_row_stride, w_k_stride, W2, M, N, K, epilogue, ep, dtype);
   if (backend == BACKEND_AUTO) backend = sk_ok ? BACKEND_SKINNY : (tc_ok ? BACKEND_TCGEN05 : BACKEND_SIMT);
   switch (backend) {
     case BACKEND_SKINNY:
       if (!sk_ok) return STU_ERR_UNSUPPORTED;
-      return skinny_dispatch(x, x_row_stride, W, w_row_stride, W2, M, N, K, epilogue, ep, nullptr, eps, dtype, st);
+      return skinny_dispatch(x, x_row_stride, W, w_row_stride, W2, M, N, K, epilogue, ep, nullptr, eps, dtype, pdl, st);
     case BACKEND_TCGEN05:
       if (!tc_ok) return STU_ERR_UNSUPPORTED;
       return gemm_tc_dispatch(x, x_row_stride, W, w_row_stride, W2, M, N, K, epilogue, causal, ep, st);

@@ -68,6 +68,42 @@ __device__ __forceinline__ void store_vec(bf16* p, const float* in) {
   *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// ---- programmatic dependent launch (overlap of a kernel's constant-data prefetch with its predecessor) ----
+// Flags OR-ed into the epilogue code of stu_linear and into the dtype code of stu_decode_approx:
+//   STU_FLAG_OVERLAP        the launch carries the programmatic-stream-serialization attribute: its CTAs may start
+//                           while the preceding kernel of the stream is still running; everything the kernel
+//                           reads before griddepcontrol.wait must be data that kernel does not write
+//   STU_FLAG_EARLY_TRIGGER  the kernel lets its own successor start as soon as all its CTAs are resident
+//                           (otherwise: right after its own wait, i.e. once its predecessor has completed)
+// Both instructions are no-ops in a launch without programmatic neighbours.
+#define STU_FLAG_OVERLAP 0x200
+#define STU_FLAG_EARLY_TRIGGER 0x400
+// stu_decode_approx only: the caller promises that every sequence of the batch stands at the same position (the
+// kernel checks and reports status 6 otherwise); selects the kernel that shares the taps between sequences.
+#define STU_FLAG_UNIFORM_POS 0x800
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// STU_B200_DISABLE_PDL=1 turns every launch back into a plain stream-ordered one.
+bool pdl_enabled();
+
+// Launch with or without the programmatic attribute.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_maybe_overlapped(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                                  cudaStream_t st, bool overlap, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = (overlap && pdl_enabled()) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -95,3 +131,26 @@ __host__ __device__ __forceinline__ size_t hist_off(int b, int c, int t, int d, 
 }
 
 static inline bool aligned16(const void* p) { return (((uintptr_t)p) & 15u) == 0; }
+
+// Normalise eight activation values the way the reference's RMSNorm output tensor holds them
+// (x * r * w rounded to bf16) and pack them as four bf16x2 words.
+__device__ __forceinline__ uint4 norm_pack(const uint4& raw, float r, const uint4& nraw) {
+  float xv[8], wv[8];
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  const uint32_t n[4] = {nraw.x, nraw.y, nraw.z, nraw.w};
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    xv[2 * i] = __uint_as_float(w[i] << 16);
+    xv[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    wv[2 * i] = __uint_as_float(n[i] << 16);
+    wv[2 * i + 1] = __uint_as_float(n[i] & 0xffff0000u);
+  }
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(xv[2 * i] * r * wv[2 * i], xv[2 * i + 1] * r * wv[2 * i + 1]);
+    o[i] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+

@@ -58,6 +58,6 @@ int gemm_tc_dispatch(const void* A, long long lda, const void* B, long long ldb,
 bool gemm_tc_supported(const void* A, long long lda, const void* B, long long ldb, long long skb, const void* B2,
                        int M, int N, int K, int epi, const EpiArgsAny& ep, int dtype);
 int skinny_dispatch(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N, int K,
-                    int epi, const EpiArgsAny& ep, const void* norm_w, float eps, int dtype, cudaStream_t st);
+                    int epi, const EpiArgsAny& ep, const void* norm_w, float eps, int dtype, int pdl, cudaStream_t st);
 bool skinny_supported(const void* A, long long lda, const void* B, long long ldb, long long skb, const void* B2,
                       int M, int N, int K, int epi, int dtype);

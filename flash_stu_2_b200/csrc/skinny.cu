@@ -24,28 +24,6 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, uint32_t a0, uint32_t a
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Normalise eight activation values the way the reference's RMSNorm output tensor holds them
-// (x * r * w rounded to bf16) and pack them as four bf16x2 words.
-__device__ __forceinline__ uint4 norm_pack(const uint4& raw, float r, const uint4& nraw) {
-  float xv[8], wv[8];
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-  const uint32_t n[4] = {nraw.x, nraw.y, nraw.z, nraw.w};
-#pragma unroll
-  for (int i = 0; i < 4; i++) {
-    xv[2 * i] = __uint_as_float(w[i] << 16);
-    xv[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    wv[2 * i] = __uint_as_float(n[i] << 16);
-    wv[2 * i + 1] = __uint_as_float(n[i] & 0xffff0000u);
-  }
-  uint32_t o[4];
-#pragma unroll
-  for (int i = 0; i < 4; i++) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(xv[2 * i] * r * wv[2 * i], xv[2 * i + 1] * r * wv[2 * i + 1]);
-    o[i] = *reinterpret_cast<uint32_t*>(&h);
-  }
-  return make_uint4(o[0], o[1], o[2], o[3]);
-}
-
 // One CTA = eight output features; its NW warps split K in interleaved 32-element chunks.  Every lane
 // loads 16 bytes of its weight row and 16 bytes of its activation row(s) per chunk straight from global
 // memory (the activations are L2-resident) and feeds them to mma.sync with the k-order permuted so that
@@ -57,7 +35,7 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
                                                               const bf16* __restrict__ W, long long ldb,
                                                               const bf16* __restrict__ W2, int M, int N, int K,
                                                               EpiArgs<bf16> ep, const bf16* __restrict__ nw,
-                                                              float eps) {
+                                                              float eps, int pdl) {
   constexpr bool DUAL = (EPI == EPI_GELU_MUL);
   constexpr int NACC = DUAL ? 2 : 1;
   constexpr int NH = LOW8 ? 1 : 2;  // activation half-tiles (rows g and g+8) per m-tile
@@ -74,7 +52,9 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
   const int nchunks = (K + 31) >> 5;
 
   uint4 wv[U], wv2[DUAL ? U : 1], xv[U][MT][NH], nwv[NORM ? U : 1];
-  auto issue = [&](int c0) {
+  // constants of a round (weights, norm weights) and its activations are issued separately: in an overlapped
+  // launch the constants are fetched while the kernel that produces the activations is still running
+  auto issue_w = [&](int c0) {
 #pragma unroll
     for (int u = 0; u < U; u++) {
       const int ch = c0 + NW * u;
@@ -83,6 +63,14 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
       wv[u] = (kok && nvalid) ? ldg_stream(wrow + k) : make_uint4(0, 0, 0, 0);
       if (DUAL) wv2[u] = (kok && nvalid) ? ldg_stream(wrow2 + k) : make_uint4(0, 0, 0, 0);
       if (NORM) nwv[u] = kok ? *reinterpret_cast<const uint4*>(nw + k) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  auto issue_x = [&](int c0) {
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int ch = c0 + NW * u;
+      const int k = (ch << 5) + q * 8;
+      const bool kok = ch < nchunks && (k + 8) <= K;
 #pragma unroll
       for (int t = 0; t < MT; t++)
 #pragma unroll
@@ -93,7 +81,11 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
         }
     }
   };
-  issue(warp);
+  if (pdl & STU_FLAG_EARLY_TRIGGER) pdl_trigger();
+  issue_w(warp);
+  pdl_wait();
+  if (!(pdl & STU_FLAG_EARLY_TRIGGER)) pdl_trigger();
+  issue_x(warp);
 
   if (NORM) {
     for (int m = warp; m < MT * 16; m += NW) {
@@ -124,11 +116,13 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
       for (int i = 0; i < 4; i++) acc[a][t][i] = 0.f;
 
   for (int c0 = warp; c0 < nchunks; c0 += NW * U) {
-    if (c0 != warp) issue(c0);
+    if (c0 != warp) {
+      issue_w(c0);
+      issue_x(c0);
+    }
 #pragma unroll
     for (int u = 0; u < U; u++) {
       const int ch = c0 + NW * u;
-      const int k = (ch << 5) + q * 8;
       // ch is the same for the whole warp: mma.sync must be reached by all 32 lanes, so a lane whose k falls
       // past the end of a partial chunk takes part with zero operands (its loads above were predicated off)
       if (ch < nchunks) {
@@ -220,14 +214,19 @@ bool skinny_supported(const void* A, long long lda, const void* B, long long ldb
 
 template <int EPI, int MT, bool LOW8, int U, int NW>
 static int launch_skinny_cfg(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N,
-                             int K, const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st) {
+                             int K, const EpiArgs<bf16>& ep, const void* nw, float eps, int pdl, cudaStream_t st) {
   dim3 grid((N + 7) / 8);
+  const bool ov = (pdl & STU_FLAG_OVERLAP) != 0;
+  cudaError_t e;
   if (nw)
-    skinny_bf16_kernel<EPI, MT, LOW8, true, U, NW><<<grid, NW * 32, 0, st>>>(
-        (const bf16*)A, lda, (const bf16*)B, ldb, (const bf16*)B2, M, N, K, ep, (const bf16*)nw, eps);
+    e = launch_maybe_overlapped(skinny_bf16_kernel<EPI, MT, LOW8, true, U, NW>, grid, dim3(NW * 32), 0, st, ov,
+                                (const bf16*)A, lda, (const bf16*)B, ldb, (const bf16*)B2, M, N, K, ep,
+                                (const bf16*)nw, eps, pdl);
   else
-    skinny_bf16_kernel<EPI, MT, LOW8, false, U, NW><<<grid, NW * 32, 0, st>>>(
-        (const bf16*)A, lda, (const bf16*)B, ldb, (const bf16*)B2, M, N, K, ep, nullptr, eps);
+    e = launch_maybe_overlapped(skinny_bf16_kernel<EPI, MT, LOW8, false, U, NW>, grid, dim3(NW * 32), 0, st, ov,
+                                (const bf16*)A, lda, (const bf16*)B, ldb, (const bf16*)B2, M, N, K, ep,
+                                (const bf16*)nullptr, eps, pdl);
+  if (e != cudaSuccess) return (int)e;
   STU_CHECK_LAUNCH();
   return STU_OK;
 }
@@ -236,45 +235,45 @@ static int launch_skinny_cfg(const void* A, long long lda, const void* B, long l
 // per lane.  Long K rows use 16 warps so that one or two rounds cover the row.
 template <int EPI, int MT, bool LOW8>
 static int launch_skinny_shape(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M,
-                               int N, int K, const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st) {
+                               int N, int K, const EpiArgs<bf16>& ep, const void* nw, float eps, int pdl, cudaStream_t st) {
   constexpr bool light = (EPI != EPI_GELU_MUL) && (MT == 1);  // few registers per chunk: deeper rounds fit
   const int chunks = (K + 31) / 32;
   const int per8 = (chunks + 7) / 8;
   if constexpr (light) {
-    if (per8 <= 4) return launch_skinny_cfg<EPI, MT, LOW8, 4, 8>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
-    if (per8 <= 8) return launch_skinny_cfg<EPI, MT, LOW8, 8, 8>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
-    return launch_skinny_cfg<EPI, MT, LOW8, 8, 16>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+    if (per8 <= 4) return launch_skinny_cfg<EPI, MT, LOW8, 4, 8>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, pdl, st);
+    if (per8 <= 8) return launch_skinny_cfg<EPI, MT, LOW8, 8, 8>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, pdl, st);
+    return launch_skinny_cfg<EPI, MT, LOW8, 8, 16>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, pdl, st);
   } else if constexpr (MT <= 2) {
-    return launch_skinny_cfg<EPI, MT, LOW8, 4, 8>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+    return launch_skinny_cfg<EPI, MT, LOW8, 4, 8>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, pdl, st);
   } else {
-    return launch_skinny_cfg<EPI, MT, LOW8, 2, 8>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+    return launch_skinny_cfg<EPI, MT, LOW8, 2, 8>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, pdl, st);
   }
 }
 
 template <int EPI>
 static int launch_skinny_bf16_mt(int MT, const void* A, long long lda, const void* B, long long ldb, const void* B2,
-                                 int M, int N, int K, const EpiArgs<bf16>& ep, const void* nw, float eps,
+                                 int M, int N, int K, const EpiArgs<bf16>& ep, const void* nw, float eps, int pdl,
                                  cudaStream_t st) {
-  if (M <= 8) return launch_skinny_shape<EPI, 1, true>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+  if (M <= 8) return launch_skinny_shape<EPI, 1, true>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, pdl, st);
   switch (MT) {
-    case 1: return launch_skinny_shape<EPI, 1, false>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
-    case 2: return launch_skinny_shape<EPI, 2, false>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
-    case 3: return launch_skinny_shape<EPI, 3, false>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
-    case 4: return launch_skinny_shape<EPI, 4, false>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+    case 1: return launch_skinny_shape<EPI, 1, false>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, pdl, st);
+    case 2: return launch_skinny_shape<EPI, 2, false>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, pdl, st);
+    case 3: return launch_skinny_shape<EPI, 3, false>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, pdl, st);
+    case 4: return launch_skinny_shape<EPI, 4, false>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, pdl, st);
   }
   return STU_ERR_SHAPE;
 }
 
 int skinny_dispatch(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N, int K,
-                    int epi, const EpiArgsAny& ep, const void* norm_w, float eps, int dtype, cudaStream_t st) {
+                    int epi, const EpiArgsAny& ep, const void* norm_w, float eps, int dtype, int pdl, cudaStream_t st) {
   if (dtype == STU_BF16) {
     int MT = (M + 15) / 16;
     EpiArgs<bf16> e = ep.as<bf16>();
     switch (epi) {
-      case EPI_STORE: return launch_skinny_bf16_mt<EPI_STORE>(MT, A, lda, B, ldb, B2, M, N, K, e, norm_w, eps, st);
-      case EPI_RESID: return launch_skinny_bf16_mt<EPI_RESID>(MT, A, lda, B, ldb, B2, M, N, K, e, norm_w, eps, st);
+      case EPI_STORE: return launch_skinny_bf16_mt<EPI_STORE>(MT, A, lda, B, ldb, B2, M, N, K, e, norm_w, eps, pdl, st);
+      case EPI_RESID: return launch_skinny_bf16_mt<EPI_RESID>(MT, A, lda, B, ldb, B2, M, N, K, e, norm_w, eps, pdl, st);
       case EPI_GELU_MUL:
-        return launch_skinny_bf16_mt<EPI_GELU_MUL>(MT, A, lda, B, ldb, B2, M, N, K, e, norm_w, eps, st);
+        return launch_skinny_bf16_mt<EPI_GELU_MUL>(MT, A, lda, B, ldb, B2, M, N, K, e, norm_w, eps, pdl, st);
     }
     return STU_ERR_UNSUPPORTED;
   }

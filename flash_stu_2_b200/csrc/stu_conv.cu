@@ -570,40 +570,139 @@ __global__ void __launch_bounds__(256) stu_decode_kernel(const T* __restrict__ x
 // two MMAs per 16-byte load, with the access pattern of the CUDA-core kernel (one contiguous run per warp).
 // The taps come from a table stored reversed and in all eight 16-byte alignments (taps8[e][c][Lh+8],
 // taps8[e][c][u] = tap[Lh-1-(u+e)]), so the tap operand is an aligned 16-byte load at every position.
-// Ragged positions need no special case: every warp has its own position and tap alignment.
-constexpr int DD_U = 4;  // 512-byte runs of history (and of taps) a warp keeps in flight
+// The eight warps of a CTA are the (up to) eight sequences of one channel.  When they all stand at the same
+// position (the usual case in batched generation) the channel's reversed tap row is copied once into shared
+// memory and every warp takes its B fragments from there: the taps then cross the L2-to-SM fabric once per CTA
+// instead of once per warp, which halves the kernel's load traffic, and the registers that held tap words hold
+// history words instead (eight 512-byte runs in flight per warp).  With ragged positions every warp streams
+// its own alignment of the table from global memory (four runs of history and four of taps in flight).
+constexpr int DD_U = 8;  // uint4 registers per lane for data in flight
+
+__device__ __forceinline__ uint4 lds_v4(const bf16* p) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"((uint32_t)__cvta_generic_to_shared(p)));
+  return v;
+}
+
+// Masked A fragment of the last, partial run: elements [i0, i0 + 8) of which the first `keep` are history.
+__device__ __forceinline__ void mask_tail(uint32_t (&a)[4], const uint4& raw, int keep) {
+  a[0] = raw.x; a[1] = raw.y; a[2] = raw.z; a[3] = raw.w;
+  if (keep < 8) {
+#pragma unroll
+    for (int jj = 0; jj < 4; jj++) {
+      if (2 * jj + 1 >= keep) a[jj] = (2 * jj < keep) ? (a[jj] & 0x0000ffffu) : 0u;
+    }
+  }
+}
+
+// diagonal of the two accumulator tiles: D0[g][g] sits in lane (g, q = g/2) register g&1; D1[g+8][g] in the same
+// lane, register 2+(g&1)
+__device__ __forceinline__ float diag_part(const float (&acc0)[4], const float (&acc1)[4], int lane) {
+  const int g = lane >> 2, q = lane & 3;
+  return (q == (g >> 1)) ? ((g & 1) ? (acc0[1] + acc1[3]) : (acc0[0] + acc1[2])) : 0.f;
+}
+
+// Ragged positions: the warp streams its own alignment of the tap table from global memory (four runs of
+// history and four of taps in flight).  Kept out of line so that its registers do not add to the common path.
+__device__ __noinline__ float ragged_tap_dot(const bf16* __restrict__ hrow, const bf16* __restrict__ trow, int s,
+                                             int lane) {
+  constexpr int RU = 4;
+  const int nfull = s >> 8;
+  float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+  uint4 hv[RU], tv[RU];
+  for (int j0 = 0; j0 < nfull; j0 += RU) {
+#pragma unroll
+    for (int u = 0; u < RU; u++) {
+      if (j0 + u < nfull) {
+        hv[u] = ldg_nc_v4(hrow + ((j0 + u) << 8) + 8 * lane);
+        tv[u] = ldg_nc_v4(trow + ((j0 + u) << 8) + 8 * lane);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < RU; u++) {
+      if (j0 + u < nfull) {  // warp-uniform
+        mma_bf16(acc0, hv[u].x, hv[u].y, hv[u].z, hv[u].w, tv[u].x, tv[u].z);
+        mma_bf16(acc1, hv[u].x, hv[u].y, hv[u].z, hv[u].w, tv[u].y, tv[u].w);
+      }
+    }
+  }
+  if (s & 255) {
+    const int i0 = (nfull << 8) + 8 * lane;
+    const int keep = s - i0;
+    uint32_t a[4] = {0u, 0u, 0u, 0u};
+    uint4 tt = make_uint4(0, 0, 0, 0);
+    if (keep > 0) {
+      mask_tail(a, ldg_nc_v4(hrow + i0), keep);
+      tt = ldg_nc_v4(trow + i0);
+    }
+    mma_bf16(acc0, a[0], a[1], a[2], a[3], tt.x, tt.z);
+    mma_bf16(acc1, a[0], a[1], a[2], a[3], tt.y, tt.w);
+  }
+  return diag_part(acc0, acc1, lane);
+}
 
 __global__ void __launch_bounds__(256, 4) stu_decode_diag_kernel(const bf16* __restrict__ x, long long x_rstride,
                                                               const bf16* __restrict__ norm_w,
                                                               const bf16* __restrict__ MinT, bf16* __restrict__ hist,
                                                               const bf16* __restrict__ taps8, int* __restrict__ pos,
                                                               bf16* __restrict__ out, long long out_rstride, int B,
-                                                              int d, int Lh, float eps, int* __restrict__ status) {
-  const int c = blockIdx.x, b = blockIdx.y * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+                                                              int d, int Lh, float eps, int* __restrict__ status,
+                                                              int pdl) {
+  extern __shared__ __align__(16) unsigned char dd_smem[];
+  bf16* s_tap = reinterpret_cast<bf16*>(dd_smem);  // [Lh + 8] reversed taps of this channel (uniform positions)
+  __shared__ int s_t[8];
+  if (pdl & STU_FLAG_EARLY_TRIGGER) pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5;
+  const int c = blockIdx.x, b = blockIdx.y * 8 + warp;
+  const int lane = threadIdx.x & 31;
   const int LP = Lh + 8;
-  bool run = b < B;
-  int t = run ? pos[2 * b] : 0;
-  if (run && (t < 0 || t >= 2 * Lh)) {
-    if (lane == 0 && status) atomicExch(status, 2);
-    run = false;
-  }
-  if (run) {
-    const int p = t & 1, s = t >> 1;
-    bf16* hrow = hist + ((size_t)((size_t)b * d + c) * 2 + p) * Lh;
+  const bool inb = b < B;
+  const int t = inb ? pos[2 * b] : -1;
+  const bool run = inb && t >= 0 && t < 2 * Lh;
+  if (inb && !run && lane == 0 && status) atomicExch(status, 2);
+  if (lane == 0) s_t[warp] = run ? t : -1;
+  const int p = t & 1, s = run ? (t >> 1) : 0;
+  bf16* hrow = hist + ((size_t)((size_t)(inb ? b : 0) * d + c) * 2 + p) * Lh;
+  // own alignment of the tap table (ragged positions): trow[i] = tap[s - i], 16-byte aligned
+  auto tap_row = [&]() {
     const int o = Lh - 1 - s, e = o & 7;
-    const bf16* trow = taps8 + ((size_t)e * d + c) * LP + (o - e);  // trow[i] = tap[s - i], 16-byte aligned
-    const int nfull = s >> 8;                                        // complete 256-element runs before s
-    uint4 hv[DD_U], tv[DD_U];
+    return taps8 + ((size_t)e * d + c) * LP + (o - e);
+  };
+  const int nfull = s >> 8;  // complete 256-element runs before s
+  __syncthreads();
+  // uniform: every sequence of this CTA that runs stands at the same position
+  int tu = -1;
+  bool uniform = true;
 #pragma unroll
-    for (int u = 0; u < DD_U; u++) {
-      if (u < nfull) {
-        hv[u] = ldg_nc_v4(hrow + (u << 8) + 8 * lane);
-        tv[u] = ldg_nc_v4(trow + (u << 8) + 8 * lane);
-      }
+  for (int w = 0; w < 8; w++) {
+    const int tw = s_t[w];
+    if (tw >= 0) {
+      if (tu < 0) tu = tw;
+      else if (tw != tu) uniform = false;
     }
-    // ---- RMSNorm statistic of row b and the projection onto channel c (overlaps the loads above)
-    const bf16* xr = x + (size_t)b * x_rstride;
+  }
+  uint4 hv[DD_U];
+  if (uniform) {
+    if (run) {  // first half of the first round now, second half after the projection (register budget)
+#pragma unroll
+      for (int u = 0; u < DD_U / 2; u++)
+        if (u < nfull) hv[u] = ldg_nc_v4(hrow + (u << 8) + 8 * lane);
+    }
+    if (tu >= 0) {  // all threads copy the tap row of position tu: elements [0, roundup8(su))
+      const int su = tu >> 1;
+      const int ou = Lh - 1 - su, eu = ou & 7;
+      const bf16* tr = taps8 + ((size_t)eu * d + c) * LP + (ou - eu);
+      const int nv = (su + 7) >> 3;
+      for (int i = threadIdx.x; i < nv; i += 256) *reinterpret_cast<uint4*>(s_tap + 8 * i) = ldg_nc_v4(tr + 8 * i);
+    }
+  }
+  // ---- RMSNorm statistic of row b and the projection onto channel c (overlaps the loads above)
+  float xp = 0.f;
+  const bf16* xr = x + (size_t)(inb ? b : 0) * x_rstride;
+  if (run) {
     float ss = 0.f;
     for (int k = lane * 8; k < d; k += 256) {
       float v[8];
@@ -624,54 +723,227 @@ __global__ void __launch_bounds__(256, 4) stu_decode_diag_kernel(const bf16* __r
       for (int j = 0; j < 8; j++) dot = fmaf(round_to<bf16>(v[j] * r * gw[j]), m[j], dot);
     }
     dot = warp_sum(dot);
-    const float xp = round_to<bf16>(dot);
+    xp = round_to<bf16>(dot);
     if (lane == 0) hrow[s] = __float2bfloat16_rn(xp);
+    if (uniform) {
+#pragma unroll
+      for (int u = DD_U / 2; u < DD_U; u++)
+        if (u < nfull) hv[u] = ldg_nc_v4(hrow + (u << 8) + 8 * lane);
+    }
+  }
+  __syncthreads();  // the tap row is in shared memory
+  if (run) {
     // ---- tap dot product over the stored history [0, s)
-    float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int j0 = 0; j0 < nfull; j0 += DD_U) {
-      if (j0) {
+    float part;
+    if (uniform) {
+      float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int j0 = 0; j0 < nfull; j0 += DD_U) {
+        if (j0) {
+#pragma unroll
+          for (int u = 0; u < DD_U; u++)
+            if (j0 + u < nfull) hv[u] = ldg_nc_v4(hrow + ((j0 + u) << 8) + 8 * lane);
+        }
 #pragma unroll
         for (int u = 0; u < DD_U; u++) {
-          if (j0 + u < nfull) {
-            hv[u] = ldg_nc_v4(hrow + ((j0 + u) << 8) + 8 * lane);
-            tv[u] = ldg_nc_v4(trow + ((j0 + u) << 8) + 8 * lane);
+          if (j0 + u < nfull) {  // warp-uniform
+            const uint4 tv = lds_v4(s_tap + ((j0 + u) << 8) + 8 * lane);
+            mma_bf16(acc0, hv[u].x, hv[u].y, hv[u].z, hv[u].w, tv.x, tv.z);
+            mma_bf16(acc1, hv[u].x, hv[u].y, hv[u].z, hv[u].w, tv.y, tv.w);
           }
         }
       }
-#pragma unroll
-      for (int u = 0; u < DD_U; u++) {
-        if (j0 + u < nfull) {  // warp-uniform
-          mma_bf16(acc0, hv[u].x, hv[u].y, hv[u].z, hv[u].w, tv[u].x, tv[u].z);
-          mma_bf16(acc1, hv[u].x, hv[u].y, hv[u].z, hv[u].w, tv[u].y, tv[u].w);
+      if (s & 255) {  // last, partial run: elements [256*nfull, s)
+        const int i0 = (nfull << 8) + 8 * lane;
+        const int keep = s - i0;
+        uint32_t a[4] = {0u, 0u, 0u, 0u};
+        uint4 tt = make_uint4(0, 0, 0, 0);
+        if (keep > 0) {
+          mask_tail(a, ldg_nc_v4(hrow + i0), keep);
+          tt = lds_v4(s_tap + i0);
         }
+        mma_bf16(acc0, a[0], a[1], a[2], a[3], tt.x, tt.z);
+        mma_bf16(acc1, a[0], a[1], a[2], a[3], tt.y, tt.w);
       }
+      part = diag_part(acc0, acc1, lane);
+    } else {
+      part = ragged_tap_dot(hrow, tap_row(), s, lane);
     }
-    if (s & 255) {  // last, partial run: elements [256*nfull, s)
-      const int i0 = (nfull << 8) + 8 * lane;
-      const int keep = s - i0;
-      uint32_t a[4] = {0u, 0u, 0u, 0u};
-      uint4 tt = make_uint4(0, 0, 0, 0);
-      if (keep > 0) {
-        const uint4 raw = ldg_nc_v4(hrow + i0);
-        tt = ldg_nc_v4(trow + i0);
-        a[0] = raw.x; a[1] = raw.y; a[2] = raw.z; a[3] = raw.w;
-        if (keep < 8) {
-#pragma unroll
-          for (int jj = 0; jj < 4; jj++) {
-            if (2 * jj + 1 >= keep) a[jj] = (2 * jj < keep) ? (a[jj] & 0x0000ffffu) : 0u;
-          }
-        }
-      }
-      mma_bf16(acc0, a[0], a[1], a[2], a[3], tt.x, tt.z);
-      mma_bf16(acc1, a[0], a[1], a[2], a[3], tt.y, tt.w);
-    }
-    // diagonal: D0[g][g] sits in lane (g, q = g/2) register g&1; D1[g+8][g] in the same lane, register 2+(g&1)
-    float part = (q == (g >> 1)) ? ((g & 1) ? (acc0[1] + acc1[3]) : (acc0[0] + acc1[2])) : 0.f;
     part = warp_sum(part);
     if (lane == 0) {
       const float tap0 = __bfloat162float(taps8[(size_t)c * LP + (Lh - 1)]);
       const float y = round_to<bf16>(2.f * fmaf(xp, tap0, part));
       out[(size_t)b * out_rstride + c] = __float2bfloat16_rn(__bfloat162float(xr[c]) + y);
+    }
+  }
+  // ---- arrival counter: the last CTA advances the positions
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int total = gridDim.x * gridDim.y;
+    if (atomicAdd(&pos[1], 1) == total - 1) {
+      pos[1] = 0;
+      for (int i = 0; i < B; i++) {
+        const int tv2 = pos[2 * i];
+        if (tv2 >= 0 && tv2 < 2 * Lh) pos[2 * i] = tv2 + 1;
+      }
+      __threadfence();
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Decode step for a batch whose sequences all stand at the same position (batched generation).
+//
+// The warp-per-(sequence, channel) kernel above is bound by instruction issue, not by memory: every warp
+// recomputes the RMSNorm statistic and the normalised row and takes one row of M_inputs^T through scalar FMAs
+// (~700 of its ~900 instructions), while a plain streaming read of the same history runs at 5.2 TB/s.  Here a
+// CTA owns 8 channels x 8 sequences and both contractions are real MMAs with the sequences as rows:
+//   projection  xp[b][c] = sum_k xn[b][k] MinT[c][k]   rows b, columns = the 8 channels, K split over the 32 warps
+//   taps        y[b]     = sum_i hist[b][c][i] tap_c[s-i]   rows b, every column the tap vector of channel c
+// Warp w streams channel (w & 7) for all eight sequences over the time slice (w >> 3) of four: a lane's 16-byte
+// load is 8 consecutive history values of sequence g = lane / 4, and the k-order inside a 32-value chunk is
+// permuted identically for history and taps, so no shuffles are needed.  The eight tap rows are staged once per
+// CTA in shared memory (reversed, at the alignment of the common position).
+constexpr int R8_U = 8;        // 16-byte history loads a lane keeps in flight
+constexpr int R8_WARPS = 32;
+constexpr int R8_SLICES = 4;
+
+__device__ __forceinline__ void mma_rows8(float (&c)[4], const uint4& a, const uint4& b) {
+  // rows 8..15 of the A tile are zero (a1 = a3 = 0)
+  mma_bf16(c, a.x, 0u, a.y, 0u, b.x, b.y);
+  mma_bf16(c, a.z, 0u, a.w, 0u, b.z, b.w);
+}
+
+__global__ void __launch_bounds__(R8_WARPS * 32, 1)
+    stu_decode_rows8_kernel(const bf16* __restrict__ x, long long x_rstride, const bf16* __restrict__ norm_w,
+                            const bf16* __restrict__ MinT, bf16* __restrict__ hist, const bf16* __restrict__ taps8,
+                            int* __restrict__ pos, bf16* __restrict__ out, long long out_rstride, int B, int d, int Lh,
+                            float eps, int* __restrict__ status, int pdl) {
+  extern __shared__ __align__(16) unsigned char dd_smem[];
+  bf16* s_tap = reinterpret_cast<bf16*>(dd_smem);  // [8][Lh + 8]
+  __shared__ float s_r[8];
+  __shared__ float s_red[R8_WARPS][64];
+  __shared__ float s_xp[64];
+  __shared__ float s_part[R8_SLICES][64];
+  if (pdl & STU_FLAG_EARLY_TRIGGER) pdl_trigger();
+  pdl_wait();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, q = lane & 3;
+  const int LP = Lh + 8;
+  const int c0 = blockIdx.x * 8, b0 = blockIdx.y * 8;
+  const int nb = min(8, B - b0);
+  // ---- common position of the CTA's sequences
+  const int t = pos[2 * b0];
+  int bad = (t < 0 || t >= 2 * Lh) ? 1 : 0;
+  if (tid < nb && pos[2 * (b0 + tid)] != t) bad = 2;
+  bad = __syncthreads_or(bad);
+  if (bad) {
+    // 2: position outside the cache; 6: the caller promised one common position and the batch is ragged
+    if (tid == 0 && status) atomicExch(status, (t < 0 || t >= 2 * Lh) ? 2 : 6);
+  } else {
+    const int p = t & 1, s = t >> 1;
+    const int ch = warp & 7, slice = warp >> 3;
+    const int nch = (s + 31) >> 5;  // 32-value chunks of history, the last one partial
+    const bool rowok = g < nb;
+    const bf16* hrow = hist + ((size_t)((size_t)(b0 + (rowok ? g : 0)) * d + c0 + ch) * 2 + p) * Lh;
+    uint4 hv[R8_U];
+    auto issue = [&](int sc) {  // super-chunk sc = R8_U consecutive chunks
+#pragma unroll
+      for (int u = 0; u < R8_U; u++) {
+        const int i0 = ((sc * R8_U + u) << 5) + q * 8;
+        hv[u] = (rowok && i0 < s) ? ldg_nc_v4(hrow + i0) : make_uint4(0, 0, 0, 0);
+      }
+    };
+    issue(slice);
+    {  // the eight tap rows: elements [0, roundup8(s)) of trow_c[i] = tap_c[s - i]
+      const int o = Lh - 1 - s, e = o & 7;
+      const int nv = (s + 7) >> 3;
+      const bf16* tbase = taps8 + ((size_t)e * d + c0) * LP + (o - e);
+      for (int idx = tid; idx < 8 * nv; idx += R8_WARPS * 32) {
+        const int cc = idx / nv, i = idx - cc * nv;
+        *reinterpret_cast<uint4*>(s_tap + (size_t)cc * LP + 8 * i) = ldg_nc_v4(tbase + (size_t)cc * LP + 8 * i);
+      }
+    }
+    // ---- RMSNorm statistics of the eight rows
+    if (warp < 8) {
+      float r = 0.f;
+      if (warp < nb) {
+        const bf16* xr = x + (size_t)(b0 + warp) * x_rstride;
+        float ss = 0.f;
+        for (int k = lane * 8; k < d; k += 256) {
+          float v[8];
+          load_vec(xr + k, v);
+#pragma unroll
+          for (int j = 0; j < 8; j++) ss += v[j] * v[j];
+        }
+        ss = warp_sum(ss);
+        r = rsqrtf(ss / (float)d + eps);
+      }
+      if (lane == 0) s_r[warp] = r;
+    }
+    __syncthreads();
+    // ---- projection: rows = sequences, columns = the CTA's channels, K chunks dealt round-robin to the warps
+    {
+      float accp[4] = {0.f, 0.f, 0.f, 0.f};
+      const bf16* xr = x + (size_t)(b0 + (rowok ? g : 0)) * x_rstride;
+      const bf16* mrow = MinT + (size_t)(c0 + g) * d;
+      const float rg = s_r[g];
+      for (int kc = warp; kc < ((d + 31) >> 5); kc += R8_WARPS) {  // warp-uniform trip count
+        const int k = (kc << 5) + q * 8;
+        const bool kok = (k + 8) <= d;
+        uint4 xa = make_uint4(0, 0, 0, 0), wv = make_uint4(0, 0, 0, 0);
+        if (kok) {
+          wv = *reinterpret_cast<const uint4*>(mrow + k);
+          if (rowok) xa = norm_pack(*reinterpret_cast<const uint4*>(xr + k), rg, *reinterpret_cast<const uint4*>(norm_w + k));
+        }
+        mma_rows8(accp, xa, wv);
+      }
+      // accp[0], accp[1] = (sequence g, channels 2q, 2q+1)
+      s_red[warp][g * 8 + 2 * q] = accp[0];
+      s_red[warp][g * 8 + 2 * q + 1] = accp[1];
+    }
+    __syncthreads();
+    if (tid < 64) {
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < R8_WARPS; w++) sum += s_red[w][tid];
+      const float xp = round_to<bf16>(sum);
+      s_xp[tid] = xp;
+      const int bb = tid >> 3, cc = tid & 7;
+      if (bb < nb) hist[((size_t)((size_t)(b0 + bb) * d + c0 + cc) * 2 + p) * Lh + s] = __float2bfloat16_rn(xp);
+    }
+    // ---- taps over the stored history [0, s): super-chunks dealt round-robin to the four time slices
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const bf16* tp = s_tap + (size_t)ch * LP;
+    for (int sc = slice; sc * R8_U < nch; sc += R8_SLICES) {
+      if (sc != slice) issue(sc);
+#pragma unroll
+      for (int u = 0; u < R8_U; u++) {
+        if (sc * R8_U + u < nch) {  // warp-uniform: every lane reaches the MMAs
+          const int i0 = ((sc * R8_U + u) << 5) + q * 8;
+          const int keep = s - i0;  // values of this lane's vector that are history (the rest is masked)
+          uint4 tv = make_uint4(0, 0, 0, 0);
+          uint32_t a[4] = {0u, 0u, 0u, 0u};
+          if (keep > 0) {
+            tv = lds_v4(tp + i0);
+            mask_tail(a, hv[u], keep);
+          }
+          mma_rows8(acc, make_uint4(a[0], a[1], a[2], a[3]), tv);
+        }
+      }
+    }
+    if (q == 0) s_part[slice][g * 8 + ch] = acc[0];  // every column of the tile holds the same dot product
+    __syncthreads();
+    if (tid < 64) {
+      const int bb = tid >> 3, cc = tid & 7;
+      if (bb < nb) {
+        float part = 0.f;
+#pragma unroll
+        for (int sl = 0; sl < R8_SLICES; sl++) part += s_part[sl][tid];
+        const float tap0 = __bfloat162float(taps8[(size_t)(c0 + cc) * LP + (Lh - 1)]);
+        const float y = round_to<bf16>(2.f * fmaf(s_xp[tid], tap0, part));
+        const float xin = __bfloat162float(x[(size_t)(b0 + bb) * x_rstride + c0 + cc]);
+        out[(size_t)(b0 + bb) * out_rstride + c0 + cc] = __float2bfloat16_rn(xin + y);
+      }
     }
   }
   // ---- arrival counter: the last CTA advances the positions
@@ -719,15 +991,48 @@ extern "C" int stu_decode_approx(const void* x, long long x_row_stride, const vo
   if (!x || !norm_w || !MinT || !hist || !taps || !pos || !out) return STU_ERR_NULL;
   if (B <= 0 || d <= 0 || Lh <= 0) return STU_ERR_SHAPE;
   cudaStream_t st = (cudaStream_t)stream;
+  const int pdl = dtype & (STU_FLAG_OVERLAP | STU_FLAG_EARLY_TRIGGER);  // honoured by the tensor-core kernels
+  const bool uniform = (dtype & STU_FLAG_UNIFORM_POS) != 0;
+  dtype &= ~(STU_FLAG_OVERLAP | STU_FLAG_EARLY_TRIGGER | STU_FLAG_UNIFORM_POS);
+  if (taps8 && dtype == STU_BF16 && uniform && d % 8 == 0 && Lh % 8 == 0 &&
+      (size_t)8 * (Lh + 8) * sizeof(bf16) <= (size_t)180 * 1024) {
+    // common position promised by the caller: 8 channels x 8 sequences per CTA, both contractions as MMAs
+    if (x_row_stride % 8 || !aligned16(x) || !aligned16(MinT) || !aligned16(hist) || !aligned16(norm_w) ||
+        !aligned16(taps8))
+      return STU_ERR_ALIGN;
+    const size_t dsm = (size_t)8 * (Lh + 8) * sizeof(bf16);
+    cudaError_t ae = cudaFuncSetAttribute(stu_decode_rows8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)dsm);
+    if (ae != cudaSuccess) return (int)ae;
+    dim3 gd(d / 8, (B + 7) / 8);
+    cudaError_t le = launch_maybe_overlapped(stu_decode_rows8_kernel, gd, dim3(R8_WARPS * 32), dsm, st,
+                                             (pdl & STU_FLAG_OVERLAP) != 0, (const bf16*)x, x_row_stride,
+                                             (const bf16*)norm_w, (const bf16*)MinT, (bf16*)hist,
+                                             (const bf16*)taps8, pos, (bf16*)out, out_row_stride, B, d, Lh, eps,
+                                             status, pdl);
+    if (le != cudaSuccess) return (int)le;
+    STU_CHECK_LAUNCH();
+    return STU_OK;
+  }
   if (taps8 && dtype == STU_BF16) {
     // tensor-core kernel: needs the reversed 8-alignment tap table
     if (d % 8 || Lh % 8 || x_row_stride % 8 || !aligned16(x) || !aligned16(MinT) || !aligned16(hist) ||
         !aligned16(norm_w) || !aligned16(taps8))
       return STU_ERR_ALIGN;
     dim3 gd(d, (B + 7) / 8);
-    stu_decode_diag_kernel<<<gd, 256, 0, st>>>((const bf16*)x, x_row_stride, (const bf16*)norm_w, (const bf16*)MinT,
-                                               (bf16*)hist, (const bf16*)taps8, pos, (bf16*)out, out_row_stride, B, d,
-                                               Lh, eps, status);
+    const size_t dsm = (size_t)(Lh + 8) * sizeof(bf16);
+    if (dsm > 48 * 1024) {
+      if (dsm > 200 * 1024) return STU_ERR_UNSUPPORTED;
+      cudaError_t ae = cudaFuncSetAttribute(stu_decode_diag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            (int)dsm);
+      if (ae != cudaSuccess) return (int)ae;
+    }
+    cudaError_t le = launch_maybe_overlapped(stu_decode_diag_kernel, gd, dim3(256), dsm, st,
+                                             (pdl & STU_FLAG_OVERLAP) != 0, (const bf16*)x, x_row_stride,
+                                             (const bf16*)norm_w, (const bf16*)MinT, (bf16*)hist,
+                                             (const bf16*)taps8, pos, (bf16*)out, out_row_stride, B, d, Lh, eps,
+                                             status, pdl);
+    if (le != cudaSuccess) return (int)le;
     STU_CHECK_LAUNCH();
     return STU_OK;
   }

@@ -39,7 +39,7 @@ class STULayer(nn.Module):
             entry = self.stu.full_decode_step(xn, x2, mid, entry)
         inter = self.mlp.intermediate_size
         if ops.can_fuse_norm(B, inter, d, ops.EPI_GELU_MUL, x.dtype):
-            self.mlp.apply_residual(mid, mid, x2, norm_w=self.mlp_norm.weight, eps=self.mlp_norm.eps)
+            self.mlp.apply_residual(mid, mid, x2, norm_w=self.mlp_norm.weight, eps=self.mlp_norm.eps, overlap=True)
         else:
             self.mlp.apply_residual(ops.rmsnorm(mid, self.mlp_norm.weight, self.mlp_norm.eps), mid, x2)
         return entry
@@ -80,7 +80,7 @@ class AttentionLayer(nn.Module):
         ops.linear(y.view(B * T, d), self.attn.c_proj.weight, resid=x2, out=x2, epilogue=ops.EPI_RESID)
         inter = self.mlp.intermediate_size
         if T == 1 and ops.can_fuse_norm(B, inter, d, ops.EPI_GELU_MUL, x.dtype):
-            self.mlp.apply_residual(x2, x2, x2, norm_w=self.mlp_norm.weight, eps=self.mlp_norm.eps)
+            self.mlp.apply_residual(x2, x2, x2, norm_w=self.mlp_norm.weight, eps=self.mlp_norm.eps, overlap=True)
         else:
             self.mlp.apply_residual(ops.rmsnorm(x2, self.mlp_norm.weight, self.mlp_norm.eps), x2, x2)
         if xc is not x:

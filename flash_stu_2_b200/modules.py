@@ -73,11 +73,13 @@ class MLP(nn.Module):
         self.dropout = nn.Dropout(config.dropout)
 
     def apply_residual(self, xn2d: torch.Tensor, resid2d: torch.Tensor, out2d: torch.Tensor,
-                       norm_w: Optional[torch.Tensor] = None, eps: float = ops.RMS_EPS):
-        """out = resid + down(gelu(gate(xn)) * up(xn)); with norm_w, xn is RMS-normalised inside the kernel."""
-        h = ops.linear(xn2d, self.gate_proj.weight, W2=self.up_proj.weight, epilogue=ops.EPI_GELU_MUL,
+                       norm_w: Optional[torch.Tensor] = None, eps: float = ops.RMS_EPS, overlap: bool = False):
+        """out = resid + down(gelu(gate(xn)) * up(xn)); with norm_w, xn is RMS-normalised inside the kernel.
+        overlap (decode steps): both kernels fetch their weights while the kernel before them is still running."""
+        ov = ops.FLAG_OVERLAP if (overlap and ops.overlap_decode) else 0
+        h = ops.linear(xn2d, self.gate_proj.weight, W2=self.up_proj.weight, epilogue=ops.EPI_GELU_MUL | ov,
                        norm_w=norm_w, eps=eps)
-        return ops.linear(h, self.down_proj.weight, resid=resid2d, out=out2d, epilogue=ops.EPI_RESID)
+        return ops.linear(h, self.down_proj.weight, resid=resid2d, out=out2d, epilogue=ops.EPI_RESID | ov)
 
     def forward(self, x):
         x2 = x.reshape(-1, x.shape[-1])
@@ -261,6 +263,7 @@ class STU(nn.Module):
 
     tensor_core_conv = True    # class switches used by tests to compare the tensor-core and CUDA-core kernels
     tensor_core_decode = True
+    shared_tap_decode = True   # batches at one common position: the kernel with 8 channels x 8 sequences per CTA
 
     def decode_step(self, x2d: torch.Tensor, norm_w: torch.Tensor, eps: float, entry, out2d: torch.Tensor):
         """out = x + STU(rmsnorm(x)) for one new token per sequence; appends to the cache."""
@@ -270,7 +273,9 @@ class STU(nn.Module):
         if t + 1 > self.seq_len:
             raise ValueError(f"sequence position {t + 1} exceeds seq_len={self.seq_len}")
         ops.decode_approx(x2d, norm_w, MinT, hist, taps, pos, out2d, eps,
-                          taps8=taps8 if STU.tensor_core_decode else None)
+                          taps8=taps8 if STU.tensor_core_decode else None,
+                          flags=(ops.FLAG_EARLY_TRIGGER if ops.overlap_decode else 0) |
+                                (ops.FLAG_UNIFORM_POS if (uniform_pos(pos) and STU.shared_tap_decode) else 0))
         pos._host_t = t + 1
         return hist, pos
 

@@ -12,6 +12,17 @@ from . import _lib
 
 EPI_STORE, EPI_RESID, EPI_GELU_MUL, EPI_HIST = 0, 1, 2, 3
 EPI_FLAG_CAUSAL = 0x100  # OR-ed into the epilogue: the weight is lower triangular
+# Overlapped (programmatic dependent) launches of the decode kernels: OR-ed into the epilogue code of linear() and
+# passed as flags to decode_approx().  FLAG_OVERLAP: the kernel may start while its predecessor in the stream is
+# still running and fetches its constants (weights; history and taps) meanwhile; FLAG_EARLY_TRIGGER: it lets its
+# own successor start at once.  The decode paths of the layers use them when overlap_decode is True: the MLP kernels
+# overlap their weight fetch with the drain of the kernel before them (measured 1.3 us per layer step on a B200);
+# the STU decode kernel only triggers early - letting it start early made the step slower, its history loads
+# compete with the down projection it would overlap.
+FLAG_OVERLAP = 0x200
+FLAG_EARLY_TRIGGER = 0x400
+FLAG_UNIFORM_POS = 0x800  # decode_approx: every sequence of the batch stands at the same position (checked on device)
+overlap_decode = True
 BACKEND_AUTO, BACKEND_SIMT, BACKEND_TCGEN05, BACKEND_SKINNY = 0, 1, 2, 3
 RMS_EPS = float(torch.finfo(torch.float32).eps)  # what torch.nn.RMSNorm(eps=None) resolves to
 
@@ -58,7 +69,8 @@ def status_word(device) -> torch.Tensor:
 
 STATUS_TEXT = {1: "token id outside the vocabulary", 2: "position outside the cache capacity (seq_len)",
                3: "a bounded mbarrier wait ran out inside the tcgen05 GEMM", 4: "more top-k ties than the candidate list holds",
-               5: "top_p without top_k is not implemented on the device"}
+               5: "top_p without top_k is not implemented on the device",
+               6: "decode step told that all sequences share one position, but the cached positions differ"}
 
 
 def check_status(device=None):
@@ -191,9 +203,11 @@ def conv_prefill_approx_static(hist, taps, x, t0: int, t_end: int, use_tensor_co
     return x
 
 
-def decode_approx(x, norm_w, MinT, hist, taps, pos, out, eps: float = RMS_EPS, taps8=None):
+def decode_approx(x, norm_w, MinT, hist, taps, pos, out, eps: float = RMS_EPS, taps8=None, flags: int = 0):
     """One fused decode step of an approx STU layer (norm, projection, cache append, taps, residual).
-    With taps8 (bf16) the tensor-core kernel runs, otherwise the CUDA-core one."""
+    With taps8 (bf16) a tensor-core kernel runs, otherwise the CUDA-core one.  flags: FLAG_UNIFORM_POS selects the
+    kernel for batches at one common position (taps shared between sequences); FLAG_EARLY_TRIGGER lets an
+    overlapped successor (the MLP's gate/up kernel) start fetching its weights while this kernel runs."""
     _cuda(x, norm_w, MinT, hist, taps, pos, out, taps8)
     B, d, _, Lh = hist.shape
     assert x.shape == (B, d) and out.shape == (B, d) and x.stride(1) == 1 and out.stride(1) == 1
@@ -202,7 +216,7 @@ def decode_approx(x, norm_w, MinT, hist, taps, pos, out, eps: float = RMS_EPS, t
     rc = _lib.load().stu_decode_approx(x.data_ptr(), x.stride(0), norm_w.data_ptr(), MinT.data_ptr(), hist.data_ptr(),
                                        taps.data_ptr(), _p(taps8), pos.data_ptr(), out.data_ptr(), out.stride(0), B, d,
                                        Lh, eps,
-                                       status_word(x.device).data_ptr(), _dt(x), _stream())
+                                       status_word(x.device).data_ptr(), _dt(x) | flags, _stream())
     _lib.check(rc, "stu_decode_approx")
     _count()
     return out

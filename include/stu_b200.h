@@ -54,6 +54,10 @@ int stu_embed(const long long* ids, const void* table, void* out, int rows, int 
  *              decode shapes (see stu_linear_can_fuse_norm), otherwise -4.
  *   backend    0 auto (M<=64: weight-streaming mma.sync/FMA kernel; bf16 aligned: tcgen05+TMA GEMM; else
  *              CUDA-core GEMM), 1 CUDA-core, 2 tcgen05, 3 decode kernel. */
+/* epilogue flags: 0x100 = W is lower triangular (k-blocks above the diagonal are skipped); 0x200 = launch with
+ * programmatic stream serialization: the kernel fetches W (which the preceding kernel must not write) while that
+ * kernel drains, and reads x only after it has completed (skinny shapes, M <= 64; ignored otherwise);
+ * 0x400 = let the next 0x200 launch start at once. */
 int stu_linear(const void* x, long long x_row_stride, const void* W, long long w_row_stride, long long w_k_stride,
                const void* W2, const void* resid, long long resid_row_stride, void* y, long long y_row_stride,
                int M, int N, int K, int epilogue, int hist_T, int hist_t0, int hist_Lh, const void* norm_w,
@@ -93,6 +97,9 @@ int stu_conv_prefill_approx_static(const void* hist, const void* taps, void* x, 
  * flash_stu/layers/stu_layer.py:78-93.  out must not alias x.
  * taps8 (bf16 only, may be NULL) is the table made by stu_taps_rev8; with it the step runs on mma.sync tensor
  * cores, without it on CUDA cores (one warp per sequence and channel).
+ * Flags OR-ed into dtype: 0x800 = every sequence stands at the same position (checked on the device, status 6
+ * if not): selects the kernel that owns 8 channels x 8 sequences per CTA and shares the taps between sequences;
+ * 0x400 = let a following stu_linear launched with 0x200 start before this kernel has finished.
  */
 int stu_decode_approx(const void* x, long long x_row_stride, const void* norm_w, const void* MinT, void* hist,
                       const void* taps, const void* taps8, int* pos, void* out, long long out_row_stride, int B,

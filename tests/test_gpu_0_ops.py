@@ -182,6 +182,44 @@ def test_decode_step_equals_prefill_row(dt, tc, shape):
     assert rel(hist, _hist_from(xp, Lh)) <= (1e-5 if dt == torch.float32 else 1e-2)
 
 
+@pytest.mark.parametrize("shape", [(3, 45, 64, 64), (9, 70, 40, 160), (8, 300, 256, 600), (17, 140, 1024, 300)])
+def test_decode_step_shared_tap_kernel(shape):
+    """Batches at one common position: the kernel that owns 8 channels x 8 sequences per CTA (taps staged once
+    in shared memory, projection and tap contraction as MMAs with the sequences as rows) reproduces the
+    full-prefix rows; a ragged batch under the same flag is refused with status 6 and leaves the cache alone."""
+    from flash_stu_2_b200 import ops
+    dt = torch.bfloat16
+    B, T, d, L = shape
+    Lh = ((L + 1) // 2 + 7) // 8 * 8
+    x, nw, Mi, fp, xp, ref = _decode_fixture(dt, B, T, d, L)
+    hist = torch.zeros(B, d, 2, Lh, dtype=dt, device=dev())
+    pos = torch.zeros(B, 2, dtype=torch.int32, device=dev())
+    taps = ops.taps_even(fp.to(dev()), Lh)
+    taps8 = ops.taps_rev8(taps)
+    MinT = Mi.t().contiguous().to(dev())
+    xd, nwd = x.to(dev()), nw.to(dev())
+    outs = []
+    for t in range(T):
+        out = torch.empty(B, d, dtype=dt, device=dev())
+        ops.decode_approx(xd[:, t].contiguous(), nwd, MinT, hist, taps, pos, out, taps8=taps8,
+                          flags=ops.FLAG_UNIFORM_POS)
+        outs.append(out)
+    ops.check_status()
+    got = torch.stack(outs, 1).cpu()
+    assert pos[:, 0].tolist() == [T] * B and int(pos[0, 1]) == 0
+    assert rel(got, ref) <= 1.5e-2, rel(got, ref)
+    assert rel(hist, _hist_from(xp, Lh)) <= 1e-2
+    if B > 1:
+        pos[:, 0] = 5
+        pos[1, 0] = 4          # ragged inside the first group of eight sequences
+        before = hist.clone()
+        ops.decode_approx(xd[:, 5].contiguous(), nwd, MinT, hist, taps, pos, out, taps8=taps8,
+                          flags=ops.FLAG_UNIFORM_POS)
+        with pytest.raises(RuntimeError, match="status 6"):
+            ops.check_status()
+        assert torch.equal(before[:2], hist[:2])
+
+
 @pytest.mark.parametrize("tc", [False, True])
 def test_decode_step_with_ragged_positions(tc):
     """Sequences of one batch at different positions (what _reorder_cache / ragged prompts produce)."""

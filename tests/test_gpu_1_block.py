@@ -112,3 +112,55 @@ def test_block_properties_at_benchmark_width():
     lsd = {k[len("layer."):]: v for k, v in sd.items() if k.startswith("layer.")}
     ref = O.stu_layer(x[:1], lsd, sd["phi"], O.fft_length(L), True)
     assert O.rel_err(full[:1], ref) <= 2e-2
+
+
+def test_overlapped_decode_launches_equal_plain_launches(golden):
+    """The decode kernels launched with programmatic stream serialization (prefetch of weights / history while
+    the preceding kernel drains) give bit-identical rows to plain stream-ordered launches, eagerly and when the
+    token step is replayed from a captured CUDA graph."""
+    from flash_stu_2_b200 import ops
+    r = golden("blocks")["approx_bfloat16"]
+    blk = make_block(r, torch.bfloat16)
+    x = r["x"].to(dev())
+    T = x.shape[1]
+    T1 = T - 24
+
+    def run(overlap, graph):
+        ops.overlap_decode = overlap
+        try:
+            with torch.no_grad():
+                _, cache = blk(x[:, :T1].clone(), use_cache=True)
+                step = torch.empty_like(x[:, :1])
+                rows = []
+                g = None
+                if graph:
+                    # two eager steps first (derived weights, scratch), then capture one step and rewind
+                    for t in range(T1, T1 + 2):
+                        step.copy_(x[:, t:t + 1])
+                        blk(step, past_key_value=cache, use_cache=True)
+                    cache[1][:, 0] = T1
+                    cache[1]._host_t = T1
+                    torch.cuda.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        blk(step, past_key_value=cache, use_cache=True)
+                    cache[1][:, 0] = T1
+                    cache[1]._host_t = T1
+                for t in range(T1, T):
+                    step.copy_(x[:, t:t + 1])
+                    if g is not None:
+                        g.replay()
+                    else:
+                        blk(step, past_key_value=cache, use_cache=True)
+                    rows.append(step.clone())
+                torch.cuda.synchronize()
+                assert int(cache[1][0, 0]) == T
+            return torch.cat(rows, 1).cpu()
+        finally:
+            ops.overlap_decode = True
+
+    plain = run(False, False)
+    assert torch.equal(run(True, False), plain)
+    assert torch.equal(run(True, True), plain)
+    ops.check_status()
+    assert O.rel_err(plain, r["y"][:, T1:]) <= 2e-2
