@@ -30,9 +30,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 D_MODEL, NUM_FILTERS = 1024, 24
-# dram__bytes_read.sum + dram__bytes_write.sum of one stu_decode_kernel launch at B=8, L=8192, t~7690, from the
+# dram__bytes_read.sum + dram__bytes_write.sum of one stu_decode_rows8_kernel launch at B=8, L=8192, t~7690, from the
 # ncu capture summarised in profiles/stu_decode_kernel_block_8k.md (algorithmic bytes there: 73.0 MB)
-DECODE_KERNEL_DRAM_BYTES = 79.5e6
+DECODE_KERNEL_DRAM_BYTES = 79.8e6
 
 
 def parse():
@@ -45,6 +45,8 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=8192, help="context length (default: the benchmark's 8192)")
     ap.add_argument("--decode-steps", type=int, default=512)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-split", action="store_true",
+                    help="also time every kernel of the token step in a graph of its own (adds `decode_split`)")
     ap.add_argument("--no-overlap", action="store_true",
                     help="plain stream-ordered launches for the decode kernels (no programmatic dependent launch)")
     ap.add_argument("--no-graph", action="store_true", help="launch decode steps eagerly instead of replaying a CUDA graph")
@@ -339,6 +341,47 @@ def run_b200(a):
         # the even taps of every channel, M_inputs, and the token's row in and out
         kern_bytes = B * d * (t_mid / 2) * 2 + d * (t_mid / 2 + 1) * 2 + d * d * 2 + 3 * B * d * 2
 
+        # ---- optional: every kernel of the token step in a graph of its own (64 launches each)
+        split = None
+        if a.kernel_split and not a.no_graph:
+            mlp = layer.mlp
+            mid = torch.empty_like(x2)
+            hbuf = torch.empty(B, mlp.intermediate_size, dtype=torch.bfloat16, device=dev)
+
+            def graph_us(fn, n=64):
+                rewind()
+                for _ in range(2):
+                    fn()
+                g, _ = capture(lambda: [fn() for _ in range(n)])
+                best = float("inf")
+                for _ in range(3):
+                    rewind()
+                    torch.cuda.synchronize()
+                    g0, g1 = ev(), ev()
+                    g0.record(); g.replay(); g1.record()
+                    torch.cuda.synchronize()
+                    best = min(best, g0.elapsed_time(g1) / n * 1e3)
+                return best
+
+            def dec(flags):
+                ops.decode_approx(x2, layer.stu_norm.weight, MinT, hist, taps, pos, mid, taps8=taps8, flags=flags)
+
+            def gate_up(f=0):
+                ops.linear(mid, mlp.gate_proj.weight, W2=mlp.up_proj.weight, out=hbuf, epilogue=ops.EPI_GELU_MUL | f,
+                           norm_w=layer.mlp_norm.weight, eps=layer.mlp_norm.eps)
+
+            def down(f=0):
+                ops.linear(hbuf, mlp.down_proj.weight, resid=mid, out=out2, epilogue=ops.EPI_RESID | f)
+
+            UN, OV, EA = ops.FLAG_UNIFORM_POS, ops.FLAG_OVERLAP, ops.FLAG_EARLY_TRIGGER
+            split = {"unit": "us per launch, 64 launches replayed from one graph",
+                     "stu_decode_rows8_kernel": graph_us(lambda: dec(UN)),
+                     "stu_decode_diag_kernel": graph_us(lambda: dec(0)),
+                     "skinny gate/up (norm fused)": graph_us(gate_up),
+                     "skinny down (+residual)": graph_us(down),
+                     "step, plain launches": graph_us(lambda: (dec(UN), gate_up(), down())),
+                     "step, MLP kernels overlapped": graph_us(lambda: (dec(UN | EA), gate_up(OV), down(OV)))}
+
         # ---- end to end through the module API from pinned host memory
         y_host = torch.empty(B, 1, d, dtype=torch.bfloat16).pin_memory()
         yp_host = torch.empty(B, L, d, dtype=torch.bfloat16).pin_memory()
@@ -412,6 +455,8 @@ def run_b200(a):
     }
     if (B, L, d) == (8, 8192, 1024):
         line["roofline"]["traffic"] = DECODE_KERNEL_DRAM_BYTES
+    if split is not None:
+        line["decode_split"] = split
     if world == 1 and not a.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(a, make_state(L), x_host)
     print(json.dumps(line))
