@@ -260,6 +260,51 @@ def golden_slopes():
     save("alibi_slopes", out)
 
 
+def golden_c1_full(tmp):
+    """The 12-layer d=512 fp32 configuration at full size (6 STU + 6 sliding-window layers, vocabulary 50257,
+    seq_len 2048, mlp_scale 12): batch 2, prompt 128, 128 greedy tokens through the reference's own generate()
+    (no cache, sgn re-sliced per step).  Weights are synthetic (synth_weights.fill_state_dict) so that the test
+    can rebuild them; the fixture holds the filters, the prompt, the generated ids, the margin between the two
+    largest logits at every step and a sample of the logits at the last prompt position."""
+    sys.path.insert(0, HERE)
+    from synth_weights import fill_state_dict, C1_CONFIG, C1_SEED
+    cfg = dict(C1_CONFIG)
+    L, K = cfg["seq_len"], cfg["num_eigh"]
+    phi = make_phi(L, K)
+    fp = os.path.join(tmp, f"phi_{L}_{K}.pt")
+    save_spectral_filters(phi, fp)
+    m = FlashSTU(FlashSTUConfig(filter_path=fp, use_flash_fft=False, torch_dtype=torch.float32, **cfg)).eval()
+    shapes = {k: v.shape for k, v in m.state_dict().items()}
+    sd = fill_state_dict(shapes, C1_SEED)
+    missing = m.load_state_dict(sd, strict=False)
+    assert set(missing.missing_keys) <= {"phi"} and not missing.unexpected_keys, missing
+    full = full_sgn(m)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg["vocab_size"], (2, 128), generator=g)
+    margins, first_logits = [], []
+    orig_forward = m.forward
+
+    def fwd(input_ids, *a, **k):
+        set_len(m, input_ids.shape[1], full)
+        out = orig_forward(input_ids, *a, **k)
+        last = out.logits[:, -1].float()
+        top2 = last.topk(2, dim=-1).values
+        margins.append((top2[:, 0] - top2[:, 1]).clone())
+        if not first_logits:
+            first_logits.append(last.clone())
+        return out
+
+    m.forward = fwd
+    with torch.no_grad():
+        gen = m.generate(ids, max_length=256, do_sample=False, use_cache=False)
+    rec = {"phi": m.state_dict()["phi"].clone(), "prompt": ids, "gen_greedy": gen.clone(),
+           "margins": torch.stack(margins, 1), "logits_prompt_end_sample": first_logits[0][:, ::16].clone(),
+           "logits_prompt_end_top": first_logits[0].topk(32, dim=-1), "shapes": {k: tuple(v) for k, v in shapes.items()},
+           "attention_pinned": False}
+    rec["logits_prompt_end_top"] = (rec["logits_prompt_end_top"].values.clone(), rec["logits_prompt_end_top"].indices.clone())
+    save("c1_full", rec)
+
+
 if __name__ == "__main__":
     with tempfile.TemporaryDirectory() as tmp:
         golden_stu_modules(tmp)
@@ -267,3 +312,4 @@ if __name__ == "__main__":
         golden_blocks(tmp)
         golden_mini(tmp)
         golden_slopes()
+        golden_c1_full(tmp)

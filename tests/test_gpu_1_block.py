@@ -1,5 +1,7 @@
 """FlashSTUBlock on a B200 against the reference's own outputs (tests/golden/blocks.pt) and the
 size-independent properties of the cached token loop."""
+import os
+
 import pytest
 import torch
 
@@ -164,3 +166,41 @@ def test_overlapped_decode_launches_equal_plain_launches(golden):
     assert torch.equal(run(True, True), plain)
     ops.check_status()
     assert O.rel_err(plain, r["y"][:, T1:]) <= 2e-2
+
+
+@pytest.mark.parametrize("approx", [True, False])
+def test_benchmark_block_at_full_size_against_the_oracle(approx):
+    """The benchmark block at its full size (d_model=1024, K=24, L=8192, bf16; both STU variants), two sequences:
+    a prefill over all 8192 positions and the last 24 positions again as cached single-token steps, against the
+    CPU oracle on the same weights and inputs (bf16 tolerance 2e-2)."""
+    import flash_stu_2_b200 as F
+    from flash_stu_2_b200 import ops
+    torch.manual_seed(1)
+    L, K, d, B = 8192, 24, 1024, 2
+    dt = torch.bfloat16
+    fpath = os.path.join(os.path.dirname(F.__file__), "data", f"phi_{L}_{K}.pt")
+    phi = F.load_spectral_filters(fpath, device="cpu", dtype=dt, verify_shape=(L, K))
+    cfg = F.FlashSTUConfig(n_embd=d, seq_len=L, num_eigh=K, use_attn=False, use_approx=approx, mlp_scale=4,
+                           torch_dtype=dt, n_layers=1, vocab_size=1, n_heads=16)
+    blk = F.FlashSTUBlock(config=cfg, phi=phi, n=O.fft_length(L))
+    for n_, p in blk.named_parameters():
+        if ".stu.M_" in n_:
+            torch.nn.init.xavier_normal_(p)
+    sd = {k: v.clone() for k, v in blk.state_dict().items()}
+    blk = blk.to(dev()).eval()
+    x = torch.randn(B, L, d).to(dt)
+    S = 24
+    with torch.no_grad():
+        full = blk(x.clone().to(dev())).cpu()
+        y1, cache = blk(x[:, :L - S].clone().to(dev()), use_cache=True)
+        rows = []
+        for t in range(L - S, L):
+            yt, cache = blk(x[:, t:t + 1].clone().to(dev()), past_key_value=cache, use_cache=True)
+            rows.append(yt.cpu())
+    ops.check_status()
+    lsd = {k[len("layer."):]: v for k, v in sd.items() if k.startswith("layer.")}
+    # one sequence at a time: the full variant's FFT stack takes 10 GB of host memory per sequence
+    ref = torch.cat([O.stu_layer(x[b:b + 1], lsd, sd["phi"], O.fft_length(L), approx) for b in range(B)])
+    assert O.rel_err(full, ref) <= 2e-2, O.rel_err(full, ref)
+    assert O.rel_err(torch.cat(rows, 1), ref[:, L - S:]) <= 2e-2
+    assert O.rel_err(y1.cpu(), ref[:, :L - S]) <= 2e-2

@@ -105,3 +105,24 @@ def test_lds_params_fixture(golden):
     p = golden("lds_params")
     assert p["A"].shape == (160,) and p["C"].shape == (160, 48) and p["B"].shape == (1, 160)
     assert float(p["A"].abs().max()) < 1.0
+
+
+def test_full_size_12_layer_model_prompt_logits(golden):
+    """The oracle on the full-size d=512 / 12-layer / vocabulary-50257 configuration: logits at the end of the
+    128-token prompt and the first greedy token against the reference's run (fixture c1_full; synthetic weights
+    rebuilt from the shared seeded generator)."""
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location(
+        "synth_weights", os.path.join(os.path.dirname(__file__), "golden", "synth_weights.py"))
+    sw = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(sw)
+    r = golden("c1_full")
+    sd = sw.fill_state_dict(r["shapes"], sw.C1_SEED)
+    sd["phi"] = r["phi"]
+    with torch.no_grad():
+        last = O.model_logits(r["prompt"], sd, dict(sw.C1_CONFIG), last_only=True).float()
+    assert O.rel_err(last[:, ::16], r["logits_prompt_end_sample"]) <= 1e-5
+    top_v, top_i = r["logits_prompt_end_top"]
+    assert torch.equal(last.argmax(-1), top_i[:, 0])
+    assert torch.equal(last.argmax(-1), r["gen_greedy"][:, r["prompt"].shape[1]])
