@@ -45,6 +45,10 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=8192, help="context length (default: the benchmark's 8192)")
     ap.add_argument("--decode-steps", type=int, default=512)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--model", choices=["c1", "c3"], default=None,
+                    help="instead of the headline block workload, time FlashSTU.generate() on a whole model: "
+                         "c1 = d512/12 layers/fp32/B=2/prompt 128/+128 greedy; "
+                         "c3 = d1536/24 layers/bf16/B=32/prompt 2048/+512, top_k=40, T=0.8")
     ap.add_argument("--kernel-split", action="store_true",
                     help="also time every kernel of the token step in a graph of its own (adds `decode_split`)")
     ap.add_argument("--no-overlap", action="store_true",
@@ -464,9 +468,81 @@ def run_b200(a):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------------------------- whole models
+MODEL_CONFIGS = {
+    "c1": dict(cfg=dict(n_embd=512, n_layers=12, n_heads=8, seq_len=2048, window_size=512, vocab_size=50257,
+                        mlp_scale=12, num_eigh=24, use_attn=True, use_approx=True), dtype="float32", B=2, prompt=128,
+               new=128, sampling=dict(do_sample=False)),
+    "c3": dict(cfg=dict(n_embd=1536, n_layers=24, n_heads=12, seq_len=8192, window_size=1024, vocab_size=50257,
+                        mlp_scale=4, num_eigh=24, use_attn=True, use_approx=True), dtype="bfloat16", B=32, prompt=2048,
+               new=512, sampling=dict(do_sample=True, temperature=0.8, top_k=40)),
+}
+
+
+def run_model(a):
+    """FlashSTU.generate() on a whole model with random-init weights (secondary workloads; the headline is the
+    block).  Decode tokens/s = B * (new - 1) / (time of a full generate - time of a generate that stops after the
+    first new token), CUDA events, one GPU."""
+    import tempfile
+    import flash_stu_2_b200 as F
+    from flash_stu_2_b200 import ops
+    from oracle import stu_oracle as O   # only for the filter values (host eigh) when no filter file is shipped
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py --model needs a CUDA device: the kernels have no CPU fallback")
+    dev = torch.device("cuda:0")
+    spec = MODEL_CONFIGS[a.model]
+    cfg, dt = dict(spec["cfg"]), getattr(torch, spec["dtype"])
+    L, K = cfg["seq_len"], cfg["num_eigh"]
+    with tempfile.TemporaryDirectory() as tmp:
+        fp = filter_file(L)
+        if fp is None:
+            fp = os.path.join(tmp, "phi.pt")
+            F.save_spectral_filters(O.spectral_filters(L, K), fp)
+        torch.manual_seed(0)
+        model = F.FlashSTU(F.FlashSTUConfig(filter_path=fp, torch_dtype=dt, **cfg)).to(dev).eval()
+    B, T0, new = spec["B"], spec["prompt"], spec["new"]
+    ids = torch.randint(0, cfg["vocab_size"], (B, T0), device=dev)
+    gen = torch.Generator(device=dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def timed(max_length, graph):
+        gen.manual_seed(0)
+        e0, e1 = ev(), ev()
+        torch.cuda.synchronize()
+        e0.record()
+        out = model.generate(ids, max_length=max_length, generator=gen, cuda_graph=graph, **spec["sampling"])
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1), out
+
+    res = {}
+    for graph in (True, False):
+        timed(T0 + 8, graph)                                    # warm-up (derived weights, scratch)
+        t_first = min(timed(T0 + 1, graph)[0] for _ in range(2))
+        t_full, out = timed(T0 + new, graph)
+        res[graph] = (t_first, t_full, out)
+    ops.check_status()
+    t_first, t_full, out = res[True]
+    dec_ms = t_full - t_first
+    n_param = sum(p.numel() for p in model.parameters())
+    print(json.dumps({
+        "metric": "decode tokens/s (aggregate over GPUs)", "value": B * (new - 1) / (dec_ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": 1, "higher_is_better": True, "dtype": spec["dtype"], "data": "synthetic",
+        "config": {"workload": f"FlashSTU.generate {a.model}: {cfg['n_layers']} layers d={cfg['n_embd']} "
+                               f"V={cfg['vocab_size']} L={L} B={B} prompt {T0} +{new} tokens, {n_param / 1e6:.0f} M parameters",
+                   "sampling": spec["sampling"], "decode_launch": "one CUDA graph per token step"},
+        "decode_ms_per_token_step": dec_ms / (new - 1),
+        "prefill": {"value": B * T0 / (t_first * 1e-3), "unit": "tokens/s", "ms": t_first},
+        "eager_loop": {"decode_tokens_per_s": B * (new - 1) / ((res[False][1] - res[False][0]) * 1e-3),
+                       "same_tokens_as_graph": bool(torch.equal(out, res[False][2]))},
+    }))
+
+
 if __name__ == "__main__":
     args = parse()
     if args.impl == "reference":
         run_reference(args)
+    elif args.model:
+        run_model(args)
     else:
         run_b200(args)

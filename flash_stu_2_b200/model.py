@@ -12,6 +12,7 @@ from typing import Any, Dict, Optional, Tuple
 
 import torch
 import torch.nn as nn
+import transformers
 from transformers import PreTrainedModel
 from transformers.modeling_outputs import CausalLMOutputWithPast
 
@@ -24,7 +25,10 @@ from .modules import STU, Attention, RMSNorm
 
 class FlashSTU(PreTrainedModel):
     config_class = FlashSTUConfig
-    _tied_weights_keys = ["lm_head.weight"]
+    # lm_head.weight is tok_emb.weight (flash_stu/model.py:50,99-102); transformers >= 5 wants the tie as a
+    # {tied: source} mapping, older versions as a list of tied keys
+    _tied_weights_keys = ({"lm_head.weight": "tok_emb.weight"} if int(transformers.__version__.split(".")[0]) >= 5
+                          else ["lm_head.weight"])
 
     def __init__(self, config: FlashSTUConfig) -> None:
         super().__init__(config)
@@ -50,7 +54,22 @@ class FlashSTU(PreTrainedModel):
         self.lm_head = nn.Linear(config.n_embd, config.vocab_size, bias=False, dtype=config.torch_dtype)
         self.tok_emb.weight = self.lm_head.weight
         self.std = config.n_embd ** -0.5
-        self.apply(self._init_weights)
+        # registers the tie and the other bookkeeping transformers keeps per model, then applies _init_weights to
+        # every module (what the reference does with self.apply, flash_stu/model.py:104-105)
+        self.post_init()
+
+    # ------------------------------------------------------------------ embeddings (resize_token_embeddings)
+    def get_input_embeddings(self):
+        return self.tok_emb
+
+    def set_input_embeddings(self, value):
+        self.tok_emb = value
+
+    def get_output_embeddings(self):
+        return self.lm_head
+
+    def set_output_embeddings(self, value):
+        self.lm_head = value
 
     # ------------------------------------------------------------------ backbone
     def _backbone(self, input_ids, past_key_values, use_cache: bool, collect_hidden: bool = False):
@@ -142,8 +161,44 @@ class FlashSTU(PreTrainedModel):
         generated[:, :T0] = input_ids
         all_logits = []
         past = None
+        # Cached token steps after the first are replayed from one captured CUDA graph (every kernel reads its
+        # position from device memory): the step is ~100 small launches for a 24-layer model, which the interpreter
+        # cannot issue as fast as the GPU retires them.  cuda_graph=False keeps the eager loop.
+        use_graph = bool(kwargs.get("cuda_graph", True)) and use_cache and steps > 3 and \
+            max_length - 1 <= self.config.seq_len
+        graph = None
         for step in range(steps):
             cur = T0 + step
+            u = None
+            if do_sample:
+                u = uniforms[step].to(device=dev, dtype=torch.float32).contiguous() if uniforms is not None else \
+                    torch.rand(B, device=dev, generator=generator)
+            if use_graph and past is not None and step >= 2:
+                if graph is None:
+                    tok_in = torch.empty(B, 1, dtype=torch.int64, device=dev)
+                    tok_out = torch.empty(B, 1, dtype=torch.int64, device=dev)
+                    u_buf = torch.zeros(B, dtype=torch.float32, device=dev)
+                    host_t = [getattr(e[-1], "_host_t", None) if e is not None else None for e in past]
+                    torch.cuda.synchronize(dev)
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        logits_g, _ = self.last_logits(tok_in, past, True)
+                        ops.sample(logits_g, temperature, top_k, top_p, do_sample, u_buf if do_sample else None, tok_out,
+                                   out_stride=1)
+                    for e, t in zip(past, host_t):   # capturing ran the host bookkeeping, not the kernels
+                        if e is not None and t is not None:
+                            e[-1]._host_t = t
+                tok_in.copy_(generated[:, cur - 1:cur])
+                if do_sample:
+                    u_buf.copy_(u)
+                graph.replay()
+                for e in past:
+                    if e is not None and getattr(e[-1], "_host_t", None) is not None:
+                        e[-1]._host_t += 1
+                generated[:, cur:cur + 1].copy_(tok_out)
+                if return_logits:
+                    all_logits.append(logits_g.clone())
+                continue
             if use_cache and past is not None:
                 inp = generated[:, cur - 1:cur]
             else:
@@ -152,10 +207,6 @@ class FlashSTU(PreTrainedModel):
             logits, past = self.last_logits(inp, past, use_cache)
             if return_logits:
                 all_logits.append(logits)
-            u = None
-            if do_sample:
-                u = uniforms[step].to(device=dev, dtype=torch.float32).contiguous() if uniforms is not None else \
-                    torch.rand(B, device=dev, generator=generator)
             ops.sample(logits, temperature, top_k, top_p, do_sample, u, generated[:, cur:], out_stride=max_length)
         if return_logits:
             return generated, torch.stack(all_logits, dim=1)

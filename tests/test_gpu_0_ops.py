@@ -282,6 +282,35 @@ def test_attention_prefill_and_cached_decode(dt, cfg):
     assert rel(y, ref) <= (1e-4 if dt == torch.float32 else 1.5e-2)
 
 
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("cfg", [(2, 300, 2, 64, 100), (1, 700, 3, 128, 256), (3, 260, 2, 128, 1024)])
+def test_attention_chunked_prefill_across_many_key_tiles(dt, cfg):
+    """Windows spanning several 64-key tiles, a second prefill chunk whose older keys come from the ring, then
+    cached single-token steps (tensor-core prefill kernel and memory-bound decode kernel for bf16)."""
+    from flash_stu_2_b200 import ops
+    B, T, H, hd, w = cfg
+    d = H * hd
+    torch.manual_seed(11)
+    x = torch.randn(B, T, d).to(dt)
+    p = {"attn.c_attn.weight": (torch.randn(3 * d, d) / math.sqrt(d)).to(dt),
+         "attn.c_proj.weight": torch.eye(d).to(dt)}
+    ref, _ = O.attention(x, p, H, w, 50.0)
+    qkv = (x @ p["attn.c_attn.weight"].t()).to(dev())
+    slopes = O.alibi_slopes(H).float().to(dev())
+    W = w + 1
+    kr = torch.zeros(B, W, d, dtype=dt, device=dev())
+    vr = torch.zeros_like(kr)
+    pos = torch.zeros(B, 2, dtype=torch.int32, device=dev())
+    cuts = [0, 131, T - 6]
+    ys = [ops.swa_forward(qkv[:, a:b].contiguous(), kr, vr, pos, slopes, H, w, 50.0, update_cache=True)
+          for a, b in zip(cuts[:-1], cuts[1:])]
+    for t in range(T - 6, T):
+        ys.append(ops.swa_forward(qkv[:, t:t + 1].contiguous(), kr, vr, pos, slopes, H, w, 50.0, update_cache=True))
+    got = torch.cat(ys, 1)
+    assert pos[:, 0].tolist() == [T] * B and int(pos[0, 1]) == 0
+    assert rel(got, ref) <= (1e-4 if dt == torch.float32 else 1.5e-2), rel(got, ref)
+
+
 def test_sampling_matches_oracle():
     from flash_stu_2_b200 import ops
     torch.manual_seed(8)

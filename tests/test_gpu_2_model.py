@@ -125,3 +125,22 @@ def test_full_size_12_layer_model_follows_the_reference(golden, tmp_path):
         assert torch.equal(got[b, :T0 + stop], want[b, :T0 + stop]), (b, stop)
         checked += stop
     assert checked >= 64
+
+
+@pytest.mark.parametrize("name", ["stu_only_full_fp32", "hybrid_approx_bf16"])
+def test_graph_replayed_token_loop_equals_eager_loop(golden, tmp_path, name):
+    """generate() replays its cached token steps from one captured CUDA graph; ids and logits are identical to the
+    eager loop's (greedy and sampled with given uniforms)."""
+    from flash_stu_2_b200 import ops
+    r = golden("models")[name]
+    m = build(r, tmp_path)
+    T0, new = 9, 20
+    prompt = r["ids"][:, :T0].to(dev())
+    torch.manual_seed(0)
+    u = torch.rand(new, prompt.shape[0])
+    for kw in (dict(do_sample=False), dict(do_sample=True, temperature=0.8, top_k=5, uniforms=u)):
+        a, la = m.generate(prompt, max_length=T0 + new, return_logits=True, cuda_graph=True, **kw)
+        b, lb = m.generate(prompt, max_length=T0 + new, return_logits=True, cuda_graph=False, **kw)
+        ops.check_status()
+        assert torch.equal(a, b)
+        assert torch.equal(la, lb)

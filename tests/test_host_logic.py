@@ -73,3 +73,35 @@ def test_reorder_cache_keeps_structure():
     kv = (torch.arange(12.).view(3, 2, 2), torch.arange(12.).view(3, 2, 2), pos.clone())
     out = F.FlashSTU._reorder_cache(((hist, pos), kv, None), torch.tensor([2, 0, 0]))
     assert out[2] is None and torch.equal(out[0][0][0], hist[2]) and out[1][2].shape == (3, 2)
+
+
+def test_checkpoint_round_trip_and_vocabulary_resize(tmp_path):
+    """save_pretrained / from_pretrained (flash_stu/model.py:338-366) keep every tensor, the dtype and the
+    tok_emb / lm_head tie; resize_token_embeddings keeps the tie and updates the config."""
+    import os
+    import torch
+    import flash_stu_2_b200 as F
+    from oracle import stu_oracle as O
+    L, K = 64, 8
+    fp = os.path.join(str(tmp_path), "phi.pt")
+    F.save_spectral_filters(O.spectral_filters(L, K), fp)
+    cfg = F.FlashSTUConfig(n_embd=32, n_layers=4, n_heads=4, seq_len=L, window_size=8, vocab_size=97, mlp_scale=4,
+                           num_eigh=K, torch_dtype=torch.bfloat16, filter_path=fp, use_attn=True)
+    torch.manual_seed(0)
+    m = F.FlashSTU(cfg)
+    ckpt = os.path.join(str(tmp_path), "ckpt")
+    m.save_pretrained(ckpt)
+    m2 = F.FlashSTU.from_pretrained(ckpt)
+    assert m2.config.torch_dtype == torch.bfloat16 and next(m2.parameters()).dtype == torch.bfloat16
+    sd1, sd2 = m.state_dict(), m2.state_dict()
+    assert set(sd1) == set(sd2) and all(torch.equal(sd1[k], sd2[k]) for k in sd1)
+    assert m2.lm_head.weight.data_ptr() == m2.tok_emb.weight.data_ptr()
+    m2.resize_token_embeddings(101)
+    assert m2.tok_emb.weight.shape == (101, 32) and m2.lm_head.weight.shape == (101, 32)
+    assert m2.config.vocab_size == 101 and m2.lm_head.weight.data_ptr() == m2.tok_emb.weight.data_ptr()
+    assert torch.equal(m2.tok_emb.weight[:97], sd1["tok_emb.weight"])
+    # beam reordering of a cache (flash_stu/model.py:404-426): every tensor of every layer entry, batch on dim 0
+    hist = torch.arange(2 * 3 * 2 * 8, dtype=torch.float32).view(2, 3, 2, 8)
+    pos = torch.tensor([[5, 0], [7, 0]], dtype=torch.int32)
+    out = F.FlashSTU._reorder_cache(((hist, pos), None), torch.tensor([1, 0]))
+    assert torch.equal(out[0][0], hist[[1, 0]]) and out[0][1][:, 0].tolist() == [7, 5] and out[1] is None
