@@ -19,6 +19,9 @@ bool pdl_enabled() {
   return !off;
 }
 
+// Small-M shapes for which the tcgen05 GEMM beats the weight-streaming kernel.
+static bool prefers_tensor_gemm(int M, int N) { return (M >= 32 && N >= 5120) || (M >= 16 && N >= 32768); }
+
 extern "C" int stu_linear(const void* x, long long x_row_stride, const void* W, long long w_row_stride,
                           long long w_k_stride, const void* W2, const void* resid, long long resid_row_stride,
                           void* y, long long y_row_stride, int M, int N, int K, int epilogue, int hist_T,
@@ -54,7 +57,12 @@ extern "C" int stu_linear(const void* x, long long x_row_stride, const void* W, 
     return skinny_dispatch(x, x_row_stride, W, w_row_stride, W2, M, N, K, epilogue, ep, norm_w, eps, dtype, pdl, st);
   }
   bool tc_ok = gemm_tc_supported(x, x_row_stride, W, w_row_stride, w_k_stride, W2, M, N, K, epilogue, ep, dtype);
-  if (backend == BACKEND_AUTO) backend = sk_ok ? BACKEND_SKINNY : (tc_ok ? BACKEND_TCGEN05 : BACKEND_SIMT);
+  if (backend == BACKEND_AUTO) {
+    // 17..64 rows: the weight-streaming kernel's time grows with M, the tcgen05 GEMM's does not but it needs enough
+    // 128-wide column tiles to fill the machine (measured cross-over on a B200, weights from HBM)
+    if (sk_ok && tc_ok && prefers_tensor_gemm(M, N)) sk_ok = false;
+    backend = sk_ok ? BACKEND_SKINNY : (tc_ok ? BACKEND_TCGEN05 : BACKEND_SIMT);
+  }
   switch (backend) {
     case BACKEND_SKINNY:
       if (!sk_ok) return STU_ERR_UNSUPPORTED;
@@ -70,7 +78,7 @@ extern "C" int stu_linear(const void* x, long long x_row_stride, const void* W, 
 
 // 1 when stu_linear would fuse the RMSNorm for this shape (decode path), else 0.
 extern "C" int stu_linear_can_fuse_norm(int M, int N, int K, int epilogue, int dtype) {
-  (void)N;
   if (dtype != STU_BF16 || M < 1 || M > 64 || K % 8 || epilogue == EPI_HIST) return 0;
+  if (prefers_tensor_gemm(M, N)) return 0;   // a separate norm kernel + the tcgen05 GEMM is faster there
   return 1;
 }

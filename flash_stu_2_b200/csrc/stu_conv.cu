@@ -805,8 +805,9 @@ __global__ void __launch_bounds__(256, 4) stu_decode_diag_kernel(const bf16* __r
 // permuted identically for history and taps, so no shuffles are needed.  The eight tap rows are staged once per
 // CTA in shared memory (reversed, at the alignment of the common position).
 constexpr int R8_U = 8;        // 16-byte history loads a lane keeps in flight
-constexpr int R8_WARPS = 32;
-constexpr int R8_SLICES = 4;
+// NW warps per CTA = 8 channels x NW/8 time slices.  One CTA of 32 warps per SM when the grid is small (one wave);
+// 16-warp CTAs, two per SM, when there are several waves of CTAs, so that one CTA's prologue (statistics,
+// projection, tap staging) overlaps the other's streaming.
 
 __device__ __forceinline__ void mma_rows8(float (&c)[4], const uint4& a, const uint4& b) {
   // rows 8..15 of the A tile are zero (a1 = a3 = 0)
@@ -814,13 +815,15 @@ __device__ __forceinline__ void mma_rows8(float (&c)[4], const uint4& a, const u
   mma_bf16(c, a.z, 0u, a.w, 0u, b.z, b.w);
 }
 
-__global__ void __launch_bounds__(R8_WARPS * 32, 1)
+template <int NW>
+__global__ void __launch_bounds__(NW * 32, 32 / NW)
     stu_decode_rows8_kernel(const bf16* __restrict__ x, long long x_rstride, const bf16* __restrict__ norm_w,
                             const bf16* __restrict__ MinT, bf16* __restrict__ hist, const bf16* __restrict__ taps8,
                             int* __restrict__ pos, bf16* __restrict__ out, long long out_rstride, int B, int d, int Lh,
                             float eps, int* __restrict__ status, int pdl) {
   extern __shared__ __align__(16) unsigned char dd_smem[];
   bf16* s_tap = reinterpret_cast<bf16*>(dd_smem);  // [8][Lh + 8]
+  constexpr int R8_WARPS = NW, R8_SLICES = NW / 8;
   __shared__ float s_r[8];
   __shared__ float s_red[R8_WARPS][64];
   __shared__ float s_xp[64];
@@ -1001,15 +1004,23 @@ extern "C" int stu_decode_approx(const void* x, long long x_row_stride, const vo
         !aligned16(taps8))
       return STU_ERR_ALIGN;
     const size_t dsm = (size_t)8 * (Lh + 8) * sizeof(bf16);
-    cudaError_t ae = cudaFuncSetAttribute(stu_decode_rows8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)dsm);
-    if (ae != cudaSuccess) return (int)ae;
     dim3 gd(d / 8, (B + 7) / 8);
-    cudaError_t le = launch_maybe_overlapped(stu_decode_rows8_kernel, gd, dim3(R8_WARPS * 32), dsm, st,
+    const bool two_per_sm = (size_t)gd.x * gd.y > 160 && 2 * (dsm + 8 * 1024) <= (size_t)220 * 1024;
+    cudaError_t ae = two_per_sm
+                         ? cudaFuncSetAttribute(stu_decode_rows8_kernel<16>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm)
+                         : cudaFuncSetAttribute(stu_decode_rows8_kernel<32>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm);
+    if (ae != cudaSuccess) return (int)ae;
+    cudaError_t le =
+        two_per_sm ? launch_maybe_overlapped(stu_decode_rows8_kernel<16>, gd, dim3(16 * 32), dsm, st,
                                              (pdl & STU_FLAG_OVERLAP) != 0, (const bf16*)x, x_row_stride,
-                                             (const bf16*)norm_w, (const bf16*)MinT, (bf16*)hist,
-                                             (const bf16*)taps8, pos, (bf16*)out, out_row_stride, B, d, Lh, eps,
-                                             status, pdl);
+                                             (const bf16*)norm_w, (const bf16*)MinT, (bf16*)hist, (const bf16*)taps8,
+                                             pos, (bf16*)out, out_row_stride, B, d, Lh, eps, status, pdl)
+                   : launch_maybe_overlapped(stu_decode_rows8_kernel<32>, gd, dim3(32 * 32), dsm, st,
+                                             (pdl & STU_FLAG_OVERLAP) != 0, (const bf16*)x, x_row_stride,
+                                             (const bf16*)norm_w, (const bf16*)MinT, (bf16*)hist, (const bf16*)taps8,
+                                             pos, (bf16*)out, out_row_stride, B, d, Lh, eps, status, pdl);
     if (le != cudaSuccess) return (int)le;
     STU_CHECK_LAUNCH();
     return STU_OK;

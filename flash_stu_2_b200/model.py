@@ -128,10 +128,14 @@ class FlashSTU(PreTrainedModel):
         last = x[:, -1]
         V = self.lm_head.weight.shape[0]
         B = last.shape[0]
+        # logits rows padded to a multiple of 8 elements: the tensor-core GEMM needs 16-byte aligned output rows
+        # and the vocabulary (50257) is odd
+        Vp = (V + 7) // 8 * 8
+        logits = torch.empty(B, Vp, dtype=last.dtype, device=last.device)[:, :V]
         if ops.can_fuse_norm(B, V, last.shape[1], ops.EPI_STORE, last.dtype) and last.stride(1) == 1:
-            logits = ops.linear(last, self.lm_head.weight, norm_w=self.norm.weight, eps=self.norm.eps)
+            ops.linear(last, self.lm_head.weight, out=logits, norm_w=self.norm.weight, eps=self.norm.eps)
         else:
-            logits = ops.linear(ops.rmsnorm(last.contiguous(), self.norm.weight, self.norm.eps), self.lm_head.weight)
+            ops.linear(ops.rmsnorm(last.contiguous(), self.norm.weight, self.norm.eps), self.lm_head.weight, out=logits)
         return logits, cache
 
     # ------------------------------------------------------------------ token loop
