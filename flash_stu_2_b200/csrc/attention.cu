@@ -378,8 +378,7 @@ __global__ void __launch_bounds__(128) swa_flash_kernel(const bf16* __restrict__
   constexpr int KS = HD / 16;         // k-steps of the score product
   extern __shared__ __align__(128) unsigned char fa_smem[];
   bf16* Qs = reinterpret_cast<bf16*>(fa_smem);             // [64][HD], chunk index XOR (row & 7)
-  bf16* Ks = Qs + FA_BM * HD;
-  bf16* Vs = Ks + FA_BN * HD;
+  bf16* KV = Qs + FA_BM * HD;                              // two stages of [K tile][V tile]
   const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * FA_BM;
   const int d = H * HD;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, q = lane & 3;
@@ -415,8 +414,9 @@ __global__ void __launch_bounds__(128) swa_flash_kernel(const bf16* __restrict__
   const int j_lo = max(0, i_first - window), j_hi = i_last;
   const int irow0 = t0 + q0 + warp * 16 + g;   // absolute position of row g (row g+8: +8)
 
-  for (int jt = j_lo; jt <= j_hi; jt += FA_BN) {
-    __syncthreads();   // everyone is done with the previous K/V tile
+  auto load_tile = [&](int jt, int stage) {
+    bf16* Kd = KV + (size_t)stage * 2 * FA_BN * HD;
+    bf16* Vd = Kd + FA_BN * HD;
     for (int idx = tid; idx < FA_BN * CH; idx += 128) {
       const int row = idx / CH, c = idx - row * CH;
       const int j = jt + row;
@@ -430,12 +430,24 @@ __global__ void __launch_bounds__(128) swa_flash_kernel(const bf16* __restrict__
         ksrc = k_ring + off;
         vsrc = v_ring + off;
       }
-      cp_async16_zfill(Ks + sw(row, c) * 8, ksrc, ok);
-      cp_async16_zfill(Vs + sw(row, c) * 8, vsrc, ok);
+      cp_async16_zfill(Kd + sw(row, c) * 8, ksrc, ok);
+      cp_async16_zfill(Vd + sw(row, c) * 8, vsrc, ok);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  };
+  // two-stage pipeline: the next key tile is in flight while the current one is multiplied
+  load_tile(j_lo, 0);
+  int stage = 0;
+  for (int jt = j_lo; jt <= j_hi; jt += FA_BN, stage ^= 1) {
+    if (jt + FA_BN <= j_hi) {
+      load_tile(jt + FA_BN, stage ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
     __syncthreads();
+    const bf16* Ks = KV + (size_t)stage * 2 * FA_BN * HD;
+    const bf16* Vs = Ks + FA_BN * HD;
 
     // ---- S = Q K^T : 16 rows x 64 keys per warp
     float sacc[FA_BN / 8][4];
@@ -514,6 +526,7 @@ __global__ void __launch_bounds__(128) swa_flash_kernel(const bf16* __restrict__
         mma_16816(o[2 * np + 1], pf[kk], vf[2], vf[3]);
       }
     }
+    __syncthreads();   // this stage is refilled by the load issued at the top of the next iteration
   }
   // ---- normalise and store
 #pragma unroll
@@ -579,13 +592,15 @@ extern "C" int stu_swa_forward(const void* qkv, void* k_ring, void* v_ring, int*
                           aligned16(out);
     if (flash_ok) {
       dim3 fg((Tn + FA_BM - 1) / FA_BM, H, B);
-      const size_t fsm = (size_t)(FA_BM + 2 * FA_BN) * hd * sizeof(bf16);
+      const size_t fsm = (size_t)(FA_BM + 4 * FA_BN) * hd * sizeof(bf16);
       if (hd == 128) {
         ea = cudaFuncSetAttribute(swa_flash_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fsm);
         if (ea != cudaSuccess) return (int)ea;
         swa_flash_kernel<128><<<fg, 128, fsm, st>>>((const bf16*)qkv, (const bf16*)k_ring, (const bf16*)v_ring, pos,
                                                     slopes, (bf16*)out, Tn, H, W, window, scale, softcap);
       } else {
+        ea = cudaFuncSetAttribute(swa_flash_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fsm);
+        if (ea != cudaSuccess) return (int)ea;
         swa_flash_kernel<64><<<fg, 128, fsm, st>>>((const bf16*)qkv, (const bf16*)k_ring, (const bf16*)v_ring, pos,
                                                    slopes, (bf16*)out, Tn, H, W, window, scale, softcap);
       }

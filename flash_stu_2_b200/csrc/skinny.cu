@@ -167,38 +167,84 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
   }
 }
 
-// fp32 models: one warp per output feature, lanes split K with 128-bit loads, up to 8 rows per pass.
-template <int EPI>
+// fp32 models: SPLIT warps per output feature (8 / SPLIT features per CTA), lanes and warps split K with 128-bit
+// loads, up to 8 rows per pass.  SPLIT > 1 keeps the grid large when N is small (a 512-wide down projection
+// would otherwise be 64 CTAs streaming 12 MB of weights).
+template <int EPI, int SPLIT>
 __global__ void __launch_bounds__(256) skinny_f32_kernel(const float* __restrict__ x, long long lda,
                                                          const float* __restrict__ W, long long ldb,
                                                          const float* __restrict__ W2, int M, int N, int K,
                                                          EpiArgs<float> ep) {
   constexpr bool DUAL = (EPI == EPI_GELU_MUL);
+  constexpr int FPC = 8 / SPLIT;
+  __shared__ float red[DUAL ? 2 : 1][8][8];  // [acc][warp][row]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int n = blockIdx.x * 8 + warp;
-  if (n >= N) return;
-  const float* wr = W + (size_t)n * ldb;
-  const float* wr2 = DUAL ? W2 + (size_t)n * ldb : nullptr;
+  const int feat = warp / SPLIT, part = warp % SPLIT;
+  const int n = blockIdx.x * FPC + feat;
+  const bool nok = n < N;
+  const float* wr = W + (size_t)(nok ? n : 0) * ldb;
+  const float* wr2 = DUAL ? W2 + (size_t)(nok ? n : 0) * ldb : nullptr;
   for (int m0 = 0; m0 < M; m0 += 8) {
     float acc[8] = {}, acc2[8] = {};
-    for (int k = lane * 4; k < K; k += 128) {
-      float4 w4 = *reinterpret_cast<const float4*>(wr + k);
-      float4 v4 = DUAL ? *reinterpret_cast<const float4*>(wr2 + k) : make_float4(0, 0, 0, 0);
+    if (nok) {
+      for (int k = (part * 32 + lane) * 4; k < K; k += 128 * SPLIT) {
+        const float4 w4 = *reinterpret_cast<const float4*>(wr + k);
+        const float4 v4 = DUAL ? *reinterpret_cast<const float4*>(wr2 + k) : make_float4(0, 0, 0, 0);
 #pragma unroll
-      for (int i = 0; i < 8; i++) {
-        if (m0 + i < M) {
-          float4 a = *reinterpret_cast<const float4*>(x + (size_t)(m0 + i) * lda + k);
-          acc[i] += a.x * w4.x + a.y * w4.y + a.z * w4.z + a.w * w4.w;
-          if (DUAL) acc2[i] += a.x * v4.x + a.y * v4.y + a.z * v4.z + a.w * v4.w;
+        for (int i = 0; i < 8; i++) {
+          if (m0 + i < M) {
+            const float4 a = *reinterpret_cast<const float4*>(x + (size_t)(m0 + i) * lda + k);
+            acc[i] += a.x * w4.x + a.y * w4.y + a.z * w4.z + a.w * w4.w;
+            if (DUAL) acc2[i] += a.x * v4.x + a.y * v4.y + a.z * v4.z + a.w * v4.w;
+          }
         }
       }
     }
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-      float s = warp_sum(acc[i]);
-      float s2 = DUAL ? warp_sum(acc2[i]) : 0.f;
-      if (lane == 0 && m0 + i < M) epilogue_store<float, EPI>(ep, m0 + i, n, s, s2);
+      acc[i] = warp_sum(acc[i]);
+      if (DUAL) acc2[i] = warp_sum(acc2[i]);
     }
+    if (SPLIT == 1) {
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+        if (lane == 0 && nok && m0 + i < M) epilogue_store<float, EPI>(ep, m0 + i, n, acc[i], acc2[i]);
+    } else {
+      __syncthreads();  // the previous pass has read red
+      if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          red[0][warp][i] = acc[i];
+          if (DUAL) red[DUAL ? 1 : 0][warp][i] = acc2[i];
+        }
+      }
+      __syncthreads();
+      if (part == 0 && lane < 8 && nok && m0 + lane < M) {
+        float s = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int pp = 0; pp < SPLIT; pp++) {
+          s += red[0][feat * SPLIT + pp][lane];
+          if (DUAL) s2 += red[DUAL ? 1 : 0][feat * SPLIT + pp][lane];
+        }
+        epilogue_store<float, EPI>(ep, m0 + lane, n, s, s2);
+      }
+    }
+  }
+}
+
+template <int EPI>
+static void launch_skinny_f32(const float* A, long long lda, const float* B, long long ldb, const float* B2, int M, int N,
+                              int K, const EpiArgs<float>& e, cudaStream_t st) {
+  // enough CTAs for about four per SM
+  const int want = 592;
+  if (N / 8 >= want || K < 1024) {
+    skinny_f32_kernel<EPI, 1><<<(N + 7) / 8, 256, 0, st>>>(A, lda, B, ldb, B2, M, N, K, e);
+  } else if (N / 4 >= want || K < 2048) {
+    skinny_f32_kernel<EPI, 2><<<(N + 3) / 4, 256, 0, st>>>(A, lda, B, ldb, B2, M, N, K, e);
+  } else if (N / 2 >= want || K < 4096) {
+    skinny_f32_kernel<EPI, 4><<<(N + 1) / 2, 256, 0, st>>>(A, lda, B, ldb, B2, M, N, K, e);
+  } else {
+    skinny_f32_kernel<EPI, 8><<<N, 256, 0, st>>>(A, lda, B, ldb, B2, M, N, K, e);
   }
 }
 
@@ -280,19 +326,15 @@ int skinny_dispatch(const void* A, long long lda, const void* B, long long ldb, 
   if (dtype == STU_F32) {
     if (norm_w) return STU_ERR_UNSUPPORTED;
     EpiArgs<float> e = ep.as<float>();
-    dim3 grid((N + 7) / 8);
     switch (epi) {
       case EPI_STORE:
-        skinny_f32_kernel<EPI_STORE><<<grid, 256, 0, st>>>((const float*)A, lda, (const float*)B, ldb, nullptr, M, N,
-                                                           K, e);
+        launch_skinny_f32<EPI_STORE>((const float*)A, lda, (const float*)B, ldb, nullptr, M, N, K, e, st);
         break;
       case EPI_RESID:
-        skinny_f32_kernel<EPI_RESID><<<grid, 256, 0, st>>>((const float*)A, lda, (const float*)B, ldb, nullptr, M, N,
-                                                           K, e);
+        launch_skinny_f32<EPI_RESID>((const float*)A, lda, (const float*)B, ldb, nullptr, M, N, K, e, st);
         break;
       case EPI_GELU_MUL:
-        skinny_f32_kernel<EPI_GELU_MUL><<<grid, 256, 0, st>>>((const float*)A, lda, (const float*)B, ldb,
-                                                              (const float*)B2, M, N, K, e);
+        launch_skinny_f32<EPI_GELU_MUL>((const float*)A, lda, (const float*)B, ldb, (const float*)B2, M, N, K, e, st);
         break;
       default: return STU_ERR_UNSUPPORTED;
     }
