@@ -49,6 +49,7 @@ def parse():
                     help="instead of the headline block workload, time FlashSTU.generate() on a whole model: "
                          "c1 = d512/12 layers/fp32/B=2/prompt 128/+128 greedy; "
                          "c3 = d1536/24 layers/bf16/B=32/prompt 2048/+512, top_k=40, T=0.8")
+    ap.add_argument("--new-tokens", type=int, default=None, help="with --model: tokens to generate (default: the config's)")
     ap.add_argument("--kernel-split", action="store_true",
                     help="also time every kernel of the token step in a graph of its own (adds `decode_split`)")
     ap.add_argument("--no-overlap", action="store_true",
@@ -500,7 +501,7 @@ def run_model(a):
             F.save_spectral_filters(O.spectral_filters(L, K), fp)
         torch.manual_seed(0)
         model = F.FlashSTU(F.FlashSTUConfig(filter_path=fp, torch_dtype=dt, **cfg)).to(dev).eval()
-    B, T0, new = spec["B"], spec["prompt"], spec["new"]
+    B, T0, new = spec["B"], spec["prompt"], (a.new_tokens or spec["new"])
     ids = torch.randint(0, cfg["vocab_size"], (B, T0), device=dev)
     gen = torch.Generator(device=dev)
     ev = lambda: torch.cuda.Event(enable_timing=True)
@@ -517,7 +518,7 @@ def run_model(a):
 
     res = {}
     for graph in (True, False):
-        timed(T0 + 8, graph)                                    # warm-up (derived weights, scratch)
+        timed(T0 + min(8, new), graph)                          # warm-up (derived weights, scratch)
         t_first = min(timed(T0 + 1, graph)[0] for _ in range(2))
         t_full, out = timed(T0 + new, graph)
         res[graph] = (t_first, t_full, out)
