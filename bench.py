@@ -45,6 +45,8 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=8192, help="context length (default: the benchmark's 8192)")
     ap.add_argument("--decode-steps", type=int, default=512)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--variant", choices=["approx", "full"], default="approx",
+                    help="STU variant of the block: approx (M_inputs/M_filters, the headline) or full (M_phi_plus/minus)")
     ap.add_argument("--model", choices=["c1", "c3"], default=None,
                     help="instead of the headline block workload, time FlashSTU.generate() on a whole model: "
                          "c1 = d512/12 layers/fp32/B=2/prompt 128/+128 greedy; "
@@ -116,7 +118,7 @@ class ClockSampler:
 
 
 def workload_name(a):
-    return (f"FlashSTUBlock(use_attention=False, approx) bf16 B={a.batch}/GPU L={a.seq_len} d_model={D_MODEL} "
+    return (f"FlashSTUBlock(use_attention=False, {a.variant}) bf16 B={a.batch}/GPU L={a.seq_len} d_model={D_MODEL} "
             f"K={NUM_FILTERS} mlp_scale=4: prefill over L positions + {a.decode_steps} cached decode steps")
 
 
@@ -125,13 +127,14 @@ def filter_file(L):
     return p if os.path.exists(p) else None
 
 
-def make_state(L, seed=1):
+def make_state(L, seed=1, approx=True):
     """Random-init block parameters (seed 1, xavier for the STU projections, default Linear init)."""
     import flash_stu_2_b200 as F
     torch.manual_seed(seed)
     fp = filter_file(L)
-    cfg = F.FlashSTUConfig(n_embd=D_MODEL, seq_len=L, num_eigh=NUM_FILTERS, use_attn=False, mlp_scale=4,
-                           torch_dtype=torch.bfloat16, n_layers=1, vocab_size=1, n_heads=D_MODEL // 64, filter_path=fp)
+    cfg = F.FlashSTUConfig(n_embd=D_MODEL, seq_len=L, num_eigh=NUM_FILTERS, use_attn=False, use_approx=approx,
+                           mlp_scale=4, torch_dtype=torch.bfloat16, n_layers=1, vocab_size=1, n_heads=D_MODEL // 64,
+                           filter_path=fp)
     phi = None
     if fp is not None:
         phi = F.load_spectral_filters(fp, device="cpu", dtype=torch.bfloat16, verify_shape=(L, NUM_FILTERS))
@@ -148,7 +151,7 @@ def cpu_forward_seconds(blk_sd, n, x1, T):
     lsd = {k[len("layer."):]: v for k, v in blk_sd.items() if k.startswith("layer.")}
     t = time.perf_counter()
     with torch.no_grad():
-        O.stu_layer(x1[:, :T], lsd, blk_sd["phi"], n, True)
+        O.stu_layer(x1[:, :T], lsd, blk_sd["phi"], n, "layer.stu.M_inputs" in blk_sd)
     return time.perf_counter() - t
 
 
@@ -175,7 +178,7 @@ def run_reference(a):
     from oracle import stu_oracle as O
     # torchrun exports OMP_NUM_THREADS=1 to its workers; the host arm uses every core this process may run on
     torch.set_num_threads(len(os.sched_getaffinity(0)))
-    blk = make_state(a.seq_len)
+    blk = make_state(a.seq_len, approx=(a.variant == "approx"))
     sd = {k: v.detach().clone() for k, v in blk.state_dict().items()}
     n = O.fft_length(a.seq_len)
     torch.manual_seed(1)
@@ -217,7 +220,8 @@ def run_b200(a):
     B, L, d, S = a.batch, a.seq_len, D_MODEL, a.decode_steps
     if a.no_overlap:
         ops.overlap_decode = False
-    blk = make_state(L).to(dev).eval()
+    approx = a.variant == "approx"
+    blk = make_state(L, approx=approx).to(dev).eval()
     torch.manual_seed(1 + rank)
     x_host = torch.randn(B, L, d).bfloat16().pin_memory()
     x_dev = x_host.to(dev)
@@ -311,44 +315,46 @@ def run_b200(a):
 
         # ---- dominant kernel alone (fused decode kernel), CUDA events on the launching stream
         layer = blk.layer
-        hist, pos = state["cache"]
-        MinT, taps, taps8 = layer.stu.prepared()
-        x2 = x_step.view(B, d)
-        out2 = torch.empty_like(x2)
-        reps = min(256, S)
+        kern_ms, kern_bytes = None, None
+        if approx:
+            hist, pos = state["cache"]
+            MinT, taps, taps8 = layer.stu.prepared()
+            x2 = x_step.view(B, d)
+            out2 = torch.empty_like(x2)
+            reps = min(256, S)
 
-        def kernel_only():
-            ops.decode_approx(x2, layer.stu_norm.weight, MinT, hist, taps, pos, out2, taps8=taps8,
-                              flags=ops.FLAG_UNIFORM_POS)
+            def kernel_only():
+                ops.decode_approx(x2, layer.stu_norm.weight, MinT, hist, taps, pos, out2, taps8=taps8,
+                                  flags=ops.FLAG_UNIFORM_POS)
 
-        rewind()
-        for _ in range(3):
-            kernel_only()
-        # the launches are replayed from a graph: issued one by one from Python they would be paced by the host
-        # (the kernel is shorter than a ctypes call), and the figure would be the interpreter's, not the GPU's
-        kg = None
-        if not a.no_graph:
-            kg, _ = capture(lambda: [kernel_only() for _ in range(reps)])
-        rewind()
-        torch.cuda.synchronize()
-        k0, k1 = ev(), ev()
-        k0.record()
-        if kg is not None:
-            kg.replay()
-        else:
-            for _ in range(reps):
+            rewind()
+            for _ in range(3):
                 kernel_only()
-        k1.record()
-        torch.cuda.synchronize()
-        kern_ms = k0.elapsed_time(k1) / reps
-        t_mid = first + reps / 2.0
-        # algorithmic bytes of one launch at position t: half the history (one parity) of every sequence,
-        # the even taps of every channel, M_inputs, and the token's row in and out
-        kern_bytes = B * d * (t_mid / 2) * 2 + d * (t_mid / 2 + 1) * 2 + d * d * 2 + 3 * B * d * 2
+            # the launches are replayed from a graph: issued one by one from Python they would be paced by the host
+            # (the kernel is shorter than a ctypes call), and the figure would be the interpreter's, not the GPU's
+            kg = None
+            if not a.no_graph:
+                kg, _ = capture(lambda: [kernel_only() for _ in range(reps)])
+            rewind()
+            torch.cuda.synchronize()
+            k0, k1 = ev(), ev()
+            k0.record()
+            if kg is not None:
+                kg.replay()
+            else:
+                for _ in range(reps):
+                    kernel_only()
+            k1.record()
+            torch.cuda.synchronize()
+            kern_ms = k0.elapsed_time(k1) / reps
+            t_mid = first + reps / 2.0
+            # algorithmic bytes of one launch at position t: half the history (one parity) of every sequence,
+            # the even taps of every channel, M_inputs, and the token's row in and out
+            kern_bytes = B * d * (t_mid / 2) * 2 + d * (t_mid / 2 + 1) * 2 + d * d * 2 + 3 * B * d * 2
 
         # ---- optional: every kernel of the token step in a graph of its own (64 launches each)
         split = None
-        if a.kernel_split and not a.no_graph:
+        if a.kernel_split and not a.no_graph and approx:
             mlp = layer.mlp
             mid = torch.empty_like(x2)
             hbuf = torch.empty(B, mlp.intermediate_size, dtype=torch.bfloat16, device=dev)
@@ -426,12 +432,26 @@ def run_b200(a):
     dec_tokens = world * B * S * a.steps
     pre_tokens = world * B * L * a.steps
     value = dec_tokens / (t_dec / 1e3)
-    achieved = kern_bytes / (kern_ms / 1e3) / 1e9
-    # prefill FLOPs per token: dense 2*(d^2 + 3*4*d^2) plus the FFT-as-GEMM form of one convolution per channel
+    step_us = t_dec / a.steps / S * 1e3
+    t_mid_step = first + S / 2.0
+    if approx:
+        achieved = kern_bytes / (kern_ms / 1e3) / 1e9
+        roof_kernel = "stu_decode_rows8_kernel"
+    else:
+        # full variant: no single dominant kernel; the roofline object describes the whole token step: the history of
+        # every sequence (both parities), the 2K d x d matrices M_phi_plus/minus, the MLP weights
+        kern_bytes = B * d * t_mid_step * 2 + 2 * NUM_FILTERS * d * d * 2 + 12 * d * d * 2 + 3 * B * d * 2
+        kern_ms = step_us / 1e3
+        achieved = kern_bytes / (kern_ms / 1e3) / 1e9
+        roof_kernel = "whole token step (prepare, history x filters GEMM, combine, contraction, MLP)"
+    # prefill FLOPs per token: dense 2*(P + 3*4*d^2) with P = d^2 (approx) or 2K d^2 (full), plus the FFT-as-GEMM form of
+    # the convolutions: one per channel (approx) or (2K+1)/2 per channel (full)
     n_fft = 1 << (2 * L - 2).bit_length()          # 2^ceil(log2(2L-1))
     n1 = 1 << ((n_fft.bit_length() - 1) // 2)      # two-factor split n_fft = n1 * n2
     n2 = n_fft // n1
-    flops_tok = 2 * 13 * d * d + d * 16 * n_fft * (n1 + n2) / L
+    conv_mult = 1.0 if approx else (2 * NUM_FILTERS + 1) / 2.0
+    p_stu = d * d if approx else 2 * NUM_FILTERS * d * d
+    flops_tok = 2 * (p_stu + 12 * d * d) + conv_mult * d * 16 * n_fft * (n1 + n2) / L
     pre_tflops = flops_tok * B * L / (t_pre / a.steps / 1e3) / 1e12
     ws_mb = (B * d * L * 2 + d * L + 13 * d * d * 2) / 1e6
     line = {
@@ -448,7 +468,7 @@ def run_b200(a):
                     "tflops_algorithmic": pre_tflops,
                     "frac_of_tensor_peak": pre_tflops / pk["bf16_tflops_sustained"],
                     "peak_tflops": pk["bf16_tflops_sustained"], "peak_source": pk["source"] + " (sustained)"},
-        "roofline": {"bound": "hbm", "kernel": "stu_decode_rows8_kernel", "achieved": achieved, "peak": pk["hbm_gbs"],
+        "roofline": {"bound": "hbm", "kernel": roof_kernel, "achieved": achieved, "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "peak_source": pk["source"],
                      "bytes_per_launch": kern_bytes, "us_per_launch": kern_ms * 1e3, "traffic": None},
         "e2e": {"value": world * B * S * e2e_steps / dec_s, "unit": "tokens/s",
@@ -458,12 +478,12 @@ def run_b200(a):
                         "of each step also copies its 134 MB input in and its output back"},
         "gpu_launches": launches, "wall_s_timed_region": wall, "clocks": clocks,
     }
-    if (B, L, d) == (8, 8192, 1024):
+    if (B, L, d) == (8, 8192, 1024) and approx:
         line["roofline"]["traffic"] = DECODE_KERNEL_DRAM_BYTES
     if split is not None:
         line["decode_split"] = split
     if world == 1 and not a.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(a, make_state(L), x_host)
+        line["cpu_baseline"] = cpu_baseline(a, make_state(L, approx=approx), x_host)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

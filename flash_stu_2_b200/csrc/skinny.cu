@@ -4,8 +4,12 @@
 // sit in shared memory (optionally RMS-normalised on the way in).  bf16 uses mma.sync m16n8k16
 // with fp32 accumulation (at 8..64 rows CUDA-core FMA throughput would cap the kernel below the HBM
 // rate); fp32 models use fp32 FMAs.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "epilogue.cuh"
+
+namespace cg = cooperative_groups;
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   uint4 v;
@@ -30,7 +34,10 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, uint32_t a0, uint32_t a
 // no shuffle or shared-memory staging is needed.  All loads of a round (U chunks) are issued before any
 // is used; with NORM the row statistics are computed while they are in flight.
 //   MT   16-row activation tiles (M <= 16*MT);  LOW8: M <= 8, the upper half-tile is implicit zeros
-template <int EPI, int MT, bool LOW8, bool NORM, int U, int NW>
+//   KSPLIT > 1: the CTAs of a thread-block cluster (1 x KSPLIT x 1) split K between them; the partial tiles meet in
+//   the shared memory of the cluster's first CTA (distributed shared memory), which runs the epilogue.  Used when N
+//   alone gives too few CTAs to pull the weight through every SM (narrow outputs with long rows: down projections).
+template <int EPI, int MT, bool LOW8, bool NORM, int U, int NW, int KSPLIT = 1>
 __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __restrict__ x, long long lda,
                                                               const bf16* __restrict__ W, long long ldb,
                                                               const bf16* __restrict__ W2, int M, int N, int K,
@@ -49,7 +56,11 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
   const bool nvalid = n < N;
   const bf16* wrow = W + (size_t)(nvalid ? n : 0) * ldb;
   const bf16* wrow2 = DUAL ? (W2 + (size_t)(nvalid ? n : 0) * ldb) : nullptr;
-  const int nchunks = (K + 31) >> 5;
+  const int nchunks_all = (K + 31) >> 5;
+  // this CTA's share of the K chunks
+  const int per = (nchunks_all + KSPLIT - 1) / KSPLIT;
+  const int c_begin = KSPLIT > 1 ? (int)blockIdx.y * per : 0;
+  const int nchunks = KSPLIT > 1 ? min(nchunks_all, c_begin + per) : nchunks_all;
 
   uint4 wv[U], wv2[DUAL ? U : 1], xv[U][MT][NH], nwv[NORM ? U : 1];
   // constants of a round (weights, norm weights) and its activations are issued separately: in an overlapped
@@ -82,10 +93,10 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
     }
   };
   if (pdl & STU_FLAG_EARLY_TRIGGER) pdl_trigger();
-  issue_w(warp);
+  issue_w(c_begin + warp);
   pdl_wait();
   if (!(pdl & STU_FLAG_EARLY_TRIGGER)) pdl_trigger();
-  issue_x(warp);
+  issue_x(c_begin + warp);
 
   if (NORM) {
     for (int m = warp; m < MT * 16; m += NW) {
@@ -115,8 +126,8 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
 #pragma unroll
       for (int i = 0; i < 4; i++) acc[a][t][i] = 0.f;
 
-  for (int c0 = warp; c0 < nchunks; c0 += NW * U) {
-    if (c0 != warp) {
+  for (int c0 = c_begin + warp; c0 < nchunks; c0 += NW * U) {
+    if (c0 != c_begin + warp) {
       issue_w(c0);
       issue_x(c0);
     }
@@ -153,17 +164,44 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
       for (int i = 0; i < 4; i++) red[(((a * NW + warp) * MT + t) * 4 + i) * 32 + lane] = acc[a][t][i];
   __syncthreads();
   // element (row, col) of m-tile t lives in lane (row%8)*4 + col/2, register (row/8)*2 + col%2
-  for (int e = threadIdx.x; e < MT * 128; e += NW * 32) {
-    int t = e >> 7, r = (e >> 3) & 15, cidx = e & 7;
-    int src_lane = (r & 7) * 4 + (cidx >> 1), reg = (r >> 3) * 2 + (cidx & 1);
-    float s = 0.f, s2 = 0.f;
+  auto tile_sum = [&](int e, float& s, float& s2) {
+    const int t = e >> 7, r = (e >> 3) & 15, cidx = e & 7;
+    const int src_lane = (r & 7) * 4 + (cidx >> 1), reg = (r >> 3) * 2 + (cidx & 1);
+    s = 0.f;
+    s2 = 0.f;
 #pragma unroll
     for (int w = 0; w < NW; w++) {
       s += red[(((0 * NW + w) * MT + t) * 4 + reg) * 32 + src_lane];
       if (DUAL) s2 += red[(((1 * NW + w) * MT + t) * 4 + reg) * 32 + src_lane];
     }
-    int m = t * 16 + r, nn = n0 + cidx;
-    if (m < M && nn < N) epilogue_store<bf16, EPI>(ep, m, nn, s, s2);
+  };
+  if constexpr (KSPLIT == 1) {
+    for (int e = threadIdx.x; e < MT * 128; e += NW * 32) {
+      float s, s2;
+      tile_sum(e, s, s2);
+      const int m = (e >> 7) * 16 + ((e >> 3) & 15), nn = n0 + (e & 7);
+      if (m < M && nn < N) epilogue_store<bf16, EPI>(ep, m, nn, s, s2);
+    }
+  } else {
+    static_assert(KSPLIT == 1 || !DUAL, "the cluster split is used for single-weight epilogues");
+    __shared__ float part[MT * 128];
+    cg::cluster_group cluster = cg::this_cluster();
+    for (int e = threadIdx.x; e < MT * 128; e += NW * 32) {
+      float s, s2;
+      tile_sum(e, s, s2);
+      part[e] = s;
+    }
+    cluster.sync();  // every CTA's partial tile is complete and visible cluster-wide
+    if (cluster.block_rank() == 0) {
+      for (int e = threadIdx.x; e < MT * 128; e += NW * 32) {
+        float s = part[e];
+#pragma unroll
+        for (int rk = 1; rk < KSPLIT; rk++) s += *cluster.map_shared_rank(&part[e], rk);
+        const int m = (e >> 7) * 16 + ((e >> 3) & 15), nn = n0 + (e & 7);
+        if (m < M && nn < N) epilogue_store<bf16, EPI>(ep, m, nn, s, 0.f);
+      }
+    }
+    cluster.sync();  // the other CTAs' shared memory stays alive until the first one has read it
   }
 }
 
@@ -258,13 +296,43 @@ bool skinny_supported(const void* A, long long lda, const void* B, long long ldb
   return false;
 }
 
-template <int EPI, int MT, bool LOW8, int U, int NW>
+// STU_B200_DISABLE_CLUSTER_SPLIT=1 keeps every decode linear on the single-CTA K loop.
+static bool cluster_split_enabled() {
+  static const bool off = getenv("STU_B200_DISABLE_CLUSTER_SPLIT") != nullptr;
+  return !off;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_cluster_y(void (*kern)(KArgs...), dim3 grid, dim3 block, cudaStream_t st, bool overlap,
+                                           int cluster_y, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute at[2];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 1;
+  at[0].val.clusterDim.y = cluster_y;
+  at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = (overlap && pdl_enabled()) ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+template <int EPI, int MT, bool LOW8, int U, int NW, int KSPLIT = 1>
 static int launch_skinny_cfg(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N,
                              int K, const EpiArgs<bf16>& ep, const void* nw, float eps, int pdl, cudaStream_t st) {
-  dim3 grid((N + 7) / 8);
+  dim3 grid((N + 7) / 8, KSPLIT);
   const bool ov = (pdl & STU_FLAG_OVERLAP) != 0;
   cudaError_t e;
-  if (nw)
+  if constexpr (KSPLIT > 1) {
+    e = launch_cluster_y(skinny_bf16_kernel<EPI, MT, LOW8, false, U, NW, KSPLIT>, grid, dim3(NW * 32), st, ov, KSPLIT,
+                         (const bf16*)A, lda, (const bf16*)B, ldb, (const bf16*)B2, M, N, K, ep, (const bf16*)nullptr,
+                         eps, pdl);
+  } else if (nw)
     e = launch_maybe_overlapped(skinny_bf16_kernel<EPI, MT, LOW8, true, U, NW>, grid, dim3(NW * 32), 0, st, ov,
                                 (const bf16*)A, lda, (const bf16*)B, ldb, (const bf16*)B2, M, N, K, ep,
                                 (const bf16*)nw, eps, pdl);
@@ -285,6 +353,14 @@ static int launch_skinny_shape(const void* A, long long lda, const void* B, long
   constexpr bool light = (EPI != EPI_GELU_MUL) && (MT == 1);  // few registers per chunk: deeper rounds fit
   const int chunks = (K + 31) / 32;
   const int per8 = (chunks + 7) / 8;
+  if constexpr (EPI != EPI_GELU_MUL && MT <= 2) {
+    // narrow output, long rows: too few CTAs for the machine unless K is split across a cluster
+    if (!nw && cluster_split_enabled() && (N + 7) / 8 <= 96 && chunks >= 128) {  // measured: pays for N <= 768
+      if (MT == 1 && chunks > 128)   // more than 32 chunks per CTA: deeper rounds (one m-tile leaves the registers)
+        return launch_skinny_cfg<EPI, MT, LOW8, 8, 8, 4>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, pdl, st);
+      return launch_skinny_cfg<EPI, MT, LOW8, 4, 8, 4>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, pdl, st);
+    }
+  }
   if constexpr (light) {
     if (per8 <= 4) return launch_skinny_cfg<EPI, MT, LOW8, 4, 8>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, pdl, st);
     if (per8 <= 8) return launch_skinny_cfg<EPI, MT, LOW8, 8, 8>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, pdl, st);

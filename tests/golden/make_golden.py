@@ -1,9 +1,8 @@
 """Generate the golden fixtures in this folder by running the *reference's own modules* on CPU.
 
-Run once, in a container that has the reference checkout (default /root/reference, override
-with REFERENCE_ROOT):
+Run once, in a container that has the reference checkout, with REFERENCE_ROOT pointing at it:
 
-    python tests/golden/make_golden.py
+    REFERENCE_ROOT=<reference checkout> python tests/golden/make_golden.py
 
 Nothing in the test-suite or the product imports the reference; the fixtures written here
 (*.pt, a few hundred KB in total) are what travels.  Shims applied to make the unmodified
@@ -26,7 +25,9 @@ import tempfile
 
 os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
 sys.modules["liger_kernel"] = None
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("REFERENCE_ROOT")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set REFERENCE_ROOT to a checkout of the reference (hazan-lab/flash-stu-2)")
 sys.path.insert(0, REF)
 HERE = os.path.dirname(os.path.abspath(__file__))
 

@@ -65,6 +65,22 @@ def test_linear_backends(backend, dt, epi):
         assert rel(y, ref) <= TOL[dt] / 2, (M, N, K, rel(y, ref))
 
 
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_linear_narrow_output_long_rows(dt):
+    """Decode linears whose output is narrow and whose rows are long (down projections of a wide MLP): bf16 splits K
+    across a thread-block cluster and reduces through distributed shared memory, fp32 across the warps of a CTA."""
+    from flash_stu_2_b200 import ops
+    torch.manual_seed(4)
+    for (M, N, K, epi) in [(5, 512, 6144, 1), (20, 384, 4096, 0), (2, 512, 6144, 1), (8, 760, 8200, 0)]:
+        x = torch.randn(M, K).to(dt)
+        W = (torch.randn(N, K) / math.sqrt(K)).to(dt)
+        resid = torch.randn(M, N).to(dt)
+        ref = _lin_ref(x, W, None, resid, epi, dt)
+        y = ops.linear(x.to(dev()), W.to(dev()), resid=resid.to(dev()) if epi == 1 else None, epilogue=epi, backend=3)
+        ops.check_status()
+        assert rel(y, ref) <= TOL[dt] / 2, (M, N, K, rel(y, ref))
+
+
 def test_linear_fused_norm_decode():
     from flash_stu_2_b200 import ops
     torch.manual_seed(2)
