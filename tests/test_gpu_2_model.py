@@ -144,3 +144,37 @@ def test_graph_replayed_token_loop_equals_eager_loop(golden, tmp_path, name):
         ops.check_status()
         assert torch.equal(a, b)
         assert torch.equal(la, lb)
+
+
+@pytest.mark.parametrize("hd,B", [(64, 3), (128, 9)])
+def test_mid_size_hybrid_bf16_model_against_the_oracle(tmp_path, hd, B):
+    """A bf16 hybrid model wide enough to reach the tensor-core kernels inside the model (head size 64 / 128 for
+    the flash-style prefill attention, 8-aligned widths for the shared-tap decode kernel, B > 8 for two sequence
+    groups): prefill logits and eight cached steps (teacher-forced with the oracle's own tokens) against the oracle."""
+    import flash_stu_2_b200 as F
+    from flash_stu_2_b200 import ops
+    H = 4
+    d = H * hd
+    L, K, V, w, T0, new = 1024, 16, 1000, 200, 600, 8
+    cfg = dict(n_embd=d, n_layers=4, n_heads=H, seq_len=L, window_size=w, vocab_size=V, mlp_scale=4, num_eigh=K,
+               use_approx=True, use_attn=True, softcap=50.0)
+    fp = os.path.join(str(tmp_path), "phi.pt")
+    F.save_spectral_filters(O.spectral_filters(L, K), fp)
+    torch.manual_seed(5)
+    m = F.FlashSTU(F.FlashSTUConfig(filter_path=fp, torch_dtype=torch.bfloat16, **cfg)).eval()
+    sd = {k: v.detach().cpu().clone() for k, v in m.state_dict().items()}   # (the filters load onto the GPU)
+    m = m.to(dev())
+    ids = torch.randint(0, V, (B, T0))
+    with torch.no_grad():
+        want, want_logits = O.generate(ids[:2], sd, cfg, T0 + new, do_sample=False, return_logits=True)
+        # teacher-force the oracle's tokens so that a near-tie cannot make the two runs diverge
+        logits, past = m.last_logits(ids.to(dev()), None, True)
+        got = [logits[:2].float().cpu()]
+        for s in range(new - 1):
+            tok = torch.cat([want[:, T0 + s:T0 + s + 1], ids[2:, :1]], 0).to(dev())
+            logits, past = m.last_logits(tok, past, True)
+            got.append(logits[:2].float().cpu())
+    ops.check_status()
+    for s in range(new):
+        err = O.rel_err(got[s], want_logits[:, s].float())
+        assert err <= 2e-2, (s, err)
