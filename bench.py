@@ -47,10 +47,11 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--variant", choices=["approx", "full"], default="approx",
                     help="STU variant of the block: approx (M_inputs/M_filters, the headline) or full (M_phi_plus/minus)")
-    ap.add_argument("--model", choices=["c1", "c3"], default=None,
+    ap.add_argument("--model", choices=["c1", "c3", "c4"], default=None,
                     help="instead of the headline block workload, time FlashSTU.generate() on a whole model: "
                          "c1 = d512/12 layers/fp32/B=2/prompt 128/+128 greedy; "
-                         "c3 = d1536/24 layers/bf16/B=32/prompt 2048/+512, top_k=40, T=0.8")
+                         "c3 = d1536/24 layers/bf16/B=32/prompt 2048/+512, top_k=40, T=0.8; "
+                         "c4 = 12 stacked MiniSTU(backend='lds', 1024->1024), bf16, B=16, prefill 15360 + 1024 steps")
     ap.add_argument("--new-tokens", type=int, default=None, help="with --model: tokens to generate (default: the config's)")
     ap.add_argument("--kernel-split", action="store_true",
                     help="also time every kernel of the token step in a graph of its own (adds `decode_split`)")
@@ -500,6 +501,76 @@ MODEL_CONFIGS = {
 }
 
 
+def run_lds_stack(a):
+    """12 x MiniSTU(backend='lds') applied one after the other (no norm or residual between them): prefill of
+    16 x 15360 positions through the convolution form, then 1024 recurrent steps replayed from one CUDA graph."""
+    import flash_stu_2_b200 as F
+    from flash_stu_2_b200 import ops
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py --model needs a CUDA device: the kernels have no CPU fallback")
+    dev = torch.device("cuda:0")
+    B, L, d, n_layers = 16, 16384, 1024, 12
+    new = a.new_tokens or 1024
+    T0 = L - 1024
+    torch.manual_seed(0)
+    layers = [F.MiniSTU(seq_len=L, num_filters=24, input_dim=d, output_dim=d, backend="lds", dtype=torch.bfloat16,
+                        device=dev) for _ in range(n_layers)]
+    x = (torch.randn(B, L, d, device=dev) * 0.5).bfloat16()
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def prefill():
+        h, caches = x[:, :T0].contiguous(), []
+        for m in layers:
+            h, c = m(h, use_cache=True)
+            caches.append(c)
+        return caches
+
+    def step(tok, caches):
+        h = tok
+        for i, m in enumerate(layers):
+            h, caches[i] = m(h, past_key_value=caches[i], use_cache=True)
+        return h
+
+    with torch.no_grad():
+        caches = prefill()                        # warm-up (impulse responses, scratch)
+        torch.cuda.synchronize()
+        e0, e1 = ev(), ev()
+        e0.record(); caches = prefill(); e1.record()
+        torch.cuda.synchronize()
+        pre_ms = e0.elapsed_time(e1)
+        tok = x[:, T0:T0 + 1].contiguous()
+        step(tok, caches)                         # eager warm-up of the decode path
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = step(tok, caches)
+        e0, e1 = ev(), ev()
+        e0.record()
+        for i in range(new):
+            tok.copy_(x[:, T0 + (i % 1024):T0 + (i % 1024) + 1])
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        dec_ms = e0.elapsed_time(e1)
+    ops.check_status()
+    D_, F_ = 160, 48
+    step_bytes = n_layers * (F_ * d * d * 2 + B * d * D_ * 16 + D_ * F_ * 2)
+    pk = peaks()
+    print(json.dumps({
+        "metric": "decode tokens/s (aggregate over GPUs)", "value": B * new / (dec_ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": 1, "higher_is_better": True, "dtype": "bf16 (LDS state float64)", "data": "synthetic",
+        "config": {"workload": f"12 x MiniSTU(backend='lds', 1024->1024) L={L} B={B}: prefill {T0} + {new} recurrent steps",
+                   "decode_launch": "one CUDA graph per token step"},
+        "decode_ms_per_token_step": dec_ms / new,
+        "roofline": {"bound": "hbm", "kernel": "whole token step", "achieved": step_bytes / (dec_ms / new * 1e-3) / 1e9,
+                     "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": step_bytes / (dec_ms / new * 1e-3) / 1e9 / pk["hbm_gbs"],
+                     "bytes_per_launch": step_bytes},
+        "prefill": {"value": B * T0 / (pre_ms * 1e-3), "unit": "tokens/s", "ms": pre_ms,
+                    "note": "convolution form with the LDS impulse responses (48 filters x 3 causal Toeplitz GEMMs per "
+                            "layer), O(T^2) per channel"},
+    }))
+
+
 def run_model(a):
     """FlashSTU.generate() on a whole model with random-init weights (secondary workloads; the headline is the
     block).  Decode tokens/s = B * (new - 1) / (time of a full generate - time of a generate that stops after the
@@ -563,6 +634,8 @@ if __name__ == "__main__":
     args = parse()
     if args.impl == "reference":
         run_reference(args)
+    elif args.model == "c4":
+        run_lds_stack(args)
     elif args.model:
         run_model(args)
     else:

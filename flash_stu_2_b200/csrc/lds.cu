@@ -54,44 +54,45 @@ __global__ void __launch_bounds__(256) lds_final_state_kernel(const T* __restric
 }
 
 // One recurrent step: h <- A (.) h + B (.) x_t, then U[b][f*d + i] = round(sum_n h[n] C[n,f]).
-// One warp per (b,i); C is staged in shared memory as fp32.
+// One warp per (b,i).  The state update is spread over the lanes by mode (lane, lane+32, ...); for the contraction
+// the warp puts its new state into shared memory and the lanes switch to features: lane f walks the D modes with
+// the state as a broadcast read and C[n][f] as a conflict-free row read, so no cross-lane reduction is needed.
 template <typename T>
 __global__ void __launch_bounds__(256) lds_decode_kernel(const T* __restrict__ x, long long x_rstride,
                                                          double* __restrict__ h, const double* __restrict__ A,
                                                          const double* __restrict__ Bv, const T* __restrict__ C,
                                                          T* __restrict__ U, int B, int d, int D, int F) {
-  extern __shared__ float Cs[];  // [D][F]
+  extern __shared__ __align__(16) unsigned char lds_smem[];
+  double* st_s = reinterpret_cast<double*>(lds_smem);            // [8 warps][D]
+  float* Cs = reinterpret_cast<float*>(st_s + 8 * D);            // [D][F]
   for (int e = threadIdx.x; e < D * F; e += 256) Cs[e] = Elem<T>::to_f(C[e]);
-  __syncthreads();
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= B * d) return;
-  const int b = row / d, i = row - b * d;
-  const double xv = (double)Elem<T>::to_f(x[(size_t)b * x_rstride + i]);
-  double st[8];
-#pragma unroll
-  for (int m = 0; m < 8; m++) {
-    const int n = lane + 32 * m;
-    st[m] = 0.0;
-    if (n < D) {
-      st[m] = fma(A[n], h[(size_t)row * D + n], Bv[n] * xv);
-      h[(size_t)row * D + n] = st[m];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool rok = row < B * d;
+  const int b = rok ? row / d : 0, i = rok ? row - b * d : 0;
+  if (rok) {
+    const double xv = (double)Elem<T>::to_f(x[(size_t)b * x_rstride + i]);
+    for (int n = lane; n < D; n += 32) {
+      const double v = fma(A[n], h[(size_t)row * D + n], Bv[n] * xv);
+      h[(size_t)row * D + n] = v;
+      st_s[warp * D + n] = v;
     }
   }
-  for (int f0 = 0; f0 < F; f0 += 32) {
-    float mine = 0.f;  // lane keeps feature f0 + lane
-    for (int ff = 0; ff < 32 && f0 + ff < F; ff++) {
-      double part = 0.0;
-#pragma unroll
-      for (int m = 0; m < 8; m++) {
-        const int n = lane + 32 * m;
-        if (n < D) part = fma(st[m], (double)Cs[n * F + f0 + ff], part);
+  __syncthreads();
+  if (rok) {
+    const double* sw = st_s + warp * D;
+    for (int f = lane; f < F; f += 32) {
+      double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
+      int n = 0;
+      for (; n + 4 <= D; n += 4) {
+        a0 = fma(sw[n], (double)Cs[n * F + f], a0);
+        a1 = fma(sw[n + 1], (double)Cs[(n + 1) * F + f], a1);
+        a2 = fma(sw[n + 2], (double)Cs[(n + 2) * F + f], a2);
+        a3 = fma(sw[n + 3], (double)Cs[(n + 3) * F + f], a3);
       }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-      if (lane == ff) mine = (float)part;
+      for (; n < D; n++) a0 = fma(sw[n], (double)Cs[n * F + f], a0);
+      U[(size_t)b * F * d + (size_t)f * d + i] = Elem<T>::from_f((float)((a0 + a1) + (a2 + a3)));
     }
-    if (f0 + lane < F) U[(size_t)b * F * d + (size_t)(f0 + lane) * d + i] = Elem<T>::from_f(mine);
   }
 }
 
@@ -120,7 +121,7 @@ extern "C" int stu_lds_decode_features(const void* x, long long x_row_stride, do
   if (!x || !h || !A || !Bv || !C || !U) return STU_ERR_NULL;
   if (B <= 0 || d <= 0 || D <= 0 || D > LDS_MAXD || F <= 0 || F > LDS_MAXF) return STU_ERR_SHAPE;
   const int rows = B * d;
-  const size_t smem = (size_t)D * F * sizeof(float);
+  const size_t smem = (size_t)D * F * sizeof(float) + (size_t)8 * D * sizeof(double);
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
   if (dtype == STU_F32) {
