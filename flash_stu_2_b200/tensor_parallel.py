@@ -1,0 +1,210 @@
+"""Tensor-parallel token loop for models too large (or too slow) for one GPU: one process per GPU, every rank
+holds a 1/g slice of every layer and the full residual stream.
+
+Sharding (g ranks, rank r), one exchange per sub-layer:
+  * STU layer (approx variant, flash_stu/modules/stu.py:85-98): `M_inputs` and `M_filters` are split by output
+    channel; the projected history, the taps and the causal convolution are per-channel and therefore local;
+    the d/g output channels are all-gathered into the residual stream.
+  * MLP (flash_stu/modules/swiglu.py:22-29): gate/up split by column of the hidden layer, down by the matching
+    rows of its input; the partial d-wide outputs are all-reduced.
+  * attention (flash_stu/modules/attention.py:72-101): heads split; `c_proj` split by the matching input columns;
+    partial outputs all-reduced.  The KV ring of a rank holds its heads only.
+  * LM head: vocabulary split; the logits shards are all-gathered (rank-major, padded rows cut off).
+The collectives are torch.distributed calls (NCCL over NVLink on GPUs) between the same CUDA kernels the
+single-GPU path uses; every rank ends a step with identical logits and, given the same uniforms, identical tokens.
+"""
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import ops
+from .modules import _round_up, host_pos, new_pos
+
+
+def _rng(n: int, world: int, rank: int):
+    if n % world:
+        raise ValueError(f"dimension {n} does not divide over {world} ranks")
+    w = n // world
+    return rank * w, (rank + 1) * w
+
+
+def shard_state_dict(sd: Dict[str, torch.Tensor], cfg: dict, rank: int, world: int) -> Dict[str, torch.Tensor]:
+    """The tensors rank `rank` of `world` keeps, cut out of a full FlashSTU state dict (keys as in
+    flash_stu/model.py).  Replicated: embeddings' consumer side (tok_emb), all norm weights, phi.
+      layers.i.stu.M_inputs [d, d/g], layers.i.stu.M_filters [K, d/g]           output channels
+      layers.i.mlp.gate_proj/up_proj.weight [inter/g, d], down_proj.weight [d, inter/g]
+      layers.i.attn.c_attn.weight [3*d/g, d] (q|k|v of the rank's heads), c_proj.weight [d, d/g]
+      lm_head.weight [ceil(V/g), d] (rows past the vocabulary are zero)"""
+    d, H = cfg["n_embd"], cfg["n_heads"]
+    hd = d // H
+    out = {}
+    for k, v in sd.items():
+        if k.endswith("stu.M_inputs") or k.endswith("stu.M_filters"):
+            lo, hi = _rng(d, world, rank)
+            out[k] = v[:, lo:hi].contiguous()
+        elif k.endswith("stu.M_phi_plus") or k.endswith("stu.M_phi_minus"):
+            raise NotImplementedError("tensor parallelism covers the approx STU variant")
+        elif k.endswith("gate_proj.weight") or k.endswith("up_proj.weight"):
+            lo, hi = _rng(v.shape[0], world, rank)
+            out[k] = v[lo:hi].contiguous()
+        elif k.endswith("down_proj.weight"):
+            lo, hi = _rng(v.shape[1], world, rank)
+            out[k] = v[:, lo:hi].contiguous()
+        elif k.endswith("c_attn.weight"):
+            lo, hi = _rng(H, world, rank)
+            out[k] = v.view(3, H, hd, d)[:, lo:hi].reshape(3 * (hi - lo) * hd, d).contiguous()
+        elif k.endswith("c_proj.weight"):
+            lo, hi = _rng(H, world, rank)
+            out[k] = v[:, lo * hd:hi * hd].contiguous()
+        elif k == "lm_head.weight":
+            V = v.shape[0]
+            vl = -(-V // world)
+            w = torch.zeros(vl, v.shape[1], dtype=v.dtype, device=v.device)
+            rows = v[rank * vl:min(V, (rank + 1) * vl)]
+            w[:rows.shape[0]] = rows
+            out[k] = w
+        else:
+            out[k] = v
+    return out
+
+
+class TensorParallelFlashSTU:
+    """FlashSTU (approx STU layers, optional sliding-window attention layers) over the ranks of a process group.
+    `state_dict` is the full model's; each rank cuts out its share.  Call from every rank with identical inputs."""
+
+    def __init__(self, config, state_dict: Dict[str, torch.Tensor], device, group=None):
+        self.cfg = config
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.device(device)
+        if not config.use_approx:
+            raise NotImplementedError("tensor parallelism covers the approx STU variant")
+        c = dict(n_embd=config.n_embd, n_heads=config.n_heads)
+        self.sd = {k: v.to(self.device) for k, v in shard_state_dict(state_dict, c, self.rank, self.world).items()}
+        if "tok_emb.weight" not in self.sd:
+            raise ValueError("state_dict lacks tok_emb.weight")
+        self.d, self.H = config.n_embd, config.n_heads
+        self.hd = self.d // self.H
+        self.dl = self.d // self.world
+        self.Hl = self.H // self.world
+        self.V = state_dict["lm_head.weight"].shape[0] if "lm_head.weight" in state_dict else state_dict["tok_emb.weight"].shape[0]
+        if "lm_head.weight" not in self.sd:   # tied head stored once
+            self.sd["lm_head.weight"] = shard_state_dict({"lm_head.weight": state_dict["tok_emb.weight"]}, c, self.rank,
+                                                         self.world)["lm_head.weight"].to(self.device)
+        self.dtype = self.sd["tok_emb.weight"].dtype
+        self.Lh = _round_up((config.seq_len + 1) // 2, 8)
+        ws = config.window_size
+        self.window = int(ws[0] if isinstance(ws, (tuple, list)) else ws)
+        self.eps = ops.RMS_EPS
+        self._derived = {}
+        from .modules import Attention
+        self.slopes = Attention._get_alibi_slopes(Attention, self.H)[self.rank * self.Hl:(self.rank + 1) * self.Hl] \
+            .to(self.device).contiguous()
+
+    # ------------------------------------------------------------------ helpers
+    def _is_attn(self, i: int) -> bool:
+        return (i % 2 == 1) and bool(self.cfg.use_attn)
+
+    def _stu_weights(self, i: int):
+        """(MinT [d/g, d], taps [d/g, Lh]) of layer i, derived once."""
+        if i not in self._derived:
+            p = f"layers.{i}.stu."
+            MinT = self.sd[p + "M_inputs"].t().contiguous()
+            fp = ops.linear(self.sd["phi"].to(self.dtype), self.sd[p + "M_filters"], transposed_weight=True,
+                            backend=ops.BACKEND_SIMT)
+            self._derived[i] = (MinT, ops.taps_even(fp, self.Lh))
+        return self._derived[i]
+
+    def new_cache(self, B: int):
+        cache = []
+        for i in range(self.cfg.n_layers):
+            if self._is_attn(i):
+                W = self.window + 1
+                cache.append((torch.zeros(B, W, self.dl, dtype=self.dtype, device=self.device),
+                              torch.zeros(B, W, self.dl, dtype=self.dtype, device=self.device), new_pos(B, self.device)))
+            else:
+                cache.append((torch.zeros(B, self.dl, 2, self.Lh, dtype=self.dtype, device=self.device),
+                              new_pos(B, self.device)))
+        return cache
+
+    def _all_reduce_add(self, x2: torch.Tensor, part: torch.Tensor):
+        dist.all_reduce(part, group=self.group)
+        x2.add_(part)
+
+    def _mlp(self, x2: torch.Tensor, i: int):
+        p = f"layers.{i}."
+        xn = ops.rmsnorm(x2, self.sd[p + "mlp_norm.weight"], self.eps)
+        h = ops.linear(xn, self.sd[p + "mlp.gate_proj.weight"], W2=self.sd[p + "mlp.up_proj.weight"],
+                       epilogue=ops.EPI_GELU_MUL)
+        self._all_reduce_add(x2, ops.linear(h, self.sd[p + "mlp.down_proj.weight"]))
+
+    # ------------------------------------------------------------------ forward
+    def hidden(self, ids: torch.Tensor, cache):
+        """Residual stream [B,T,d] after all layers for the T new tokens; the cache is updated in place."""
+        B, T = ids.shape
+        d, dl = self.d, self.dl
+        x = ops.embed(ids, self.sd["tok_emb.weight"])
+        x2 = x.view(B * T, d)
+        for i in range(self.cfg.n_layers):
+            p = f"layers.{i}."
+            if self._is_attn(i):
+                k_ring, v_ring, pos = cache[i]
+                t0 = host_pos(pos)
+                xn = ops.rmsnorm(x2, self.sd[p + "attn_norm.weight"], self.eps)
+                qkv = ops.linear(xn, self.sd[p + "attn.c_attn.weight"]).view(B, T, 3 * dl)
+                y = ops.swa_forward(qkv, k_ring, v_ring, pos, self.slopes, self.Hl, self.window, self.cfg.softcap,
+                                    update_cache=True)
+                pos._host_t = t0 + T
+                self._all_reduce_add(x2, ops.linear(y.view(B * T, dl), self.sd[p + "attn.c_proj.weight"]))
+            else:
+                hist, pos = cache[i]
+                t0 = host_pos(pos)
+                if t0 + T > self.cfg.seq_len:
+                    raise ValueError(f"sequence position {t0 + T} exceeds seq_len={self.cfg.seq_len}")
+                MinT, taps = self._stu_weights(i)
+                xn = ops.rmsnorm(x2, self.sd[p + "stu_norm.weight"], self.eps)
+                ops.linear(xn, MinT, out=hist, epilogue=ops.EPI_HIST, hist_T=T, hist_t0=t0, hist_Lh=self.Lh)
+                y_loc = torch.zeros(B, T, dl, dtype=self.dtype, device=self.device)
+                yT = torch.empty(B, dl, 2, _round_up((t0 + T + 1) // 2, 8), dtype=self.dtype, device=self.device)
+                ops.conv_prefill_approx(hist, taps, yT, y_loc, t0, t0 + T,
+                                        use_tensor_cores=(self.dtype == torch.bfloat16 and dl % 8 == 0))
+                pos[:, 0] += T
+                pos._host_t = t0 + T
+                gathered = torch.empty(self.world, B, T, dl, dtype=self.dtype, device=self.device)
+                dist.all_gather_into_tensor(gathered, y_loc, group=self.group)
+                x.add_(gathered.permute(1, 2, 0, 3).reshape(B, T, d))
+            self._mlp(x2, i)
+        return x
+
+    def last_logits(self, ids: torch.Tensor, cache):
+        x = self.hidden(ids, cache)
+        last = ops.rmsnorm(x[:, -1].contiguous(), self.sd["norm.weight"], self.eps)
+        loc = ops.linear(last, self.sd["lm_head.weight"])                     # [B, ceil(V/g)]
+        allv = torch.empty(self.world, *loc.shape, dtype=loc.dtype, device=loc.device)
+        dist.all_gather_into_tensor(allv, loc.contiguous(), group=self.group)
+        return allv.permute(1, 0, 2).reshape(loc.shape[0], -1)[:, :self.V].contiguous()
+
+    @torch.no_grad()
+    def generate(self, input_ids: torch.Tensor, max_length: int, temperature: float = 1.0,
+                 top_k: Optional[int] = None, top_p: Optional[float] = None, do_sample: bool = False,
+                 uniforms: Optional[torch.Tensor] = None, return_logits: bool = False):
+        """Cached token loop; `uniforms` [steps, B] must be the same on every rank when sampling."""
+        B, T0 = input_ids.shape
+        steps = max_length - T0
+        if do_sample and uniforms is None:
+            raise ValueError("sampling under tensor parallelism needs the same uniforms on every rank")
+        gen = torch.empty(B, max_length, dtype=torch.int64, device=self.device)
+        gen[:, :T0] = input_ids
+        cache = self.new_cache(B)
+        logs = []
+        for step in range(steps):
+            cur = T0 + step
+            inp = gen[:, :cur] if step == 0 else gen[:, cur - 1:cur]
+            logits = self.last_logits(inp.contiguous(), cache)
+            if return_logits:
+                logs.append(logits)
+            u = uniforms[step].to(self.device, torch.float32).contiguous() if do_sample else None
+            ops.sample(logits, temperature, top_k, top_p, do_sample, u, gen[:, cur:], out_stride=max_length)
+        return (gen, torch.stack(logs, 1)) if return_logits else gen
