@@ -52,6 +52,9 @@ def parse():
                          "c1 = d512/12 layers/fp32/B=2/prompt 128/+128 greedy; "
                          "c3 = d1536/24 layers/bf16/B=32/prompt 2048/+512, top_k=40, T=0.8; "
                          "c4 = 12 stacked MiniSTU(backend='lds', 1024->1024), bf16, B=16, prefill 15360 + 1024 steps")
+    ap.add_argument("--tp", action="store_true",
+                    help="with --model c1|c3 under torchrun: shard the model over the ranks (tensor parallelism) "
+                         "instead of running it on one GPU")
     ap.add_argument("--new-tokens", type=int, default=None, help="with --model: tokens to generate (default: the config's)")
     ap.add_argument("--kernel-split", action="store_true",
                     help="also time every kernel of the token step in a graph of its own (adds `decode_split`)")
@@ -571,6 +574,77 @@ def run_lds_stack(a):
     }))
 
 
+def run_model_tp(a):
+    """The --model workload with the model sharded over the ranks of the job (one process per GPU, NCCL).  Every
+    rank builds the same random-init model on the host and keeps its shard; times are the max over ranks."""
+    import tempfile
+    import torch.distributed as dist
+    import flash_stu_2_b200 as F
+    from flash_stu_2_b200 import ops, parallel
+    from flash_stu_2_b200.tensor_parallel import TensorParallelFlashSTU
+    from oracle import stu_oracle as O   # only for the filter values (host eigh) when no filter file is shipped
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py --model --tp needs CUDA devices: the kernels have no CPU fallback")
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    spec = MODEL_CONFIGS[a.model]
+    cfg, dt = dict(spec["cfg"]), getattr(torch, spec["dtype"])
+    L, K = cfg["seq_len"], cfg["num_eigh"]
+    with tempfile.TemporaryDirectory() as tmp:
+        fp = filter_file(L)
+        if fp is None:
+            fp = os.path.join(tmp, "phi.pt")
+            F.save_spectral_filters(O.spectral_filters(L, K), fp)
+        torch.manual_seed(0)
+        config = F.FlashSTUConfig(filter_path=fp, torch_dtype=dt, **cfg)
+        full = F.FlashSTU(config)
+        sd = {k: v.detach().cpu() for k, v in full.state_dict().items()}
+        del full
+    tp = TensorParallelFlashSTU(config, sd, dev)
+    del sd
+    B, T0, new = spec["B"], spec["prompt"], (a.new_tokens or spec["new"])
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg["vocab_size"], (B, T0), generator=g).to(dev)
+    uniforms = torch.rand(new, B, generator=g)
+    samp = dict(spec["sampling"])
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def timed(max_length):
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = ev(), ev()
+        e0.record()
+        out = tp.generate(ids, max_length=max_length, uniforms=uniforms if samp.get("do_sample") else None, **samp)
+        e1.record()
+        torch.cuda.synchronize()
+        return parallel.max_over_ranks([e0.elapsed_time(e1)], device=dev)[0], out
+
+    timed(T0 + min(4, new))
+    t_first = min(timed(T0 + 1)[0] for _ in range(2))
+    t_full, out = timed(T0 + new)
+    ops.check_status()
+    same = parallel.gather_token_ids(out[:1].contiguous(), world)
+    if rank == 0:
+        dec_ms = t_full - t_first
+        print(json.dumps({
+            "metric": "decode tokens/s (aggregate over GPUs)", "value": B * (new - 1) / (dec_ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "higher_is_better": True, "scaling": "strong", "dtype": spec["dtype"],
+            "data": "synthetic",
+            "config": {"workload": f"FlashSTU.generate {a.model}, tensor parallel over {world} GPUs: {cfg['n_layers']} layers "
+                                   f"d={cfg['n_embd']} B={B} prompt {T0} +{new} tokens",
+                       "parallelism": f"tp{world} (all-gather per STU layer, all-reduce per attention / MLP block, NCCL)",
+                       "decode_launch": "one CUDA graph per token step (NCCL collectives captured), fused STU step on the rank's channels"},
+            "decode_ms_per_token_step": dec_ms / (new - 1),
+            "prefill": {"value": B * T0 / (t_first * 1e-3), "unit": "tokens/s", "ms": t_first},
+            "ranks_agree": bool((same == same[0]).all()),
+        }))
+    dist.destroy_process_group()
+
+
 def run_model(a):
     """FlashSTU.generate() on a whole model with random-init weights (secondary workloads; the headline is the
     block).  Decode tokens/s = B * (new - 1) / (time of a full generate - time of a generate that stops after the
@@ -636,6 +710,8 @@ if __name__ == "__main__":
         run_reference(args)
     elif args.model == "c4":
         run_lds_stack(args)
+    elif args.model and args.tp:
+        run_model_tp(args)
     elif args.model:
         run_model(args)
     else:

@@ -804,6 +804,8 @@ __global__ void __launch_bounds__(256, 4) stu_decode_diag_kernel(const bf16* __r
 // load is 8 consecutive history values of sequence g = lane / 4, and the k-order inside a 32-value chunk is
 // permuted identically for history and taps, so no shuffles are needed.  The eight tap rows are staged once per
 // CTA in shared memory (reversed, at the alignment of the common position).
+// d is the width of the layer input (rows of x, rows of M_inputs^T); dch the number of channels this launch owns
+// (history, taps, output columns): equal for a whole layer, dch = d/g for a tensor-parallel channel shard.
 constexpr int R8_U = 8;        // 16-byte history loads a lane keeps in flight
 // NW warps per CTA = 8 channels x NW/8 time slices.  One CTA of 32 warps per SM when the grid is small (one wave);
 // 16-warp CTAs, two per SM, when there are several waves of CTAs, so that one CTA's prologue (statistics,
@@ -819,7 +821,8 @@ template <int NW>
 __global__ void __launch_bounds__(NW * 32, 32 / NW)
     stu_decode_rows8_kernel(const bf16* __restrict__ x, long long x_rstride, const bf16* __restrict__ norm_w,
                             const bf16* __restrict__ MinT, bf16* __restrict__ hist, const bf16* __restrict__ taps8,
-                            int* __restrict__ pos, bf16* __restrict__ out, long long out_rstride, int B, int d, int Lh,
+                            int* __restrict__ pos, bf16* __restrict__ out, long long out_rstride, int B, int d, int dch,
+                            int add_resid, int Lh,
                             float eps, int* __restrict__ status, int pdl) {
   extern __shared__ __align__(16) unsigned char dd_smem[];
   bf16* s_tap = reinterpret_cast<bf16*>(dd_smem);  // [8][Lh + 8]
@@ -847,7 +850,7 @@ __global__ void __launch_bounds__(NW * 32, 32 / NW)
     const int ch = warp & 7, slice = warp >> 3;
     const int nch = (s + 31) >> 5;  // 32-value chunks of history, the last one partial
     const bool rowok = g < nb;
-    const bf16* hrow = hist + ((size_t)((size_t)(b0 + (rowok ? g : 0)) * d + c0 + ch) * 2 + p) * Lh;
+    const bf16* hrow = hist + ((size_t)((size_t)(b0 + (rowok ? g : 0)) * dch + c0 + ch) * 2 + p) * Lh;
     uint4 hv[R8_U];
     auto issue = [&](int sc) {  // super-chunk sc = R8_U consecutive chunks
 #pragma unroll
@@ -860,7 +863,7 @@ __global__ void __launch_bounds__(NW * 32, 32 / NW)
     {  // the eight tap rows: elements [0, roundup8(s)) of trow_c[i] = tap_c[s - i]
       const int o = Lh - 1 - s, e = o & 7;
       const int nv = (s + 7) >> 3;
-      const bf16* tbase = taps8 + ((size_t)e * d + c0) * LP + (o - e);
+      const bf16* tbase = taps8 + ((size_t)e * dch + c0) * LP + (o - e);
       for (int idx = tid; idx < 8 * nv; idx += R8_WARPS * 32) {
         const int cc = idx / nv, i = idx - cc * nv;
         *reinterpret_cast<uint4*>(s_tap + (size_t)cc * LP + 8 * i) = ldg_nc_v4(tbase + (size_t)cc * LP + 8 * i);
@@ -912,7 +915,7 @@ __global__ void __launch_bounds__(NW * 32, 32 / NW)
       const float xp = round_to<bf16>(sum);
       s_xp[tid] = xp;
       const int bb = tid >> 3, cc = tid & 7;
-      if (bb < nb) hist[((size_t)((size_t)(b0 + bb) * d + c0 + cc) * 2 + p) * Lh + s] = __float2bfloat16_rn(xp);
+      if (bb < nb) hist[((size_t)((size_t)(b0 + bb) * dch + c0 + cc) * 2 + p) * Lh + s] = __float2bfloat16_rn(xp);
     }
     // ---- taps over the stored history [0, s): super-chunks dealt round-robin to the four time slices
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -944,7 +947,8 @@ __global__ void __launch_bounds__(NW * 32, 32 / NW)
         for (int sl = 0; sl < R8_SLICES; sl++) part += s_part[sl][tid];
         const float tap0 = __bfloat162float(taps8[(size_t)(c0 + cc) * LP + (Lh - 1)]);
         const float y = round_to<bf16>(2.f * fmaf(s_xp[tid], tap0, part));
-        const float xin = __bfloat162float(x[(size_t)(b0 + bb) * x_rstride + c0 + cc]);
+        // add_resid: the layer's residual (input width == channel count); a channel shard returns y alone
+        const float xin = add_resid ? __bfloat162float(x[(size_t)(b0 + bb) * x_rstride + c0 + cc]) : 0.f;
         out[(size_t)(b0 + bb) * out_rstride + c0 + cc] = __float2bfloat16_rn(xin + y);
       }
     }
@@ -987,6 +991,53 @@ extern "C" int stu_taps_rev8(const void* taps, void* taps8, int d, int Lh, int d
   return STU_OK;
 }
 
+static int launch_rows8(const void* x, long long x_row_stride, const void* norm_w, const void* MinT, void* hist,
+                        const void* taps8, int* pos, void* out, long long out_row_stride, int B, int d, int dch,
+                        int add_resid, int Lh, float eps, int* status, int pdl, cudaStream_t st) {
+  if (x_row_stride % 8 || !aligned16(x) || !aligned16(MinT) || !aligned16(hist) || !aligned16(norm_w) ||
+      !aligned16(taps8))
+    return STU_ERR_ALIGN;
+  const size_t dsm = (size_t)8 * (Lh + 8) * sizeof(bf16);
+  dim3 gd(dch / 8, (B + 7) / 8);
+  const bool two_per_sm = (size_t)gd.x * gd.y > 160 && 2 * (dsm + 8 * 1024) <= (size_t)220 * 1024;
+  cudaError_t ae = two_per_sm ? cudaFuncSetAttribute(stu_decode_rows8_kernel<16>,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm)
+                              : cudaFuncSetAttribute(stu_decode_rows8_kernel<32>,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm);
+  if (ae != cudaSuccess) return (int)ae;
+  cudaError_t le =
+      two_per_sm ? launch_maybe_overlapped(stu_decode_rows8_kernel<16>, gd, dim3(16 * 32), dsm, st,
+                                           (pdl & STU_FLAG_OVERLAP) != 0, (const bf16*)x, x_row_stride,
+                                           (const bf16*)norm_w, (const bf16*)MinT, (bf16*)hist, (const bf16*)taps8, pos,
+                                           (bf16*)out, out_row_stride, B, d, dch, add_resid, Lh, eps, status, pdl)
+                 : launch_maybe_overlapped(stu_decode_rows8_kernel<32>, gd, dim3(32 * 32), dsm, st,
+                                           (pdl & STU_FLAG_OVERLAP) != 0, (const bf16*)x, x_row_stride,
+                                           (const bf16*)norm_w, (const bf16*)MinT, (bf16*)hist, (const bf16*)taps8, pos,
+                                           (bf16*)out, out_row_stride, B, d, dch, add_resid, Lh, eps, status, pdl);
+  if (le != cudaSuccess) return (int)le;
+  STU_CHECK_LAUNCH();
+  return STU_OK;
+}
+
+// Channel shard of the fused decode step (tensor parallelism): x [B, d_in] is the full layer input, MinT
+// [d_ch][d_in], hist [B][d_ch][2][Lh], taps8 [8][d_ch][Lh+8] and out [B, d_ch] belong to the d_ch channels of this
+// rank; with add_residual = 0 out receives the STU output alone (the caller all-gathers the shards and adds them to
+// the residual stream).  bf16, common position (checked on the device, status 6), d_ch % 8 == 0.
+extern "C" int stu_decode_approx_shard(const void* x, long long x_row_stride, const void* norm_w, const void* MinT,
+                                       void* hist, const void* taps8, int* pos, void* out, long long out_row_stride,
+                                       int B, int d_in, int d_ch, int Lh, float eps, int add_residual, int* status,
+                                       int dtype, void* stream) {
+  if (!x || !norm_w || !MinT || !hist || !taps8 || !pos || !out) return STU_ERR_NULL;
+  if (B <= 0 || d_in <= 0 || d_ch <= 0 || Lh <= 0 || d_in % 8 || d_ch % 8 || Lh % 8) return STU_ERR_SHAPE;
+  if (add_residual && d_in != d_ch) return STU_ERR_SHAPE;
+  const int pdl = dtype & (STU_FLAG_OVERLAP | STU_FLAG_EARLY_TRIGGER);
+  dtype &= ~(STU_FLAG_OVERLAP | STU_FLAG_EARLY_TRIGGER | STU_FLAG_UNIFORM_POS);
+  if (dtype != STU_BF16) return STU_ERR_DTYPE;
+  if ((size_t)8 * (Lh + 8) * sizeof(bf16) > (size_t)180 * 1024) return STU_ERR_UNSUPPORTED;
+  return launch_rows8(x, x_row_stride, norm_w, MinT, hist, taps8, pos, out, out_row_stride, B, d_in, d_ch,
+                      add_residual, Lh, eps, status, pdl, (cudaStream_t)stream);
+}
+
 extern "C" int stu_decode_approx(const void* x, long long x_row_stride, const void* norm_w, const void* MinT,
                                  void* hist, const void* taps, const void* taps8, int* pos, void* out,
                                  long long out_row_stride, int B, int d, int Lh, float eps, int* status, int dtype,
@@ -1000,30 +1051,8 @@ extern "C" int stu_decode_approx(const void* x, long long x_row_stride, const vo
   if (taps8 && dtype == STU_BF16 && uniform && d % 8 == 0 && Lh % 8 == 0 &&
       (size_t)8 * (Lh + 8) * sizeof(bf16) <= (size_t)180 * 1024) {
     // common position promised by the caller: 8 channels x 8 sequences per CTA, both contractions as MMAs
-    if (x_row_stride % 8 || !aligned16(x) || !aligned16(MinT) || !aligned16(hist) || !aligned16(norm_w) ||
-        !aligned16(taps8))
-      return STU_ERR_ALIGN;
-    const size_t dsm = (size_t)8 * (Lh + 8) * sizeof(bf16);
-    dim3 gd(d / 8, (B + 7) / 8);
-    const bool two_per_sm = (size_t)gd.x * gd.y > 160 && 2 * (dsm + 8 * 1024) <= (size_t)220 * 1024;
-    cudaError_t ae = two_per_sm
-                         ? cudaFuncSetAttribute(stu_decode_rows8_kernel<16>,
-                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm)
-                         : cudaFuncSetAttribute(stu_decode_rows8_kernel<32>,
-                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm);
-    if (ae != cudaSuccess) return (int)ae;
-    cudaError_t le =
-        two_per_sm ? launch_maybe_overlapped(stu_decode_rows8_kernel<16>, gd, dim3(16 * 32), dsm, st,
-                                             (pdl & STU_FLAG_OVERLAP) != 0, (const bf16*)x, x_row_stride,
-                                             (const bf16*)norm_w, (const bf16*)MinT, (bf16*)hist, (const bf16*)taps8,
-                                             pos, (bf16*)out, out_row_stride, B, d, Lh, eps, status, pdl)
-                   : launch_maybe_overlapped(stu_decode_rows8_kernel<32>, gd, dim3(32 * 32), dsm, st,
-                                             (pdl & STU_FLAG_OVERLAP) != 0, (const bf16*)x, x_row_stride,
-                                             (const bf16*)norm_w, (const bf16*)MinT, (bf16*)hist, (const bf16*)taps8,
-                                             pos, (bf16*)out, out_row_stride, B, d, Lh, eps, status, pdl);
-    if (le != cudaSuccess) return (int)le;
-    STU_CHECK_LAUNCH();
-    return STU_OK;
+    return launch_rows8(x, x_row_stride, norm_w, MinT, hist, taps8, pos, out, out_row_stride, B, d, d, 1, Lh, eps,
+                        status, pdl, st);
   }
   if (taps8 && dtype == STU_BF16) {
     // tensor-core kernel: needs the reversed 8-alignment tap table

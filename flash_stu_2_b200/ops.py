@@ -222,6 +222,24 @@ def decode_approx(x, norm_w, MinT, hist, taps, pos, out, eps: float = RMS_EPS, t
     return out
 
 
+def decode_approx_shard(x, norm_w, MinT, hist, taps8, pos, out, eps: float = RMS_EPS, add_residual: bool = False,
+                        flags: int = 0):
+    """Fused decode step for the d_ch channels of a tensor-parallel rank: x [B,d_in] (full layer input), MinT
+    [d_ch,d_in], hist [B,d_ch,2,Lh], taps8 [8,d_ch,Lh+8] -> out [B,d_ch] (the STU output, plus x when add_residual)."""
+    _cuda(x, norm_w, MinT, hist, taps8, pos, out)
+    B, dch, _, Lh = hist.shape
+    d_in = x.shape[1]
+    assert x.shape[0] == B and MinT.shape == (dch, d_in) and out.shape == (B, dch) and x.stride(1) == 1
+    assert out.stride(1) == 1 and taps8.shape == (8, dch, Lh + 8) and pos.dtype == torch.int32
+    rc = _lib.load().stu_decode_approx_shard(x.data_ptr(), x.stride(0), norm_w.data_ptr(), MinT.data_ptr(),
+                                             hist.data_ptr(), taps8.data_ptr(), pos.data_ptr(), out.data_ptr(),
+                                             out.stride(0), B, d_in, dch, Lh, eps, int(add_residual),
+                                             status_word(x.device).data_ptr(), _dt(x) | flags, _stream())
+    _lib.check(rc, "stu_decode_approx_shard")
+    _count()
+    return out
+
+
 def to_history(x, hist, t0: int):
     """x [B,T,d] -> hist[b][c][t&1][t>>1] for t in [t0, t0+T)."""
     _cuda(x, hist)

@@ -98,6 +98,7 @@ class TensorParallelFlashSTU:
         ws = config.window_size
         self.window = int(ws[0] if isinstance(ws, (tuple, list)) else ws)
         self.eps = ops.RMS_EPS
+        self.fused_decode = True
         self._derived = {}
         from .modules import Attention
         self.slopes = Attention._get_alibi_slopes(Attention, self.H)[self.rank * self.Hl:(self.rank + 1) * self.Hl] \
@@ -108,13 +109,15 @@ class TensorParallelFlashSTU:
         return (i % 2 == 1) and bool(self.cfg.use_attn)
 
     def _stu_weights(self, i: int):
-        """(MinT [d/g, d], taps [d/g, Lh]) of layer i, derived once."""
+        """(MinT [d/g, d], taps [d/g, Lh], taps8 or None) of layer i, derived once."""
         if i not in self._derived:
             p = f"layers.{i}.stu."
             MinT = self.sd[p + "M_inputs"].t().contiguous()
             fp = ops.linear(self.sd["phi"].to(self.dtype), self.sd[p + "M_filters"], transposed_weight=True,
                             backend=ops.BACKEND_SIMT)
-            self._derived[i] = (MinT, ops.taps_even(fp, self.Lh))
+            taps = ops.taps_even(fp, self.Lh)
+            taps8 = ops.taps_rev8(taps) if (self.dtype == torch.bfloat16 and self.dl % 8 == 0) else None
+            self._derived[i] = (MinT, taps, taps8)
         return self._derived[i]
 
     def new_cache(self, B: int):
@@ -163,14 +166,21 @@ class TensorParallelFlashSTU:
                 t0 = host_pos(pos)
                 if t0 + T > self.cfg.seq_len:
                     raise ValueError(f"sequence position {t0 + T} exceeds seq_len={self.cfg.seq_len}")
-                MinT, taps = self._stu_weights(i)
-                xn = ops.rmsnorm(x2, self.sd[p + "stu_norm.weight"], self.eps)
-                ops.linear(xn, MinT, out=hist, epilogue=ops.EPI_HIST, hist_T=T, hist_t0=t0, hist_Lh=self.Lh)
-                y_loc = torch.zeros(B, T, dl, dtype=self.dtype, device=self.device)
-                yT = torch.empty(B, dl, 2, _round_up((t0 + T + 1) // 2, 8), dtype=self.dtype, device=self.device)
-                ops.conv_prefill_approx(hist, taps, yT, y_loc, t0, t0 + T,
-                                        use_tensor_cores=(self.dtype == torch.bfloat16 and dl % 8 == 0))
-                pos[:, 0] += T
+                MinT, taps, taps8 = self._stu_weights(i)
+                if T == 1 and taps8 is not None and self.fused_decode:
+                    # one token: the fused kernel on this rank's channels (norm, projection, cache append, taps;
+                    # position read on the device, so the step can be replayed from a graph)
+                    y_loc = torch.empty(B, 1, dl, dtype=self.dtype, device=self.device)
+                    ops.decode_approx_shard(x2, self.sd[p + "stu_norm.weight"], MinT, hist, taps8, pos, y_loc.view(B, dl),
+                                            self.eps)
+                else:
+                    xn = ops.rmsnorm(x2, self.sd[p + "stu_norm.weight"], self.eps)
+                    ops.linear(xn, MinT, out=hist, epilogue=ops.EPI_HIST, hist_T=T, hist_t0=t0, hist_Lh=self.Lh)
+                    y_loc = torch.zeros(B, T, dl, dtype=self.dtype, device=self.device)
+                    yT = torch.empty(B, dl, 2, _round_up((t0 + T + 1) // 2, 8), dtype=self.dtype, device=self.device)
+                    ops.conv_prefill_approx(hist, taps, yT, y_loc, t0, t0 + T,
+                                            use_tensor_cores=(self.dtype == torch.bfloat16 and dl % 8 == 0))
+                    pos[:, 0] += T
                 pos._host_t = t0 + T
                 gathered = torch.empty(self.world, B, T, dl, dtype=self.dtype, device=self.device)
                 dist.all_gather_into_tensor(gathered, y_loc, group=self.group)
@@ -189,7 +199,7 @@ class TensorParallelFlashSTU:
     @torch.no_grad()
     def generate(self, input_ids: torch.Tensor, max_length: int, temperature: float = 1.0,
                  top_k: Optional[int] = None, top_p: Optional[float] = None, do_sample: bool = False,
-                 uniforms: Optional[torch.Tensor] = None, return_logits: bool = False):
+                 uniforms: Optional[torch.Tensor] = None, return_logits: bool = False, cuda_graph: bool = True):
         """Cached token loop; `uniforms` [steps, B] must be the same on every rank when sampling."""
         B, T0 = input_ids.shape
         steps = max_length - T0
@@ -199,12 +209,42 @@ class TensorParallelFlashSTU:
         gen[:, :T0] = input_ids
         cache = self.new_cache(B)
         logs = []
+        # as in FlashSTU.generate: cached steps after the first are replayed from one captured CUDA graph (the NCCL
+        # collectives are captured with the kernels; every rank captures and replays in lock step)
+        # (the unfused one-token path passes its position to the kernels as an argument and cannot be replayed)
+        use_graph = cuda_graph and steps > 3 and max_length - 1 <= self.cfg.seq_len and self.fused_decode and \
+            self.dtype == torch.bfloat16 and self.dl % 8 == 0
+        graph = None
         for step in range(steps):
             cur = T0 + step
+            u = uniforms[step].to(self.device, torch.float32).contiguous() if do_sample else None
+            if use_graph and step >= 2:
+                if graph is None:
+                    tok_in = torch.empty(B, 1, dtype=torch.int64, device=self.device)
+                    tok_out = torch.empty(B, 1, dtype=torch.int64, device=self.device)
+                    u_buf = torch.zeros(B, dtype=torch.float32, device=self.device)
+                    host_t = [getattr(e[-1], "_host_t", None) for e in cache]
+                    torch.cuda.synchronize(self.device)
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        logits_g = self.last_logits(tok_in, cache)
+                        ops.sample(logits_g, temperature, top_k, top_p, do_sample, u_buf if do_sample else None, tok_out,
+                                   out_stride=1)
+                    for e, t in zip(cache, host_t):
+                        e[-1]._host_t = t
+                tok_in.copy_(gen[:, cur - 1:cur])
+                if do_sample:
+                    u_buf.copy_(u)
+                graph.replay()
+                for e in cache:
+                    e[-1]._host_t += 1
+                gen[:, cur:cur + 1].copy_(tok_out)
+                if return_logits:
+                    logs.append(logits_g.clone())
+                continue
             inp = gen[:, :cur] if step == 0 else gen[:, cur - 1:cur]
             logits = self.last_logits(inp.contiguous(), cache)
             if return_logits:
                 logs.append(logits)
-            u = uniforms[step].to(self.device, torch.float32).contiguous() if do_sample else None
             ops.sample(logits, temperature, top_k, top_p, do_sample, u, gen[:, cur:], out_stride=max_length)
         return (gen, torch.stack(logs, 1)) if return_logits else gen

@@ -110,6 +110,16 @@ int stu_decode_approx(const void* x, long long x_row_stride, const void* norm_w,
  * 16-byte load at every position.  bf16, Lh % 8 == 0.  Derived data, no counterpart in the reference. */
 int stu_taps_rev8(const void* taps, void* taps8, int d, int Lh, int dtype, void* stream);
 
+/* Channel shard of stu_decode_approx for tensor parallelism (the reference is single-GPU; the STU sub-layer is
+ * flash_stu/layers/stu_layer.py:78-93): x [B, d_in] is the full layer input, MinT [d_ch][d_in], hist
+ * [B][d_ch][2][Lh], taps8 [8][d_ch][Lh+8] and out [B, d_ch] hold the d_ch channels owned by the caller.  With
+ * add_residual = 0 out receives the STU output alone (to be all-gathered and added to the residual stream);
+ * add_residual = 1 needs d_in == d_ch.  bf16 only, all sequences at one position (status 6 otherwise),
+ * d_in, d_ch, Lh multiples of 8.  dtype takes the launch flags 0x200 / 0x400 of stu_decode_approx. */
+int stu_decode_approx_shard(const void* x, long long x_row_stride, const void* norm_w, const void* MinT, void* hist,
+                            const void* taps8, int* pos, void* out, long long out_row_stride, int B, int d_in,
+                            int d_ch, int Lh, float eps, int add_residual, int* status, int dtype, void* stream);
+
 /* ---- full STU variant (flash_stu/modules/stu.py:100-118, mini_stu/stu.py:240-269): U+-[b,t,k,i] =
  * sum_j (+-1)^j phi[j,k] x[b,t-j,i] contracted with M_phi_plus / M_phi_minus.  The filters are shared by all
  * channels, so per filter the convolution is three GEMMs (stu_linear with epilogue | 0x100 = lower-triangular

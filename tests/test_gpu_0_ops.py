@@ -236,6 +236,41 @@ def test_decode_step_shared_tap_kernel(shape):
         assert torch.equal(before[:2], hist[:2])
 
 
+def test_decode_step_channel_shards_tile_the_layer():
+    """Tensor-parallel form of the fused decode step: two ranks' channel shards (own history, own rows of
+    M_inputs^T, own taps) give, concatenated and added to the input, exactly the whole-layer kernel's output."""
+    from flash_stu_2_b200 import ops
+    dt = torch.bfloat16
+    B, T, d, L = 5, 40, 64, 96
+    Lh = ((L + 1) // 2 + 7) // 8 * 8
+    x, nw, Mi, fp, xp, ref = _decode_fixture(dt, B, T, d, L)
+    taps = ops.taps_even(fp.to(dev()), Lh)
+    MinT = Mi.t().contiguous().to(dev())
+    xd, nwd = x.to(dev()), nw.to(dev())
+    hist = torch.zeros(B, d, 2, Lh, dtype=dt, device=dev())
+    pos = torch.zeros(B, 2, dtype=torch.int32, device=dev())
+    taps8 = ops.taps_rev8(taps)
+    halves = []
+    for r in range(2):
+        sl = slice(r * d // 2, (r + 1) * d // 2)
+        halves.append((MinT[sl].contiguous(), torch.zeros(B, d // 2, 2, Lh, dtype=dt, device=dev()),
+                       ops.taps_rev8(taps[sl].contiguous()), torch.zeros(B, 2, dtype=torch.int32, device=dev())))
+    for t in range(T):
+        xt = xd[:, t].contiguous()
+        whole = torch.empty(B, d, dtype=dt, device=dev())
+        ops.decode_approx(xt, nwd, MinT, hist, taps, pos, whole, taps8=taps8, flags=ops.FLAG_UNIFORM_POS)
+        ys = []
+        for (Ms, hs, t8s, ps) in halves:
+            y = torch.empty(B, d // 2, dtype=dt, device=dev())
+            ops.decode_approx_shard(xt, nwd, Ms, hs, t8s, ps, y)
+            ys.append(y)
+        sharded = (xt.float() + torch.cat(ys, 1).float()).to(dt)
+        assert torch.equal(sharded, whole), t
+    ops.check_status()
+    assert torch.equal(torch.cat([h[1] for h in halves], 1), hist)
+    assert halves[0][3][:, 0].tolist() == [T] * B
+
+
 @pytest.mark.parametrize("tc", [False, True])
 def test_decode_step_with_ragged_positions(tc):
     """Sequences of one batch at different positions (what _reorder_cache / ragged prompts produce)."""
