@@ -19,9 +19,8 @@
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int BM = 128, BK = 64;
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int B_BYTES = BN * BK * 2;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 enum { EPI_HIST_T = 4 };  // internal: rows = channels, columns = tokens (operands swapped by the host)
 
@@ -85,10 +84,11 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   d |= (uint64_t)2 << 61;                 // 128-byte swizzle
   return d;
 }
-// Instruction descriptor: D fp32, A/B bf16, both K-major, M = 128, N = BN.
-constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-
+// Instruction descriptor: D fp32, A/B bf16, both K-major, M = 128, N = the tile width (128 or 256).
+template <int BN_>
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+  constexpr uint32_t IDESC =
+      (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN_ >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
@@ -125,24 +125,28 @@ __device__ __forceinline__ float gelu_tanh_fast(float x) {
 
 // With `causal` the B operand is lower triangular (B[n][k] = 0 for k > n, the Toeplitz matrices of the STU
 // full variant): k-blocks that lie entirely above the diagonal of the tile's last column are skipped.
-__device__ __forceinline__ int tile_kb(int num_kb, int n0, int causal) {
+__device__ __forceinline__ int tile_kb(int num_kb, int n0, int causal, int bn) {
   if (!causal) return num_kb;
-  const int need = (n0 + BN + BK - 1) / BK;
+  const int need = (n0 + bn + BK - 1) / BK;
   return need < num_kb ? need : num_kb;
 }
 
 // Persistent kernel: CTA i handles tiles i, i + gridDim.x, ...  The accumulator is double-buffered in TMEM
-// (2 x 128 columns, or 2 x 256 for the gate/up epilogue), so the MMA warp starts the next tile while
-// the epilogue warps drain the previous one.
-template <int EPI, int STAGES>
+// (2 x TN columns, or 2 x 256 for the two accumulators of the gate/up epilogue), so the MMA warp starts the next
+// tile while the epilogue warps drain the previous one.  TN = 256 (128 x 256 tiles) moves a third less operand
+// data per flop through shared memory than 128 x 128 and is used when the problem has enough wide tiles.
+template <int EPI, int STAGES, int TN = 128>
 __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,
                                                          const __grid_constant__ CUtensorMap tmB,
                                                          const __grid_constant__ CUtensorMap tmB2, int M, int N,
                                                          int K, int tiles_m, int tiles_n, int m_fast,
                                                          int causal, EpiArgs<bf16> ep, int* status) {
   constexpr bool DUAL = (EPI == EPI_GELU_MUL);
+  static_assert(!DUAL || TN == 128, "the two-accumulator epilogue uses 128-wide tiles");
+  constexpr int BN = TN;                       // shadows the file-level default inside the kernel
+  constexpr int B_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES * (DUAL ? 2 : 1);
-  constexpr uint32_t ACC_COLS = DUAL ? 256 : 128;
+  constexpr uint32_t ACC_COLS = DUAL ? 256 : (uint32_t)BN;
   constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -192,7 +196,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         const int tm = m_fast ? (tile % tiles_m) : (tile / tiles_n);
         const int tn = m_fast ? (tile / tiles_m) : (tile % tiles_n);
         const int m0 = tm * BM, n0 = tn * BN;
-        const int kb_end = tile_kb(num_kb, n0, causal);
+        const int kb_end = tile_kb(num_kb, n0, causal, BN);
         for (int kb = 0; kb < kb_end; kb++, g++) {
           const int s = g % STAGES;
           const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
@@ -215,7 +219,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         const int buf = it & 1;
         const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS;
         const int tn_ = m_fast ? (tile / tiles_m) : (tile % tiles_n);
-        const int kb_end = tile_kb(num_kb, tn_ * BN, causal);
+        const int kb_end = tile_kb(num_kb, tn_ * BN, causal, BN);
         if (!mbar_wait(&tmem_empty[buf], (((uint32_t)it >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         for (int kb = 0; kb < kb_end; kb++, g++) {
@@ -228,10 +232,10 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
 #pragma unroll
           for (int kk = 0; kk < BK / 16; kk++) {
             // advancing 16 bf16 = 32 bytes along K inside the swizzled row: +2 in the (>>4) address field
-            umma(acc_addr, da + 2 * kk, db + 2 * kk, (kb | kk) ? 1u : 0u);
+            umma<BN>(acc_addr, da + 2 * kk, db + 2 * kk, (kb | kk) ? 1u : 0u);
             if (DUAL) {
               const uint64_t db2 = make_smem_desc(sa + A_BYTES + B_BYTES);
-              umma(acc_addr + BN, da + 2 * kk, db2 + 2 * kk, (kb | kk) ? 1u : 0u);
+              umma<BN>(acc_addr + BN, da + 2 * kk, db2 + 2 * kk, (kb | kk) ? 1u : 0u);
             }
           }
           umma_commit(&empty_bar[s]);  // arrives when the MMAs above have finished reading this stage
@@ -377,13 +381,13 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2-D map over a row-major bf16 matrix [rows, cols] with row stride ld (elements); box 64 x 128, 128B swizzle.
-int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld) {
+// 2-D map over a row-major bf16 matrix [rows, cols] with row stride ld (elements); box 64 x box_rows, 128B swizzle.
+int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows = BM) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return STU_ERR_UNSUPPORTED;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -391,13 +395,14 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
   return r == CUDA_SUCCESS ? STU_OK : STU_ERR_UNSUPPORTED;
 }
 
-template <int EPI, int STAGES>
+template <int EPI, int STAGES, int TN = 128>
 int launch_tc(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& b2, int M, int N, int K, int m_fast,
               int causal, const EpiArgs<bf16>& ep, int* status, cudaStream_t st) {
   constexpr bool DUAL = (EPI == EPI_GELU_MUL);
-  constexpr int STAGE_BYTES = A_BYTES + B_BYTES * (DUAL ? 2 : 1);
+  constexpr int BN = TN;
+  constexpr int STAGE_BYTES = A_BYTES + BN * BK * 2 * (DUAL ? 2 : 1);
   const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
-  auto k = gemm_tc_kernel<EPI, STAGES>;
+  auto k = gemm_tc_kernel<EPI, STAGES, TN>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
@@ -437,6 +442,14 @@ bool gemm_tc_supported(const void* A, long long lda, const void* B, long long ld
   return get_encode_fn() != nullptr;
 }
 
+// 128 x 256 tiles when the output has at least two waves of them (rows x cols of the GEMM as the kernel sees it).
+// STU_B200_TILE_N=128 forces the square tiles.
+static bool wide_tiles(long long rows, long long cols) {
+  static const char* env = getenv("STU_B200_TILE_N");
+  if (env && atoi(env) == 128) return false;
+  return cols >= 512 && ((rows + BM - 1) / BM) * ((cols + 255) / 256) >= 2 * 148;
+}
+
 int gemm_tc_dispatch(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N,
                      int K, int epi, int causal, const EpiArgsAny& epa, cudaStream_t st) {
   CUtensorMap ma, mb, mb2;
@@ -445,15 +458,24 @@ int gemm_tc_dispatch(const void* A, long long lda, const void* B, long long ldb,
   if (epi == EPI_HIST) {
     // swap operands: rows = channels (the weight), columns = tokens, so that each epilogue thread owns
     // one channel row of the history and writes whole 16-byte runs per parity
+    const bool wide = wide_tiles(N, M);
     if ((rc = make_map(&ma, B, N, K, ldb)) != STU_OK) return rc;
-    if ((rc = make_map(&mb, A, M, K, lda)) != STU_OK) return rc;
+    if ((rc = make_map(&mb, A, M, K, lda, wide ? 256 : BM)) != STU_OK) return rc;
     ep.ldy = N;  // channel count
+    if (wide) return launch_tc<EPI_HIST_T, 4, 256>(ma, mb, mb, N, M, K, /*m_fast=*/1, 0, ep, g_status_word, st);
     return launch_tc<EPI_HIST_T, 6>(ma, mb, mb, N, M, K, /*m_fast=*/1, 0, ep, g_status_word, st);
   }
+  const bool wide = epi != EPI_GELU_MUL && wide_tiles(M, N);
   if ((rc = make_map(&ma, A, M, K, lda)) != STU_OK) return rc;
-  if ((rc = make_map(&mb, B, N, K, ldb)) != STU_OK) return rc;
+  if ((rc = make_map(&mb, B, N, K, ldb, wide ? 256 : BM)) != STU_OK) return rc;
   mb2 = mb;
   if (epi == EPI_GELU_MUL && (rc = make_map(&mb2, B2, N, K, ldb)) != STU_OK) return rc;
+  if (wide) {
+    switch (epi) {
+      case EPI_STORE: return launch_tc<EPI_STORE, 4, 256>(ma, mb, mb2, M, N, K, 0, causal, ep, g_status_word, st);
+      case EPI_RESID: return launch_tc<EPI_RESID, 4, 256>(ma, mb, mb2, M, N, K, 0, causal, ep, g_status_word, st);
+    }
+  }
   switch (epi) {
     case EPI_STORE: return launch_tc<EPI_STORE, 6>(ma, mb, mb2, M, N, K, 0, causal, ep, g_status_word, st);
     case EPI_RESID: return launch_tc<EPI_RESID, 6>(ma, mb, mb2, M, N, K, 0, causal, ep, g_status_word, st);

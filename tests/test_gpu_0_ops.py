@@ -81,6 +81,22 @@ def test_linear_narrow_output_long_rows(dt):
         assert rel(y, ref) <= TOL[dt] / 2, (M, N, K, rel(y, ref))
 
 
+@pytest.mark.parametrize("epi", [0, 1])
+def test_linear_wide_tensor_core_tiles(epi):
+    """Outputs with at least two waves of 128 x 256 tiles take the wide-tile tcgen05 kernel; ragged M, N and K."""
+    from flash_stu_2_b200 import ops
+    torch.manual_seed(5)
+    dt = torch.bfloat16
+    for (M, N, K) in [(20000, 520, 136), (9000, 1024, 264), (38000, 776, 64)]:
+        x = torch.randn(M, K).to(dt)
+        W = (torch.randn(N, K) / math.sqrt(K)).to(dt)
+        resid = torch.randn(M, N).to(dt)
+        ref = _lin_ref(x, W, None, resid, epi, dt)
+        y = ops.linear(x.to(dev()), W.to(dev()), resid=resid.to(dev()) if epi == 1 else None, epilogue=epi, backend=2)
+        ops.check_status()
+        assert rel(y, ref) <= TOL[dt] / 2, (M, N, K, rel(y, ref))
+
+
 def test_linear_fused_norm_decode():
     from flash_stu_2_b200 import ops
     torch.manual_seed(2)
