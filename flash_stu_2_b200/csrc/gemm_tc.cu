@@ -232,11 +232,13 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
 #pragma unroll
           for (int kk = 0; kk < BK / 16; kk++) {
             // advancing 16 bf16 = 32 bytes along K inside the swizzled row: +2 in the (>>4) address field
-            umma<BN>(acc_addr, da + 2 * kk, db + 2 * kk, (kb | kk) ? 1u : 0u);
-            if (DUAL) {
-              const uint64_t db2 = make_smem_desc(sa + A_BYTES + B_BYTES);
-              umma<BN>(acc_addr + BN, da + 2 * kk, db2 + 2 * kk, (kb | kk) ? 1u : 0u);
-            }
+            // gate/up: the two 128-row weight tiles lie back to back in the stage and form one 256-row B operand,
+            // so one N = 256 instruction fills both accumulators (columns 0..127 gate, 128..255 up) and the A tile
+            // is read from shared memory once instead of twice
+            if (DUAL)
+              umma<256>(acc_addr, da + 2 * kk, db + 2 * kk, (kb | kk) ? 1u : 0u);
+            else
+              umma<BN>(acc_addr, da + 2 * kk, db + 2 * kk, (kb | kk) ? 1u : 0u);
           }
           umma_commit(&empty_bar[s]);  // arrives when the MMAs above have finished reading this stage
           *consumed_ctr = g + 1;
