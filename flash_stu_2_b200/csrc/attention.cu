@@ -468,6 +468,11 @@ __global__ void __launch_bounds__(128) swa_flash_kernel(const bf16* __restrict__
     }
     // ---- soft-capping, ALiBi, mask, online softmax (exp2 domain)
     float mnew[2] = {mrow[0], mrow[1]};
+    // interior tile: every (query, key) pair of this warp's 16 rows x 64 keys lies inside the window (warp-uniform)
+    const int iw0 = t0 + q0 + warp * 16;
+    const bool interior = (jt + FA_BN - 1 <= iw0) && (jt >= iw0 + 15 - window) && (jt + FA_BN - 1 <= j_hi) &&
+                          (iw0 + 15 <= i_last);
+    const float cap2 = 2.f / softcap;
 #pragma unroll
     for (int n = 0; n < FA_BN / 8; n++) {
 #pragma unroll
@@ -476,10 +481,16 @@ __global__ void __launch_bounds__(128) swa_flash_kernel(const bf16* __restrict__
         const int i = irow0 + 8 * r;
         const int j = jt + n * 8 + 2 * q + (e & 1);
         float sc = sacc[n][e] * scale;
-        if (softcap > 0.f) sc = softcap * (1.f - 2.f / (1.f + __expf(2.f * sc / softcap)));   // softcap * tanh(sc / softcap)
+        if (softcap > 0.f) {   // softcap * tanh(sc / softcap); tanh.approx: relative error 2^-11, below P's bf16 rounding
+          float th;
+          asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(sc * 0.5f * cap2));
+          sc = softcap * th;
+        }
         sc = (sc - slope * (float)(i - j)) * LOG2E;
-        const bool valid = (j <= i) && (j >= i - window) && (j <= j_hi) && (i <= i_last);
-        sc = valid ? sc : -INFINITY;
+        if (!interior) {
+          const bool valid = (j <= i) && (j >= i - window) && (j <= j_hi) && (i <= i_last);
+          sc = valid ? sc : -INFINITY;
+        }
         sacc[n][e] = sc;
         mnew[r] = fmaxf(mnew[r], sc);
       }
