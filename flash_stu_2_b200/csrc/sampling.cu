@@ -81,9 +81,17 @@ __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logi
       __syncthreads();
       const unsigned prefix = s_prefix;
       const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-      for (int i = tid; i < V; i += SP_T) {
-        unsigned key = ord_key(scaled_logit(row, i, temperature));
-        if ((key & mask) == prefix) atomicAdd(&s_hist[(key >> shift) & 255u], 1u);
+      // logits share their sign and exponent bytes, so almost every key of a pass lands in one or two bins: lanes
+      // that hit the same bin are counted by one of them (match_any) instead of serialising on the shared counter
+      for (int base = 0; base < V; base += SP_T) {
+        const int i = base + tid;
+        unsigned bin = 0xffffffffu;
+        if (i < V) {
+          const unsigned key = ord_key(scaled_logit(row, i, temperature));
+          if ((key & mask) == prefix) bin = (key >> shift) & 255u;
+        }
+        const unsigned peers = __match_any_sync(0xffffffffu, bin);
+        if (bin != 0xffffffffu && lane == __ffs(peers) - 1) atomicAdd(&s_hist[bin], (unsigned)__popc(peers));
       }
       __syncthreads();
       if (tid == 0) {
@@ -120,11 +128,13 @@ __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logi
     }
     if (tid >= C) { s_val[tid] = -INFINITY; s_idx[tid] = 0x7fffffff; }
     __syncthreads();
+    int SN = 2;   // sort width: the power of two that holds the C survivors (the padding sorts to the end)
+    while (SN < C) SN <<= 1;
     // ---- bitonic sort by (value descending, index ascending)
-    for (int k = 2; k <= SP_CAND; k <<= 1)
+    for (int k = 2; k <= SN; k <<= 1)
       for (int j = k >> 1; j > 0; j >>= 1) {
         int ixj = tid ^ j;
-        if (ixj > tid) {
+        if (ixj > tid && ixj < SN) {
           float va = s_val[tid], vb = s_val[ixj];
           int ia = s_idx[tid], ib = s_idx[ixj];
           bool a_first = (va > vb) || (va == vb && ia < ib);  // a ranks before b
@@ -156,10 +166,10 @@ __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logi
     // re-sort the kept entries by index ascending for the vocabulary-order running sum
     if (tid >= keep) s_idx[tid] = 0x7fffffff;
     __syncthreads();
-    for (int k = 2; k <= SP_CAND; k <<= 1)
+    for (int k = 2; k <= SN; k <<= 1)
       for (int j = k >> 1; j > 0; j >>= 1) {
         int ixj = tid ^ j;
-        if (ixj > tid) {
+        if (ixj > tid && ixj < SN) {
           int ia = s_idx[tid], ib = s_idx[ixj];
           bool up = ((tid & k) == 0);
           if (up ? (ia > ib) : (ia < ib)) {
