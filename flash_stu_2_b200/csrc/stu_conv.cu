@@ -135,6 +135,11 @@ __global__ void __launch_bounds__(256) conv_mma_kernel(const bf16* __restrict__ 
   const unsigned short* tg = reinterpret_cast<const unsigned short*>(taps + (size_t)c * Lh);
 
   for (int M0 = (mlo_min / CM_SB) * CM_SB; M0 < cnt_max; M0 += CM_SB) {
+    // A superblock's cost grows with its index (causal: K0 <= M0).  The superblocks of a channel are dealt to two
+    // CTAs (blockIdx.z) as {0,3,4,7,...} and {1,2,5,6,...}, which have equal cost, so that the grid is twice as
+    // fine and its last wave half as long.
+    const int sbi = M0 / CM_SB;
+    if ((int)(((sbi & 3) == 1) || ((sbi & 3) == 2)) != (int)blockIdx.z) continue;
     float acc[4][2][4];
 #pragma unroll
     for (int i = 0; i < 4; i++)
@@ -310,7 +315,7 @@ extern "C" int stu_conv_prefill_approx(const void* hist, const void* taps, void*
   if (use_tensor_cores) {
     if (dtype != STU_BF16) return STU_ERR_DTYPE;
     if (Lh % 8 || !aligned16(hist)) return STU_ERR_ALIGN;
-    dim3 grid(d, (2 * B + 15) / 16);
+    dim3 grid(d, (2 * B + 15) / 16, 2);
     conv_mma_kernel<<<grid, 256, 0, st>>>((const bf16*)hist, (const bf16*)taps, (bf16*)yT, B, d, Lh, y_Lh, t0, t_end);
   } else {
     int cnt = parity_count(t_end, 0);
