@@ -1,6 +1,8 @@
 """Spectral filters: the input data of the STU path (flash_stu/utils/stu_utils.py:18-193,
-flash_stu/utils/numerics.py:3-6).  Generation is an init-time host computation (float64 eigh of the
-Hankel matrix); the `.pt` file format {phi, shape, dtype, metadata} is the reference's."""
+flash_stu/utils/numerics.py:3-6).  Generation is an init-time float64 eigendecomposition of the Hankel matrix:
+on the GPU when the filters are wanted there (what the reference does, stu_utils.py:146-193 - at seq_len 32768
+the host eigh takes hours), on the host otherwise; the `.pt` file format {phi, shape, dtype, metadata} is the
+reference's."""
 import math
 from pathlib import Path
 from typing import Any, Dict, Optional
@@ -58,7 +60,51 @@ def get_spectral_filters(seq_len: int, K: int, use_hankel_L: bool = False, devic
         return load_spectral_filters(load_from, device=device, dtype=dtype, verify_shape=(seq_len, K))
     if device is None:
         device = torch.device("cuda" if torch.cuda.is_available() else "cpu")
+    device = torch.device(device)
+    if device.type == "cuda":
+        return spectral_filters_on_device(seq_len, K, use_hankel_L, device, dtype)
     sigma, phi = np.linalg.eigh(get_hankel(seq_len, use_hankel_L))
     sigma, phi = np.clip(sigma[-K:], 0.0, None), phi[:, -K:]
     phi = phi * sigma ** 0.25
     return torch.tensor(phi, device=device, dtype=dtype)
+
+
+def top_eigenpairs_subspace(Z: torch.Tensor, K: int, sweeps: int = 40, oversample: int = 16):
+    """The K largest eigenpairs (ascending, like eigh) of a symmetric positive semi-definite matrix by block power
+    iteration with re-orthonormalisation and a final Rayleigh-Ritz step, all in float64 on Z's device.  Eigenvalues
+    below the float64 noise of the largest one come out as noise, exactly as they do from a dense solver."""
+    n = Z.shape[0]
+    p = min(n, K + oversample)
+    g = torch.Generator(device="cpu").manual_seed(0)
+    X = torch.randn(n, p, dtype=torch.float64, generator=g).to(Z.device)
+    for _ in range(sweeps):
+        X, _ = torch.linalg.qr(Z @ X)
+    T = X.T @ (Z @ X)
+    w, V = torch.linalg.eigh((T + T.T) * 0.5)
+    return w[-K:], X @ V[:, -K:]
+
+
+def spectral_filters_on_device(seq_len: int, K: int, use_hankel_L: bool, device: torch.device,
+                               dtype: torch.dtype) -> torch.Tensor:
+    """The same filters with the Hankel matrix built and decomposed on the GPU (float64 torch.linalg.eigh, as
+    flash_stu/utils/stu_utils.py:189-193).  Eigenvector signs are whatever the solver returns; columns are made
+    reproducible by flipping each so that its largest-magnitude entry is positive."""
+    idx = torch.arange(1, seq_len + 1, dtype=torch.float64, device=device)
+    s = idx[:, None] + idx[None, :]
+    if use_hankel_L:
+        Z = ((-1.0) ** (s - 2.0) + 1.0) * (8.0 / ((s + 3.0) * (s - 1.0) * (s + 1.0)))
+    else:
+        Z = 2.0 / (s ** 3 - s)
+    del s
+    try:
+        sigma, phi = torch.linalg.eigh(Z)
+        sigma, phi = sigma[-K:], phi[:, -K:]
+    except RuntimeError:
+        # the dense solver refuses very large matrices (seq_len 32768 on this stack): only K eigenpairs are
+        # wanted and the spectrum decays geometrically, so block power iteration gets them in O(L^2 K) per sweep
+        sigma, phi = top_eigenpairs_subspace(Z, K)
+    del Z
+    sigma = sigma.clamp_min(0.0)
+    pick = phi.abs().argmax(dim=0)
+    phi = phi * torch.sign(phi.gather(0, pick[None, :]))
+    return (phi * sigma ** 0.25).to(dtype)

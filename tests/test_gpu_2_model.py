@@ -178,3 +178,21 @@ def test_mid_size_hybrid_bf16_model_against_the_oracle(tmp_path, hd, B):
     for s in range(new):
         err = O.rel_err(got[s], want_logits[:, s].float())
         assert err <= 2e-2, (s, err)
+
+
+def test_filters_generated_on_the_gpu_match_the_host_eigendecomposition():
+    """get_spectral_filters on a CUDA device decomposes the Hankel matrix there; the well-separated leading
+    filters equal the host (numpy) ones up to sign and every column satisfies Z phi = sigma phi."""
+    import numpy as np
+    import flash_stu_2_b200 as F
+    from flash_stu_2_b200.filters import get_hankel
+    L, K = 512, 16
+    phi = F.get_spectral_filters(L, K, device=dev(), dtype=torch.float64).cpu()
+    host = F.get_spectral_filters(L, K, device=torch.device("cpu"), dtype=torch.float64)
+    assert phi.shape == (L, K)
+    lead = slice(K - 8, K)                                   # the eight largest eigenvalues
+    assert (phi[:, lead].abs() - host[:, lead].abs()).abs().max() < 1e-7
+    Z = torch.tensor(get_hankel(L))
+    v = phi[:, -1] / phi[:, -1].norm()
+    assert ((Z @ v) - (v @ Z @ v) * v).norm() < 1e-10
+    assert int(phi[:, -1].abs().argmax()) >= 0 and phi[:, -1][phi[:, -1].abs().argmax()] > 0

@@ -105,3 +105,17 @@ def test_checkpoint_round_trip_and_vocabulary_resize(tmp_path):
     pos = torch.tensor([[5, 0], [7, 0]], dtype=torch.int32)
     out = F.FlashSTU._reorder_cache(((hist, pos), None), torch.tensor([1, 0]))
     assert torch.equal(out[0][0], hist[[1, 0]]) and out[0][1][:, 0].tolist() == [7, 5] and out[1] is None
+
+
+def test_block_power_iteration_reproduces_the_leading_hankel_eigenpairs():
+    """top_eigenpairs_subspace (used for filters when the dense solver refuses the matrix) against numpy eigh."""
+    import numpy as np
+    import torch
+    from flash_stu_2_b200.filters import get_hankel, top_eigenpairs_subspace
+    L, K = 384, 16
+    Zn = get_hankel(L)
+    w, V = top_eigenpairs_subspace(torch.tensor(Zn), K)
+    wr, Vr = np.linalg.eigh(Zn)
+    assert np.allclose(w.numpy()[-10:], wr[-10:], rtol=1e-9, atol=1e-15)
+    assert (V[:, -8:].abs() - torch.tensor(Vr[:, -8:]).abs()).abs().max() < 1e-9
+    assert torch.allclose(V.T @ V, torch.eye(K, dtype=torch.float64), atol=1e-10)
