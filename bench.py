@@ -47,10 +47,12 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--variant", choices=["approx", "full"], default="approx",
                     help="STU variant of the block: approx (M_inputs/M_filters, the headline) or full (M_phi_plus/minus)")
-    ap.add_argument("--model", choices=["c1", "c3", "c4"], default=None,
+    ap.add_argument("--model", choices=["c1", "c3", "c4", "c5"], default=None,
                     help="instead of the headline block workload, time FlashSTU.generate() on a whole model: "
                          "c1 = d512/12 layers/fp32/B=2/prompt 128/+128 greedy; "
                          "c3 = d1536/24 layers/bf16/B=32/prompt 2048/+512, top_k=40, T=0.8; "
+                         "c5 = d3072/32 layers/bf16/B=64/prompt 8192/+1024 greedy, seq_len 32768 (cache laid out for "
+                         "9216 positions); "
                          "c4 = 12 stacked MiniSTU(backend='lds', 1024->1024), bf16, B=16, prefill 15360 + 1024 steps")
     ap.add_argument("--tp", action="store_true",
                     help="with --model c1|c3 under torchrun: shard the model over the ranks (tensor parallelism) "
@@ -501,6 +503,9 @@ MODEL_CONFIGS = {
     "c3": dict(cfg=dict(n_embd=1536, n_layers=24, n_heads=12, seq_len=8192, window_size=1024, vocab_size=50257,
                         mlp_scale=4, num_eigh=24, use_attn=True, use_approx=True), dtype="bfloat16", B=32, prompt=2048,
                new=512, sampling=dict(do_sample=True, temperature=0.8, top_k=40)),
+    "c5": dict(cfg=dict(n_embd=3072, n_layers=32, n_heads=24, seq_len=32768, window_size=2048, vocab_size=50257,
+                        mlp_scale=4, num_eigh=32, use_attn=True, use_approx=True, cache_len=9216), dtype="bfloat16",
+               B=64, prompt=8192, new=1024, sampling=dict(do_sample=False)),
 }
 
 
@@ -582,7 +587,6 @@ def run_model_tp(a):
     import flash_stu_2_b200 as F
     from flash_stu_2_b200 import ops, parallel
     from flash_stu_2_b200.tensor_parallel import TensorParallelFlashSTU
-    from oracle import stu_oracle as O   # only for the filter values (host eigh) when no filter file is shipped
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -598,7 +602,7 @@ def run_model_tp(a):
         fp = filter_file(L)
         if fp is None:
             fp = os.path.join(tmp, "phi.pt")
-            F.save_spectral_filters(O.spectral_filters(L, K), fp)
+            F.save_spectral_filters(F.get_spectral_filters(L, K, device=dev, dtype=torch.float32), fp)
         torch.manual_seed(0)
         config = F.FlashSTUConfig(filter_path=fp, torch_dtype=dt, **cfg)
         full = F.FlashSTU(config)
@@ -652,7 +656,6 @@ def run_model(a):
     import tempfile
     import flash_stu_2_b200 as F
     from flash_stu_2_b200 import ops
-    from oracle import stu_oracle as O   # only for the filter values (host eigh) when no filter file is shipped
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py --model needs a CUDA device: the kernels have no CPU fallback")
     dev = torch.device("cuda:0")
@@ -660,10 +663,10 @@ def run_model(a):
     cfg, dt = dict(spec["cfg"]), getattr(torch, spec["dtype"])
     L, K = cfg["seq_len"], cfg["num_eigh"]
     with tempfile.TemporaryDirectory() as tmp:
-        fp = filter_file(L)
+        fp = filter_file(L) if K == NUM_FILTERS else None
         if fp is None:
             fp = os.path.join(tmp, "phi.pt")
-            F.save_spectral_filters(O.spectral_filters(L, K), fp)
+            F.save_spectral_filters(F.get_spectral_filters(L, K, device=dev, dtype=torch.float32), fp)
         torch.manual_seed(0)
         model = F.FlashSTU(F.FlashSTUConfig(filter_path=fp, torch_dtype=dt, **cfg)).to(dev).eval()
     B, T0, new = spec["B"], spec["prompt"], (a.new_tokens or spec["new"])

@@ -43,6 +43,7 @@ class FlashSTUConfig(PretrainedConfig):
         filter_path: Optional[str] = None,
         d_in_tile: Optional[int] = None,
         d_out_tile: Optional[int] = None,
+        cache_len: Optional[int] = None,
         **kwargs,
     ):
         super().__init__(tie_word_embeddings=tie_word_embeddings, **kwargs)
@@ -52,7 +53,7 @@ class FlashSTUConfig(PretrainedConfig):
             use_hankel_L=use_hankel_L, use_flash_fft=use_flash_fft, use_approx=use_approx, use_attn=use_attn,
             use_cache=use_cache, use_gradient_checkpointing=use_gradient_checkpointing, softcap=softcap,
             stu_enable_mlp_sandwich=stu_enable_mlp_sandwich, stu_mlp_hidden_size=stu_mlp_hidden_size,
-            filter_path=filter_path, d_in_tile=d_in_tile, d_out_tile=d_out_tile,
+            filter_path=filter_path, d_in_tile=d_in_tile, d_out_tile=d_out_tile, cache_len=cache_len,
         ).items():
             setattr(self, name, value)
         self.hidden_size = n_embd

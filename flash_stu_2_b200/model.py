@@ -168,8 +168,8 @@ class FlashSTU(PreTrainedModel):
         # Cached token steps after the first are replayed from one captured CUDA graph (every kernel reads its
         # position from device memory): the step is ~100 small launches for a 24-layer model, which the interpreter
         # cannot issue as fast as the GPU retires them.  cuda_graph=False keeps the eager loop.
-        use_graph = bool(kwargs.get("cuda_graph", True)) and use_cache and steps > 3 and \
-            max_length - 1 <= self.config.seq_len
+        capacity = min(self.config.seq_len, getattr(self.config, "cache_len", None) or self.config.seq_len)
+        use_graph = bool(kwargs.get("cuda_graph", True)) and use_cache and steps > 3 and max_length - 1 <= capacity
         graph = None
         for step in range(steps):
             cur = T0 + step

@@ -117,6 +117,9 @@ class STU(nn.Module):
                 self.M_phi_minus = nn.Parameter(torch.empty(self.K, self.d_in, self.d_out, dtype=dt))
         self._prep_key = None
         self._prep = None
+        # optional cap on the positions a cache (and the tap tables) are laid out for: a model whose filters span
+        # 32768 positions but that will only ever see 9216 keeps 9216-position histories (config.cache_len)
+        self.cache_len = getattr(config, "cache_len", None)
 
     # ---- derived, cached per parameter version: M_inputs^T (K-major rows) and the even-tap table
     @property
@@ -124,8 +127,13 @@ class STU(nn.Module):
         return self.phi.shape[0]
 
     @property
+    def capacity(self) -> int:
+        """Positions this operator can hold: seq_len (the filters have seq_len taps), or config.cache_len if smaller."""
+        return min(self.seq_len, self.cache_len) if self.cache_len else self.seq_len
+
+    @property
     def Lh(self) -> int:
-        return _round_up((self.seq_len + 1) // 2, 8)
+        return _round_up((self.capacity + 1) // 2, 8)
 
     def prepared(self):
         if not self.use_approx:
@@ -134,7 +142,8 @@ class STU(nn.Module):
                self.M_filters.data_ptr(), self.phi.data_ptr())
         if self._prep_key != key:
             with torch.no_grad():
-                phi = self.phi.to(self.M_filters.dtype).contiguous()
+                # only the taps of positions a cache can hold are ever used
+                phi = self.phi[:self.capacity].to(self.M_filters.dtype).contiguous()
                 MinT = self.M_inputs.detach().t().contiguous()
                 # fp = phi @ M_filters, rounded to the model dtype as in the reference (stu.py:88)
                 fp = ops.linear(phi, self.M_filters.detach(), transposed_weight=True, backend=ops.BACKEND_SIMT)
@@ -180,8 +189,9 @@ class STU(nn.Module):
         else:
             pos = None
             hist = torch.zeros(B, d, 2, _round_up((T + 1) // 2, 8), dtype=xn.dtype, device=xn.device)
-        if t0 + T > self.seq_len:
-            raise ValueError(f"sequence position {t0 + T} exceeds seq_len={self.seq_len} (the filters have seq_len taps)")
+        if t0 + T > self.capacity:
+            raise ValueError(f"sequence position {t0 + T} exceeds the capacity {self.capacity} (seq_len={self.seq_len}: "
+                             f"the filters have seq_len taps; cache_len={self.cache_len})")
         Lh = hist.shape[3]
         ops.to_history(xn, hist, t0)
         S = _round_up((t0 + T + 1) // 2, 8)
@@ -217,8 +227,8 @@ class STU(nn.Module):
         B, d, _, Lh = hist.shape
         K, nsign = self.K, (1 if self.use_hankel_L else 2)
         t = host_pos(pos)
-        if t + 1 > self.seq_len:
-            raise ValueError(f"sequence position {t + 1} exceeds seq_len={self.seq_len}")
+        if t + 1 > self.capacity:
+            raise ValueError(f"sequence position {t + 1} exceeds the capacity {self.capacity} (seq_len={self.seq_len})")
         key = (B, xn2d.device, xn2d.dtype)
         if getattr(self, "_dec_scratch_key", None) != key:
             self._dec_scratch = (torch.zeros(2 * K, Lh, dtype=xn2d.dtype, device=xn2d.device),
@@ -248,8 +258,9 @@ class STU(nn.Module):
         else:
             pos = None
             hist = torch.empty(B, d, 2, self.Lh, dtype=xn.dtype, device=xn.device)
-        if t0 + T > self.seq_len:
-            raise ValueError(f"sequence position {t0 + T} exceeds seq_len={self.seq_len} (the filters have seq_len taps)")
+        if t0 + T > self.capacity:
+            raise ValueError(f"sequence position {t0 + T} exceeds the capacity {self.capacity} (seq_len={self.seq_len}: "
+                             f"the filters have seq_len taps; cache_len={self.cache_len})")
         Lh = hist.shape[3]
         ops.linear(xn.reshape(B * T, d), MinT, out=hist, epilogue=ops.EPI_HIST, hist_T=T, hist_t0=t0, hist_Lh=Lh)
         yT = torch.empty(B, d, 2, _round_up((t0 + T + 1) // 2, 8), dtype=xn.dtype, device=xn.device)
@@ -270,8 +281,8 @@ class STU(nn.Module):
         hist, pos = entry
         MinT, taps, taps8 = self.prepared()
         t = host_pos(pos)
-        if t + 1 > self.seq_len:
-            raise ValueError(f"sequence position {t + 1} exceeds seq_len={self.seq_len}")
+        if t + 1 > self.capacity:
+            raise ValueError(f"sequence position {t + 1} exceeds the capacity {self.capacity} (seq_len={self.seq_len})")
         ops.decode_approx(x2d, norm_w, MinT, hist, taps, pos, out2d, eps,
                           taps8=taps8 if STU.tensor_core_decode else None,
                           flags=(ops.FLAG_EARLY_TRIGGER if ops.overlap_decode else 0) |

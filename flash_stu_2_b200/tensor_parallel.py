@@ -94,7 +94,8 @@ class TensorParallelFlashSTU:
             self.sd["lm_head.weight"] = shard_state_dict({"lm_head.weight": state_dict["tok_emb.weight"]}, c, self.rank,
                                                          self.world)["lm_head.weight"].to(self.device)
         self.dtype = self.sd["tok_emb.weight"].dtype
-        self.Lh = _round_up((config.seq_len + 1) // 2, 8)
+        self.capacity = min(config.seq_len, getattr(config, "cache_len", None) or config.seq_len)
+        self.Lh = _round_up((self.capacity + 1) // 2, 8)
         ws = config.window_size
         self.window = int(ws[0] if isinstance(ws, (tuple, list)) else ws)
         self.eps = ops.RMS_EPS
@@ -113,7 +114,8 @@ class TensorParallelFlashSTU:
         if i not in self._derived:
             p = f"layers.{i}.stu."
             MinT = self.sd[p + "M_inputs"].t().contiguous()
-            fp = ops.linear(self.sd["phi"].to(self.dtype), self.sd[p + "M_filters"], transposed_weight=True,
+            fp = ops.linear(self.sd["phi"][:self.capacity].to(self.dtype).contiguous(), self.sd[p + "M_filters"],
+                            transposed_weight=True,
                             backend=ops.BACKEND_SIMT)
             taps = ops.taps_even(fp, self.Lh)
             taps8 = ops.taps_rev8(taps) if (self.dtype == torch.bfloat16 and self.dl % 8 == 0) else None
@@ -164,8 +166,8 @@ class TensorParallelFlashSTU:
             else:
                 hist, pos = cache[i]
                 t0 = host_pos(pos)
-                if t0 + T > self.cfg.seq_len:
-                    raise ValueError(f"sequence position {t0 + T} exceeds seq_len={self.cfg.seq_len}")
+                if t0 + T > self.capacity:
+                    raise ValueError(f"sequence position {t0 + T} exceeds the capacity {self.capacity}")
                 MinT, taps, taps8 = self._stu_weights(i)
                 if T == 1 and taps8 is not None and self.fused_decode:
                     # one token: the fused kernel on this rank's channels (norm, projection, cache append, taps;
@@ -212,7 +214,7 @@ class TensorParallelFlashSTU:
         # as in FlashSTU.generate: cached steps after the first are replayed from one captured CUDA graph (the NCCL
         # collectives are captured with the kernels; every rank captures and replays in lock step)
         # (the unfused one-token path passes its position to the kernels as an argument and cannot be replayed)
-        use_graph = cuda_graph and steps > 3 and max_length - 1 <= self.cfg.seq_len and self.fused_decode and \
+        use_graph = cuda_graph and steps > 3 and max_length - 1 <= self.capacity and self.fused_decode and \
             self.dtype == torch.bfloat16 and self.dl % 8 == 0
         graph = None
         for step in range(steps):

@@ -204,3 +204,30 @@ def test_benchmark_block_at_full_size_against_the_oracle(approx):
     assert O.rel_err(full, ref) <= 2e-2, O.rel_err(full, ref)
     assert O.rel_err(torch.cat(rows, 1), ref[:, L - S:]) <= 2e-2
     assert O.rel_err(y1.cpu(), ref[:, :L - S]) <= 2e-2
+
+
+def test_cache_laid_out_for_fewer_positions_than_the_filters(golden):
+    """config.cache_len: a block whose filters span seq_len positions but whose caches and tap tables are laid out
+    for fewer gives the same rows as the full-capacity block, and refuses positions beyond its capacity."""
+    import flash_stu_2_b200 as F
+    from flash_stu_2_b200 import ops
+    r = golden("blocks")["approx_bfloat16"]
+    x = r["x"].to(dev())
+    T = x.shape[1]
+    cap = T - 40
+    cfg = F.FlashSTUConfig(n_embd=r["d"], seq_len=r["L"], num_eigh=r["K"], use_attn=False, mlp_scale=4,
+                           torch_dtype=torch.bfloat16, n_layers=1, vocab_size=1, n_heads=1, cache_len=cap)
+    blk = F.FlashSTUBlock(config=cfg, phi=r["sd"]["phi"].clone(), n=r["n"])
+    blk.load_state_dict(r["sd"])
+    blk = blk.to(dev()).eval()
+    with torch.no_grad():
+        y1, cache = blk(x[:, :cap - 5].clone(), use_cache=True)
+        rows = [y1]
+        for t in range(cap - 5, cap):
+            yt, cache = blk(x[:, t:t + 1].clone(), past_key_value=cache, use_cache=True)
+            rows.append(yt)
+        with pytest.raises(ValueError, match="capacity"):
+            blk(x[:, cap:cap + 1].clone(), past_key_value=cache, use_cache=True)
+    ops.check_status()
+    assert cache[0].shape[3] < (r["L"] + 1) // 2
+    assert O.rel_err(torch.cat(rows, 1).cpu(), r["y"][:, :cap]) <= 2e-2
