@@ -78,8 +78,11 @@ def _worker(rank, world, port, q):
     dist.destroy_process_group()
 
 
-def test_two_rank_tensor_parallel_algebra_matches_reference():
-    world = 2
+import pytest
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_algebra_matches_reference(world):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
@@ -90,8 +93,8 @@ def test_two_rank_tensor_parallel_algebra_matches_reference():
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    assert res[0][1] <= 1e-4 and res[1][1] <= 1e-4, res
-    assert res[0][2] == res[1][2]          # every rank ends with the same logits
+    assert all(r[1] <= 1e-4 for r in res), res
+    assert all(r[2] == res[0][2] for r in res)          # every rank ends with the same logits
 
 
 def test_shards_tile_the_full_weights():
