@@ -1,13 +1,13 @@
 // Prefill linear layers on the 5th-generation tensor cores: D[M,N] = A[M,K] . B[N,K]^T in bf16 with
 // fp32 accumulators held in tensor memory (TMEM).
 //
-// One CTA computes a 128 x 128 output tile.  Warp 0 is the TMA producer (cp.async.bulk.tensor, 128-byte
-// swizzled 128x64 operand tiles into a ring of shared-memory stages), warp 1 allocates TMEM and
+// One CTA computes 128 x 128 or 128 x 256 output tiles.  Warp 0 is the TMA producer (cp.async.bulk.tensor, 128-byte
+// swizzled 128x64 / 256x64 operand tiles into a ring of shared-memory stages), warp 1 allocates TMEM and
 // issues tcgen05.mma from one thread, warps 2..5 drain the accumulator with tcgen05.ld and run the
 // fused epilogue (store / residual add / tanh-GELU gate * up / transposed scatter into the projected
 // history).  The kernel is persistent (one CTA per SM walks the tile list) and the accumulator is
-// double-buffered in TMEM, so one tile's epilogue overlaps the next tile's main loop.  No cluster
-// features and no multicast are used.
+// double-buffered in TMEM, so one tile's epilogue overlaps the next tile's main loop.  Every load is a plain
+// single-CTA TMA load of this GPU's own memory.
 //
 // Every wait on an mbarrier is bounded: on expiry the waiter raises the status word, the CTA drains
 // its outstanding bulk copies (bounded as well), frees its TMEM and returns.

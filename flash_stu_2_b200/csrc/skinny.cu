@@ -1,7 +1,7 @@
 // Decode-time linear layers: M <= 64 activation rows against an [N,K] weight.  The step is bound by
 // streaming the weight from HBM once, so the kernel is organised around 128-bit weight loads with
-// all eight warps of a CTA splitting K for eight output features; the handful of activation rows
-// sit in shared memory (optionally RMS-normalised on the way in).  bf16 uses mma.sync m16n8k16
+// the warps of a CTA splitting K for eight output features; the activation rows are L2-resident and are
+// loaded straight into MMA fragments (optionally RMS-normalised on the way in).  bf16 uses mma.sync m16n8k16
 // with fp32 accumulation (at 8..64 rows CUDA-core FMA throughput would cap the kernel below the HBM
 // rate); fp32 models use fp32 FMAs.
 #include <cooperative_groups.h>
