@@ -46,6 +46,14 @@ class FlashSTUConfig(PretrainedConfig):
         cache_len: Optional[int] = None,
         **kwargs,
     ):
+        # transformers >= 5 serialises a model's dtype under the key `dtype` (and drops `torch_dtype` from the dict it
+        # hands back to this constructor): a checkpoint written from a float32 model must not come back as the
+        # bfloat16 default, so an explicit `dtype` wins over an unset / default `torch_dtype`
+        dtype_kw = kwargs.get("dtype")
+        if isinstance(dtype_kw, str):
+            dtype_kw = getattr(torch, dtype_kw.replace("torch.", ""), None)
+        if isinstance(dtype_kw, torch.dtype) and (torch_dtype is None or torch_dtype == torch.bfloat16):
+            torch_dtype = dtype_kw
         super().__init__(tie_word_embeddings=tie_word_embeddings, **kwargs)
         for name, value in dict(
             bsz=bsz, n_embd=n_embd, n_heads=n_heads, n_layers=n_layers, seq_len=seq_len, window_size=window_size,
@@ -70,4 +78,5 @@ class FlashSTUConfig(PretrainedConfig):
         dt = getattr(self, "torch_dtype", None)
         if isinstance(dt, torch.dtype):
             out["torch_dtype"] = str(dt).replace("torch.", "")
+            out["dtype"] = out["torch_dtype"]
         return out

@@ -12,6 +12,8 @@
 #define STU_ERR_NULL (-5)
 #define STU_ERR_DEVICE_STATUS (-6)
 
+#define STU_MAX_DEVICES 64  // per-device tables (status word, SM count, static scratch address)
+
 #define STU_F32 0
 #define STU_BF16 1
 

@@ -17,6 +17,8 @@
 #include "common.cuh"
 #include "epilogue.cuh"
 
+int device_sm_count();   // SM count of the current device (cached per device)
+
 namespace {
 
 constexpr int BM = 128, BK = 64;
@@ -44,14 +46,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after WAIT_LIMIT polls or two seconds of wall time, whichever comes first.
+// Bounded wait: gives up after WAIT_LIMIT polls or wait_ns of wall time (two seconds unless a test shortened it),
+// whichever comes first.
 // Returns false when the limit ran out or another role already gave up.
 __device__ __forceinline__ uint64_t global_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long wait_ns) {
   uint64_t start = 0;
   for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -59,7 +63,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       if (*abort_flag) return false;
       uint64_t now = global_ns();
       if (start == 0) start = now;
-      else if (now - start > 2000000000ull) break;
+      else if (now - start > wait_ns) break;
     }
   }
   *abort_flag = 1;
@@ -140,7 +144,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
                                                          const __grid_constant__ CUtensorMap tmB,
                                                          const __grid_constant__ CUtensorMap tmB2, int M, int N,
                                                          int K, int tiles_m, int tiles_n, int m_fast,
-                                                         int causal, EpiArgs<bf16> ep, int* status) {
+                                                         int causal, EpiArgs<bf16> ep, int* status,
+                                                         int drop_first_copy, unsigned long long wait_ns) {
   constexpr bool DUAL = (EPI == EPI_GELU_MUL);
   static_assert(!DUAL || TN == 128, "the two-accumulator epilogue uses 128-wide tiles");
   constexpr int BN = TN;                       // shadows the file-level default inside the kernel
@@ -200,13 +205,17 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         for (int kb = 0; kb < kb_end; kb++, g++) {
           const int s = g % STAGES;
           const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, wait_ns)) { ok = false; break; }
           unsigned char* sa = smem + s * STAGE_BYTES;
           mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-          tma_load_2d(sa, &tmA, &full_bar[s], kb * BK, m0);
-          tma_load_2d(sa + A_BYTES, &tmB, &full_bar[s], kb * BK, n0);
-          if (DUAL) tma_load_2d(sa + A_BYTES + B_BYTES, &tmB2, &full_bar[s], kb * BK, n0);
-          *issued_ctr = g + 1;
+          // drop_first_copy (failure-detection test only): the first stage's copies are never issued, so its
+          // barrier never completes and the consumer's bounded wait has to run out
+          if (!(drop_first_copy && g == 0)) {
+            tma_load_2d(sa, &tmA, &full_bar[s], kb * BK, m0);
+            tma_load_2d(sa + A_BYTES, &tmB, &full_bar[s], kb * BK, n0);
+            if (DUAL) tma_load_2d(sa + A_BYTES + B_BYTES, &tmB2, &full_bar[s], kb * BK, n0);
+            *issued_ctr = g + 1;
+          }
         }
       }
     }
@@ -220,12 +229,12 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS;
         const int tn_ = m_fast ? (tile / tiles_m) : (tile % tiles_n);
         const int kb_end = tile_kb(num_kb, tn_ * BN, causal, BN);
-        if (!mbar_wait(&tmem_empty[buf], (((uint32_t)it >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&tmem_empty[buf], (((uint32_t)it >> 1) & 1u) ^ 1u, abort_flag, wait_ns)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         for (int kb = 0; kb < kb_end; kb++, g++) {
           const int s = g % STAGES;
           const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
-          if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, wait_ns)) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
           const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
@@ -258,7 +267,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
       const int m = m0 + row;
       const int buf = it & 1;
       const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS;
-      bool ok = mbar_wait(&tmem_full[buf], ((uint32_t)it >> 1) & 1u, abort_flag);
+      bool ok = mbar_wait(&tmem_full[buf], ((uint32_t)it >> 1) & 1u, abort_flag, wait_ns);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -349,11 +358,14 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
     if (threadIdx.x == 0) {
       if (status) atomicExch(status, 3);
       const int issued = *issued_ctr, consumed = *consumed_ctr;
+      const uint64_t drain_start = global_ns();
       for (int g = consumed; g < issued; g++) {
         const int s = g % STAGES;
         const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
-        for (uint32_t w = 0; w < WAIT_LIMIT; ++w)
+        for (uint32_t w = 0; w < WAIT_LIMIT; ++w) {
           if (mbar_try_wait(&full_bar[s], ph)) break;
+          if ((w & 255u) == 255u && global_ns() - drain_start > wait_ns) break;
+        }
       }
     }
     __syncthreads();
@@ -397,6 +409,11 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
   return r == CUDA_SUCCESS ? STU_OK : STU_ERR_UNSUPPORTED;
 }
 
+// Failure-detection test hooks (stu_test_inject_wait_expiry): drop the first operand copy of the next launch, and the
+// wall-time bound of every mbarrier wait.
+int g_drop_first_copy = 0;
+unsigned long long g_wait_ns = 2000000000ull;
+
 template <int EPI, int STAGES, int TN = 128>
 int launch_tc(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& b2, int M, int N, int K, int m_fast,
               int causal, const EpiArgs<bf16>& ep, int* status, cudaStream_t st) {
@@ -408,26 +425,59 @@ int launch_tc(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& b2,
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
-      sm_count = 148;
-  }
+  const int sm_count = device_sm_count();
   const int tiles = tiles_m * tiles_n;
   const int grid = tiles < sm_count ? tiles : sm_count;  // one persistent CTA per SM
-  k<<<grid, 192, smem, st>>>(a, b, b2, M, N, K, tiles_m, tiles_n, m_fast, causal, ep, status);
+  const int drop = g_drop_first_copy;
+  g_drop_first_copy = 0;   // the injected fault applies to one launch
+  k<<<grid, 192, smem, st>>>(a, b, b2, M, N, K, tiles_m, tiles_n, m_fast, causal, ep, status, drop, g_wait_ns);
   STU_CHECK_LAUNCH();
   return STU_OK;
 }
 
-int* g_status_word = nullptr;  // optional device status word registered by the host wrapper
-
 }  // namespace
 
+// Per-device state of the library: the status word the host wrapper registered for the device that was current at
+// the time (a kernel must never be handed a word that lives on another GPU) and that device's SM count.
+static int* g_status_words[STU_MAX_DEVICES] = {nullptr};
+static int g_sm_counts[STU_MAX_DEVICES] = {0};
+
+static int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= STU_MAX_DEVICES) return 0;
+  return dev;
+}
+
+int device_sm_count() {
+  const int dev = current_device();
+  int n = g_sm_counts[dev];
+  if (n <= 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    g_sm_counts[dev] = n;
+  }
+  return n;
+}
+
+static int* device_status_word() { return g_status_words[current_device()]; }
+
+// Test hook for the failure-detection path: the next tcgen05 GEMM launch of this process never issues the copies of
+// its first pipeline stage, and every bounded wait gives up after wait_ms milliseconds (0 restores the default of
+// two seconds without arming a fault).  The kernel then reports status 3, drains what it did issue, frees its tensor
+// memory and returns; nothing faults and the context stays usable.
+extern "C" int stu_test_inject_wait_expiry(int wait_ms) {
+  if (wait_ms < 0 || wait_ms > 10000) return STU_ERR_SHAPE;
+  if (wait_ms == 0) {
+    g_drop_first_copy = 0;
+    g_wait_ns = 2000000000ull;
+  } else {
+    g_drop_first_copy = 1;
+    g_wait_ns = (unsigned long long)wait_ms * 1000000ull;
+  }
+  return STU_OK;
+}
+
 extern "C" int stu_set_status_word(int* device_status) {
-  g_status_word = device_status;
+  g_status_words[current_device()] = device_status;
   return STU_OK;
 }
 
@@ -464,8 +514,8 @@ int gemm_tc_dispatch(const void* A, long long lda, const void* B, long long ldb,
     if ((rc = make_map(&ma, B, N, K, ldb)) != STU_OK) return rc;
     if ((rc = make_map(&mb, A, M, K, lda, wide ? 256 : BM)) != STU_OK) return rc;
     ep.ldy = N;  // channel count
-    if (wide) return launch_tc<EPI_HIST_T, 4, 256>(ma, mb, mb, N, M, K, /*m_fast=*/1, 0, ep, g_status_word, st);
-    return launch_tc<EPI_HIST_T, 6>(ma, mb, mb, N, M, K, /*m_fast=*/1, 0, ep, g_status_word, st);
+    if (wide) return launch_tc<EPI_HIST_T, 4, 256>(ma, mb, mb, N, M, K, /*m_fast=*/1, 0, ep, device_status_word(), st);
+    return launch_tc<EPI_HIST_T, 6>(ma, mb, mb, N, M, K, /*m_fast=*/1, 0, ep, device_status_word(), st);
   }
   const bool wide = epi != EPI_GELU_MUL && wide_tiles(M, N);
   if ((rc = make_map(&ma, A, M, K, lda)) != STU_OK) return rc;
@@ -474,14 +524,14 @@ int gemm_tc_dispatch(const void* A, long long lda, const void* B, long long ldb,
   if (epi == EPI_GELU_MUL && (rc = make_map(&mb2, B2, N, K, ldb)) != STU_OK) return rc;
   if (wide) {
     switch (epi) {
-      case EPI_STORE: return launch_tc<EPI_STORE, 4, 256>(ma, mb, mb2, M, N, K, 0, causal, ep, g_status_word, st);
-      case EPI_RESID: return launch_tc<EPI_RESID, 4, 256>(ma, mb, mb2, M, N, K, 0, causal, ep, g_status_word, st);
+      case EPI_STORE: return launch_tc<EPI_STORE, 4, 256>(ma, mb, mb2, M, N, K, 0, causal, ep, device_status_word(), st);
+      case EPI_RESID: return launch_tc<EPI_RESID, 4, 256>(ma, mb, mb2, M, N, K, 0, causal, ep, device_status_word(), st);
     }
   }
   switch (epi) {
-    case EPI_STORE: return launch_tc<EPI_STORE, 6>(ma, mb, mb2, M, N, K, 0, causal, ep, g_status_word, st);
-    case EPI_RESID: return launch_tc<EPI_RESID, 6>(ma, mb, mb2, M, N, K, 0, causal, ep, g_status_word, st);
-    case EPI_GELU_MUL: return launch_tc<EPI_GELU_MUL, 4>(ma, mb, mb2, M, N, K, 0, 0, ep, g_status_word, st);
+    case EPI_STORE: return launch_tc<EPI_STORE, 6>(ma, mb, mb2, M, N, K, 0, causal, ep, device_status_word(), st);
+    case EPI_RESID: return launch_tc<EPI_RESID, 6>(ma, mb, mb2, M, N, K, 0, causal, ep, device_status_word(), st);
+    case EPI_GELU_MUL: return launch_tc<EPI_GELU_MUL, 4>(ma, mb, mb2, M, N, K, 0, 0, ep, device_status_word(), st);
   }
   return STU_ERR_UNSUPPORTED;
 }

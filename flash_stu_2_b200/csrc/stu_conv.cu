@@ -311,10 +311,14 @@ extern "C" int stu_conv_prefill_approx(const void* hist, const void* taps, void*
   if (!hist || !taps || !yT || !x) return STU_ERR_NULL;
   if (B <= 0 || d <= 0 || Lh <= 0 || t0 < 0 || t_end <= t0 || t_end > 2 * Lh || t_end > 2 * y_Lh)
     return STU_ERR_SHAPE;
+  if (dtype != STU_F32 && dtype != STU_BF16) return STU_ERR_DTYPE;
+  // the residual add reads yT with 16-byte loads along a parity row: the base and the row pitch must keep every
+  // row start on a 16-byte boundary (y_Lh a multiple of 8 for bf16, of 4 for fp32)
+  if (!aligned16(yT) || y_Lh % (dtype == STU_F32 ? 4 : 8)) return STU_ERR_ALIGN;
   cudaStream_t st = (cudaStream_t)stream;
   if (use_tensor_cores) {
     if (dtype != STU_BF16) return STU_ERR_DTYPE;
-    if (Lh % 8 || !aligned16(hist)) return STU_ERR_ALIGN;
+    if (Lh % 8 || !aligned16(hist) || (((uintptr_t)taps) & 1u)) return STU_ERR_ALIGN;
     dim3 grid(d, (2 * B + 15) / 16, 2);
     conv_mma_kernel<<<grid, 256, 0, st>>>((const bf16*)hist, (const bf16*)taps, (bf16*)yT, B, d, Lh, y_Lh, t0, t_end);
   } else {
@@ -1133,7 +1137,7 @@ static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_B
 
 #include <mutex>
 static std::mutex g_static_scratch_mutex;
-static void* g_static_scratch_ptr[64] = {nullptr};
+static void* g_static_scratch_ptr[STU_MAX_DEVICES] = {nullptr};
 
 // Same computation and arguments as stu_conv_prefill_approx, minus yT / y_Lh.
 //   * Limit: B * d * 2 * roundup8(ceil(t_end / 2)) elements of the dtype must fit in 32 MiB
@@ -1157,7 +1161,7 @@ extern "C" int stu_conv_prefill_approx_static(const void* hist, const void* taps
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
-  if (dev < 0 || dev >= 64) return STU_ERR_UNSUPPORTED;
+  if (dev < 0 || dev >= STU_MAX_DEVICES) return STU_ERR_UNSUPPORTED;
   void* scratch = nullptr;
   {
     std::lock_guard<std::mutex> lock(g_static_scratch_mutex);

@@ -63,7 +63,8 @@ def status_word(device) -> torch.Tensor:
     if key not in _status:
         w = torch.zeros(1, dtype=torch.int32, device=dev)
         _status[key] = w
-        _lib.check(_lib.load().stu_set_status_word(w.data_ptr()), "stu_set_status_word")
+        with torch.cuda.device(key):   # the library keeps one word per device, registered with that device current
+            _lib.check(_lib.load().stu_set_status_word(w.data_ptr()), "stu_set_status_word")
     return _status[key]
 
 
@@ -142,6 +143,7 @@ def linear(x: torch.Tensor, W: torch.Tensor, *, W2: Optional[torch.Tensor] = Non
     if resid is not None:
         assert resid.shape == (M, N) and resid.stride(1) == 1
         r_rs = resid.stride(0)
+    status_word(x.device)   # the tcgen05 GEMM reports an expired device-side wait through the registered word
     rc = _lib.load().stu_linear(x.data_ptr(), x.stride(0), W.data_ptr(), w_rs, w_ks, _p(W2), _p(resid), r_rs,
                                 out.data_ptr(), y_rs, M, N, K, epilogue, hist_T, hist_t0, hist_Lh, _p(norm_w), eps,
                                 _dt(x), backend, _stream())

@@ -35,3 +35,32 @@ def gather_token_ids(local_ids: torch.Tensor, global_batch: int) -> torch.Tensor
     out = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(out, padded)
     return torch.cat([o[: e - s] for o, (s, e) in zip(out, sizes)], dim=0)
+
+
+class RankLost(RuntimeError):
+    """A rank of the job did not reach a step fence in time (it raised, exited or never joined)."""
+
+
+class StepFence:
+    """Host-side membership check between token steps of a multi-rank job.
+
+    Every rank calls `arrive(step)` between steps, with none of its kernels or collectives in flight; the call
+    returns once all `world` ranks have arrived at that step and raises RankLost after `timeout_s` otherwise, so the
+    survivors learn of a lost rank on the host BEFORE they launch a collective that would wait for it.  The state
+    lives in a torch.distributed store (TCPStore / FileStore): one counter per step, nothing on the GPU."""
+
+    def __init__(self, store, world: int, timeout_s: float = 5.0, poll_s: float = 0.01, prefix: str = "stu_fence"):
+        self.store, self.world, self.timeout_s, self.poll_s, self.prefix = store, world, timeout_s, poll_s, prefix
+
+    def arrive(self, step: int) -> None:
+        import time
+        key = f"{self.prefix}/{step}"
+        self.store.add(key, 1)
+        deadline = time.monotonic() + self.timeout_s
+        while True:
+            n = self.store.add(key, 0)
+            if n >= self.world:
+                return
+            if time.monotonic() > deadline:
+                raise RankLost(f"step {step}: {n} of {self.world} ranks arrived within {self.timeout_s} s")
+            time.sleep(self.poll_s)

@@ -201,8 +201,11 @@ class TensorParallelFlashSTU:
     @torch.no_grad()
     def generate(self, input_ids: torch.Tensor, max_length: int, temperature: float = 1.0,
                  top_k: Optional[int] = None, top_p: Optional[float] = None, do_sample: bool = False,
-                 uniforms: Optional[torch.Tensor] = None, return_logits: bool = False, cuda_graph: bool = True):
-        """Cached token loop; `uniforms` [steps, B] must be the same on every rank when sampling."""
+                 uniforms: Optional[torch.Tensor] = None, return_logits: bool = False, cuda_graph: bool = True,
+                 fence=None, fence_every: int = 16):
+        """Cached token loop; `uniforms` [steps, B] must be the same on every rank when sampling.
+        `fence` (parallel.StepFence): every `fence_every` steps the ranks meet on the host between steps; a rank that
+        is gone makes the others raise parallel.RankLost instead of entering a collective that would never finish."""
         B, T0 = input_ids.shape
         steps = max_length - T0
         if do_sample and uniforms is None:
@@ -219,6 +222,10 @@ class TensorParallelFlashSTU:
         graph = None
         for step in range(steps):
             cur = T0 + step
+            if fence is not None and step % fence_every == 0:
+                if self.device.type == "cuda":
+                    torch.cuda.synchronize(self.device)   # nothing of this rank is in flight while it waits
+                fence.arrive(step)
             u = uniforms[step].to(self.device, torch.float32).contiguous() if do_sample else None
             if use_graph and step >= 2:
                 if graph is None:

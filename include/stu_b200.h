@@ -31,8 +31,16 @@ extern "C" {
 
 int stu_b200_version(void);
 
-/* Registers the device int that kernels set on a device-side problem (NULL to unregister). */
+/* Registers, for the CURRENT device, the device int that kernels launched on that device set on a device-side
+ * problem (NULL to unregister).  One word per device: a process that drives several GPUs registers one word on
+ * each, with that GPU current. */
 int stu_set_status_word(int* device_status);
+
+/* Failure-detection test hook (no counterpart in the reference): arms ONE injected fault for the next tcgen05 GEMM
+ * launched by stu_linear -- the copies of its first pipeline stage are never issued -- and shortens every bounded
+ * device-side wait to wait_ms milliseconds.  That launch must report status 3 and return; the GPU context stays
+ * usable.  wait_ms = 0 disarms and restores the two-second bound. */
+int stu_test_inject_wait_expiry(int wait_ms);
 
 /* y[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps) * w.
  * Replaces torch.nn.RMSNorm / LigerRMSNorm as used in flash_stu/layers/stu_layer.py:32-36,67-71,
@@ -73,8 +81,9 @@ int stu_taps_even(const void* fp, void* taps, int L, int d, int Lh, int dtype, v
  * i.e. spectral_plus + spectral_minus of flash_stu/modules/stu.py:95-98,120 (torch.fft path
  * flash_stu/utils/stu_utils.py:208-228), added to the residual stream.  hist must already hold the
  * projected inputs of times [0, t_end).  yT is scratch with the history layout and y_Lh elements per
- * parity row (y_Lh >= ceil(t_end/2)).  use_tensor_cores=1 (bf16 only) runs the Toeplitz product on
- * mma.sync tensor cores, 0 the fp32 CUDA-core kernel. */
+ * parity row (y_Lh >= ceil(t_end/2)); yT must be 16-byte aligned and y_Lh a multiple of 8 (bf16) or 4 (fp32),
+ * because the residual add reads it in 16-byte vectors: anything else returns -3 before a kernel is launched.
+ * use_tensor_cores=1 (bf16 only) runs the Toeplitz product on tensor cores, 0 the fp32 CUDA-core kernel. */
 int stu_conv_prefill_approx(const void* hist, const void* taps, void* yT, void* x, long long x_bstride,
                             long long x_tstride, int B, int d, int Lh, int y_Lh, int t0, int t_end, int dtype,
                             int use_tensor_cores, void* stream);

@@ -345,6 +345,26 @@ def lds_impulse_response(A: Tensor, Bv: Tensor, C: Tensor, T: int) -> Tensor:
 
 # --------------------------------------------------------------------------- helpers for tests
 def rel_err(a: Tensor, b: Tensor) -> float:
-    """max |a-b| / max |b| (the relative measure the tolerances 1e-3 / 2e-2 are read in)."""
+    """max |a-b| / max |b| over the whole tensor."""
     a, b = a.double(), b.double()
     return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
+
+
+def row_err(a: Tensor, b: Tensor, floor: float = 1e-3) -> float:
+    """Worst row of max_row |a-b| / max_row |b|, a row being one vector along the last dimension (one token's
+    channels, one sequence's logits).  Stricter than rel_err: a result that is wrong on every small-magnitude row
+    passes rel_err (whose denominator is the largest value anywhere) and fails here.  Rows whose largest reference
+    value is below `floor` times the tensor's largest are measured against that floor (an all-zero row has no
+    relative error)."""
+    a, b = a.double(), b.double()
+    if a.dim() == 0:
+        return rel_err(a, b)
+    a, b = a.reshape(-1, a.shape[-1]), b.reshape(-1, b.shape[-1])
+    den = b.abs().amax(dim=1).clamp_min(floor * float(b.abs().max()) + 1e-30)
+    return float(((a - b).abs().amax(dim=1) / den).max())
+
+
+def rms_err(a: Tensor, b: Tensor) -> float:
+    """||a-b||_2 / ||b||_2 over the whole tensor."""
+    a, b = a.double(), b.double()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))

@@ -38,6 +38,12 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert lib.stu_linear_can_fuse_norm(8, 4096, 1024, 2, 1) == 1
     assert lib.stu_linear_can_fuse_norm(8, 4096, 1024, 2, 0) == 0
     assert lib.stu_linear_can_fuse_norm(128, 4096, 1024, 2, 1) == 0
+    # the prefill convolution reads its scratch in 16-byte vectors: a row pitch that is not a multiple of 8 bf16
+    # (4 fp32) elements, or a misaligned scratch base, is refused with -3 and nothing is launched
+    a = 0x10000   # stands for an aligned device address; the checks return before anything dereferences it
+    assert lib.stu_conv_prefill_approx(a, a, a, a, 333 * 8, 8, 1, 8, 168, 167, 0, 333, 1, 1, None) == -3
+    assert lib.stu_conv_prefill_approx(a, a, a, a, 333 * 8, 8, 1, 8, 168, 166, 0, 332, 0, 0, None) == -3
+    assert lib.stu_conv_prefill_approx(a, a, a + 2, a, 333 * 8, 8, 1, 8, 168, 168, 0, 333, 1, 1, None) == -3
 
 
 def test_ops_refuse_cpu_tensors():

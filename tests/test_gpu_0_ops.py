@@ -6,6 +6,7 @@ import pytest
 import torch
 
 from oracle import stu_oracle as O
+from parity import close
 
 pytestmark = pytest.mark.gpu
 
@@ -18,8 +19,6 @@ def dev():
     return torch.device("cuda:0")
 
 
-def rel(a, b):
-    return O.rel_err(a.detach().cpu(), b.detach().cpu())
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
@@ -31,7 +30,7 @@ def test_rmsnorm(dt, shape):
     w = torch.randn(shape[-1]).to(dt)
     y = ops.rmsnorm(x.to(dev()), w.to(dev()))
     ref = O.rmsnorm(x, w)
-    assert rel(y, ref) <= (1e-6 if dt == torch.float32 else 2 ** -7)
+    close(y, ref, (1e-6 if dt == torch.float32 else 2 ** -7))
 
 
 def _lin_ref(x, W, W2, resid, epi, dt):
@@ -62,7 +61,7 @@ def test_linear_backends(backend, dt, epi):
         y = ops.linear(x.to(dev()), W.to(dev()), W2=W2.to(dev()) if epi == 2 else None,
                        resid=resid.to(dev()) if epi == 1 else None, epilogue=epi, backend=backend)
         ops.check_status()
-        assert rel(y, ref) <= TOL[dt] / 2, (M, N, K, rel(y, ref))
+        close(y, ref, TOL[dt] / 2)
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
@@ -78,7 +77,7 @@ def test_linear_narrow_output_long_rows(dt):
         ref = _lin_ref(x, W, None, resid, epi, dt)
         y = ops.linear(x.to(dev()), W.to(dev()), resid=resid.to(dev()) if epi == 1 else None, epilogue=epi, backend=3)
         ops.check_status()
-        assert rel(y, ref) <= TOL[dt] / 2, (M, N, K, rel(y, ref))
+        close(y, ref, TOL[dt] / 2)
 
 
 @pytest.mark.parametrize("epi", [0, 1])
@@ -94,7 +93,39 @@ def test_linear_wide_tensor_core_tiles(epi):
         ref = _lin_ref(x, W, None, resid, epi, dt)
         y = ops.linear(x.to(dev()), W.to(dev()), resid=resid.to(dev()) if epi == 1 else None, epilogue=epi, backend=2)
         ops.check_status()
-        assert rel(y, ref) <= TOL[dt] / 2, (M, N, K, rel(y, ref))
+        close(y, ref, TOL[dt] / 2)
+
+
+def test_bounded_wait_expiry_is_reported_and_the_context_survives():
+    """Failure detection inside the tcgen05 GEMM: with the copies of its first pipeline stage dropped (test hook) the
+    consumer's bounded wait runs out after the shortened limit; the kernel reports status 3, frees its tensor memory
+    and returns, the host raises, and the next GEMM on the same context is correct.  Nothing faults or hangs."""
+    import time
+    from flash_stu_2_b200 import _lib, ops
+    lib = _lib.load()
+    torch.manual_seed(21)
+    dt = torch.bfloat16
+    x = torch.randn(128, 64).to(dt)
+    W = (torch.randn(128, 64) / 8).to(dt)
+    xd, Wd = x.to(dev()), W.to(dev())
+    ref = _lin_ref(x, W, None, None, 0, dt)
+    close(ops.linear(xd, Wd, backend=2), ref, TOL[dt] / 2)      # the healthy kernel first
+    ops.check_status()
+    assert lib.stu_test_inject_wait_expiry(100) == 0
+    try:
+        t0 = time.monotonic()
+        ops.linear(xd, Wd, backend=2)
+        torch.cuda.synchronize()
+        assert time.monotonic() - t0 < 5.0                           # returned by itself, within the shortened bound
+        with pytest.raises(RuntimeError, match="status 3"):
+            ops.check_status()
+    finally:
+        assert lib.stu_test_inject_wait_expiry(0) == 0
+    close(ops.linear(xd, Wd, backend=2), ref, TOL[dt] / 2)      # same context, same kernel, healthy again
+    big = torch.randn(300, 136).to(dt)
+    Wb = (torch.randn(200, 136) / 12).to(dt)
+    close(ops.linear(big.to(dev()), Wb.to(dev()), backend=2), _lin_ref(big, Wb, None, None, 0, dt), TOL[dt] / 2)
+    ops.check_status()
 
 
 def test_linear_fused_norm_decode():
@@ -110,7 +141,7 @@ def test_linear_fused_norm_decode():
         ref = _lin_ref(O.rmsnorm(x, nw), W, W2, resid, epi, dt)
         y = ops.linear(x.to(dev()), W.to(dev()), W2=W2.to(dev()) if epi == 2 else None,
                        resid=resid.to(dev()) if epi == 1 else None, epilogue=epi, norm_w=nw.to(dev()))
-        assert rel(y, ref) <= 1e-2, rel(y, ref)
+        close(y, ref, 1e-2)
 
 
 def test_linear_transposed_small_k():
@@ -121,7 +152,7 @@ def test_linear_transposed_small_k():
         phi = torch.randn(130, 24).to(dt)
         Mf = torch.randn(24, 72).to(dt)
         y = ops.linear(phi.to(dev()), Mf.to(dev()), transposed_weight=True, backend=1)
-        assert rel(y, (phi.double() @ Mf.double()).to(dt)) <= TOL[dt] / 4
+        close(y, (phi.double() @ Mf.double()).to(dt), TOL[dt] / 4)
 
 
 def _hist_from(xp, Lh):
@@ -154,7 +185,9 @@ def test_conv_prefill_matches_fft_oracle(dt, tc, shape):
     x = x0[:, t0:].contiguous().to(dev())
     ops.conv_prefill_approx(hist, taps, yT, x, t0, T, use_tensor_cores=tc)
     # bf16: the reference rounds each branch before the add, the kernel rounds the folded sum once
-    assert rel(x, ref[:, t0:]) <= (2e-5 if dt == torch.float32 else 1.5e-2), rel(x, ref[:, t0:])
+    # bf16: the reference rounds each branch before adding them, the kernel rounds the folded sum once; on rows whose
+    # largest value is small that is up to two bf16 ulps of the branch magnitude (observed 1.75e-2 per row)
+    close(x, ref[:, t0:], (2e-5 if dt == torch.float32 else 1.5e-2), row_tol=(2e-5 if dt == torch.float32 else 2e-2))
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
@@ -172,7 +205,7 @@ def test_history_scatter_epilogue(dt):
         ops.check_status()
         full = torch.zeros(B, t0 + T, d, dtype=dt)
         full[:, t0:] = xp
-        assert rel(hist, _hist_from(full, Lh)) <= TOL[dt] / 2
+        close(hist, _hist_from(full, Lh), TOL[dt] / 2)
 
 
 def _decode_fixture(dt, B, T, d, L, seed=6):
@@ -210,8 +243,8 @@ def test_decode_step_equals_prefill_row(dt, tc, shape):
     ops.check_status()
     got = torch.stack(outs, 1)
     assert pos[:, 0].tolist() == [T] * B and int(pos[0, 1]) == 0
-    assert rel(got, ref) <= (1e-5 if dt == torch.float32 else 1.5e-2), rel(got, ref)
-    assert rel(hist, _hist_from(xp, Lh)) <= (1e-5 if dt == torch.float32 else 1e-2)
+    close(got, ref, (1e-5 if dt == torch.float32 else 1.5e-2))
+    close(hist, _hist_from(xp, Lh), (1e-5 if dt == torch.float32 else 1e-2))
 
 
 @pytest.mark.parametrize("shape", [(3, 45, 64, 64), (9, 70, 40, 160), (8, 300, 256, 600), (17, 140, 1024, 300)])
@@ -239,8 +272,8 @@ def test_decode_step_shared_tap_kernel(shape):
     ops.check_status()
     got = torch.stack(outs, 1).cpu()
     assert pos[:, 0].tolist() == [T] * B and int(pos[0, 1]) == 0
-    assert rel(got, ref) <= 1.5e-2, rel(got, ref)
-    assert rel(hist, _hist_from(xp, Lh)) <= 1e-2
+    close(got, ref, 1.5e-2)
+    close(hist, _hist_from(xp, Lh), 1e-2)
     if B > 1:
         pos[:, 0] = 5
         pos[1, 0] = 4          # ragged inside the first group of eight sequences
@@ -314,7 +347,7 @@ def test_decode_step_with_ragged_positions(tc):
     ops.check_status()
     want = torch.stack([ref[b, t] for b, t in enumerate(where)])
     assert pos[:, 0].tolist() == [t + 1 for t in where]
-    assert rel(out, want) <= 1.5e-2, rel(out, want)
+    close(out, want, 1.5e-2)
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
@@ -341,12 +374,12 @@ def test_attention_prefill_and_cached_decode(dt, cfg):
         ys.append(ops.swa_forward(qkv[:, t:t + 1].contiguous(), kr, vr, pos, slopes, H, w, 50.0, update_cache=True))
     got = torch.cat(ys, 1)
     assert pos[:, 0].tolist() == [T] * B
-    assert rel(got, ref) <= (1e-4 if dt == torch.float32 else 1.5e-2), rel(got, ref)
+    close(got, ref, (1e-4 if dt == torch.float32 else 1.5e-2))
     # uncached call over the whole sequence
     dummy = torch.zeros(1, 1, 1, dtype=dt, device=dev())
     y = ops.swa_forward(qkv, dummy, dummy, torch.zeros(B, 2, dtype=torch.int32, device=dev()), slopes, H, w, 50.0,
                         update_cache=False)
-    assert rel(y, ref) <= (1e-4 if dt == torch.float32 else 1.5e-2)
+    close(y, ref, (1e-4 if dt == torch.float32 else 1.5e-2))
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
@@ -375,7 +408,7 @@ def test_attention_chunked_prefill_across_many_key_tiles(dt, cfg):
         ys.append(ops.swa_forward(qkv[:, t:t + 1].contiguous(), kr, vr, pos, slopes, H, w, 50.0, update_cache=True))
     got = torch.cat(ys, 1)
     assert pos[:, 0].tolist() == [T] * B and int(pos[0, 1]) == 0
-    assert rel(got, ref) <= (1e-4 if dt == torch.float32 else 1.5e-2), rel(got, ref)
+    close(got, ref, (1e-4 if dt == torch.float32 else 1.5e-2))
 
 
 def test_sampling_matches_oracle():
@@ -398,7 +431,8 @@ def test_sampling_matches_oracle():
             # chosen token to be inside the filtered support and almost all draws identical
             assert all(torch.isfinite(z[b, got[b]]) for b in range(B))
             if dt == torch.float32:
-                assert (got == want).float().mean() >= 0.8, (got, want)
+                frac = float((got == want).float().mean())
+                assert frac >= 0.8, f"{frac:.2f} of the fp32 draws equal the oracle's ({got.tolist()} vs {want.tolist()})"
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
@@ -426,9 +460,9 @@ def test_full_variant_building_blocks(dt):
     dense = ops.linear(rows, Tz[0], backend=0)
     causal = ops.linear(rows, Tz[0], epilogue=ops.EPI_STORE | ops.EPI_FLAG_CAUSAL, backend=0)
     ops.check_status()
-    assert rel(causal, dense) <= 1e-6
+    close(causal, dense, 1e-6)
     ref = (rows.cpu().double() @ Tz[0].cpu().double().t()).to(dt)
-    assert rel(causal, ref) <= TOL[dt] / 2
+    close(causal, ref, TOL[dt] / 2)
     # E, Q -> U for one filter
     E = torch.randn(B * d * 2, S).to(dt)
     Q = torch.randn(B * d * 2, S).to(dt)
@@ -467,8 +501,8 @@ def test_stu_operator_matches_reference_golden(golden, name, tol):
         T = r["T_short"]
         ys = m(r["x"][:, :T].contiguous().to(dev()))
     ops.check_status()
-    assert rel(y, r["y_full"]) <= tol, rel(y, r["y_full"])
-    assert rel(ys, r["y_short"]) <= tol, rel(ys, r["y_short"])
+    close(y, r["y_full"], tol)
+    close(ys, r["y_short"], tol)
 
 
 def test_mini_stu_spectral_matches_reference_golden(golden):
@@ -483,7 +517,7 @@ def test_mini_stu_spectral_matches_reference_golden(golden):
     with torch.no_grad():
         y = m(r["x"].to(dev()))
     ops.check_status()
-    assert rel(y, r["y"]) <= 1e-3, rel(y, r["y"])
+    close(y, r["y"], 1e-3)
 
 
 @pytest.mark.parametrize("dt,tol", [(torch.float32, 1e-3), (torch.bfloat16, 2e-2)])
@@ -512,9 +546,9 @@ def test_mini_stu_lds_prefill_and_recurrent_decode(golden, dt, tol, shape):
             yt, cache = m(x[:, t:t + 1].to(dev()), past_key_value=cache, use_cache=True)
             rows.append(yt)
     ops.check_status()
-    assert rel(y_all, want) <= tol, rel(y_all, want)
+    close(y_all, want, tol)
     got = torch.cat(rows, 1)
-    assert rel(got, want) <= tol, rel(got, want)
+    close(got, want, tol)
     if shape == (2, 48, 6, 10) and dt == torch.float32:
         # the reference module's own output (float64 run of MiniSTU(backend='lds')) with its M
         m2 = F.MiniSTU(seq_len=T, num_filters=24, input_dim=din, output_dim=dout, backend="lds", dtype=dt)
@@ -523,4 +557,4 @@ def test_mini_stu_lds_prefill_and_recurrent_decode(golden, dt, tol, shape):
         m2 = m2.to(dev())
         with torch.no_grad():
             y2 = m2(g["x"].to(dt).to(dev()))
-        assert rel(y2, g["y"]) <= 1e-3, rel(y2, g["y"])
+        close(y2, g["y"], 1e-3)

@@ -6,6 +6,7 @@ import pytest
 import torch
 
 from oracle import stu_oracle as O
+from parity import close
 
 pytestmark = pytest.mark.gpu
 
@@ -40,8 +41,7 @@ def test_block_forward_matches_reference_golden(golden, name, tol):
         y = blk(x)
     ops.check_status()
     assert y.data_ptr() == x.data_ptr()  # in place on the caller's tensor, like the reference
-    err = O.rel_err(y.cpu(), r["y"])
-    assert err <= tol, err
+    close(y.cpu(), r["y"], tol)
 
 
 @pytest.mark.parametrize("name,tol", ALL_BLOCKS)
@@ -63,8 +63,7 @@ def test_block_cached_decode_equals_prefill_rows(golden, name, tol):
     ops.check_status()
     got = torch.cat(rows, 1).cpu()
     assert int(cache[1][0, 0]) == T
-    err = O.rel_err(got, r["y"])
-    assert err <= tol, err
+    close(got, r["y"], tol)
 
 
 def test_block_tensor_core_and_cuda_core_convolutions_agree(golden):
@@ -79,7 +78,7 @@ def test_block_tensor_core_and_cuda_core_convolutions_agree(golden):
             b = blk(x.clone())
         finally:
             F.STU.tensor_core_conv = True
-    assert O.rel_err(a.cpu(), b.cpu()) <= 4e-3
+    close(a.cpu(), b.cpu(), 4e-3)
 
 
 def test_block_properties_at_benchmark_width():
@@ -108,12 +107,12 @@ def test_block_properties_at_benchmark_width():
         y2, cache = blk(x[:, 768:1500].clone().to(dev()), past_key_value=cache, use_cache=True)
         y3, cache = blk(x[:, 1500:1501].clone().to(dev()), past_key_value=cache, use_cache=True)
     ops.check_status()
-    assert O.rel_err(short, full[:, :T]) <= 1e-6          # prefix consistency (same kernels, same order)
+    close(short, full[:, :T], 1e-6)          # prefix consistency (same kernels, same order)
     chunked = torch.cat([y1.cpu(), y2.cpu(), y3.cpu()], 1)
-    assert O.rel_err(chunked, full[:, :1501]) <= 2e-2
+    close(chunked, full[:, :1501], 2e-2)
     lsd = {k[len("layer."):]: v for k, v in sd.items() if k.startswith("layer.")}
     ref = O.stu_layer(x[:1], lsd, sd["phi"], O.fft_length(L), True)
-    assert O.rel_err(full[:1], ref) <= 2e-2
+    close(full[:1], ref, 2e-2)
 
 
 def test_overlapped_decode_launches_equal_plain_launches(golden):
@@ -165,7 +164,7 @@ def test_overlapped_decode_launches_equal_plain_launches(golden):
     assert torch.equal(run(True, False), plain)
     assert torch.equal(run(True, True), plain)
     ops.check_status()
-    assert O.rel_err(plain, r["y"][:, T1:]) <= 2e-2
+    close(plain, r["y"][:, T1:], 2e-2)
 
 
 @pytest.mark.parametrize("approx", [True, False])
@@ -201,9 +200,9 @@ def test_benchmark_block_at_full_size_against_the_oracle(approx):
     lsd = {k[len("layer."):]: v for k, v in sd.items() if k.startswith("layer.")}
     # one sequence at a time: the full variant's FFT stack takes 10 GB of host memory per sequence
     ref = torch.cat([O.stu_layer(x[b:b + 1], lsd, sd["phi"], O.fft_length(L), approx) for b in range(B)])
-    assert O.rel_err(full, ref) <= 2e-2, O.rel_err(full, ref)
-    assert O.rel_err(torch.cat(rows, 1), ref[:, L - S:]) <= 2e-2
-    assert O.rel_err(y1.cpu(), ref[:, :L - S]) <= 2e-2
+    close(full, ref, 2e-2)
+    close(torch.cat(rows, 1), ref[:, L - S:], 2e-2)
+    close(y1.cpu(), ref[:, :L - S], 2e-2)
 
 
 def test_cache_laid_out_for_fewer_positions_than_the_filters(golden):
@@ -230,4 +229,4 @@ def test_cache_laid_out_for_fewer_positions_than_the_filters(golden):
             blk(x[:, cap:cap + 1].clone(), past_key_value=cache, use_cache=True)
     ops.check_status()
     assert cache[0].shape[3] < (r["L"] + 1) // 2
-    assert O.rel_err(torch.cat(rows, 1).cpu(), r["y"][:, :cap]) <= 2e-2
+    close(torch.cat(rows, 1).cpu(), r["y"][:, :cap], 2e-2)

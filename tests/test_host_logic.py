@@ -93,6 +93,14 @@ def test_checkpoint_round_trip_and_vocabulary_resize(tmp_path):
     m.save_pretrained(ckpt)
     m2 = F.FlashSTU.from_pretrained(ckpt)
     assert m2.config.torch_dtype == torch.bfloat16 and next(m2.parameters()).dtype == torch.bfloat16
+    # a float32 model comes back as float32 (not as the bfloat16 default of the config class), bit for bit
+    m32 = F.FlashSTU(F.FlashSTUConfig(n_embd=32, n_layers=2, n_heads=4, seq_len=L, window_size=8, vocab_size=97,
+                                      mlp_scale=4, num_eigh=K, torch_dtype=torch.float32, filter_path=fp))
+    ck32 = os.path.join(str(tmp_path), "ckpt32")
+    m32.save_pretrained(ck32)
+    r32 = F.FlashSTU.from_pretrained(ck32)
+    assert r32.config.torch_dtype == torch.float32
+    assert all(v.dtype == torch.float32 and torch.equal(v, m32.state_dict()[k]) for k, v in r32.state_dict().items())
     sd1, sd2 = m.state_dict(), m2.state_dict()
     assert set(sd1) == set(sd2) and all(torch.equal(sd1[k], sd2[k]) for k in sd1)
     assert m2.lm_head.weight.data_ptr() == m2.tok_emb.weight.data_ptr()
