@@ -63,6 +63,11 @@ def parse():
     ap.add_argument("--no-overlap", action="store_true",
                     help="plain stream-ordered launches for the decode kernels (no programmatic dependent launch)")
     ap.add_argument("--no-graph", action="store_true", help="launch decode steps eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--early-decode", type=int, default=1, choices=[0, 1],
+                    help="1: the STU decode kernel starts while the down projection before it still runs (only its "
+                         "projection waits for it); 0: it starts after it")
+    ap.add_argument("--decode-kernel", choices=["pipe", "rows8"], default="pipe",
+                    help="fused decode kernel: the persistent bulk-copy pipeline (default) or the 8x8 register-streaming one")
     return ap.parse_args()
 
 
@@ -224,8 +229,11 @@ def run_b200(a):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     B, L, d, S = a.batch, a.seq_len, D_MODEL, a.decode_steps
+    from flash_stu_2_b200.modules import STU
     if a.no_overlap:
         ops.overlap_decode = False
+    ops.early_decode = bool(a.early_decode)
+    STU.pipelined_decode = (a.decode_kernel == "pipe")
     approx = a.variant == "approx"
     blk = make_state(L, approx=approx).to(dev).eval()
     torch.manual_seed(1 + rank)
@@ -330,8 +338,11 @@ def run_b200(a):
             reps = min(256, S)
 
             def kernel_only():
-                ops.decode_approx(x2, layer.stu_norm.weight, MinT, hist, taps, pos, out2, taps8=taps8,
-                                  flags=ops.FLAG_UNIFORM_POS)
+                if STU.pipelined_decode:
+                    ops.decode_approx_pipelined(x2, layer.stu_norm.weight, MinT, hist, taps8, pos, out2)
+                else:
+                    ops.decode_approx(x2, layer.stu_norm.weight, MinT, hist, taps, pos, out2, taps8=taps8,
+                                      flags=ops.FLAG_UNIFORM_POS)
 
             rewind()
             for _ in range(3):
@@ -383,6 +394,9 @@ def run_b200(a):
             def dec(flags):
                 ops.decode_approx(x2, layer.stu_norm.weight, MinT, hist, taps, pos, mid, taps8=taps8, flags=flags)
 
+            def decp(flags=0):
+                ops.decode_approx_pipelined(x2, layer.stu_norm.weight, MinT, hist, taps8, pos, mid, flags=flags)
+
             def gate_up(f=0):
                 ops.linear(mid, mlp.gate_proj.weight, W2=mlp.up_proj.weight, out=hbuf, epilogue=ops.EPI_GELU_MUL | f,
                            norm_w=layer.mlp_norm.weight, eps=layer.mlp_norm.eps)
@@ -392,12 +406,17 @@ def run_b200(a):
 
             UN, OV, EA = ops.FLAG_UNIFORM_POS, ops.FLAG_OVERLAP, ops.FLAG_EARLY_TRIGGER
             split = {"unit": "us per launch, 64 launches replayed from one graph",
+                     "stu_decode_pipe_kernel": graph_us(decp),
                      "stu_decode_rows8_kernel": graph_us(lambda: dec(UN)),
                      "stu_decode_diag_kernel": graph_us(lambda: dec(0)),
                      "skinny gate/up (norm fused)": graph_us(gate_up),
                      "skinny down (+residual)": graph_us(down),
                      "step, plain launches": graph_us(lambda: (dec(UN), gate_up(), down())),
-                     "step, MLP kernels overlapped": graph_us(lambda: (dec(UN | EA), gate_up(OV), down(OV)))}
+                     "step, MLP kernels overlapped": graph_us(lambda: (dec(UN | EA), gate_up(OV), down(OV))),
+                     "step (pipe), plain launches": graph_us(lambda: (decp(), gate_up(), down())),
+                     "step (pipe), MLP kernels overlapped": graph_us(lambda: (decp(EA), gate_up(OV), down(OV))),
+                     "step (pipe), MLP overlapped + decode started early":
+                         graph_us(lambda: (decp(EA | OV), gate_up(OV), down(OV | EA)))}
 
         # ---- end to end through the module API from pinned host memory
         y_host = torch.empty(B, 1, d, dtype=torch.bfloat16).pin_memory()
@@ -442,7 +461,7 @@ def run_b200(a):
     t_mid_step = first + S / 2.0
     if approx:
         achieved = kern_bytes / (kern_ms / 1e3) / 1e9
-        roof_kernel = "stu_decode_rows8_kernel"
+        roof_kernel = "stu_decode_pipe_kernel" if STU.pipelined_decode else "stu_decode_rows8_kernel"
     else:
         # full variant: no single dominant kernel; the roofline object describes the whole token step: the history of
         # every sequence (both parities), the 2K d x d matrices M_phi_plus/minus, the MLP weights
@@ -484,8 +503,16 @@ def run_b200(a):
                         "of each step also copies its 134 MB input in and its output back"},
         "gpu_launches": launches, "wall_s_timed_region": wall, "clocks": clocks,
     }
-    if (B, L, d) == (8, 8192, 1024) and approx:
+    if (B, L, d) == (8, 8192, 1024) and approx and not STU.pipelined_decode:
         line["roofline"]["traffic"] = DECODE_KERNEL_DRAM_BYTES
+    if approx:
+        # the whole token step of the block: the decode kernel's bytes plus the MLP weights (gate, up, down)
+        step_bytes = (B * d * (t_mid_step / 2) * 2 + d * (t_mid_step / 2 + 1) * 2 + d * d * 2 + 3 * B * d * 2
+                      + 12 * d * d * 2)
+        line["roofline_step"] = {"bound": "hbm", "what": "whole token step (STU decode kernel + gate/up + down)",
+                                 "bytes_per_step": step_bytes, "us_per_step": step_us,
+                                 "achieved": step_bytes / (step_us * 1e-6) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                                 "frac": step_bytes / (step_us * 1e-6) / 1e9 / pk["hbm_gbs"]}
     if split is not None:
         line["decode_split"] = split
     if world == 1 and not a.no_cpu_baseline:

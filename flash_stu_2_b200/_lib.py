@@ -43,6 +43,8 @@ _SIGNATURES = {
                           c_int),
     "stu_decode_approx_shard": ([_P, _LL, _P, _P, _P, _P, _P, _P, _LL, c_int, c_int, c_int, c_int, c_float, c_int, _P,
                                  c_int, _P], c_int),
+    "stu_decode_approx_pipelined": ([_P, _LL, _P, _P, _P, _P, _P, _P, _LL, c_int, c_int, c_int, c_int, c_float, c_int,
+                                     _P, c_int, _P], c_int),
     "stu_to_history": ([_P, _LL, _LL, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P], c_int),
     "stu_toeplitz": ([_P, _LL, c_int, _P, c_int, _LL, c_int, _P], c_int),
     "stu_full_combine": ([_P, _P, _LL, _P, _LL, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P], c_int),

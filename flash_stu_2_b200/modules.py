@@ -79,7 +79,10 @@ class MLP(nn.Module):
         ov = ops.FLAG_OVERLAP if (overlap and ops.overlap_decode) else 0
         h = ops.linear(xn2d, self.gate_proj.weight, W2=self.up_proj.weight, epilogue=ops.EPI_GELU_MUL | ov,
                        norm_w=norm_w, eps=eps)
-        return ops.linear(h, self.down_proj.weight, resid=resid2d, out=out2d, epilogue=ops.EPI_RESID | ov)
+        # early_decode: the down projection releases its successor at once, so that an STU decode kernel that follows
+        # streams its history while this kernel runs (the successor's projection still waits for this output)
+        ovd = ov | (ops.FLAG_EARLY_TRIGGER if (ov and ops.early_decode) else 0)
+        return ops.linear(h, self.down_proj.weight, resid=resid2d, out=out2d, epilogue=ops.EPI_RESID | ovd)
 
     def forward(self, x):
         x2 = x.reshape(-1, x.shape[-1])
@@ -275,6 +278,7 @@ class STU(nn.Module):
     tensor_core_conv = True    # class switches used by tests to compare the tensor-core and CUDA-core kernels
     tensor_core_decode = True
     shared_tap_decode = True   # batches at one common position: the kernel with 8 channels x 8 sequences per CTA
+    pipelined_decode = True    # ... and, of those, the persistent bulk-copy pipeline kernel
 
     def decode_step(self, x2d: torch.Tensor, norm_w: torch.Tensor, eps: float, entry, out2d: torch.Tensor):
         """out = x + STU(rmsnorm(x)) for one new token per sequence; appends to the cache."""
@@ -283,10 +287,18 @@ class STU(nn.Module):
         t = host_pos(pos)
         if t + 1 > self.capacity:
             raise ValueError(f"sequence position {t + 1} exceeds the capacity {self.capacity} (seq_len={self.seq_len})")
-        ops.decode_approx(x2d, norm_w, MinT, hist, taps, pos, out2d, eps,
-                          taps8=taps8 if STU.tensor_core_decode else None,
-                          flags=(ops.FLAG_EARLY_TRIGGER if ops.overlap_decode else 0) |
-                                (ops.FLAG_UNIFORM_POS if (uniform_pos(pos) and STU.shared_tap_decode) else 0))
+        B, d, _, Lh = hist.shape
+        if (STU.pipelined_decode and STU.tensor_core_decode and STU.shared_tap_decode and taps8 is not None
+                and uniform_pos(pos) and d % 8 == 0 and x2d.shape[1] % 8 == 0):
+            # batch at one common position: the bulk-copy pipeline kernel
+            ops.decode_approx_pipelined(x2d, norm_w, MinT, hist, taps8, pos, out2d, eps,
+                                        flags=(ops.FLAG_EARLY_TRIGGER if ops.overlap_decode else 0) |
+                                              (ops.FLAG_OVERLAP if (ops.overlap_decode and ops.early_decode) else 0))
+        else:
+            ops.decode_approx(x2d, norm_w, MinT, hist, taps, pos, out2d, eps,
+                              taps8=taps8 if STU.tensor_core_decode else None,
+                              flags=(ops.FLAG_EARLY_TRIGGER if ops.overlap_decode else 0) |
+                                    (ops.FLAG_UNIFORM_POS if (uniform_pos(pos) and STU.shared_tap_decode) else 0))
         pos._host_t = t + 1
         return hist, pos
 

@@ -23,6 +23,10 @@ FLAG_OVERLAP = 0x200
 FLAG_EARLY_TRIGGER = 0x400
 FLAG_UNIFORM_POS = 0x800  # decode_approx: every sequence of the batch stands at the same position (checked on device)
 overlap_decode = True
+# early_decode: additionally launch the pipelined STU decode kernel overlapped with the kernel before it (the down
+# projection of the previous layer, which then triggers early): its history stream needs nothing that kernel writes,
+# only its projection waits.
+early_decode = True
 BACKEND_AUTO, BACKEND_SIMT, BACKEND_TCGEN05, BACKEND_SKINNY = 0, 1, 2, 3
 RMS_EPS = float(torch.finfo(torch.float32).eps)  # what torch.nn.RMSNorm(eps=None) resolves to
 
@@ -71,7 +75,8 @@ def status_word(device) -> torch.Tensor:
 STATUS_TEXT = {1: "token id outside the vocabulary", 2: "position outside the cache capacity (seq_len)",
                3: "a bounded mbarrier wait ran out inside the tcgen05 GEMM", 4: "more top-k ties than the candidate list holds",
                5: "top_p without top_k is not implemented on the device",
-               6: "decode step told that all sequences share one position, but the cached positions differ"}
+               6: "decode step told that all sequences share one position, but the cached positions differ",
+               7: "a bounded pipeline wait ran out inside the decode kernel"}
 
 
 def check_status(device=None):
@@ -238,6 +243,25 @@ def decode_approx_shard(x, norm_w, MinT, hist, taps8, pos, out, eps: float = RMS
                                              out.stride(0), B, d_in, dch, Lh, eps, int(add_residual),
                                              status_word(x.device).data_ptr(), _dt(x) | flags, _stream())
     _lib.check(rc, "stu_decode_approx_shard")
+    _count()
+    return out
+
+
+def decode_approx_pipelined(x, norm_w, MinT, hist, taps8, pos, out, eps: float = RMS_EPS, add_residual: bool = True,
+                            flags: int = 0):
+    """The fused decode step of an approx STU layer (or of a channel shard: MinT [d_ch, d_in], add_residual=False) as
+    the bulk-copy pipeline kernel: bf16, every sequence at the same position."""
+    _cuda(x, norm_w, MinT, hist, taps8, pos, out)
+    B, dch, _, Lh = hist.shape
+    d_in = x.shape[1]
+    assert x.shape[0] == B and MinT.shape == (dch, d_in) and out.shape == (B, dch) and x.stride(1) == 1
+    assert out.stride(1) == 1 and taps8.shape == (8, dch, Lh + 8) and pos.dtype == torch.int32 and pos.is_contiguous()
+    assert hist.is_contiguous() and taps8.is_contiguous() and x.data_ptr() != out.data_ptr()
+    rc = _lib.load().stu_decode_approx_pipelined(x.data_ptr(), x.stride(0), norm_w.data_ptr(), MinT.data_ptr(),
+                                                 hist.data_ptr(), taps8.data_ptr(), pos.data_ptr(), out.data_ptr(),
+                                                 out.stride(0), B, d_in, dch, Lh, eps, int(add_residual),
+                                                 status_word(x.device).data_ptr(), _dt(x) | flags, _stream())
+    _lib.check(rc, "stu_decode_approx_pipelined")
     _count()
     return out
 

@@ -129,6 +129,20 @@ int stu_decode_approx_shard(const void* x, long long x_row_stride, const void* n
                             const void* taps8, int* pos, void* out, long long out_row_stride, int B, int d_in,
                             int d_ch, int Lh, float eps, int add_residual, int* status, int dtype, void* stream);
 
+/* The same fused decode step (whole layer: d_in == d_ch, add_residual = 1; or a channel shard) as a persistent
+ * bulk-copy pipeline: one CTA per SM owns rows of 8 sequences x 8 channels; the history and taps of 256 positions
+ * per cp.async.bulk.tensor copy pair go through a 4-stage shared-memory ring, the dot products run on tensor cores,
+ * and a separate warp group projects the new token under the stream.  A row is summed inside one CTA, slices in
+ * order, so results do not depend on the SM count.  Replaces the same reference lines as stu_decode_approx
+ * (flash_stu/modules/stu.py:85-98,120 for one new position).  bf16, all sequences at one position (status 6
+ * otherwise), d_in, d_ch, Lh multiples of 8; status 7 = a bounded pipeline wait ran out.  dtype takes the launch
+ * flags 0x200 (start while the preceding kernel of the stream is still running: only the projection waits for it)
+ * and 0x400. */
+int stu_decode_approx_pipelined(const void* x, long long x_row_stride, const void* norm_w, const void* MinT,
+                                void* hist, const void* taps8, int* pos, void* out, long long out_row_stride, int B,
+                                int d_in, int d_ch, int Lh, float eps, int add_residual, int* status, int dtype,
+                                void* stream);
+
 /* ---- full STU variant (flash_stu/modules/stu.py:100-118, mini_stu/stu.py:240-269): U+-[b,t,k,i] =
  * sum_j (+-1)^j phi[j,k] x[b,t-j,i] contracted with M_phi_plus / M_phi_minus.  The filters are shared by all
  * channels, so per filter the convolution is three GEMMs (stu_linear with epilogue | 0x100 = lower-triangular

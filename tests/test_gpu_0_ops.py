@@ -285,6 +285,66 @@ def test_decode_step_shared_tap_kernel(shape):
         assert torch.equal(before[:2], hist[:2])
 
 
+@pytest.mark.parametrize("shape", [(3, 45, 64, 64), (9, 70, 40, 160), (8, 300, 256, 600), (17, 140, 1024, 300),
+                                   (5, 1300, 64, 2700)])
+def test_decode_step_pipelined_kernel(shape):
+    """The persistent bulk-copy pipeline form of the fused decode step (one CTA per SM, history and taps through a
+    shared-memory ring, a row of 8 sequences x 8 channels summed inside one CTA in slice order): every step's row
+    equals the full-prefix row; positions advance; a ragged batch is refused with status 6; channel shards of the same
+    kernel concatenate to exactly the whole layer's output (the sum order does not depend on the grid)."""
+    from flash_stu_2_b200 import ops
+    dt = torch.bfloat16
+    B, T, d, L = shape
+    Lh = ((L + 1) // 2 + 7) // 8 * 8
+    x, nw, Mi, fp, xp, ref = _decode_fixture(dt, B, T, d, L)
+    hist = torch.zeros(B, d, 2, Lh, dtype=dt, device=dev())
+    pos = torch.zeros(B, 2, dtype=torch.int32, device=dev())
+    taps = ops.taps_even(fp.to(dev()), Lh)
+    taps8 = ops.taps_rev8(taps)
+    MinT = Mi.t().contiguous().to(dev())
+    xd, nwd = x.to(dev()), nw.to(dev())
+    # two channel shards fed the same inputs (stale values beyond the position must not matter: poison the tails)
+    half = d // 2
+    shards = []
+    for r in range(2):
+        sl = slice(r * half, (r + 1) * half)
+        shards.append((MinT[sl].contiguous(), torch.full((B, half, 2, Lh), 3.0, dtype=dt, device=dev()),
+                       ops.taps_rev8(taps[sl].contiguous()), torch.zeros(B, 2, dtype=torch.int32, device=dev())))
+    outs = []
+    for t in range(T):
+        xt = xd[:, t].contiguous()
+        out = torch.empty(B, d, dtype=dt, device=dev())
+        ops.decode_approx_pipelined(xt, nwd, MinT, hist, taps8, pos, out)
+        outs.append(out)
+        if half % 8 == 0 and t % 7 == 0:
+            ys = []
+            for (Ms, hs, t8s, ps) in shards:
+                ps[:, 0] = t
+                if t:   # the shard caches follow the whole layer's (only steps t % 7 == 0 run through the shards)
+                    sl = slice(0, half) if Ms is shards[0][0] else slice(half, d)
+                    for par in range(2):
+                        n = (t - par + 1) // 2
+                        hs[:, :, par, :n] = hist[:, sl, par, :n]
+                y = torch.empty(B, half, dtype=dt, device=dev())
+                ops.decode_approx_pipelined(xt, nwd, Ms, hs, t8s, ps, y, add_residual=False)
+                ys.append(y)
+            sharded = (xt.float() + torch.cat(ys, 1).float()).to(dt)
+            assert torch.equal(sharded, out), t
+    ops.check_status()
+    got = torch.stack(outs, 1).cpu()
+    assert pos[:, 0].tolist() == [T] * B and int(pos[0, 1]) == 0
+    close(got, ref, 1.5e-2)
+    close(hist, _hist_from(xp, Lh), 1e-2)
+    if B > 1:
+        pos[:, 0] = 5
+        pos[1, 0] = 4
+        before = hist.clone()
+        ops.decode_approx_pipelined(xd[:, 5].contiguous(), nwd, MinT, hist, taps8, pos, out)
+        with pytest.raises(RuntimeError, match="status 6"):
+            ops.check_status()
+        assert torch.equal(before, hist)
+
+
 def test_decode_step_channel_shards_tile_the_layer():
     """Tensor-parallel form of the fused decode step: two ranks' channel shards (own history, own rows of
     M_inputs^T, own taps) give, concatenated and added to the input, exactly the whole-layer kernel's output."""
