@@ -66,6 +66,11 @@ def parse():
     ap.add_argument("--early-decode", type=int, default=1, choices=[0, 1],
                     help="1: the STU decode kernel starts while the down projection before it still runs (only its "
                          "projection waits for it); 0: it starts after it")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="skip the extra objects of the default line (`generate`: the 24-layer model through "
+                         "FlashSTU.generate(); `tp`, N > 1 only: the 3B shapes tensor-parallel over the N ranks)")
+    ap.add_argument("--extra-new-tokens", type=int, default=64, help="tokens generated for the `generate` object")
+    ap.add_argument("--tp-new-tokens", type=int, default=32, help="tokens generated for the `tp` object")
     ap.add_argument("--decode-kernel", choices=["pipe", "rows8"], default="pipe",
                     help="fused decode kernel: the persistent bulk-copy pipeline (default) or the 8x8 register-streaming one")
     return ap.parse_args()
@@ -449,6 +454,13 @@ def run_b200(a):
         e2e_wall = time.perf_counter() - w0
         dec_s, e2e_wall = parallel.max_over_ranks([dec_s, e2e_wall], device=dev)
 
+    # ---- extra objects (same line, headline unchanged): the whole-model token loop, and for N > 1 the tensor-parallel split
+    extra = {}
+    if not a.no_extra and approx:
+        with torch.no_grad():
+            extra["generate"] = generate_object(a, dev, world)
+            if world > 1:
+                extra["tp"] = tp_object(a, dev, world, rank)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -515,11 +527,179 @@ def run_b200(a):
                                  "frac": step_bytes / (step_us * 1e-6) / 1e9 / pk["hbm_gbs"]}
     if split is not None:
         line["decode_split"] = split
+    if extra.get("generate") is not None:
+        line["generate"] = extra["generate"]
+    if extra.get("tp") is not None:
+        line["tp"] = extra["tp"]
     if world == 1 and not a.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(a, make_state(L, approx=approx), x_host)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------------------------- extra objects
+def _decode_bytes_per_step(cfg, b, t, e=2):
+    """Algorithmic HBM bytes of one cached token step of a FlashSTU model at position t for b resident sequences:
+    every weight once (tied LM head included), per STU layer one parity run of the projected history of every sequence
+    plus the even taps, per attention layer the keys and values inside the window plus the new pair."""
+    d, n_layers, K, V, s_, w = cfg["n_embd"], cfg["n_layers"], cfg["num_eigh"], cfg["vocab_size"], cfg["mlp_scale"], cfg["window_size"]
+    n_attn = n_layers // 2 if cfg.get("use_attn", True) else 0
+    n_stu = n_layers - n_attn
+    weights = n_stu * (d * d + 3 * s_ * d * d + 2 * d) + n_attn * (4 * d * d + 3 * s_ * d * d + 2 * d) + V * d + d
+    taps = n_stu * d * (t // 2 + 1)
+    stu_state = n_stu * b * (d * (t // 2) + d)
+    kv_state = n_attn * b * (2 * min(t, w + 1) * d + 2 * d)
+    return e * (weights + taps + stu_state + kv_state)
+
+
+def generate_object(a, dev, world):
+    """The 24-layer d=1536 bf16 model (B=32 per GPU, prompt 2048, top_k=40, T=0.8) through FlashSTU.generate() with
+    random-init weights built on the GPU: decode tokens/s per GPU (time of a full generate minus the time of one that
+    stops after the first new token, CUDA events, max over ranks), prefill tokens/s, kernels launched per token step
+    and the fraction of the HBM roofline of a step."""
+    import tempfile
+    import flash_stu_2_b200 as F
+    from flash_stu_2_b200 import ops, parallel
+    spec = MODEL_CONFIGS["c3"]
+    cfg = dict(spec["cfg"])
+    L, K = cfg["seq_len"], cfg["num_eigh"]
+    B, T0, new = spec["B"], spec["prompt"], a.extra_new_tokens
+    with tempfile.TemporaryDirectory() as tmp:
+        fp = filter_file(L)
+        if fp is None:
+            fp = os.path.join(tmp, "phi.pt")
+            F.save_spectral_filters(F.get_spectral_filters(L, K, device=dev, dtype=torch.float32), fp)
+        torch.manual_seed(0)
+        with torch.device(dev):
+            model = F.FlashSTU(F.FlashSTUConfig(filter_path=fp, torch_dtype=torch.bfloat16, cache_len=T0 + new + 8,
+                                                **cfg))
+        model = model.to(dev).eval()
+    ids = torch.randint(0, cfg["vocab_size"], (B, T0), device=dev)
+    gen = torch.Generator(device=dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def timed(max_length, graph=True, timings=None):
+        gen.manual_seed(0)
+        e0, e1 = ev(), ev()
+        torch.cuda.synchronize()
+        e0.record()
+        out = model.generate(ids, max_length=max_length, generator=gen, cuda_graph=graph, timings=timings,
+                             **spec["sampling"])
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1), out
+
+    timed(T0 + 6)                                              # warm-up: derived weights, scratch, graph capture path
+    c0 = ops.launch_count
+    timed(T0 + 1, graph=False)
+    c1 = ops.launch_count
+    timed(T0 + 5, graph=False)
+    c2 = ops.launch_count
+    per_step = ((c2 - c1) - (c1 - c0)) / 4.0
+    t_first = min(timed(T0 + 1)[0] for _ in range(2))
+    # the token step is timed on the device over the graph-replayed steps alone (CUDA events inside generate()): the
+    # two eager steps and the capture of the step graph before them are host work that varies by tens of milliseconds
+    tm = {}
+    timed(T0 + new, timings=tm)
+    ops.check_status()
+    t_first, replay_ms = parallel.max_over_ranks([t_first, tm["replay_ms"]], device=dev)
+    dec_ms = replay_ms / tm["replayed_steps"]
+    pk = peaks()
+    nbytes = _decode_bytes_per_step(cfg, B, T0 + new // 2)
+    n_param = sum(p.numel() for p in model.parameters())
+    del model
+    torch.cuda.empty_cache()
+    return {"workload": f"FlashSTU.generate: 24 layers d=1536 H=12 window 1024 K=24 V=50257 bf16, {n_param / 1e6:.0f} M "
+                        f"parameters, B={B}/GPU, prompt {T0}, +{new} tokens top_k=40 T=0.8 (random-init weights)",
+            "decode_tokens_per_s_per_gpu": B / (dec_ms * 1e-3), "decode_ms_per_token_step": dec_ms,
+            "prefill_tokens_per_s_per_gpu": B * T0 / (t_first * 1e-3), "prefill_ms": t_first,
+            "launches_per_token_step": per_step,
+            "roofline": {"bound": "hbm", "bytes_per_step": nbytes, "achieved": nbytes / (dec_ms * 1e-3) / 1e9,
+                         "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": nbytes / (dec_ms * 1e-3) / 1e9 / pk["hbm_gbs"],
+                         "accounting": "one parity run of the STU history per step (parity-split cache), keys and values "
+                                       "inside the window, every weight once"},
+            "decode_launch": "one CUDA graph per token step", "n_gpus": world,
+            "parallelism": f"dp{world}: every rank generates for its own {B} sequences"}
+
+
+def _err_figures(a, b):
+    a, b = a.double(), b.double()
+    rel = float((a - b).abs().max() / b.abs().max())
+    a2, b2 = a.reshape(-1, a.shape[-1]), b.reshape(-1, b.shape[-1])
+    den = b2.abs().amax(1).clamp_min(1e-3 * float(b2.abs().max()))
+    return {"rel": rel, "row": float(((a2 - b2).abs().amax(1) / den).max())}
+
+
+def tp_object(a, dev, world, rank):
+    """N > 1: the 3B configuration's shapes (32 layers, d=3072, 24 heads, window 2048, K=32 filters of 32768 positions,
+    B=64, prompt 8192, greedy) tensor-parallel over the N ranks, weights generated shard by shard on the GPUs; plus the
+    parity of the sharded path against the reference's logits on the small hybrid fixtures (2 or 4 ranks)."""
+    import torch.distributed as dist
+    import flash_stu_2_b200 as F
+    from flash_stu_2_b200 import ops, parallel
+    from flash_stu_2_b200.tensor_parallel import TensorParallelFlashSTU, random_shards
+    spec = MODEL_CONFIGS["c5"]
+    cfg = dict(spec["cfg"])
+    B, T0, new = spec["B"], spec["prompt"], a.tp_new_tokens
+    cfg["cache_len"] = T0 + new + 8
+    config = F.FlashSTUConfig(torch_dtype=torch.bfloat16, **cfg)
+    phi = F.get_spectral_filters(cfg["seq_len"], cfg["num_eigh"], device=dev, dtype=torch.float32).to(torch.bfloat16)
+    # every rank must hold the same filters: take rank 0's
+    dist.broadcast(phi, src=0)
+    tp = TensorParallelFlashSTU(config, random_shards(config, phi, rank, world, dev, seed=0), dev, presharded=True)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg["vocab_size"], (B, T0), generator=g).to(dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def timed(prompt, max_length, timings=None):
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = ev(), ev()
+        e0.record()
+        out = tp.generate(prompt, max_length=max_length, do_sample=False, timings=timings)
+        e1.record()
+        torch.cuda.synchronize()
+        return parallel.max_over_ranks([e0.elapsed_time(e1)], device=dev)[0], out
+
+    timed(ids[:, :256].contiguous(), 256 + 6)                 # warm-up on a short prompt (derived weights, graph path)
+    t_first, _ = timed(ids, T0 + 1)
+    tm = {}
+    _, out = timed(ids, T0 + new, timings=tm)      # token steps: device time of the graph-replayed steps alone
+    ops.check_status()
+    same = parallel.gather_token_ids(out[:1, T0:].contiguous(), world)
+    dec_ms = parallel.max_over_ranks([tm["replay_ms"]], device=dev)[0] / tm["replayed_steps"]
+    pk = peaks()
+    nbytes = _decode_bytes_per_step(cfg, B, T0 + new // 2) / world
+    res = {"workload": f"FlashSTU.generate, 3B shapes: 32 layers d=3072 H=24 window 2048 K=32 L=32768 V=50257 bf16 "
+                       f"B={B} prompt {T0} +{new} greedy, tensor-parallel over {world} GPUs (random-init shards)",
+           "decode_ms_per_token_step": dec_ms, "decode_tokens_per_s_per_gpu": B / (dec_ms * 1e-3) / world,
+           "decode_tokens_per_s": B / (dec_ms * 1e-3),
+           "prefill_ms": t_first, "prefill_tokens_per_s": B * T0 / (t_first * 1e-3),
+           "ranks_agree": bool((same == same[0]).all()),
+           "roofline": {"bound": "hbm", "bytes_per_step_per_gpu": nbytes, "achieved": nbytes / (dec_ms * 1e-3) / 1e9,
+                        "peak": pk["hbm_gbs"], "unit": "GB/s per GPU", "frac": nbytes / (dec_ms * 1e-3) / 1e9 / pk["hbm_gbs"]},
+           "collectives": "NCCL all-gather per STU layer, all-reduce per attention / MLP block, captured in the step graph"}
+    del tp
+    torch.cuda.empty_cache()
+    # ---- parity of the sharded path on the reference's small hybrid fixtures (needs n_heads % ranks == 0)
+    par = {}
+    gold = os.path.join(ROOT, "tests", "golden", "models.pt")
+    sub = 4 if world >= 4 else 2
+    group = dist.new_group(ranks=list(range(sub)))
+    if os.path.exists(gold) and rank < sub:
+        fixtures = torch.load(gold, map_location="cpu", weights_only=False)
+        for name in ("hybrid_approx_fp32", "hybrid_approx_bf16"):
+            r = fixtures[name]
+            c = F.FlashSTUConfig(torch_dtype=getattr(torch, r["dtype"]), **r["cfg"])
+            m = TensorParallelFlashSTU(c, r["sd"], dev, group=group)
+            with torch.no_grad():
+                logits = m.last_logits(r["ids"].to(dev), m.new_cache(r["ids"].shape[0])).float().cpu()
+            ops.check_status()
+            par[name] = dict(_err_figures(logits, r["logits_full"][:, -1].float()), ranks=sub,
+                             tolerance=1e-3 if r["dtype"] == "float32" else 2e-2)
+    res["parity_vs_reference_logits"] = par if par else "fixture file missing"
+    return res
 
 
 # ----------------------------------------------------------------------------------------------- whole models
@@ -537,8 +717,8 @@ MODEL_CONFIGS = {
 
 
 def run_lds_stack(a):
-    """12 x MiniSTU(backend='lds') applied one after the other (no norm or residual between them): prefill of
-    16 x 15360 positions through the convolution form, then 1024 recurrent steps replayed from one CUDA graph."""
+    """12 x MiniSTU(backend='lds') applied one after the other (no norm or residual between them): chunked-scan
+    prefill of 16 x 15360 positions, then 1024 recurrent steps replayed from one CUDA graph."""
     import flash_stu_2_b200 as F
     from flash_stu_2_b200 import ops
     if not torch.cuda.is_available():
@@ -589,6 +769,7 @@ def run_lds_stack(a):
         dec_ms = e0.elapsed_time(e1)
     ops.check_status()
     D_, F_ = 160, 48
+    pre_flops = B * T0 * n_layers * (2 * F_ * d * d + 2 * D_ * F_ * d + 2 * D_ * d)
     step_bytes = n_layers * (F_ * d * d * 2 + B * d * D_ * 16 + D_ * F_ * 2)
     pk = peaks()
     print(json.dumps({
@@ -601,8 +782,12 @@ def run_lds_stack(a):
                      "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": step_bytes / (dec_ms / new * 1e-3) / 1e9 / pk["hbm_gbs"],
                      "bytes_per_launch": step_bytes},
         "prefill": {"value": B * T0 / (pre_ms * 1e-3), "unit": "tokens/s", "ms": pre_ms,
-                    "note": "convolution form with the LDS impulse responses (48 filters x 3 causal Toeplitz GEMMs per "
-                            "layer), O(T^2) per channel"},
+                    "tflops_algorithmic": pre_flops / (pre_ms * 1e-3) / 1e12,
+                    "frac_of_tensor_peak": pre_flops / (pre_ms * 1e-3) / 1e12 / pk["bf16_tflops_sustained"],
+                    "peak_tflops": pk["bf16_tflops_sustained"],
+                    "note": "chunked scan: float64 recurrence + rotated carry per chunk of 128 positions (one kernel), one "
+                            "tensor-core GEMM per sequence for the features of all chunks, one for the contraction with M; "
+                            "FLOPs counted per token and layer as 2*48*d^2 + 2*160*48*d + 2*160*d (recurrent form)"},
     }))
 
 
@@ -736,6 +921,13 @@ def run_model(a):
 
 if __name__ == "__main__":
     args = parse()
+    if args.impl != "reference":
+        from flash_stu_2_b200 import ops as _ops
+        from flash_stu_2_b200.modules import STU as _STU
+        _ops.early_decode = bool(args.early_decode)
+        _STU.pipelined_decode = (args.decode_kernel == "pipe")
+        if args.no_overlap:
+            _ops.overlap_decode = False
     if args.impl == "reference":
         run_reference(args)
     elif args.model == "c4":

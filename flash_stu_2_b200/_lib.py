@@ -51,6 +51,7 @@ _SIGNATURES = {
     "stu_full_decode_prepare": ([_P, _LL, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P], c_int),
     "stu_full_decode_combine": ([_P, _LL, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P], c_int),
     "stu_lds_final_state": ([_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P], c_int),
+    "stu_lds_chunk_scan": ([_P, _LL, _LL, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P], c_int),
     "stu_lds_decode_features": ([_P, _LL, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P], c_int),
     "stu_swa_forward": ([_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                          _P], c_int),

@@ -12,6 +12,8 @@ enum { BACKEND_AUTO = 0, BACKEND_SIMT = 1, BACKEND_TCGEN05 = 2, BACKEND_SKINNY =
 //            +0x100: W is lower triangular (zero for k > n); the tcgen05 path skips those k-blocks
 //            3: scatter into the parity-split history (y = hist base, hist_T tokens per sequence
 //               starting at time hist_t0, N channels, hist_Lh elements per parity row)
+//            5: y[m*y_row_stride + (n / hist_T) * resid_row_stride + (n % hist_T)] = acc  (columns in blocks of hist_T,
+//               blocks resid_row_stride elements apart; resid itself is not read)
 // norm_w != NULL asks for x to be RMS-normalised (eps) on the way in; only the decode (skinny) path
 // fuses this, other shapes return STU_ERR_UNSUPPORTED so that the caller normalises separately.
 bool pdl_enabled() {
@@ -33,7 +35,9 @@ extern "C" int stu_linear(const void* x, long long x_row_stride, const void* W, 
   const int causal = (epilogue & EPI_FLAG_CAUSAL) ? 1 : 0;
   const int pdl = epilogue & (STU_FLAG_OVERLAP | STU_FLAG_EARLY_TRIGGER);  // honoured by the skinny kernels only
   epilogue &= ~(EPI_FLAG_CAUSAL | STU_FLAG_OVERLAP | STU_FLAG_EARLY_TRIGGER);
-  if (epilogue < EPI_STORE || epilogue > EPI_HIST) return STU_ERR_UNSUPPORTED;
+  if ((epilogue < EPI_STORE || epilogue > EPI_HIST) && epilogue != EPI_BLOCKCOL) return STU_ERR_UNSUPPORTED;
+  // EPI_BLOCKCOL: hist_T = columns per block, resid_row_stride = distance between blocks (elements); resid unused
+  if (epilogue == EPI_BLOCKCOL && (hist_T <= 0 || resid_row_stride <= 0)) return STU_ERR_SHAPE;
   if (epilogue == EPI_GELU_MUL && !W2) return STU_ERR_NULL;
   if (epilogue == EPI_RESID && !resid) return STU_ERR_NULL;
   if (epilogue == EPI_HIST && (hist_T <= 0 || hist_Lh <= 0 || hist_t0 < 0 || (M % hist_T) != 0 ||
@@ -49,6 +53,7 @@ extern "C" int stu_linear(const void* x, long long x_row_stride, const void* W, 
   ep.Tseq = hist_T;
   ep.t0 = hist_t0;
   ep.Lh = hist_Lh;
+  ep.ld2 = (epilogue == EPI_BLOCKCOL) ? resid_row_stride : 0;
 
   bool sk_ok = skinny_supported(x, x_row_stride, W, w_row_stride, w_k_stride, W2, M, N, K, epilogue, dtype);
   if (norm_w) {

@@ -8,6 +8,9 @@ enum {
   EPI_RESID = 1,     // y = resid + round(acc)            x.add_(h), flash_stu/layers/stu_layer.py:93,96
   EPI_GELU_MUL = 2,  // y = round(gelu_tanh(round(acc))) * round(acc2)   flash_stu/modules/swiglu.py:22-28
   EPI_HIST = 3,      // scatter acc into the parity-split channel-major history [B][N][2][Lh]
+  EPI_BLOCKCOL = 5,  // y[m*ldy + (n / Tseq) * ld2 + (n % Tseq)] = acc: columns come in blocks of Tseq, every block ld2
+                     // elements after the last (the distilled-LDS features: rows (tau, f), columns (chunk, channel),
+                     // written straight into the [tokens, F*d] operand of the contraction with M)
 };
 // OR-ed into the epilogue code: W is lower triangular (W[n][k] = 0 for k > n); kernels may skip those blocks
 #define EPI_FLAG_CAUSAL 0x100
@@ -19,6 +22,7 @@ template <typename T> struct EpiArgs {
   long long ldr;
   // EPI_HIST: row m of the GEMM is token (m / T) * .. + (m % T) of a [B,T] batch starting at time t0
   int Tseq, t0, Lh;
+  long long ld2;  // EPI_BLOCKCOL: distance between column blocks
 };
 
 struct EpiArgsAny {
@@ -27,9 +31,11 @@ struct EpiArgsAny {
   const void* resid;
   long long ldr;
   int Tseq, t0, Lh;
+  long long ld2 = 0;
   template <typename U> EpiArgs<U> as() const {
     EpiArgs<U> e;
     e.y = (U*)y; e.ldy = ldy; e.resid = (const U*)resid; e.ldr = ldr; e.Tseq = Tseq; e.t0 = t0; e.Lh = Lh;
+    e.ld2 = ld2;
     return e;
   }
 };
@@ -44,6 +50,8 @@ __device__ __forceinline__ void epilogue_store(const EpiArgs<T>& ep, int m, int 
   } else if (EPI == EPI_GELU_MUL) {
     float g = round_to<T>(gelu_tanh(round_to<T>(acc)));
     ep.y[(size_t)m * ep.ldy + n] = Elem<T>::from_f(g * round_to<T>(acc2));
+  } else if (EPI == EPI_BLOCKCOL) {
+    ep.y[(size_t)m * ep.ldy + (size_t)(n / ep.Tseq) * ep.ld2 + (n % ep.Tseq)] = Elem<T>::from_f(acc);
   } else {  // EPI_HIST; ldy carries the channel count
     int b = m / ep.Tseq, t = ep.t0 + (m - b * ep.Tseq);
     ep.y[hist_off(b, n, t, (int)ep.ldy, ep.Lh)] = Elem<T>::from_f(acc);

@@ -73,6 +73,7 @@ static int launch_simt(const void* A, long long lda, const void* B, long long ld
     case EPI_RESID: LAUNCH(EPI_RESID); break;
     case EPI_GELU_MUL: LAUNCH(EPI_GELU_MUL); break;
     case EPI_HIST: LAUNCH(EPI_HIST); break;
+    case EPI_BLOCKCOL: LAUNCH(EPI_BLOCKCOL); break;
     default: return STU_ERR_UNSUPPORTED;
   }
 #undef LAUNCH

@@ -309,8 +309,10 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
             }
           } else {
             bf16* yrow = ep.y + (size_t)m * ep.ldy + nb;
+            if (EPI == EPI_BLOCKCOL)   // columns in blocks of Tseq, ld2 elements apart
+              yrow = ep.y + (size_t)m * ep.ldy + (size_t)(nb / ep.Tseq) * ep.ld2 + (nb % ep.Tseq);
             const bf16* rrow = (EPI == EPI_RESID) ? ep.resid + (size_t)m * ep.ldr + nb : nullptr;
-            const bool vec = (nb + 32 <= N);
+            const bool vec = (nb + 32 <= N) && (EPI != EPI_BLOCKCOL || ep.Tseq % 32 == 0);
 #pragma unroll
             for (int v8 = 0; v8 < 4; v8++) {
               float o[8];
@@ -336,6 +338,13 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
               }
               if (vec) {
                 store_vec(yrow + v8 * 8, o);
+              } else if (EPI == EPI_BLOCKCOL) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                  const int n = nb + v8 * 8 + j;
+                  if (n < N)
+                    ep.y[(size_t)m * ep.ldy + (size_t)(n / ep.Tseq) * ep.ld2 + (n % ep.Tseq)] = __float2bfloat16_rn(o[j]);
+                }
               } else {
 #pragma unroll
                 for (int j = 0; j < 8; j++)
@@ -490,6 +499,7 @@ bool gemm_tc_supported(const void* A, long long lda, const void* B, long long ld
   if (M < 1 || N < 1 || K < 8) return false;
   if (epi == EPI_HIST) return aligned16(ep.y) && get_encode_fn() != nullptr;
   if (ep.ldy % 8 || !aligned16(ep.y)) return false;
+  if (epi == EPI_BLOCKCOL && (ep.ld2 % 8 || ep.Tseq % 8 || ep.Tseq <= 0)) return false;
   if (epi == EPI_RESID && (ep.ldr % 8 || !aligned16(ep.resid))) return false;
   return get_encode_fn() != nullptr;
 }
@@ -526,12 +536,15 @@ int gemm_tc_dispatch(const void* A, long long lda, const void* B, long long ldb,
     switch (epi) {
       case EPI_STORE: return launch_tc<EPI_STORE, 4, 256>(ma, mb, mb2, M, N, K, 0, causal, ep, device_status_word(), st);
       case EPI_RESID: return launch_tc<EPI_RESID, 4, 256>(ma, mb, mb2, M, N, K, 0, causal, ep, device_status_word(), st);
+      case EPI_BLOCKCOL:
+        return launch_tc<EPI_BLOCKCOL, 4, 256>(ma, mb, mb2, M, N, K, 0, causal, ep, device_status_word(), st);
     }
   }
   switch (epi) {
     case EPI_STORE: return launch_tc<EPI_STORE, 6>(ma, mb, mb2, M, N, K, 0, causal, ep, device_status_word(), st);
     case EPI_RESID: return launch_tc<EPI_RESID, 6>(ma, mb, mb2, M, N, K, 0, causal, ep, device_status_word(), st);
     case EPI_GELU_MUL: return launch_tc<EPI_GELU_MUL, 4>(ma, mb, mb2, M, N, K, 0, 0, ep, device_status_word(), st);
+    case EPI_BLOCKCOL: return launch_tc<EPI_BLOCKCOL, 6>(ma, mb, mb2, M, N, K, 0, causal, ep, device_status_word(), st);
   }
   return STU_ERR_UNSUPPORTED;
 }

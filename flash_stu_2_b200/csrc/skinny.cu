@@ -288,7 +288,7 @@ static void launch_skinny_f32(const float* A, long long lda, const float* B, lon
 
 bool skinny_supported(const void* A, long long lda, const void* B, long long ldb, long long skb, const void* B2,
                       int M, int N, int K, int epi, int dtype) {
-  if (M < 1 || M > 64 || skb != 1 || epi == EPI_HIST) return false;
+  if (M < 1 || M > 64 || skb != 1 || epi == EPI_HIST || epi == EPI_BLOCKCOL) return false;
   if (dtype == STU_BF16)
     return !(K % 8 || lda % 8 || ldb % 8 || !aligned16(A) || !aligned16(B) || (B2 && !aligned16(B2)));
   if (dtype == STU_F32)

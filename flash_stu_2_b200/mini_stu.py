@@ -1,8 +1,8 @@
 """MiniSTU (mini_stu/stu.py:12-275): the bare full-variant spectral transform with its own input and
 output widths, same constructor signature and parameter names (M_phi_plus, M_phi_minus) as the reference.
 The spectral backend runs on the kernels of the full STU variant.  The distilled-LDS backend
-(mini_stu/stu_lds.py:213-394) produces prefill outputs through the same kernels, as the causal convolution with
-the LDS impulse responses, and decodes with a recurrent float64 state; forward() takes the optional
+(mini_stu/stu_lds.py:213-394) prefills with a chunked scan (float64 recurrence, carry term in a balanced rotated
+basis, one tensor-core GEMM per sequence for the features of all chunks) and decodes with a recurrent float64 state; forward() takes the optional
 `past_key_value` / `use_cache` pair for that (the reference has no cached call).  The optional post-MLP is not
 part of this implementation and raises."""
 import os
@@ -133,8 +133,43 @@ class MiniSTU(nn.Module):
             object.__setattr__(self, "_op", op)
             self._lds_f32 = (lds.A.to(M.device, torch.float64).contiguous(), lds.B_vec.to(M.device, torch.float64).contiguous(),
                              lds.C.to(M.device, self.dtype).contiguous())
+            self._lds_unit_b = bool((Bv == 1.0).all())
+            self._lds_scan = self._scan_operands(A, Bv, lds.C.to(self.dtype).double().cpu(), M.device)
             self._lds_key = key
         return self._op
+
+    LDS_CHUNK = 128     # positions per chunk of the scan prefill
+    LDS_RANK_CAP = 96   # at most this many balanced coordinates carry the state between chunks
+
+    def _scan_operands(self, A, Bv, C, device):
+        """Constant operands of the chunked-scan prefill (float64 on the host, once per parameter version).
+        V, lambda: leading eigenpairs of the reachability Gramian P[n,m] = B_n B_m / (1 - A_n A_m); in the basis
+        z = V^T h / sqrt(lambda) the carried state and the rotated output map are both O(1) and the carry term
+        sum_n C[n,f] A_n^(tau+1) h[n] has no cancellation left (evaluated mode by mode it cancels to 1e-4 of its terms).
+        Returns (Vs [D,R] float64, W [Ck*F, KZ] model dtype, R): W = [Q_hi | Q_hi | Q_lo | Toeplitz(G)] for bf16 (hi/lo
+        split of the carry operand, the scan kernel writes [z_hi | z_lo | z_hi | x]), [Q | Toeplitz(G)] for fp32."""
+        D, F_ = C.shape
+        Ck = self.LDS_CHUNK
+        P = torch.outer(Bv, Bv) / (1.0 - torch.outer(A, A))
+        lam, V = torch.linalg.eigh((P + P.T) * 0.5)
+        lam, V = lam.flip(0), V.flip(1)
+        R = int((lam > 1e-13 * lam[0]).sum())
+        R = max(8, min((R + 7) // 8 * 8, self.LDS_RANK_CAP, D // 8 * 8))
+        scale = lam[:R].clamp_min(1e-16 * float(lam[0])).sqrt()
+        Vs = (V[:, :R] / scale).contiguous()
+        tau = torch.arange(1, Ck + 1, dtype=torch.float64)
+        Pw = A[None, :] ** tau[:, None]                                         # [Ck, D]  A^(tau+1)
+        Q = torch.einsum("td,df,dk->tfk", Pw, C, V[:, :R] * scale)              # [Ck, F, R]
+        G = ((A[None, :] ** torch.arange(Ck, dtype=torch.float64)[:, None]) * Bv[None, :]) @ C   # [Ck, F]
+        lag = torch.arange(Ck)[:, None] - torch.arange(Ck)[None, :]             # tau - sigma
+        T2 = torch.where((lag >= 0)[:, None, :], G[lag.clamp_min(0)].permute(0, 2, 1), torch.zeros((), dtype=torch.float64))
+        if self.dtype == torch.bfloat16:
+            Qh = Q.to(torch.bfloat16)
+            Ql = (Q - Qh.double()).to(torch.bfloat16)
+            W = torch.cat([Qh, Qh, Ql, T2.to(torch.bfloat16)], dim=2)
+        else:
+            W = torch.cat([Q, T2], dim=2).to(self.dtype)
+        return Vs.to(device), W.reshape(Ck * F_, -1).contiguous().to(device), R
 
     def _forward_lds(self, x, past_key_value=None, use_cache=False):
         op = self._lds_prepared()
@@ -155,14 +190,38 @@ class MiniSTU(nn.Module):
             pos._host_t = t + 1
             return (y, (h, pos)) if use_cache else y
         y = torch.empty(B, T, self.output_dim, dtype=x.dtype, device=x.device)
-        if not use_cache:
-            op.full_forward(x, None, y)
-            return y
-        hist, pos = op.new_cache(B, x.device)
-        op.full_forward(x, None, y, (hist, pos), True)
+        if not MiniSTU.chunked_scan_prefill:
+            # the same outputs as one causal convolution per feature with the full-length impulse responses
+            # (O(T^2) per channel; kept for comparison)
+            if not use_cache:
+                op.full_forward(x, None, y)
+                return y
+            hist, pos = op.new_cache(B, x.device)
+            op.full_forward(x, None, y, (hist, pos), True)
+            h = torch.empty(B, d, D, dtype=torch.float64, device=x.device)
+            ops.lds_final_state(hist, h, A32, B32, T)
+            return y, (h, pos)
+        # chunked scan: float64 recurrence + rotated carry (one kernel), then per sequence one GEMM that produces the
+        # features of all chunks in the layout of the contraction with M, and that contraction
+        Vs, W, R = self._lds_scan
+        Ck = self.LDS_CHUNK
+        nch = (T + Ck - 1) // Ck
+        Z = torch.empty(B, nch, d, W.shape[1], dtype=x.dtype, device=x.device)
         h = torch.empty(B, d, D, dtype=torch.float64, device=x.device)
-        ops.lds_final_state(hist, h, A32, B32, T)
+        ops.lds_chunk_scan(x, A32, B32, Vs, Z, h, Ck, unit_b=self._lds_unit_b)
+        _, Mcat = op.prepared_full()
+        U2 = torch.empty(nch * Ck, F_ * d, dtype=x.dtype, device=x.device)
+        for b in range(B):
+            ops.lds_chunk_features(W, Z[b].view(nch * d, W.shape[1]), U2, d, Ck, F_)
+            ops.linear(U2[:T], Mcat, out=y[b])
+        if not use_cache:
+            return y
+        pos = new_pos(B, x.device)
+        pos[:, 0] += T
+        pos._host_t = T
         return y, (h, pos)
+
+    chunked_scan_prefill = True   # class switch: False runs the prefill as full-length convolutions
 
     def forward(self, x: torch.Tensor, past_key_value=None, use_cache: bool = False) -> torch.Tensor:
         if x.dim() == 2:

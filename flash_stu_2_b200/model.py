@@ -154,6 +154,9 @@ class FlashSTU(PreTrainedModel):
         uniforms = kwargs.get("uniforms")
         generator = kwargs.get("generator")
         return_logits = kwargs.get("return_logits", False)
+        timings = kwargs.get("timings")   # optional dict: filled with the device time of the graph-replayed steps
+        ev_first = ev_last = None
+        replayed = 0
         B, T0 = input_ids.shape
         steps = max_length - T0
         if steps <= 0:
@@ -192,10 +195,14 @@ class FlashSTU(PreTrainedModel):
                     for e, t in zip(past, host_t):   # capturing ran the host bookkeeping, not the kernels
                         if e is not None and t is not None:
                             e[-1]._host_t = t
+                if timings is not None and ev_first is None:
+                    ev_first = torch.cuda.Event(enable_timing=True)
+                    ev_first.record()
                 tok_in.copy_(generated[:, cur - 1:cur])
                 if do_sample:
                     u_buf.copy_(u)
                 graph.replay()
+                replayed += 1
                 for e in past:
                     if e is not None and getattr(e[-1], "_host_t", None) is not None:
                         e[-1]._host_t += 1
@@ -212,6 +219,12 @@ class FlashSTU(PreTrainedModel):
             if return_logits:
                 all_logits.append(logits)
             ops.sample(logits, temperature, top_k, top_p, do_sample, u, generated[:, cur:], out_stride=max_length)
+        if timings is not None and ev_first is not None:
+            ev_last = torch.cuda.Event(enable_timing=True)
+            ev_last.record()
+            ev_last.synchronize()
+            timings["replayed_steps"] = replayed
+            timings["replay_ms"] = ev_first.elapsed_time(ev_last)
         if return_logits:
             return generated, torch.stack(all_logits, dim=1)
         return generated

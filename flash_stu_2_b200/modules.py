@@ -20,6 +20,16 @@ def _round_up(x: int, m: int) -> int:
     return (x + m - 1) // m * m
 
 
+_SM_COUNT = {}
+
+
+def _sm_count(device) -> int:
+    key = torch.device(device).index
+    if key not in _SM_COUNT:
+        _SM_COUNT[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SM_COUNT[key]
+
+
 def new_pos(batch: int, device) -> torch.Tensor:
     """[B,2] int32: column 0 = tokens cached so far, column 1 (row 0) = arrival counter used by kernels."""
     p = torch.zeros(batch, 2, dtype=torch.int32, device=device)
@@ -288,8 +298,12 @@ class STU(nn.Module):
         if t + 1 > self.capacity:
             raise ValueError(f"sequence position {t + 1} exceeds the capacity {self.capacity} (seq_len={self.seq_len})")
         B, d, _, Lh = hist.shape
+        # rows of 8 sequences x 8 channels, slices of 256 cached positions per parity: the pipeline kernel pays a
+        # per-row projection latency, which only long rows (or one row per SM) hide
+        rows, nsl = (B + 7) // 8 * (d // 8), ((t >> 1) + 255) // 256
         if (STU.pipelined_decode and STU.tensor_core_decode and STU.shared_tap_decode and taps8 is not None
-                and uniform_pos(pos) and d % 8 == 0 and x2d.shape[1] % 8 == 0):
+                and uniform_pos(pos) and d % 8 == 0 and x2d.shape[1] % 8 == 0
+                and (nsl >= 8 or rows <= _sm_count(x2d.device))):
             # batch at one common position: the bulk-copy pipeline kernel
             ops.decode_approx_pipelined(x2d, norm_w, MinT, hist, taps8, pos, out2d, eps,
                                         flags=(ops.FLAG_EARLY_TRIGGER if ops.overlap_decode else 0) |

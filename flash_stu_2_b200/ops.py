@@ -329,6 +329,40 @@ def lds_final_state(hist, h, A32, B32, T: int):
     _count()
 
 
+def lds_chunk_scan(x, A64, B64, Vs, Z, hfin, Ck: int, unit_b: bool = False):
+    """Chunked scan of the distilled LDS over x [B,T,d]: float64 recurrence per (sequence, channel); at every chunk
+    start the carried state goes, rotated into the balanced basis (Vs [D,R] float64), into the leading columns of
+    Z [B, nchunks, d, KZ], the chunk's inputs into the trailing Ck columns; hfin [B,d,D] float64 = the final state.
+    unit_b: the caller has checked that every entry of B64 is exactly 1 (B*x is then x, bit for bit)."""
+    _cuda(x, A64, B64, Vs, Z, hfin)
+    B, T, d = x.shape
+    D, R = Vs.shape
+    assert x.stride(2) == 1 and Z.is_contiguous() and hfin.is_contiguous() and Vs.is_contiguous()
+    assert A64.dtype == torch.float64 and Vs.dtype == torch.float64 and hfin.dtype == torch.float64
+    KZ = (3 * R if x.dtype == torch.bfloat16 else R) + Ck
+    assert Z.shape == (B, (T + Ck - 1) // Ck, d, KZ) and Z.dtype == x.dtype and hfin.shape == (B, d, D)
+    rc = _lib.load().stu_lds_chunk_scan(x.data_ptr(), x.stride(0), x.stride(1), A64.data_ptr(), B64.data_ptr(),
+                                        Vs.data_ptr(), Z.data_ptr(), hfin.data_ptr(), B, d, T, D, R, Ck,
+                                        _dt(x) | (0x1000 if unit_b else 0), _stream())
+    _lib.check(rc, "stu_lds_chunk_scan")
+    _count()
+
+
+def lds_chunk_features(W, Zb, U2, d: int, Ck: int, F: int):
+    """U2[c*Ck + tau, f*d + i] = sum_k W[tau*F + f, k] * Zb[c*d + i, k]: the LDS features of one sequence, one GEMM over
+    all its chunks, scattered straight into the [tokens, F*d] operand of the contraction with M."""
+    _cuda(W, Zb, U2)
+    Mrows, KZ = W.shape
+    N = Zb.shape[0]
+    assert Mrows == Ck * F and Zb.shape[1] == KZ and W.is_contiguous() and Zb.is_contiguous() and U2.is_contiguous()
+    assert N % d == 0 and U2.shape == (N // d * Ck, F * d) and U2.dtype == W.dtype == Zb.dtype
+    status_word(W.device)
+    rc = _lib.load().stu_linear(W.data_ptr(), KZ, Zb.data_ptr(), KZ, 1, None, None, Ck * F * d, U2.data_ptr(), d,
+                                Mrows, N, KZ, 5, d, 0, 0, None, 0.0, _dt(W), BACKEND_AUTO, _stream())
+    _lib.check(rc, "stu_linear (LDS feature scatter)")
+    _count()
+
+
 def lds_decode_features(x2d, h, A32, B32, C, U):
     """One recurrent LDS step for every channel: h <- A*h + B*x; U[b, f*d+i] = (h @ C)[f]."""
     _cuda(x2d, h, A32, B32, C, U)

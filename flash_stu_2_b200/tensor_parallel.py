@@ -69,11 +69,52 @@ def shard_state_dict(sd: Dict[str, torch.Tensor], cfg: dict, rank: int, world: i
     return out
 
 
+def random_shards(config, phi: torch.Tensor, rank: int, world: int, device, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Random-init weights of rank `rank`, generated on `device` shard by shard (no full model is ever built: a 4.5 B
+    parameter model would take 9 GB of host memory and minutes of initialisation per rank).  Replicated tensors
+    (embedding, norms, filters) come from the same seeded generator on every rank, sharded ones from a per-rank
+    seed; distributions as flash_stu/model.py:428-452 (normal with std d^-0.5 for the linears, Xavier for the STU and
+    attention projections)."""
+    d, H, K, V = config.n_embd, config.n_heads, config.num_eigh, config.vocab_size
+    inter, dt = d * config.mlp_scale, config.torch_dtype
+    dl, hd = d // world, d // H
+    shared = torch.Generator(device=device).manual_seed(seed)
+    own = torch.Generator(device=device).manual_seed(seed + 1000 * (rank + 1))
+
+    def normal(gen, shape, std):
+        return (torch.randn(*shape, device=device, dtype=torch.float32, generator=gen) * std).to(dt)
+
+    sd = {"phi": phi.to(device), "tok_emb.weight": normal(shared, (V, d), d ** -0.5),
+          "norm.weight": torch.ones(d, device=device, dtype=dt)}
+    vl = -(-V // world)
+    head = torch.zeros(vl, d, device=device, dtype=dt)
+    rows = sd["tok_emb.weight"][rank * vl:min(V, (rank + 1) * vl)]
+    head[:rows.shape[0]] = rows
+    sd["lm_head.weight"] = head
+    for i in range(config.n_layers):
+        p = f"layers.{i}."
+        if (i % 2 == 1) and config.use_attn:
+            sd[p + "attn_norm.weight"] = torch.ones(d, device=device, dtype=dt)
+            sd[p + "attn.c_attn.weight"] = normal(own, (3 * dl, d), (2.0 / (4 * d)) ** 0.5)
+            sd[p + "attn.c_proj.weight"] = normal(own, (d, dl), (2.0 / (2 * d)) ** 0.5)
+        else:
+            sd[p + "stu_norm.weight"] = torch.ones(d, device=device, dtype=dt)
+            sd[p + "stu.M_inputs"] = normal(own, (d, dl), (2.0 / (2 * d)) ** 0.5)
+            sd[p + "stu.M_filters"] = normal(own, (K, dl), (2.0 / (K + d)) ** 0.5)
+        sd[p + "mlp_norm.weight"] = torch.ones(d, device=device, dtype=dt)
+        sd[p + "mlp.gate_proj.weight"] = normal(own, (inter // world, d), d ** -0.5)
+        sd[p + "mlp.up_proj.weight"] = normal(own, (inter // world, d), d ** -0.5)
+        sd[p + "mlp.down_proj.weight"] = normal(own, (d, inter // world), d ** -0.5 * (2 * config.n_layers) ** -0.5)
+    return sd
+
+
 class TensorParallelFlashSTU:
     """FlashSTU (approx STU layers, optional sliding-window attention layers) over the ranks of a process group.
     `state_dict` is the full model's; each rank cuts out its share.  Call from every rank with identical inputs."""
 
-    def __init__(self, config, state_dict: Dict[str, torch.Tensor], device, group=None):
+    def __init__(self, config, state_dict: Dict[str, torch.Tensor], device, group=None, presharded: bool = False):
+        """`state_dict`: the full model's tensors (each rank cuts out its share), or, with presharded=True, this
+        rank's share already in the shapes shard_state_dict documents (see random_shards)."""
         self.cfg = config
         self.group = group
         self.world = dist.get_world_size(group)
@@ -82,14 +123,18 @@ class TensorParallelFlashSTU:
         if not config.use_approx:
             raise NotImplementedError("tensor parallelism covers the approx STU variant")
         c = dict(n_embd=config.n_embd, n_heads=config.n_heads)
-        self.sd = {k: v.to(self.device) for k, v in shard_state_dict(state_dict, c, self.rank, self.world).items()}
+        if presharded:
+            self.sd = {k: v.to(self.device) for k, v in state_dict.items()}
+        else:
+            self.sd = {k: v.to(self.device) for k, v in shard_state_dict(state_dict, c, self.rank, self.world).items()}
         if "tok_emb.weight" not in self.sd:
             raise ValueError("state_dict lacks tok_emb.weight")
         self.d, self.H = config.n_embd, config.n_heads
         self.hd = self.d // self.H
         self.dl = self.d // self.world
         self.Hl = self.H // self.world
-        self.V = state_dict["lm_head.weight"].shape[0] if "lm_head.weight" in state_dict else state_dict["tok_emb.weight"].shape[0]
+        self.V = config.vocab_size if presharded else (
+            state_dict["lm_head.weight"].shape[0] if "lm_head.weight" in state_dict else state_dict["tok_emb.weight"].shape[0])
         if "lm_head.weight" not in self.sd:   # tied head stored once
             self.sd["lm_head.weight"] = shard_state_dict({"lm_head.weight": state_dict["tok_emb.weight"]}, c, self.rank,
                                                          self.world)["lm_head.weight"].to(self.device)
@@ -202,7 +247,7 @@ class TensorParallelFlashSTU:
     def generate(self, input_ids: torch.Tensor, max_length: int, temperature: float = 1.0,
                  top_k: Optional[int] = None, top_p: Optional[float] = None, do_sample: bool = False,
                  uniforms: Optional[torch.Tensor] = None, return_logits: bool = False, cuda_graph: bool = True,
-                 fence=None, fence_every: int = 16):
+                 fence=None, fence_every: int = 16, timings: Optional[dict] = None):
         """Cached token loop; `uniforms` [steps, B] must be the same on every rank when sampling.
         `fence` (parallel.StepFence): every `fence_every` steps the ranks meet on the host between steps; a rank that
         is gone makes the others raise parallel.RankLost instead of entering a collective that would never finish."""
@@ -241,10 +286,16 @@ class TensorParallelFlashSTU:
                                    out_stride=1)
                     for e, t in zip(cache, host_t):
                         e[-1]._host_t = t
+                if timings is not None and "_first" not in timings:
+                    timings["_first"] = torch.cuda.Event(enable_timing=True)
+                    timings["_first"].record()
+                    timings["replayed_steps"] = 0
                 tok_in.copy_(gen[:, cur - 1:cur])
                 if do_sample:
                     u_buf.copy_(u)
                 graph.replay()
+                if timings is not None:
+                    timings["replayed_steps"] += 1
                 for e in cache:
                     e[-1]._host_t += 1
                 gen[:, cur:cur + 1].copy_(tok_out)
@@ -256,4 +307,9 @@ class TensorParallelFlashSTU:
             if return_logits:
                 logs.append(logits)
             ops.sample(logits, temperature, top_k, top_p, do_sample, u, gen[:, cur:], out_stride=max_length)
+        if timings is not None and "_first" in timings:   # device time of the graph-replayed token steps
+            last = torch.cuda.Event(enable_timing=True)
+            last.record()
+            last.synchronize()
+            timings["replay_ms"] = timings.pop("_first").elapsed_time(last)
         return (gen, torch.stack(logs, 1)) if return_logits else gen

@@ -58,6 +58,10 @@ int stu_embed(const long long* ids, const void* table, void* out, int rows, int 
  *            2  y = round(gelu_tanh(round(x@W^T))) * round(x@W2^T)     swiglu.py:22-28
  *            3  scatter round(acc) into the history `y` (N channels, hist_T tokens per sequence starting at
  *               time hist_t0, hist_Lh elements per parity row): the projected input `x @ M_inputs`
+ *            5  y[m*y_row_stride + (n / hist_T)*resid_row_stride + (n % hist_T)] = acc: the output columns come in
+ *               blocks of hist_T, consecutive blocks resid_row_stride elements apart (resid itself is not read).  Used
+ *               for the distilled-LDS features h@C of mini_stu/stu_lds.py:337, written straight into the
+ *               [tokens, F*d] operand of the contraction with M (stu_lds.py:389-393)
  *   norm_w     when non-NULL, x is RMS-normalised with this weight (eps) inside the kernel; only fused for
  *              decode shapes (see stu_linear_can_fuse_norm), otherwise -4.
  *   backend    0 auto (M<=64: weight-streaming mma.sync/FMA kernel; bf16 aligned: tcgen05+TMA GEMM; else
@@ -179,6 +183,19 @@ int stu_full_decode_combine(const void* G, long long ldG, int* pos, void* U, int
  * the purpose of seeding the decode. */
 int stu_lds_final_state(const void* hist, double* h, const double* A, const double* Bv, int B, int d, int Lh, int Tn,
                         int D, int dtype, void* stream);
+
+/* Chunked-scan prefill of the distilled LDS (mini_stu/stu_lds.py:17-99 lds_scan_kernel / run_lds_scan, :181-200
+ * affine_scan_with_fixed_a, :280-338 FixedDiagonalLDS.forward): runs h = A*h + B*x[b,t,i] in float64 over the Tn
+ * positions of every (sequence, channel) of x [B,Tn,d]; at the start of every chunk of Ck positions writes the carried
+ * state, rotated into a balanced basis (z = Vs^T h, Vs [D][R] float64), and the chunk's inputs into
+ * Z [B][ceil(Tn/Ck)][d][KZ] (bf16: z_hi | z_lo | z_hi | x, KZ = 3R+Ck; fp32: z | x, KZ = R+Ck), and the final state into
+ * hfin [B*d][D] (bit-identical to stu_lds_final_state).  The features of all chunks of a sequence are then ONE
+ * stu_linear call with epilogue 5 on Z (see flash_stu_2_b200/mini_stu.py for the constant operand).  R % 8 == 0,
+ * Ck % 8 == 0, D <= 256.  dtype | 0x1000: the caller has checked that every Bv[n] is exactly 1 (faster kernel, same
+ * bits). */
+int stu_lds_chunk_scan(const void* x, long long x_bstride, long long x_tstride, const double* A, const double* Bv,
+                       const double* Vs, void* Z, double* hfin, int B, int d, int Tn, int D, int R, int Ck, int dtype,
+                       void* stream);
 
 /* One recurrent step (mini_stu/lds.py:95-101): h updated in place, U [B][F*d] = features in the row order of M. */
 int stu_lds_decode_features(const void* x, long long x_row_stride, double* h, const double* A, const double* Bv,

@@ -601,11 +601,21 @@ def test_mini_stu_lds_prefill_and_recurrent_decode(golden, dt, tol, shape):
     with torch.no_grad():
         y_all = m(x.to(dev()))
         y1, cache = m(x[:, :T1].to(dev()), use_cache=True)
+        state_scan = cache[0].clone()
         rows = [y1]
         for t in range(T1, T):
             yt, cache = m(x[:, t:t + 1].to(dev()), past_key_value=cache, use_cache=True)
             rows.append(yt)
+        # the convolution form of the same prefill (full-length impulse responses): same rows within tolerance, and
+        # its final-state kernel gives bit for bit the state the chunked scan hands to the recurrent decode
+        F.MiniSTU.chunked_scan_prefill = False
+        try:
+            y_conv, cache_conv = m(x[:, :T1].to(dev()), use_cache=True)
+        finally:
+            F.MiniSTU.chunked_scan_prefill = True
     ops.check_status()
+    assert torch.equal(cache_conv[0], state_scan)
+    close(y_conv, want[:, :T1], tol)
     close(y_all, want, tol)
     got = torch.cat(rows, 1)
     close(got, want, tol)
