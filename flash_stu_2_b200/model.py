@@ -58,6 +58,26 @@ class FlashSTU(PreTrainedModel):
         # every module (what the reference does with self.apply, flash_stu/model.py:104-105)
         self.post_init()
 
+    # ------------------------------------------------------------------ checkpoints
+    def _restore_derived_buffers(self):
+        """Non-persistent buffers are not in a checkpoint: the STU layers' view of the filters (the reference registers
+        it with persistent=False, flash_stu/modules/stu.py:36-41) and the ALiBi slopes (attention.py:34).  A loader
+        that builds the module tree on the meta device and then materialises it leaves them uninitialised, so after
+        loading they are re-derived from what the checkpoint does hold: `phi` and the configuration."""
+        for layer in self.layers:
+            if isinstance(layer, STULayer):
+                layer.stu.phi = self.phi
+                layer.stu._prep_key = None
+            else:
+                attn = layer.attn
+                attn.alibi_slopes = attn._get_alibi_slopes(attn.n_heads).to(self.phi.device)
+
+    @classmethod
+    def from_pretrained(cls, *args, **kwargs):
+        model = super().from_pretrained(*args, **kwargs)
+        model._restore_derived_buffers()
+        return model
+
     # ------------------------------------------------------------------ embeddings (resize_token_embeddings)
     def get_input_embeddings(self):
         return self.tok_emb

@@ -101,6 +101,10 @@ def test_checkpoint_round_trip_and_vocabulary_resize(tmp_path):
     r32 = F.FlashSTU.from_pretrained(ck32)
     assert r32.config.torch_dtype == torch.float32
     assert all(v.dtype == torch.float32 and torch.equal(v, m32.state_dict()[k]) for k, v in r32.state_dict().items())
+    # buffers that are not part of a checkpoint (the STU layers' filters, the ALiBi slopes) are re-derived on load
+    assert all(torch.equal(l.stu.phi, r32.phi) for l in r32.layers if hasattr(l, "stu"))
+    assert all(torch.equal(a.attn.alibi_slopes, b.attn.alibi_slopes)
+               for a, b in zip(m2.layers, m.layers) if hasattr(a, "attn"))
     sd1, sd2 = m.state_dict(), m2.state_dict()
     assert set(sd1) == set(sd2) and all(torch.equal(sd1[k], sd2[k]) for k in sd1)
     assert m2.lm_head.weight.data_ptr() == m2.tok_emb.weight.data_ptr()
