@@ -45,6 +45,9 @@ _SIGNATURES = {
                                  c_int, _P], c_int),
     "stu_decode_approx_pipelined": ([_P, _LL, _P, _P, _P, _P, _P, _P, _LL, c_int, c_int, c_int, c_int, c_float, c_int,
                                      _P, c_int, _P], c_int),
+    "stu_block_step_workspace_bytes": ([c_int, c_int], c_longlong),
+    "stu_block_decode_step": ([_P, _LL, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _LL, c_int, c_int, c_int, c_int, c_float,
+                               c_float, _P, _LL, c_int, _P, c_int, _P], c_int),
     "stu_to_history": ([_P, _LL, _LL, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P], c_int),
     "stu_toeplitz": ([_P, _LL, c_int, _P, c_int, _LL, c_int, _P], c_int),
     "stu_full_combine": ([_P, _P, _LL, _P, _LL, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P], c_int),

@@ -25,8 +25,44 @@ class STULayer(nn.Module):
         self.mlp = MLP(config, dtype=config.torch_dtype)
         self._scratch = {}
 
+    def _fused_decode(self, x2, entry):
+        """The whole token step as one persistent kernel (bf16, B <= 8, one common position).  The kernel leaves the
+        history partial sums of the NEXT position in a workspace kept with the cache's position tensor; when the
+        workspace holds none for the current position (first step after a prefill, a rewound or reordered cache) a
+        mode-1 launch computes them first."""
+        from .modules import host_pos
+        hist, pos = entry
+        stu = self.stu
+        MinT, taps, taps8 = stu.prepared()
+        B, d = x2.shape
+        t = host_pos(pos)
+        if t + 1 > stu.capacity:
+            raise ValueError(f"sequence position {t + 1} exceeds the capacity {stu.capacity} (seq_len={stu.seq_len})")
+        ahead = getattr(pos, "_ahead", None)
+        if ahead is None or ahead[0].device != x2.device:
+            ahead = [ops.block_step_workspace(d, self.mlp.intermediate_size, x2.device), 0 if t == 0 else -1]
+            pos._ahead = ahead
+        ws = ahead[0]
+        args = (x2, self.stu_norm.weight, MinT, hist, taps8, pos, self.mlp_norm.weight, self.mlp.gate_proj.weight,
+                self.mlp.up_proj.weight, self.mlp.down_proj.weight, x2, ws)
+        if ahead[1] != t:
+            ops.block_decode_step(*args, mode=1, eps_stu=self.stu_norm.eps, eps_mlp=self.mlp_norm.eps)
+        ops.block_decode_step(*args, mode=0, eps_stu=self.stu_norm.eps, eps_mlp=self.mlp_norm.eps)
+        ahead[1] = t + 1
+        pos._host_t = t + 1
+        return hist, pos
+
+    def _can_fuse(self, x, entry):
+        from .modules import uniform_pos
+        B, _, d = x.shape
+        return (ops.fused_step and self.stu.use_approx and x.dtype == torch.bfloat16 and B <= 8 and d % 8 == 0
+                and self.mlp.intermediate_size % 8 == 0 and STU.pipelined_decode and STU.tensor_core_decode
+                and STU.shared_tap_decode and uniform_pos(entry[1]))
+
     def _decode(self, x, entry):
         B, _, d = x.shape
+        if self._can_fuse(x, entry):
+            return self._fused_decode(x.view(B, d), entry)
         key = (B, x.device, x.dtype)
         if key not in self._scratch:
             self._scratch = {key: torch.empty(B, d, dtype=x.dtype, device=x.device)}

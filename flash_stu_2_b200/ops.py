@@ -27,6 +27,9 @@ overlap_decode = True
 # projection of the previous layer, which then triggers early): its history stream needs nothing that kernel writes,
 # only its projection waits.
 early_decode = True
+# fused_step: a cached token step of an approx STU layer with at most 8 sequences at one position runs as ONE
+# persistent kernel (STU sub-layer and MLP) that already streams the next position's history partial sums.
+fused_step = True
 BACKEND_AUTO, BACKEND_SIMT, BACKEND_TCGEN05, BACKEND_SKINNY = 0, 1, 2, 3
 RMS_EPS = float(torch.finfo(torch.float32).eps)  # what torch.nn.RMSNorm(eps=None) resolves to
 
@@ -76,7 +79,8 @@ STATUS_TEXT = {1: "token id outside the vocabulary", 2: "position outside the ca
                3: "a bounded mbarrier wait ran out inside the tcgen05 GEMM", 4: "more top-k ties than the candidate list holds",
                5: "top_p without top_k is not implemented on the device",
                6: "decode step told that all sequences share one position, but the cached positions differ",
-               7: "a bounded pipeline wait ran out inside the decode kernel"}
+               7: "a bounded pipeline wait ran out inside the decode kernel",
+               8: "the fused token-step kernel found no partial sums for the current position in its workspace"}
 
 
 def check_status(device=None):
@@ -262,6 +266,33 @@ def decode_approx_pipelined(x, norm_w, MinT, hist, taps8, pos, out, eps: float =
                                                  out.stride(0), B, d_in, dch, Lh, eps, int(add_residual),
                                                  status_word(x.device).data_ptr(), _dt(x) | flags, _stream())
     _lib.check(rc, "stu_decode_approx_pipelined")
+    _count()
+    return out
+
+
+def block_step_workspace(d: int, I: int, device) -> torch.Tensor:
+    """Zeroed workspace of block_decode_step for one layer's cache (partial sums carried from one token step to the
+    next, grid-barrier words, the step's intermediate rows)."""
+    n = int(_lib.load().stu_block_step_workspace_bytes(d, I))
+    return torch.zeros((n + 255) // 256 * 256, dtype=torch.uint8, device=device)
+
+
+def block_decode_step(x, stu_norm_w, MinT, hist, taps8, pos, mlp_norm_w, Wg, Wu, Wd, out, workspace, mode: int,
+                      eps_stu: float = RMS_EPS, eps_mlp: float = RMS_EPS):
+    """One cached token step of a whole approx STU layer (STU sub-layer + MLP, both residuals) in one persistent
+    kernel; mode 1 only prepares the partial sums of the current position (first step after a prefill)."""
+    _cuda(x, stu_norm_w, MinT, hist, taps8, pos, mlp_norm_w, Wg, Wu, Wd, out, workspace)
+    B, d, _, Lh = hist.shape
+    I = Wg.shape[0]
+    assert x.shape == (B, d) and out.shape == (B, d) and x.stride(1) == 1 and out.stride(1) == 1
+    assert MinT.shape == (d, d) and Wg.shape == (I, d) and Wu.shape == (I, d) and Wd.shape == (d, I)
+    assert all(w.is_contiguous() for w in (MinT, Wg, Wu, Wd, hist, taps8, pos)) and pos.dtype == torch.int32
+    rc = _lib.load().stu_block_decode_step(x.data_ptr(), x.stride(0), stu_norm_w.data_ptr(), MinT.data_ptr(),
+                                           hist.data_ptr(), taps8.data_ptr(), pos.data_ptr(), mlp_norm_w.data_ptr(),
+                                           Wg.data_ptr(), Wu.data_ptr(), Wd.data_ptr(), out.data_ptr(), out.stride(0),
+                                           B, d, I, Lh, eps_stu, eps_mlp, workspace.data_ptr(), workspace.numel(), mode,
+                                           status_word(x.device).data_ptr(), _dt(x), _stream())
+    _lib.check(rc, "stu_block_decode_step")
     _count()
     return out
 

@@ -147,6 +147,23 @@ int stu_decode_approx_pipelined(const void* x, long long x_row_stride, const voi
                                 int d_in, int d_ch, int Lh, float eps, int add_residual, int* status, int dtype,
                                 void* stream);
 
+/* One cached token step of a whole approx STU layer -- x += STU(norm(x)); x += MLP(norm(x)), the decode form of
+ * flash_stu/layers/stu_layer.py:78-97 with flash_stu/modules/stu.py:85-98,120 and flash_stu/modules/swiglu.py:22-29 --
+ * as ONE persistent cooperative kernel for up to 8 sequences at one common position (bf16).  The kernel pipelines
+ * across launches: while its projection / MLP warps finish position t, its streaming warps already compute the
+ * history partial sums of position t+1 (they need nothing step t produces) and leave them in `workspace` for the next
+ * launch.  mode 0: the token step (needs the partial sums of the current position in the workspace: status 8
+ * otherwise; advances pos).  mode 1: only compute the partial sums of the current position (first step after a
+ * prefill).  workspace: stu_block_step_workspace_bytes(d, I) bytes, 256-byte aligned, zeroed once by the caller (an
+ * all-zero workspace is the correct state for position 0), private to one layer's cache.  out may alias x.
+ * MinT [d][d] rows = output channels; Wg, Wu [I][d]; Wd [d][I].  d, I, Lh multiples of 8, B <= 8. */
+long long stu_block_step_workspace_bytes(int d, int I);
+int stu_block_decode_step(const void* x, long long x_row_stride, const void* stu_norm_w, const void* MinT, void* hist,
+                          const void* taps8, int* pos, const void* mlp_norm_w, const void* Wg, const void* Wu,
+                          const void* Wd, void* out, long long out_row_stride, int B, int d, int I, int Lh,
+                          float eps_stu, float eps_mlp, void* workspace, long long workspace_bytes, int mode,
+                          int* status, int dtype, void* stream);
+
 /* ---- full STU variant (flash_stu/modules/stu.py:100-118, mini_stu/stu.py:240-269): U+-[b,t,k,i] =
  * sum_j (+-1)^j phi[j,k] x[b,t-j,i] contracted with M_phi_plus / M_phi_minus.  The filters are shared by all
  * channels, so per filter the convolution is three GEMMs (stu_linear with epilogue | 0x100 = lower-triangular
