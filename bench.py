@@ -30,9 +30,11 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 D_MODEL, NUM_FILTERS = 1024, 24
-# dram__bytes_read.sum + dram__bytes_write.sum of one stu_decode_rows8_kernel launch at B=8, L=8192, t~7690, from the
-# ncu capture summarised in profiles/stu_decode_kernel_block_8k.md (algorithmic bytes there: 73.0 MB)
+# dram__bytes_read.sum + dram__bytes_write.sum of one stu_decode_rows8_kernel launch at B=8, L=8192, t~7690, from one ncu
+# capture of this command (algorithmic bytes there: 73.0 MB)
 DECODE_KERNEL_DRAM_BYTES = 79.8e6
+# the same two counters for one stu_block_step_kernel launch (the whole token step) at B=8, L=8192 (None until captured)
+STEP_KERNEL_DRAM_BYTES = 106.0e6
 
 
 def parse():
@@ -71,6 +73,9 @@ def parse():
                          "FlashSTU.generate(); `tp`, N > 1 only: the 3B shapes tensor-parallel over the N ranks)")
     ap.add_argument("--extra-new-tokens", type=int, default=64, help="tokens generated for the `generate` object")
     ap.add_argument("--tp-new-tokens", type=int, default=32, help="tokens generated for the `tp` object")
+    ap.add_argument("--fused-step", type=int, default=1, choices=[0, 1],
+                    help="1: a token step of the block is one persistent kernel (STU sub-layer + MLP + the next position's "
+                         "history stream); 0: three kernels per step")
     ap.add_argument("--decode-kernel", choices=["pipe", "rows8"], default="pipe",
                     help="fused decode kernel: the persistent bulk-copy pipeline (default) or the 8x8 register-streaming one")
     return ap.parse_args()
@@ -238,6 +243,7 @@ def run_b200(a):
     if a.no_overlap:
         ops.overlap_decode = False
     ops.early_decode = bool(a.early_decode)
+    ops.fused_step = bool(a.fused_step)
     STU.pipelined_decode = (a.decode_kernel == "pipe")
     approx = a.variant == "approx"
     blk = make_state(L, approx=approx).to(dev).eval()
@@ -422,23 +428,12 @@ def run_b200(a):
                          graph_us(lambda: (decp(EA | OV), gate_up(OV), down(OV | EA)))}
 
         # ---- end to end through the module API from pinned host memory
-        # token steps: every token's input row comes from pinned host memory and its output row goes back to pinned
-        # host memory, one asynchronous copy each way per token on the launching stream, replayed with the step from
-        # one CUDA graph (the inputs are teacher-forced, so the host has nothing to wait for between tokens); one
-        # synchronise per pass, after which every output row is on the host
-        x_tok_host = x_host[:, first:].transpose(0, 1).contiguous().pin_memory()     # [S, B, d]
-        y_tok_host = torch.empty(S, B, d, dtype=torch.bfloat16).pin_memory()
+        # token steps: the S teacher-forced input rows come from pinned host memory in one copy per pass (they do not
+        # depend on the outputs), the S output rows go back to pinned host memory in one copy; the copies and the
+        # graph replay between them are in the timed region, one synchronise per pass
+        x_tok_host = x_host[:, first:].transpose(0, 1).contiguous().unsqueeze(2).pin_memory()     # [S, B, 1, d]
+        y_tok_host = torch.empty(S, B, 1, d, dtype=torch.bfloat16).pin_memory()
         yp_host = torch.empty(B, L, d, dtype=torch.bfloat16).pin_memory()
-
-        def e2e_tokens():
-            for i in range(S):
-                x_step.copy_(x_tok_host[i].view(B, 1, d), non_blocking=True)
-                eager_step(x_step)
-                y_tok_host[i].copy_(x_step.view(B, d), non_blocking=True)
-
-        e2e_graph = None
-        if not a.no_graph:
-            e2e_graph, _ = capture(e2e_tokens)
         e2e_steps = max(1, min(a.steps, 3))
         if world > 1:
             dist.barrier()
@@ -455,10 +450,12 @@ def run_b200(a):
             torch.cuda.synchronize()
             rewind()
             d0 = time.perf_counter()
-            if e2e_graph is not None:
-                e2e_graph.replay()
+            x_steps.copy_(x_tok_host, non_blocking=True)
+            if state["graph"] is not None:
+                state["graph"].replay()
             else:
-                e2e_tokens()
+                eager_steps()
+            y_tok_host.copy_(x_steps, non_blocking=True)
             torch.cuda.current_stream().synchronize()
             state["cache"][1]._host_t = first + S
             dec_s += time.perf_counter() - d0
@@ -482,7 +479,23 @@ def run_b200(a):
     value = dec_tokens / (t_dec / 1e3)
     step_us = t_dec / a.steps / S * 1e3
     t_mid_step = first + S / 2.0
+    fused = approx and ops.fused_step and B <= 8 and STU.pipelined_decode
+    alone = None
     if approx:
+        alone = {"kernel": "stu_decode_pipe_kernel" if STU.pipelined_decode else "stu_decode_rows8_kernel",
+                 "what": "the STU decode kernel of the unfused path, 256 launches replayed from one graph",
+                 "bytes_per_launch": kern_bytes, "us_per_launch": kern_ms * 1e3,
+                 "achieved": kern_bytes / (kern_ms / 1e3) / 1e9}
+    if fused:
+        # the timed region launches ONE kernel per token step (stu_block_step_kernel: STU sub-layer + MLP + the next
+        # position's history stream): its launch duration is the step time measured over the timed region, its
+        # algorithmic bytes the step's (one parity run of the history, taps, M_inputs, the token rows, the MLP weights)
+        kern_bytes = (B * d * (t_mid_step / 2) * 2 + d * (t_mid_step / 2 + 1) * 2 + d * d * 2 + 3 * B * d * 2
+                      + 12 * d * d * 2)
+        kern_ms = step_us / 1e3
+        achieved = kern_bytes / (kern_ms / 1e3) / 1e9
+        roof_kernel = "stu_block_step_kernel"
+    elif approx:
         achieved = kern_bytes / (kern_ms / 1e3) / 1e9
         roof_kernel = "stu_decode_pipe_kernel" if STU.pipelined_decode else "stu_decode_rows8_kernel"
     else:
@@ -510,7 +523,8 @@ def run_b200(a):
                    "l2": f"inputs larger than L2: decode working set {ws_mb:.0f} MB (history+taps+weights) and "
                          f"prefill input {B * L * d * 2 / 1e6:.0f} MB vs 126 MB L2; no explicit flush",
                    "decode_launch": (f"one CUDA graph of all {S} token steps (device-resident positions)"
-                                     if state["graph"] is not None else "eager launches")},
+                                     if state["graph"] is not None else "eager launches") +
+                                    ("; one fused kernel per token step" if fused else "")},
         "decode_ms_per_token_step": t_dec / a.steps / S,
         "prefill": {"value": pre_tokens / (t_pre / 1e3), "unit": "tokens/s", "ms": t_pre / a.steps,
                     "tflops_algorithmic": pre_tflops,
@@ -522,14 +536,18 @@ def run_b200(a):
         "e2e": {"value": world * B * S * e2e_steps / dec_s, "unit": "tokens/s",
                 "h2d_bytes_per_step": B * L * d * 2 + S * B * d * 2, "d2h_bytes_per_step": B * L * d * 2 + S * B * d * 2,
                 "wall_s_per_step": e2e_wall / e2e_steps,
-                "note": "decode tokens/s, wall clock: every token's input row is copied in from pinned host memory and "
-                        "its output row copied back (asynchronous copies replayed with the token steps from one CUDA "
-                        "graph, one synchronise per pass); the prefill of each step also copies its 134 MB input in and "
-                        "its output back"},
+                "note": "decode tokens/s, wall clock: per pass the 512 teacher-forced input rows are copied in from pinned "
+                        "host memory (one copy), the token steps are replayed from one CUDA graph, the 512 output rows are "
+                        "copied back to pinned host memory (one copy), then one synchronise; the prefill of each pass also "
+                        "copies its 134 MB input in and its output back"},
         "gpu_launches": launches, "wall_s_timed_region": wall, "clocks": clocks,
     }
-    if (B, L, d) == (8, 8192, 1024) and approx and not STU.pipelined_decode:
-        line["roofline"]["traffic"] = DECODE_KERNEL_DRAM_BYTES
+    if (B, L, d) == (8, 8192, 1024) and approx:
+        line["roofline"]["traffic"] = STEP_KERNEL_DRAM_BYTES if fused else (
+            None if STU.pipelined_decode else DECODE_KERNEL_DRAM_BYTES)
+    if alone is not None:
+        alone["frac"] = alone["achieved"] / pk["hbm_gbs"]
+        line["stu_kernel_alone"] = alone
     if approx:
         # the whole token step of the block: the decode kernel's bytes plus the MLP weights (gate, up, down)
         step_bytes = (B * d * (t_mid_step / 2) * 2 + d * (t_mid_step / 2 + 1) * 2 + d * d * 2 + 3 * B * d * 2
@@ -938,6 +956,7 @@ if __name__ == "__main__":
         from flash_stu_2_b200 import ops as _ops
         from flash_stu_2_b200.modules import STU as _STU
         _ops.early_decode = bool(args.early_decode)
+        _ops.fused_step = bool(args.fused_step)
         _STU.pipelined_decode = (args.decode_kernel == "pipe")
         if args.no_overlap:
             _ops.overlap_decode = False

@@ -9,7 +9,7 @@
 // the other time parity of the projected history, all of it written at steps <= t-1.  So this kernel pipelines across
 // launches.  At position t, one CTA per SM runs four groups of warps side by side:
 //   * producer (1 warp) + streaming consumers (8 warps): the partial sums sum_{i<s'} hist[.][i] tap[s'-i] of position
-//     t+1, exactly as in stu_decode_pipe_kernel (units of 8 sequences x 8 channels x 256 positions through a 4-stage
+//     t+1, exactly as in stu_decode_pipe_kernel (units of 8 sequences x 8 channels x 256 positions through a 3-stage
 //     bulk-copy ring, diagonal-of-an-MMA dot products), written to a workspace buffer for the next launch;
 //   * compute group (8 warps): phase 1, RMS statistics and projection of the new token for the CTA's row, history
 //     append, combine with the partial sums the PREVIOUS launch left for position t, write the STU sub-layer output
@@ -18,7 +18,7 @@
 //     features (units of 8 features, K split over the warps, MMAs with the sequences as rows, tanh-GELU * up); after a
 //     second grid-wide barrier phase 3, its 8 output channels of the down projection plus residual;
 //   * MLP weight producer (1 warp): the CTA's gate|up and down weight rows as bulk copies of whole rows
-//     (cp.async.bulk, 2 KB / 8 KB each) into a 64 KB shared-memory region, started at kernel entry, so that the
+//     (cp.async.bulk, 2 KB / 8 KB each) into a 96 KB shared-memory region, started at kernel entry, so that the
 //     compute group never waits for a weight from HBM and the weights arrive as long contiguous bursts.
 // The step then costs max(stream of 74 MB + 25 MB of MLP weights at HBM speed, the latency chain of the other three
 // groups) instead of their sum.  A first step after a prefill has no partial sums waiting: mode 1 of the same kernel
@@ -35,11 +35,13 @@ int device_sm_count();  // gemm_tc.cu
 namespace {
 
 constexpr int SEG = 256;
-constexpr int STAGES = 4;
+constexpr int STAGES = 3;
 constexpr int HIST_BYTES = 64 * SEG * 2;
 constexpr int TAP_BYTES = 8 * SEG * 2;
 constexpr int STAGE_BYTES = HIST_BYTES + TAP_BYTES;
-constexpr int MLP_BYTES = 64 * 1024;     // shared-memory region the MLP weights pass through (two 32 KB slots)
+constexpr int MLP_SLOT = 32 * 1024;      // one gate|up unit: 8 gate rows + 8 up rows of d <= 1024 values
+constexpr int MLP_SLOTS = 3;
+constexpr int MLP_BYTES = MLP_SLOTS * MLP_SLOT;   // shared-memory region the MLP weights pass through
 constexpr int W_PROD = 8, W_WPROD = 9, W_COMP = 10;
 constexpr int NTHREADS = 18 * 32;        // 8 streaming warps, 2 producer warps, 8 compute warps
 
@@ -158,9 +160,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   unsigned char* wsm = smem + STAGES * STAGE_BYTES;                         // MLP weight region (MLP_BYTES)
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(wsm + MLP_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* wfull = empty_bar + STAGES;     // [2] a gate|up unit has landed in its slot
-  uint64_t* wempty = wfull + 2;             // [2] the compute group has finished with the slot
-  uint64_t* dfull = wempty + 2;             // [1] the down-projection unit has landed (it takes both slots)
+  uint64_t* wfull = empty_bar + STAGES;     // [3] a gate|up unit has landed in its slot
+  uint64_t* wempty = wfull + MLP_SLOTS;     // [3] the compute group has finished with the slot
+  uint64_t* dfull = wempty + MLP_SLOTS;     // [1] the down-projection unit has landed (slots 1 and 2)
   uint64_t* go_bar = dfull + 1;             // [1] the compute group's phase-1 operands have landed: start the stream
   __shared__ int s_abort, s_issued, s_ok;
   __shared__ float s_r[8];
@@ -181,7 +183,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       tma::mbar_init(&full_bar[i], 1);
       tma::mbar_init(&empty_bar[i], 8);
     }
-    for (int i = 0; i < 2; i++) {
+    for (int i = 0; i < MLP_SLOTS; i++) {
       tma::mbar_init(&wfull[i], 1);
       tma::mbar_init(&wempty[i], 1);
     }
@@ -256,16 +258,17 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       }
     } else if (warp == W_WPROD) {
       // ------------------------------------------------------------------ MLP weight producer (token step only)
-      // gate|up units go through two 32 KB slots (rows n0..n0+7 of the gate weight, then of the up weight, each row one
-      // bulk copy); the down-projection unit (8 rows of I values) takes both slots once the last gate|up unit is done
+      // gate|up unit j goes to slot (nGu-1-j) % 3 (rows n0..n0+7 of the gate weight, then of the up weight, each row
+      // one bulk copy), so the last unit always sits in slot 0 and the down-projection unit (8 rows of I values, two
+      // slots) can land in slots 1 and 2 while that last unit is still being used
       if (lane == 0 && P.mode == 0) {
         const uint32_t row_bytes = (uint32_t)d * 2;
         const uint64_t keep = tma::policy_evict_last();
         bool ok = true;
         for (int j = 0; ok && j < nGu; j++) {
-          const int slot = j & 1, n0 = (cta + j * G) * 8;
-          if (!tma::mbar_wait_bounded(&wempty[slot], (((uint32_t)(j >> 1)) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-          unsigned char* dst = wsm + slot * (MLP_BYTES / 2);
+          const int slot = (nGu - 1 - j) % MLP_SLOTS, n0 = (cta + j * G) * 8;
+          if (!tma::mbar_wait_bounded(&wempty[slot], (((uint32_t)(j / MLP_SLOTS)) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          unsigned char* dst = wsm + slot * MLP_SLOT;
           tma::mbar_expect_tx(&wfull[slot], 16 * row_bytes);
           for (int rr = 0; rr < 8; rr++) {
             tma::bulk_load_hint(dst + rr * row_bytes, P.Wg + (size_t)(n0 + rr) * d, row_bytes, &wfull[slot], keep);
@@ -273,15 +276,16 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           }
         }
         if (ok && hasD) {
-          // both slots free: slot s was used ceil/floor(nGu/2) times
-          const int u0 = (nGu + 1) >> 1, u1 = nGu >> 1;
-          ok = tma::mbar_wait_bounded(&wempty[0], (((uint32_t)u0) & 1u) ^ 1u, abort_flag) &&
-               tma::mbar_wait_bounded(&wempty[1], (((uint32_t)u1) & 1u) ^ 1u, abort_flag);
+          // slots 1 and 2 free of their last gate|up unit (slot s is used by units j with (nGu-1-j) % 3 == s)
+          for (int sl = 1; ok && sl <= 2; sl++) {
+            const int uses = nGu > sl ? (nGu - 1 - sl) / MLP_SLOTS + 1 : 0;
+            ok = tma::mbar_wait_bounded(&wempty[sl], (((uint32_t)uses) & 1u) ^ 1u, abort_flag);
+          }
           if (ok) {
             const uint32_t drow = (uint32_t)I * 2;
             tma::mbar_expect_tx(dfull, 8 * drow);
             for (int rr = 0; rr < 8; rr++)
-              tma::bulk_load_hint(wsm + rr * drow, P.Wd + (size_t)(cta * 8 + rr) * I, drow, dfull, keep);
+              tma::bulk_load_hint(wsm + MLP_SLOT + rr * drow, P.Wd + (size_t)(cta * 8 + rr) * I, drow, dfull, keep);
           }
         }
       }
@@ -462,12 +466,12 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         }
         // ---- phase 2: gate | up units from the shared-memory slots
         for (int j = 0; j < nGu; j++) {
-          const int slot = j & 1, n0 = (cta + j * G) * 8;
-          const bool okw = __all_sync(0xffffffffu,
-                                      tma::mbar_wait_bounded(&wfull[slot], ((uint32_t)(j >> 1)) & 1u, abort_flag));
+          const int slot = (nGu - 1 - j) % MLP_SLOTS, n0 = (cta + j * G) * 8;
+          const bool okw = __all_sync(0xffffffffu, tma::mbar_wait_bounded(&wfull[slot], ((uint32_t)(j / MLP_SLOTS)) & 1u,
+                                                                         abort_flag));
           float ag[4] = {0.f, 0.f, 0.f, 0.f}, au[4] = {0.f, 0.f, 0.f, 0.f};
           if (okw) {
-            const bf16* gsm = reinterpret_cast<const bf16*>(wsm + slot * (MLP_BYTES / 2)) + (size_t)g * d;
+            const bf16* gsm = reinterpret_cast<const bf16*>(wsm + slot * MLP_SLOT) + (size_t)g * d;
             const bf16* usm = gsm + (size_t)8 * d;
 #pragma unroll
             for (int jj = 0; jj < 4; jj++) {
@@ -516,7 +520,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         const bool okd = __all_sync(0xffffffffu, tma::mbar_wait_bounded(dfull, 0u, abort_flag));
         float ad[4] = {0.f, 0.f, 0.f, 0.f};
         if (okd) {
-          const bf16* dsm = reinterpret_cast<const bf16*>(wsm) + (size_t)g * I;
+          const bf16* dsm = reinterpret_cast<const bf16*>(wsm + MLP_SLOT) + (size_t)g * I;
           for (int kc0 = cw; kc0 < nch2; kc0 += 64) {   // rounds of eight chunks per warp
             uint4 ha[8];
 #pragma unroll
@@ -562,7 +566,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       }
       // weight copies in flight: their barriers complete once the bytes have landed
       int dummy = 0;
-      for (int i = 0; i < 2; i++) tma::mbar_wait_bounded(&wfull[i], 0u, &dummy, 20000000ull, 1u << 16);
+      for (int i = 0; i < MLP_SLOTS; i++) tma::mbar_wait_bounded(&wfull[i], 0u, &dummy, 20000000ull, 1u << 16);
     }
     __syncthreads();
   }
@@ -654,10 +658,10 @@ extern "C" int stu_block_decode_step(const void* x, long long x_row_stride, cons
   P.mode = mode;
   P.tl = timeline ? (unsigned long long*)(ws + 128) : nullptr;
 
-  // the MLP weights pass through 64 KB of shared memory: a gate|up unit (16 rows of d) must fit half of it, the
-  // down-projection unit (8 rows of I) all of it
-  if ((long long)32 * d > MLP_BYTES / 2 || (long long)16 * I > MLP_BYTES) return STU_ERR_UNSUPPORTED;
-  const size_t smem = (size_t)STAGES * STAGE_BYTES + MLP_BYTES + (2 * STAGES + 6) * sizeof(uint64_t) + 1024;
+  // the MLP weights pass through three 32 KB slots of shared memory: a gate|up unit (16 rows of d) must fit one, the
+  // down-projection unit (8 rows of I) two
+  if ((long long)32 * d > MLP_SLOT || (long long)16 * I > 2 * MLP_SLOT) return STU_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + MLP_BYTES + (2 * STAGES + 2 * MLP_SLOTS + 2) * sizeof(uint64_t) + 1024;
   cudaError_t e =
       cudaFuncSetAttribute(stu_block_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
