@@ -73,6 +73,11 @@ def parse():
                          "FlashSTU.generate(); `tp`, N > 1 only: the 3B shapes tensor-parallel over the N ranks)")
     ap.add_argument("--extra-new-tokens", type=int, default=64, help="tokens generated for the `generate` object")
     ap.add_argument("--tp-new-tokens", type=int, default=32, help="tokens generated for the `tp` object")
+    ap.add_argument("--step-timeline", action="store_true",
+                    help="adds `step_timeline`: %%globaltimer stamps of CTA 0 inside three launches of the fused token-step "
+                         "kernel (us after kernel entry)")
+    ap.add_argument("--lds-layers", type=int, default=12, help="with --model c4: number of stacked layers")
+    ap.add_argument("--lds-batch", type=int, default=16, help="with --model c4: sequences")
     ap.add_argument("--fused-step", type=int, default=1, choices=[0, 1],
                     help="1: a token step of the block is one persistent kernel (STU sub-layer + MLP + the next position's "
                          "history stream); 0: three kernels per step")
@@ -378,6 +383,26 @@ def run_b200(a):
             # the even taps of every channel, M_inputs, and the token's row in and out
             kern_bytes = B * d * (t_mid / 2) * 2 + d * (t_mid / 2 + 1) * 2 + d * d * 2 + 3 * B * d * 2
 
+        # ---- optional: timeline of the fused token-step kernel (stamps of CTA 0, written to its workspace)
+        timeline = None
+        if a.step_timeline and approx and B <= 8:
+            ws = ops.block_step_workspace(d, layer.mlp.intermediate_size, dev)
+            xs = x_step.view(B, d)
+            mlp = layer.mlp
+            targs = (xs, layer.stu_norm.weight, MinT, hist, taps8, pos, layer.mlp_norm.weight, mlp.gate_proj.weight,
+                     mlp.up_proj.weight, mlp.down_proj.weight, xs, ws)
+            rewind()
+            ops.block_decode_step(*targs, mode=1)
+            names = ["kernel entry", "positions read", "projection + combine done", "past grid barrier 1", "gate|up done",
+                     "past grid barrier 2", "down + residual done", "history stream done"]
+            timeline = []
+            for _ in range(3):
+                ops.block_decode_step(*targs, mode=0 | 0x10)
+                torch.cuda.synchronize()
+                tl = ws[128:128 + 8 * 8].view(torch.int64).cpu().tolist()
+                timeline.append({n: (v - tl[0]) / 1e3 for n, v in zip(names, tl)})
+            rewind()
+
         # ---- optional: every kernel of the token step in a graph of its own (64 launches each)
         split = None
         if a.kernel_split and not a.no_graph and approx:
@@ -558,6 +583,8 @@ def run_b200(a):
                                  "frac": step_bytes / (step_us * 1e-6) / 1e9 / pk["hbm_gbs"]}
     if split is not None:
         line["decode_split"] = split
+    if timeline is not None:
+        line["step_timeline"] = {"unit": "us after kernel entry, CTA 0, three consecutive launches", "launches": timeline}
     if extra.get("generate") is not None:
         line["generate"] = extra["generate"]
     if extra.get("tp") is not None:
@@ -755,7 +782,7 @@ def run_lds_stack(a):
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py --model needs a CUDA device: the kernels have no CPU fallback")
     dev = torch.device("cuda:0")
-    B, L, d, n_layers = 16, 16384, 1024, 12
+    B, L, d, n_layers = a.lds_batch, 16384, 1024, a.lds_layers
     new = a.new_tokens or 1024
     T0 = L - 1024
     torch.manual_seed(0)
@@ -799,6 +826,39 @@ def run_lds_stack(a):
         torch.cuda.synchronize()
         dec_ms = e0.elapsed_time(e1)
     ops.check_status()
+    split = None
+    if a.kernel_split:   # the three pieces of one layer's prefill, each alone (CUDA events, 3 repetitions)
+        m = layers[0]
+        op = m._lds_prepared()
+        A64, B64, Cm = m._lds_f32
+        Vs, W, R = m._lds_scan
+        Ck = m.LDS_CHUNK
+        nch = (T0 + Ck - 1) // Ck
+        xin = x[:, :T0].contiguous()
+        with torch.no_grad():
+            Z = torch.empty(B, nch, d, W.shape[1], dtype=x.dtype, device=dev)
+            hfin = torch.empty(B, d, Cm.shape[0], dtype=torch.float64, device=dev)
+            U2 = torch.empty(nch * Ck, Cm.shape[1] * d, dtype=x.dtype, device=dev)
+            yb = torch.empty(T0, d, dtype=x.dtype, device=dev)
+            _, Mcat = op.prepared_full()
+
+            def t3(fn):
+                fn()
+                torch.cuda.synchronize()
+                e0, e1 = ev(), ev()
+                e0.record()
+                for _ in range(3):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+                return e0.elapsed_time(e1) / 3
+
+            split = {"unit": "ms per layer", "batch": B, "positions": T0,
+                     "lds_chunk_scan_kernel (all sequences)": t3(lambda: ops.lds_chunk_scan(xin, A64, B64, Vs, Z, hfin, Ck,
+                                                                                          unit_b=m._lds_unit_b)),
+                     "features GEMM, per sequence": t3(lambda: ops.lds_chunk_features(W, Z[0].view(nch * d, W.shape[1]), U2,
+                                                                                      d, Ck, Cm.shape[1])),
+                     "contraction with M, per sequence": t3(lambda: ops.linear(U2[:T0], Mcat, out=yb))}
     D_, F_ = 160, 48
     pre_flops = B * T0 * n_layers * (2 * F_ * d * d + 2 * D_ * F_ * d + 2 * D_ * d)
     step_bytes = n_layers * (F_ * d * d * 2 + B * d * D_ * 16 + D_ * F_ * 2)
@@ -806,7 +866,7 @@ def run_lds_stack(a):
     print(json.dumps({
         "metric": "decode tokens/s (aggregate over GPUs)", "value": B * new / (dec_ms * 1e-3), "unit": "tokens/s",
         "n_gpus": 1, "higher_is_better": True, "dtype": "bf16 (LDS state float64)", "data": "synthetic",
-        "config": {"workload": f"12 x MiniSTU(backend='lds', 1024->1024) L={L} B={B}: prefill {T0} + {new} recurrent steps",
+        "config": {"workload": f"{n_layers} x MiniSTU(backend='lds', 1024->1024) L={L} B={B}: prefill {T0} + {new} recurrent steps",
                    "decode_launch": "one CUDA graph per token step"},
         "decode_ms_per_token_step": dec_ms / new,
         "roofline": {"bound": "hbm", "kernel": "whole token step", "achieved": step_bytes / (dec_ms / new * 1e-3) / 1e9,
@@ -819,6 +879,7 @@ def run_lds_stack(a):
                     "note": "chunked scan: float64 recurrence + rotated carry per chunk of 128 positions (one kernel), one "
                             "tensor-core GEMM per sequence for the features of all chunks, one for the contraction with M; "
                             "FLOPs counted per token and layer as 2*48*d^2 + 2*160*48*d + 2*160*d (recurrent form)"},
+        **({"prefill_split": split} if split is not None else {}),
     }))
 
 
