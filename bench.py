@@ -73,6 +73,9 @@ def parse():
                          "FlashSTU.generate(); `tp`, N > 1 only: the 3B shapes tensor-parallel over the N ranks)")
     ap.add_argument("--extra-new-tokens", type=int, default=64, help="tokens generated for the `generate` object")
     ap.add_argument("--tp-new-tokens", type=int, default=32, help="tokens generated for the `tp` object")
+    ap.add_argument("--conv-timeline", action="store_true",
+                    help="adds `conv_timeline`: %%globaltimer stamps of CTA 0 inside one launch of the tcgen05 prefill "
+                         "convolution (first 8 units and phases, microseconds after the first stage became free)")
     ap.add_argument("--step-timeline", action="store_true",
                     help="adds `step_timeline`: %%globaltimer stamps of CTA 0 inside three launches of the fused token-step "
                          "kernel (us after kernel entry)")
@@ -403,6 +406,26 @@ def run_b200(a):
                 timeline.append({n: (v - tl[0]) / 1e3 for n, v in zip(names, tl)})
             rewind()
 
+        # ---- optional: timeline of the tcgen05 prefill convolution (stamps of CTA 0)
+        conv_timeline = None
+        if a.conv_timeline and approx:
+            words = torch.zeros(128, dtype=torch.int64, device=dev)
+            prefill()
+            torch.cuda.synchronize()
+            ops.conv_prefill_timeline(words)
+            prefill()
+            torch.cuda.synchronize()
+            ops.conv_prefill_timeline(None)
+            tw = words.cpu().view(8, 16)
+            t_first = int(tw[0, 5])
+            unit_names = ["accumulator free", "first operands ready", "last MMA issued", "accumulator complete",
+                          "epilogue done"]
+            phase_names = ["stage free", "history chunk landed", "stage ready"]
+            conv_timeline = {
+                "units": [{n: (int(tw[u, k]) - t_first) / 1e3 for k, n in enumerate(unit_names)} for u in range(8)],
+                "phases": [{n: (int(tw[u, 5 + k]) - t_first) / 1e3 for k, n in enumerate(phase_names)} for u in range(8)]}
+            rewind()
+
         # ---- optional: every kernel of the token step in a graph of its own (64 launches each)
         split = None
         if a.kernel_split and not a.no_graph and approx:
@@ -583,6 +606,8 @@ def run_b200(a):
                                  "frac": step_bytes / (step_us * 1e-6) / 1e9 / pk["hbm_gbs"]}
     if split is not None:
         line["decode_split"] = split
+    if conv_timeline is not None:
+        line["conv_timeline"] = {"unit": "us after the first stage became free, CTA 0", **conv_timeline}
     if timeline is not None:
         line["step_timeline"] = {"unit": "us after kernel entry, CTA 0, three consecutive launches", "launches": timeline}
     if extra.get("generate") is not None:

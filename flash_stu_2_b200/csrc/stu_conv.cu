@@ -302,6 +302,23 @@ __global__ void __launch_bounds__(256) transpose_add_kernel(T* __restrict__ x, l
   }
 }
 
+// Residual add of a finished convolution: x[b, t - t0, :] += yT[b][:][t&1][t>>1] for t in [t0, t_end).
+int launch_transpose_add(void* x, long long x_bstride, long long x_tstride, const void* yT, int B, int d, int y_Lh,
+                         int t0, int t_end, int dtype, cudaStream_t st) {
+  const int v2 = (dtype == STU_F32) ? 8 : 16;  // 2V: the kernel aligns its first tile to this
+  int tb = t0 - t0 % v2;
+  const int tc = (dtype == STU_F32) ? 32 : 64;
+  dim3 g2((t_end - tb + 127) / 128, (d + tc - 1) / tc, B);
+  if (dtype == STU_F32)
+    transpose_add_kernel<float><<<g2, 256, 0, st>>>((float*)x, x_bstride, x_tstride, (const float*)yT, d, y_Lh, t0,
+                                                    t_end);
+  else
+    transpose_add_kernel<bf16><<<g2, 256, 0, st>>>((bf16*)x, x_bstride, x_tstride, (const bf16*)yT, d, y_Lh, t0,
+                                                   t_end);
+  STU_CHECK_LAUNCH();
+  return STU_OK;
+}
+
 // Prefill convolution entry point: hist holds projected inputs for times [0, t_end); computes the
 // convolution outputs for times [t0, t_end) into yT (same layout as hist, y_Lh elements per parity row) and adds them to x
 // ([B, t_end - t0, d] with the given strides).  use_tensor_cores selects conv_mma_kernel (bf16).
@@ -344,18 +361,7 @@ extern "C" int stu_conv_prefill_approx(const void* hist, const void* taps, void*
     }
   }
   STU_CHECK_LAUNCH();
-  const int v2 = (dtype == STU_F32) ? 8 : 16;  // 2V: the kernel aligns its first tile to this
-  int tb = t0 - t0 % v2;
-  const int tc = (dtype == STU_F32) ? 32 : 64;
-  dim3 g2((t_end - tb + 127) / 128, (d + tc - 1) / tc, B);
-  if (dtype == STU_F32)
-    transpose_add_kernel<float><<<g2, 256, 0, st>>>((float*)x, x_bstride, x_tstride, (const float*)yT, d, y_Lh, t0,
-                                                    t_end);
-  else
-    transpose_add_kernel<bf16><<<g2, 256, 0, st>>>((bf16*)x, x_bstride, x_tstride, (const bf16*)yT, d, y_Lh, t0,
-                                                   t_end);
-  STU_CHECK_LAUNCH();
-  return STU_OK;
+  return launch_transpose_add(x, x_bstride, x_tstride, yT, B, d, y_Lh, t0, t_end, dtype, st);
 }
 
 // ------------------------------------------------------------------------------------------------

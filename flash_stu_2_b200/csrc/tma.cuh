@@ -70,6 +70,14 @@ __device__ __forceinline__ void load_4d(void* dst, const CUtensorMap* map, uint6
       : "memory");
 }
 
+__device__ __forceinline__ void load_5d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
+                                        int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
+
 // L2 eviction policies for data read once per launch (evict_first) and data re-read by every launch (evict_last)
 __device__ __forceinline__ uint64_t policy_evict_first() {
   uint64_t p;
@@ -96,6 +104,20 @@ __device__ __forceinline__ void load_4d_hint(void* dst, const CUtensorMap* map, 
       "[%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "l"(policy)
       : "memory");
+}
+__device__ __forceinline__ void load_5d_hint(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
+                                             int c3, int c4, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "l"(policy)
+      : "memory");
+}
+// bring the box into L2 only (no shared-memory destination, no barrier)
+__device__ __forceinline__ void prefetch_5d(const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4) {
+  asm volatile("cp.async.bulk.prefetch.tensor.5d.L2.global [%0, {%1, %2, %3, %4, %5}];"
+               ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+               : "memory");
 }
 __device__ __forceinline__ void bulk_load_hint(void* dst, const void* src, uint32_t bytes, uint64_t* bar,
                                                uint64_t policy) {
@@ -131,15 +153,17 @@ static inline EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// Un-swizzled bf16 tensor map of rank `rank` (innermost dimension first; `strides_bytes` for dimensions 1..rank-1).
-// Out-of-range parts of a box are filled with zeros.
+// bf16 tensor map of rank `rank` (innermost dimension first; `strides_bytes` for dimensions 1..rank-1), un-swizzled
+// or, with swizzle128, in the 128-byte swizzle the tensor-core operand descriptors expect (the box's innermost extent
+// is then 64 elements).  Out-of-range parts of a box are filled with zeros.
 static inline int encode_bf16(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims,
-                              const cuuint64_t* strides_bytes, const cuuint32_t* box) {
+                              const cuuint64_t* strides_bytes, const cuuint32_t* box, bool swizzle128 = false) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return STU_ERR_UNSUPPORTED;
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), dims, strides_bytes,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? STU_OK : STU_ERR_UNSUPPORTED;
 }

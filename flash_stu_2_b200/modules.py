@@ -261,7 +261,7 @@ class STU(nn.Module):
         if not self.use_approx:
             return self.full_forward(xn, x, x, entry, use_cache)
         B, T, d = xn.shape
-        MinT, taps, _ = self.prepared()
+        MinT, taps, taps8 = self.prepared()
         t0 = 0
         if entry is not None:
             hist, pos = entry
@@ -277,8 +277,11 @@ class STU(nn.Module):
         Lh = hist.shape[3]
         ops.linear(xn.reshape(B * T, d), MinT, out=hist, epilogue=ops.EPI_HIST, hist_T=T, hist_t0=t0, hist_Lh=Lh)
         yT = torch.empty(B, d, 2, _round_up((t0 + T + 1) // 2, 8), dtype=xn.dtype, device=xn.device)
-        ops.conv_prefill_approx(hist, taps, yT, x, t0, t0 + T, use_tensor_cores=(xn.dtype == torch.bfloat16 and
-                                                                              STU.tensor_core_conv))
+        if STU.tensor_core_conv and STU.tcgen05_conv and taps8 is not None and ops.conv_prefill_tc5_supported(hist, x):
+            ops.conv_prefill_approx_tc5(hist, taps8, yT, x, t0, t0 + T)
+        else:
+            ops.conv_prefill_approx(hist, taps, yT, x, t0, t0 + T,
+                                    use_tensor_cores=(xn.dtype == torch.bfloat16 and STU.tensor_core_conv))
         if pos is not None:
             pos[:, 0] += T
             pos._host_t = t0 + T
@@ -286,6 +289,7 @@ class STU(nn.Module):
         return None
 
     tensor_core_conv = True    # class switches used by tests to compare the tensor-core and CUDA-core kernels
+    tcgen05_conv = True        # ... and, of the tensor-core ones, the tcgen05 kernel against the mma.sync kernel
     tensor_core_decode = True
     shared_tap_decode = True   # batches at one common position: the kernel with 8 channels x 8 sequences per CTA
     pipelined_decode = True    # ... and, of those, the persistent bulk-copy pipeline kernel

@@ -80,7 +80,8 @@ STATUS_TEXT = {1: "token id outside the vocabulary", 2: "position outside the ca
                5: "top_p without top_k is not implemented on the device",
                6: "decode step told that all sequences share one position, but the cached positions differ",
                7: "a bounded pipeline wait ran out inside the decode kernel",
-               8: "the fused token-step kernel found no partial sums for the current position in its workspace"}
+               8: "the fused token-step kernel found no partial sums for the current position in its workspace",
+               9: "a bounded pipeline wait ran out inside the tcgen05 prefill convolution"}
 
 
 def check_status(device=None):
@@ -196,6 +197,35 @@ def conv_prefill_approx(hist, taps, yT, x, t0: int, t_end: int, use_tensor_cores
     _lib.check(rc, "stu_conv_prefill_approx")
     _count(2)
     return x
+
+
+def conv_prefill_tc5_supported(hist, x) -> bool:
+    """The tcgen05 prefill convolution takes bf16 histories tiled in 128-position blocks."""
+    return x.dtype == torch.bfloat16 and hist.shape[3] % 128 == 0
+
+
+def conv_prefill_approx_tc5(hist, taps8, yT, x, t0: int, t_end: int):
+    """conv_prefill_approx on the tcgen05 tensor cores; taps8 is the reversed tap table of taps_rev8."""
+    _cuda(hist, taps8, yT, x)
+    B, d, _, Lh = hist.shape
+    assert hist.is_contiguous() and yT.is_contiguous() and taps8.shape == (8, d, Lh + 8) and taps8.is_contiguous()
+    assert x.shape == (B, t_end - t0, d) and x.stride(2) == 1
+    rc = _lib.load().stu_conv_prefill_approx_tc5(hist.data_ptr(), taps8.data_ptr(), yT.data_ptr(), x.data_ptr(),
+                                                 x.stride(0), x.stride(1), B, d, Lh, yT.shape[3], t0, t_end,
+                                                 status_word(x.device).data_ptr(), _dt(x), _stream())
+    _lib.check(rc, "stu_conv_prefill_approx_tc5")
+    _count(2)
+    return x
+
+
+def conv_prefill_timeline(words: Optional[torch.Tensor]):
+    """Register (or, with None, remove) the int64 tensor of 128 words that receives the tcgen05 convolution's
+    device-side time stamps; see stu_conv_prefill_set_timeline."""
+    if words is not None:
+        _cuda(words)
+        assert words.dtype == torch.int64 and words.numel() >= 128 and words.is_contiguous()
+    _lib.check(_lib.load().stu_conv_prefill_set_timeline(None if words is None else words.data_ptr()),
+               "stu_conv_prefill_set_timeline")
 
 
 def conv_prefill_approx_static(hist, taps, x, t0: int, t_end: int, use_tensor_cores: bool):

@@ -225,8 +225,11 @@ class TensorParallelFlashSTU:
                     ops.linear(xn, MinT, out=hist, epilogue=ops.EPI_HIST, hist_T=T, hist_t0=t0, hist_Lh=self.Lh)
                     y_loc = torch.zeros(B, T, dl, dtype=self.dtype, device=self.device)
                     yT = torch.empty(B, dl, 2, _round_up((t0 + T + 1) // 2, 8), dtype=self.dtype, device=self.device)
-                    ops.conv_prefill_approx(hist, taps, yT, y_loc, t0, t0 + T,
-                                            use_tensor_cores=(self.dtype == torch.bfloat16 and dl % 8 == 0))
+                    if taps8 is not None and ops.conv_prefill_tc5_supported(hist, y_loc):
+                        ops.conv_prefill_approx_tc5(hist, taps8, yT, y_loc, t0, t0 + T)
+                    else:
+                        ops.conv_prefill_approx(hist, taps, yT, y_loc, t0, t0 + T,
+                                                use_tensor_cores=(self.dtype == torch.bfloat16 and dl % 8 == 0))
                     pos[:, 0] += T
                 pos._host_t = t0 + T
                 gathered = torch.empty(self.world, B, T, dl, dtype=self.dtype, device=self.device)

@@ -103,6 +103,24 @@ int stu_conv_prefill_approx_static(const void* hist, const void* taps, void* x, 
                                    long long x_tstride, int B, int d, int Lh, int t0, int t_end, int dtype,
                                    int use_tensor_cores, void* stream);
 
+/* The same prefill convolution (bf16) on the tcgen05 tensor cores: per channel the Toeplitz product is regrouped by
+ * block distance so that one instruction covers every 128-position output block at once (N up to 512), the
+ * accumulator of 4096 positions x 16 parity rows lives in tensor memory, the history chunks and the Toeplitz blocks
+ * arrive by cp.async.bulk.tensor, the latter straight from the reversed tap table taps8 of stu_taps_rev8 through a
+ * tensor map with an overlapping row stride.  Replaces the same reference lines as stu_conv_prefill_approx
+ * (flash_stu/modules/stu.py:95-98,120; flash_stu/utils/stu_utils.py:208-228).  Needs Lh % 128 == 0 (-4 otherwise:
+ * use stu_conv_prefill_approx), hist, taps8 and yT 16-byte aligned, y_Lh % 8 == 0 (-3).  status receives 9 when a
+ * bounded pipeline wait ran out. */
+int stu_conv_prefill_approx_tc5(const void* hist, const void* taps8, void* yT, void* x, long long x_bstride,
+                                long long x_tstride, int B, int d, int Lh, int y_Lh, int t0, int t_end, int* status,
+                                int dtype, void* stream);
+
+/* Profiling aid of stu_conv_prefill_approx_tc5: while a device buffer of 128 64-bit words is registered, CTA 0 of
+ * every launch writes nanosecond stamps of its first 8 units into it (16 words per unit: 0 accumulator free,
+ * 1 first operands ready, 2 last MMA issued, 3 accumulator complete, 4 epilogue done; per phase: 5 stage free,
+ * 6 history chunk landed, 7 stage ready).  NULL switches it off.  No counterpart in the reference. */
+int stu_conv_prefill_set_timeline(void* device_words);
+
 /* One cached decode step of an approx STU layer, fused:
  *   out[b,:] = x[b,:] + STU(rmsnorm(x[b,:]) * norm_w)   at time t = pos[2*b]; appends to hist, advances pos.
  * MinT is M_inputs transposed ([d_out][d_in]).  The reference has no such step (its STU layers keep no

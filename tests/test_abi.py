@@ -44,6 +44,10 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert lib.stu_conv_prefill_approx(a, a, a, a, 333 * 8, 8, 1, 8, 168, 167, 0, 333, 1, 1, None) == -3
     assert lib.stu_conv_prefill_approx(a, a, a, a, 333 * 8, 8, 1, 8, 168, 166, 0, 332, 0, 0, None) == -3
     assert lib.stu_conv_prefill_approx(a, a, a + 2, a, 333 * 8, 8, 1, 8, 168, 168, 0, 333, 1, 1, None) == -3
+    # the tcgen05 convolution: misaligned scratch -3, a history that is not tiled in 128-position blocks -4, fp32 -1
+    assert lib.stu_conv_prefill_approx_tc5(a, a, a + 2, a, 333 * 8, 8, 1, 8, 256, 168, 0, 333, None, 1, None) == -3
+    assert lib.stu_conv_prefill_approx_tc5(a, a, a, a, 333 * 8, 8, 1, 8, 168, 168, 0, 333, None, 1, None) == -4
+    assert lib.stu_conv_prefill_approx_tc5(a, a, a, a, 333 * 8, 8, 1, 8, 256, 168, 0, 333, None, 0, None) == -1
 
 
 def test_ops_refuse_cpu_tensors():

@@ -190,6 +190,43 @@ def test_conv_prefill_matches_fft_oracle(dt, tc, shape):
     close(x, ref[:, t0:], (2e-5 if dt == torch.float32 else 1.5e-2), row_tol=(2e-5 if dt == torch.float32 else 2e-2))
 
 
+@pytest.mark.parametrize("shape", [(2, 250, 16, 0), (3, 700, 24, 0), (9, 1100, 8, 0), (2, 1301, 8, 655),
+                                   (1, 8800, 8, 0), (2, 9001, 8, 8300)])
+def test_conv_prefill_tcgen05_matches_fft_oracle(shape):
+    """The tcgen05 prefill convolution against the reference's FFT convolution (fp32): histories of one and of two
+    accumulator-sized superblocks (more than 4096 positions per parity), more than 8 sequences, a resumed prefill
+    (t0 > 0), and NaN in the cache past the valid positions, which must not reach any output."""
+    from flash_stu_2_b200 import ops
+    B, T, d, t0 = shape
+    torch.manual_seed(4)
+    L = T + 3
+    Lh = ((L + 1) // 2 + 127) // 128 * 128
+    xp = torch.randn(B, T, d).bfloat16()
+    fp = (torch.randn(L, d) / math.sqrt(L)).bfloat16()
+    x0 = torch.randn(B, T, d).bfloat16()
+    plus, minus = O.convolve(xp, fp, O.fft_length(L), True, True)
+    ref = (x0.float() + (plus + minus).float()).bfloat16()
+    hist = _hist_from(xp, Lh)
+    for p in range(2):
+        hist[:, :, p, (T - p + 1) // 2:] = float("nan")
+    hist = hist.to(dev())
+    taps = ops.taps_even(fp.to(dev()), Lh)
+    taps8 = ops.taps_rev8(taps)
+    yT = torch.full((B, d, 2, ((T + 1) // 2 + 7) // 8 * 8), float("nan"), dtype=torch.bfloat16, device=dev())
+    x = x0[:, t0:].contiguous().to(dev())
+    assert ops.conv_prefill_tc5_supported(hist, x)
+    ops.conv_prefill_approx_tc5(hist, taps8, yT, x, t0, T)
+    ops.check_status()
+    # the reference rounds each branch to bf16 before adding them; over thousands of positions the branches grow
+    # against their sum, so a row of 8 channels sees up to three ulps of that rounding
+    close(x, ref[:, t0:], 1.5e-2, row_tol=(2e-2 if T < 4096 else 3e-2))
+    # and against the mma.sync kernel on the same operands: same products, fp32 sums in another order
+    hist0 = torch.nan_to_num(hist, nan=0.0)
+    x2 = x0[:, t0:].contiguous().to(dev())
+    ops.conv_prefill_approx(hist0, taps, torch.zeros_like(yT), x2, t0, T, use_tensor_cores=True)
+    close(x, x2, 8e-3, row_tol=1.6e-2)
+
+
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 def test_history_scatter_epilogue(dt):
     from flash_stu_2_b200 import ops
