@@ -61,6 +61,19 @@ _SIGNATURES = {
     "stu_lds_decode_features": ([_P, _LL, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P], c_int),
     "stu_swa_forward": ([_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                          _P], c_int),
+    "stu_peer_dest_bytes": ([], c_int),
+    "stu_peer_alloc": ([_P, _LL], c_int),
+    "stu_peer_free": ([_P], c_int),
+    "stu_peer_export": ([_P, _P], c_int),
+    "stu_peer_open": ([_P, _P], c_int),
+    "stu_peer_close": ([_P], c_int),
+    "stu_peer_write": ([_P, _P, _LL], c_int),
+    "stu_peer_read": ([_P, _P, _LL], c_int),
+    "stu_linear_push": ([_P, _LL, _P, _LL, c_int, c_int, c_int, _P, _LL, c_int, _P], c_int),
+    "stu_decode_approx_push": ([_P, _LL, _P, _P, _P, _P, _P, _P, _LL, c_int, c_int, c_int, c_int, c_float, _P, c_int,
+                                _P], c_int),
+    "stu_peer_combine": ([_P, _LL, _P, _LL, _LL, c_int, _P, c_int, _P, _P, _P, _LL, c_float, c_int, c_int, _P, c_int,
+                          c_int, _P], c_int),
     "stu_sample": ([_P, _LL, c_int, c_int, c_float, c_int, c_float, c_int, _P, _P, _LL, _P, c_int, _P], c_int),
 }
 

@@ -81,6 +81,28 @@ extern "C" int stu_linear(const void* x, long long x_row_stride, const void* W, 
   return STU_ERR_UNSUPPORTED;
 }
 
+// y = x[M,K] @ W[N,K]^T for M <= 64 rows (bf16) with the exchange fused in: the rows are stored into every rank's inbox
+// (exchange descriptor `peer_dest`, device memory) with row stride dest_row_stride, and the ranks are signalled when the
+// last CTA has stored.  Weight-streaming kernel only.
+extern "C" int stu_linear_push(const void* x, long long x_row_stride, const void* W, long long w_row_stride, int M,
+                               int N, int K, const void* peer_dest, long long dest_row_stride, int dtype,
+                               void* stream) {
+  if (!x || !W || !peer_dest) return STU_ERR_NULL;
+  if (M <= 0 || N <= 0 || K <= 0) return STU_ERR_SHAPE;
+  if (dtype != STU_BF16) return STU_ERR_DTYPE;
+  if (!skinny_supported(x, x_row_stride, W, w_row_stride, 1, nullptr, M, N, K, EPI_STORE, dtype))
+    return STU_ERR_UNSUPPORTED;
+  EpiArgsAny ep;
+  ep.y = nullptr;
+  ep.ldy = dest_row_stride;
+  ep.resid = nullptr;
+  ep.ldr = 0;
+  ep.Tseq = ep.t0 = ep.Lh = 0;
+  ep.peer = (const PeerDest*)peer_dest;
+  return skinny_dispatch(x, x_row_stride, W, w_row_stride, nullptr, M, N, K, EPI_STORE, ep, nullptr, 0.f, dtype, 0,
+                         (cudaStream_t)stream);
+}
+
 // 1 when stu_linear would fuse the RMSNorm for this shape (decode path), else 0.
 extern "C" int stu_linear_can_fuse_norm(int M, int N, int K, int epilogue, int dtype) {
   if (dtype != STU_BF16 || M < 1 || M > 64 || K % 8 || epilogue == EPI_HIST) return 0;

@@ -2,6 +2,7 @@
 // the rounding points of the reference's tensor-by-tensor evaluation in the model dtype.
 #pragma once
 #include "common.cuh"
+#include "peer.cuh"
 
 enum {
   EPI_STORE = 0,     // y = acc
@@ -23,6 +24,7 @@ template <typename T> struct EpiArgs {
   // EPI_HIST: row m of the GEMM is token (m / T) * .. + (m % T) of a [B,T] batch starting at time t0
   int Tseq, t0, Lh;
   long long ld2;  // EPI_BLOCKCOL: distance between column blocks
+  const PeerDest* peer;  // EPI_STORE only, may be NULL: the rows go to every rank's inbox (row stride ldy) instead of y
 };
 
 struct EpiArgsAny {
@@ -32,10 +34,12 @@ struct EpiArgsAny {
   long long ldr;
   int Tseq, t0, Lh;
   long long ld2 = 0;
+  const PeerDest* peer = nullptr;
   template <typename U> EpiArgs<U> as() const {
     EpiArgs<U> e;
     e.y = (U*)y; e.ldy = ldy; e.resid = (const U*)resid; e.ldr = ldr; e.Tseq = Tseq; e.t0 = t0; e.Lh = Lh;
     e.ld2 = ld2;
+    e.peer = peer;
     return e;
   }
 };
@@ -43,7 +47,12 @@ struct EpiArgsAny {
 template <typename T, int EPI>
 __device__ __forceinline__ void epilogue_store(const EpiArgs<T>& ep, int m, int n, float acc, float acc2) {
   if (EPI == EPI_STORE) {
-    ep.y[(size_t)m * ep.ldy + n] = Elem<T>::from_f(acc);
+    if (sizeof(T) == 2 && ep.peer) {
+      const bf16 v = __float2bfloat16_rn(acc);
+      for (int p = 0; p < ep.peer->n; p++) ep.peer->dest[p][(size_t)m * ep.ldy + n] = v;
+    } else {
+      ep.y[(size_t)m * ep.ldy + n] = Elem<T>::from_f(acc);
+    }
   } else if (EPI == EPI_RESID) {
     float r = Elem<T>::to_f(ep.resid[(size_t)m * ep.ldr + n]);
     ep.y[(size_t)m * ep.ldy + n] = Elem<T>::from_f(r + round_to<T>(acc));

@@ -203,6 +203,10 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
     }
     cluster.sync();  // the other CTAs' shared memory stays alive until the first one has read it
   }
+  if (EPI == EPI_STORE && ep.peer) {   // the rows went to the inboxes of the tensor-parallel ranks: signal them
+    __syncthreads();
+    if (threadIdx.x == 0) peer_signal_when_last(ep.peer, gridDim.x * gridDim.y);
+  }
 }
 
 // fp32 models: SPLIT warps per output feature (8 / SPLIT features per CTA), lanes and warps split K with 128-bit

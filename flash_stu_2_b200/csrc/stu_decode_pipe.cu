@@ -28,6 +28,7 @@
 // returns.
 #include "common.cuh"
 #include "tma.cuh"
+#include "peer.cuh"
 
 int device_sm_count();  // gemm_tc.cu
 
@@ -84,6 +85,7 @@ struct Params {
   float eps;
   int* status;
   int pdl;
+  const PeerDest* peer;   // tensor parallelism: the output rows go to every rank's inbox instead of `out`
 };
 
 constexpr int NTHREADS = 13 * 32;   // 8 consumer warps, 1 producer warp, 4 projection warps
@@ -301,15 +303,22 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         const bool okp = tma::mbar_wait_bounded(&part_full[slot], ((uint32_t)(k >> 1)) & 1u, abort_flag);
         if (okp && gt < 64 && bb < nb) {
           const float y = round_to<bf16>(2.f * (s_part[slot][gt] + term));
-          P.out[(size_t)(b0 + bb) * P.out_rstride + c0 + cc] = __float2bfloat16_rn(res + y);
+          const bf16 v = __float2bfloat16_rn(res + y);
+          const size_t o = (size_t)(b0 + bb) * P.out_rstride + c0 + cc;
+          if (P.peer) {
+            for (int pr = 0; pr < P.peer->n; pr++) P.peer->dest[pr][o] = v;
+          } else {
+            P.out[o] = v;
+          }
         }
         group_bar();   // s_part[slot] read by all, s_red free for the next row
         if (gt == 0) tma::mbar_arrive(&part_free[slot]);
       }
     }
   }
-  // ---- end of the CTA: failure report
+  // ---- end of the CTA: tell the other ranks (when the last CTA gets here), failure report
   __syncthreads();
+  if (tid == 0 && P.peer) peer_signal_when_last(P.peer, (unsigned)G);
   if (s_abort) {
     if (tid == 0 && P.status) atomicExch(P.status, 7);
     if (tid == 0) {   // copies that were issued but never consumed must land before shared memory is released
@@ -328,11 +337,11 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 // The fused decode step as a bulk-copy pipeline.  Arguments as stu_decode_approx_shard (d_in = d_ch and
 // add_residual = 1 for a whole layer).  bf16, d_in % 8 == 0, d_ch % 8 == 0, Lh % 8 == 0, every sequence at the same
 // position (checked on the device: status 6).
-extern "C" int stu_decode_approx_pipelined(const void* x, long long x_row_stride, const void* norm_w, const void* MinT,
-                                           void* hist, const void* taps8, int* pos, void* out,
-                                           long long out_row_stride, int B, int d_in, int d_ch, int Lh, float eps,
-                                           int add_residual, int* status, int dtype, void* stream) {
-  if (!x || !norm_w || !MinT || !hist || !taps8 || !pos || !out) return STU_ERR_NULL;
+static int launch_pipe(const void* x, long long x_row_stride, const void* norm_w, const void* MinT, void* hist,
+                       const void* taps8, int* pos, void* out, long long out_row_stride, int B, int d_in, int d_ch,
+                       int Lh, float eps, int add_residual, int* status, int dtype, void* stream,
+                       const PeerDest* peer) {
+  if (!x || !norm_w || !MinT || !hist || !taps8 || !pos || (!out && !peer)) return STU_ERR_NULL;
   if (B <= 0 || d_in <= 0 || d_ch <= 0 || Lh <= 0 || d_in % 8 || d_ch % 8 || Lh % 8) return STU_ERR_SHAPE;
   if (add_residual && d_in != d_ch) return STU_ERR_SHAPE;
   const int pdl = dtype & (STU_FLAG_OVERLAP | STU_FLAG_EARLY_TRIGGER);
@@ -376,6 +385,7 @@ extern "C" int stu_decode_approx_pipelined(const void* x, long long x_row_stride
   P.eps = eps;
   P.status = status;
   P.pdl = pdl;
+  P.peer = peer;
 
   const size_t smem = (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * sizeof(uint64_t) + 1024;
   cudaError_t e = cudaFuncSetAttribute(stu_decode_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -388,4 +398,24 @@ extern "C" int stu_decode_approx_pipelined(const void* x, long long x_row_stride
   if (e != cudaSuccess) return (int)e;
   STU_CHECK_LAUNCH();
   return STU_OK;
+}
+
+extern "C" int stu_decode_approx_pipelined(const void* x, long long x_row_stride, const void* norm_w, const void* MinT,
+                                           void* hist, const void* taps8, int* pos, void* out,
+                                           long long out_row_stride, int B, int d_in, int d_ch, int Lh, float eps,
+                                           int add_residual, int* status, int dtype, void* stream) {
+  return launch_pipe(x, x_row_stride, norm_w, MinT, hist, taps8, pos, out, out_row_stride, B, d_in, d_ch, Lh, eps,
+                     add_residual, status, dtype, stream, nullptr);
+}
+
+// The channel shard of the decode step with its all-gather fused in: the d_ch outputs of every sequence are stored
+// straight into every rank's inbox (exchange descriptor `peer_dest`, device memory, see stu_peer_exchange_init) and
+// the ranks are signalled when the last CTA has stored.
+extern "C" int stu_decode_approx_push(const void* x, long long x_row_stride, const void* norm_w, const void* MinT,
+                                      void* hist, const void* taps8, int* pos, const void* peer_dest,
+                                      long long dest_row_stride, int B, int d_in, int d_ch, int Lh, float eps,
+                                      int* status, int dtype, void* stream) {
+  if (!peer_dest) return STU_ERR_NULL;
+  return launch_pipe(x, x_row_stride, norm_w, MinT, hist, taps8, pos, nullptr, dest_row_stride, B, d_in, d_ch, Lh, eps,
+                     0, status, dtype, stream, (const PeerDest*)peer_dest);
 }

@@ -81,7 +81,8 @@ STATUS_TEXT = {1: "token id outside the vocabulary", 2: "position outside the ca
                6: "decode step told that all sequences share one position, but the cached positions differ",
                7: "a bounded pipeline wait ran out inside the decode kernel",
                8: "the fused token-step kernel found no partial sums for the current position in its workspace",
-               9: "a bounded pipeline wait ran out inside the tcgen05 prefill convolution"}
+               9: "a bounded pipeline wait ran out inside the tcgen05 prefill convolution",
+               10: "a tensor-parallel rank waited in vain for another rank's sub-layer output"}
 
 
 def check_status(device=None):
@@ -279,6 +280,46 @@ def decode_approx_shard(x, norm_w, MinT, hist, taps8, pos, out, eps: float = RMS
     _lib.check(rc, "stu_decode_approx_shard")
     _count()
     return out
+
+
+def linear_push(x: torch.Tensor, W: torch.Tensor, dest: int, dest_row_stride: int):
+    """x[M,K] @ W[N,K]^T stored into every tensor-parallel rank's inbox through the exchange descriptor at device
+    address `dest` (peer.PeerExchange.dest); M <= 64, bf16."""
+    _cuda(x, W)
+    M, K = x.shape
+    N = W.shape[0]
+    assert W.shape[1] == K and x.stride(1) == 1 and W.stride(1) == 1
+    rc = _lib.load().stu_linear_push(x.data_ptr(), x.stride(0), W.data_ptr(), W.stride(0), M, N, K, dest,
+                                     dest_row_stride, _dt(x), _stream())
+    _lib.check(rc, "stu_linear_push")
+    _count()
+
+
+def decode_approx_push(x, norm_w, MinT, hist, taps8, pos, dest: int, dest_row_stride: int, eps: float = RMS_EPS):
+    """decode_approx_pipelined for a channel shard whose outputs go into every rank's inbox (see linear_push)."""
+    _cuda(x, norm_w, MinT, hist, taps8, pos)
+    B, d_ch, _, Lh = hist.shape
+    d_in = x.shape[1]
+    assert MinT.shape == (d_ch, d_in) and MinT.is_contiguous() and hist.is_contiguous() and taps8.is_contiguous()
+    rc = _lib.load().stu_decode_approx_push(x.data_ptr(), x.stride(0), norm_w.data_ptr(), MinT.data_ptr(),
+                                            hist.data_ptr(), taps8.data_ptr(), pos.data_ptr(), dest, dest_row_stride,
+                                            B, d_in, d_ch, Lh, eps, status_word(x.device).data_ptr(), _dt(x),
+                                            _stream())
+    _lib.check(rc, "stu_decode_approx_push")
+    _count()
+
+
+def peer_combine(x, inbox: int, slot_stride: int, in_row_stride: int, slots: int, flags: int, n_ranks: int,
+                 epoch: int, norm_w=None, xn=None, eps: float = RMS_EPS, wait_ms: int = 0):
+    """x += sum of this rank's inbox blocks once every sender has arrived; optionally xn = RMSNorm(x) * norm_w."""
+    _cuda(x)
+    rows, d = x.shape
+    assert x.stride(1) == 1 and (norm_w is None or (xn is not None and xn.shape == x.shape and xn.stride(1) == 1))
+    rc = _lib.load().stu_peer_combine(x.data_ptr(), x.stride(0), inbox, slot_stride, in_row_stride, slots, flags,
+                                      n_ranks, epoch, _p(norm_w), _p(xn), xn.stride(0) if xn is not None else 0, eps,
+                                      rows, d, status_word(x.device).data_ptr(), wait_ms, _dt(x), _stream())
+    _lib.check(rc, "stu_peer_combine")
+    _count()
 
 
 def decode_approx_pipelined(x, norm_w, MinT, hist, taps8, pos, out, eps: float = RMS_EPS, add_residual: bool = True,

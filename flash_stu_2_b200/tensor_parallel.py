@@ -10,8 +10,13 @@ Sharding (g ranks, rank r), one exchange per sub-layer:
   * attention (flash_stu/modules/attention.py:72-101): heads split; `c_proj` split by the matching input columns;
     partial outputs all-reduced.  The KV ring of a rank holds its heads only.
   * LM head: vocabulary split; the logits shards are all-gathered (rank-major, padded rows cut off).
-The collectives are torch.distributed calls (NCCL over NVLink on GPUs) between the same CUDA kernels the
-single-GPU path uses; every rank ends a step with identical logits and, given the same uniforms, identical tokens.
+Prefill: the collectives are torch.distributed calls (NCCL over NVLink on GPUs) between the same CUDA kernels the
+single-GPU path uses.  Token steps (bf16, all sequences at one position): the exchanges after the STU, attention and
+MLP sub-layers are fused into the kernels on either side of them (peer.PeerExchange): the channel-shard decode kernel
+and the down / c_proj kernels store their rows straight into every rank's inbox over NVLink and raise a flag, one
+combine kernel per exchange waits for all senders, adds the rows to the residual stream and applies the next
+sub-layer's RMSNorm.  Only the logits all-gather of a step stays a library collective.  Every rank ends a step with
+identical logits and, given the same uniforms, identical tokens.
 """
 from typing import Dict, Optional
 
@@ -145,6 +150,8 @@ class TensorParallelFlashSTU:
         self.window = int(ws[0] if isinstance(ws, (tuple, list)) else ws)
         self.eps = ops.RMS_EPS
         self.fused_decode = True
+        self.fused_exchange = True    # token steps: sub-layer exchanges inside the kernels (peer stores), not NCCL
+        self._exchange = None
         self._derived = {}
         from .modules import Attention
         self.slopes = Attention._get_alibi_slopes(Attention, self.H)[self.rank * self.Hl:(self.rank + 1) * self.Hl] \
@@ -238,9 +245,80 @@ class TensorParallelFlashSTU:
             self._mlp(x2, i)
         return x
 
+    # ------------------------------------------------------------------ token step with fused exchanges
+    def _exchange_for(self, B: int):
+        """The peer buffers for token steps of B sequences (collective on first use; every rank makes the same calls)."""
+        ok = (self.fused_exchange and self.world > 1 and self.device.type == "cuda" and self.dtype == torch.bfloat16
+              and self.fused_decode and self.dl % 8 == 0 and B <= 64 and self.world <= 8)
+        if not ok:
+            return None
+        if self._exchange is None or self._exchange.rows != B:
+            from .peer import GATHER, REDUCE, PeerExchange
+            if self._exchange is not None:
+                torch.cuda.synchronize(self.device)
+                self._exchange.close()
+            kinds = []
+            for i in range(self.cfg.n_layers):
+                kinds += [REDUCE if self._is_attn(i) else GATHER, REDUCE]
+            self._exchange = PeerExchange.connect(kinds, B, self.d, group=self.group)
+            self._xn = [torch.empty(B, self.d, dtype=self.dtype, device=self.device) for _ in range(2)]
+        return self._exchange
+
+    def _token_step_fused(self, ids: torch.Tensor, cache, ex):
+        """One new token per sequence: (residual stream [B,1,d], final-norm rows [B,d]).  Per layer the kernels are
+        [STU shard decode -> inboxes | c_attn, attention, c_proj -> inboxes], combine (+ MLP norm), gate/up,
+        down -> inboxes, combine (+ the next explicit norm)."""
+        B = ids.shape[0]
+        d, dl, n_layers = self.d, self.dl, self.cfg.n_layers
+        x = ops.embed(ids, self.sd["tok_emb.weight"])
+        x2 = x.view(B, d)
+        xa, xb = self._xn
+        have_norm = False      # xa holds the attention norm of the current layer's input
+        e = 0
+        for i in range(n_layers):
+            p = f"layers.{i}."
+            if self._is_attn(i):
+                k_ring, v_ring, pos = cache[i]
+                t0 = host_pos(pos)
+                if not have_norm:
+                    ops.rmsnorm(x2, self.sd[p + "attn_norm.weight"], self.eps, out=xa)
+                qkv = ops.linear(xa, self.sd[p + "attn.c_attn.weight"]).view(B, 1, 3 * dl)
+                y = ops.swa_forward(qkv, k_ring, v_ring, pos, self.slopes, self.Hl, self.window, self.cfg.softcap,
+                                    update_cache=True)
+                pos._host_t = t0 + 1
+                ops.linear_push(y.view(B, dl), self.sd[p + "attn.c_proj.weight"], ex.dest(e), d)
+            else:
+                hist, pos = cache[i]
+                t0 = host_pos(pos)
+                if t0 + 1 > self.capacity:
+                    raise ValueError(f"sequence position {t0 + 1} exceeds the capacity {self.capacity}")
+                MinT, _, taps8 = self._stu_weights(i)
+                ops.decode_approx_push(x2, self.sd[p + "stu_norm.weight"], MinT, hist, taps8, pos, ex.dest(e), d,
+                                       self.eps)
+                pos._host_t = t0 + 1
+            ex.combine(e, x2, norm_w=self.sd[p + "mlp_norm.weight"], xn=xb, eps=self.eps)
+            e += 1
+            h = ops.linear(xb, self.sd[p + "mlp.gate_proj.weight"], W2=self.sd[p + "mlp.up_proj.weight"],
+                           epilogue=ops.EPI_GELU_MUL)
+            ops.linear_push(h, self.sd[p + "mlp.down_proj.weight"], ex.dest(e), d)
+            if i + 1 == n_layers:
+                nw = self.sd["norm.weight"]
+            elif self._is_attn(i + 1):
+                nw = self.sd[f"layers.{i + 1}.attn_norm.weight"]
+            else:
+                nw = None      # the STU shard kernel normalises its input itself
+            ex.combine(e, x2, norm_w=nw, xn=xa if nw is not None else None, eps=self.eps)
+            have_norm = nw is not None
+            e += 1
+        return x, xa
+
     def last_logits(self, ids: torch.Tensor, cache):
-        x = self.hidden(ids, cache)
-        last = ops.rmsnorm(x[:, -1].contiguous(), self.sd["norm.weight"], self.eps)
+        ex = self._exchange_for(ids.shape[0]) if ids.shape[1] == 1 else None
+        if ex is not None:
+            x, last = self._token_step_fused(ids, cache, ex)
+        else:
+            x = self.hidden(ids, cache)
+            last = ops.rmsnorm(x[:, -1].contiguous(), self.sd["norm.weight"], self.eps)
         loc = ops.linear(last, self.sd["lm_head.weight"])                     # [B, ceil(V/g)]
         allv = torch.empty(self.world, *loc.shape, dtype=loc.dtype, device=loc.device)
         dist.all_gather_into_tensor(allv, loc.contiguous(), group=self.group)

@@ -253,6 +253,50 @@ int stu_sample(const void* logits, long long ld, int B, int V, float temperature
                int do_sample, const float* uniforms, long long* out, long long out_stride, int* status, int dtype,
                void* stream);
 
+/* ---- exchange between the GPUs of a tensor-parallel group, fused into the token loop's kernels ----------------
+ * The reference is single-GPU (its sub-layers: flash_stu/layers/stu_layer.py:78-98,
+ * flash_stu/layers/attention_layer.py); these calls replace the all-gather after a channel-sharded STU sub-layer and the
+ * all-reduce after a column-sharded MLP / attention sub-layer for the one new token of a cached decode step.  Every
+ * rank owns one peer buffer (stu_peer_alloc) that the other ranks map (stu_peer_export / stu_peer_open, CUDA IPC); it
+ * holds, per exchange point of the token step, an inbox, one arrival counter per sender, a send counter and a CTA
+ * counter.  A producing kernel stores its rows straight into every rank's inbox (plain stores to peer memory) and its
+ * last CTA raises the sender's counter on every rank; stu_peer_combine waits (bounded) for all senders.  No load ever
+ * targets another GPU's memory.
+ *
+ * An exchange descriptor (stu_peer_dest_bytes() bytes of the sender's device memory) is laid out as
+ *   int n, pad;  void* dest[8];  unsigned* flag[8];  unsigned* epoch;  unsigned* ctr;
+ * dest[p] = where this rank's rows start inside rank p's inbox, flag[p] = rank p's arrival counter for this sender,
+ * epoch / ctr = this rank's send counter and CTA counter of the exchange (both start at 0). */
+int stu_peer_dest_bytes(void);
+int stu_peer_alloc(void** ptr, long long bytes);            /* zero-filled; a dedicated cudaMalloc allocation */
+int stu_peer_free(void* ptr);
+int stu_peer_export(void* ptr, void* handle64);             /* 64-byte inter-process handle of the allocation */
+int stu_peer_open(const void* handle64, void** ptr);        /* map another rank's allocation */
+int stu_peer_close(void* ptr);
+int stu_peer_write(void* dst, const void* host_src, long long bytes);   /* synchronous host -> buffer copy */
+int stu_peer_read(void* host_dst, const void* src, long long bytes);    /* synchronous buffer -> host copy */
+
+/* y = x[M,K] @ W[N,K]^T (bf16, M <= 64: the weight-streaming kernel) stored into every rank's inbox through the
+ * exchange descriptor, rows dest_row_stride elements apart; -4 for shapes that kernel does not take. */
+int stu_linear_push(const void* x, long long x_row_stride, const void* W, long long w_row_stride, int M, int N, int K,
+                    const void* peer_dest, long long dest_row_stride, int dtype, void* stream);
+
+/* stu_decode_approx_pipelined for a channel shard (add_residual = 0) whose d_ch outputs per sequence go into every
+ * rank's inbox through the exchange descriptor instead of `out`. */
+int stu_decode_approx_push(const void* x, long long x_row_stride, const void* norm_w, const void* MinT, void* hist,
+                           const void* taps8, int* pos, const void* peer_dest, long long dest_row_stride, int B,
+                           int d_in, int d_ch, int Lh, float eps, int* status, int dtype, void* stream);
+
+/* Receiving side of one exchange, one CTA per row: waits until all n_ranks arrival counters (flags) have reached
+ * this rank's send counter (epoch), then x[row] = round(x[row] + round(sum of the `slots` inbox blocks' rows)) and,
+ * with norm_w, xn[row] = RMSNorm(x[row]) * norm_w (the next sub-layer's normalisation).  inbox blocks are slot_stride
+ * elements apart, their rows in_row_stride.  The wait gives up after wait_ms (0: two seconds): status 10, x untouched.
+ * bf16, d % 8 == 0, d <= 16384. */
+int stu_peer_combine(void* x, long long x_row_stride, const void* inbox, long long slot_stride, long long in_row_stride,
+                     int slots, const void* flags, int n_ranks, const void* epoch, const void* norm_w, void* xn,
+                     long long xn_row_stride, float eps, int rows, int d, int* status, int wait_ms, int dtype,
+                     void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -382,6 +382,87 @@ def test_decode_step_pipelined_kernel(shape):
         assert torch.equal(before, hist)
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_peer_exchange_of_the_token_step_with_all_ranks_emulated_on_one_gpu(world):
+    """The fused exchanges of a tensor-parallel token step with every rank's buffers on this GPU: the channel-shard
+    decode kernel stores its outputs straight into all inboxes (all-gather), the down projection stores its partial
+    rows into all inboxes (all-reduce), and the combine kernel of every rank ends with the residual stream (and the
+    next RMSNorm) the unfused path computes.  All producing kernels are launched before the first combine, so no
+    kernel ever waits for one that has not run.  Repeated steps reuse the same inboxes and counters."""
+    from flash_stu_2_b200 import ops
+    from flash_stu_2_b200.peer import GATHER, REDUCE, PeerExchange
+    dt = torch.bfloat16
+    B, d, L, inter = 8, 64 * world, 40, 128 * world
+    dl, il = d // world, inter // world
+    Lh = ((L + 1) // 2 + 7) // 8 * 8
+    torch.manual_seed(11)
+    x, nw, Mi, fp, xp, ref = _decode_fixture(dt, B, 6, d, L)
+    taps = ops.taps_even(fp.to(dev()), Lh)
+    MinT = Mi.t().contiguous().to(dev())
+    nwd = nw.to(dev())
+    Wd = (torch.randn(d, inter) / math.sqrt(inter)).to(dt).to(dev())
+    norm2 = (1 + 0.1 * torch.randn(d)).to(dt).to(dev())
+    exs = PeerExchange.emulate([GATHER, REDUCE], B, d, world)
+    try:
+        ranks = []
+        for r in range(world):
+            sl = slice(r * dl, (r + 1) * dl)
+            ranks.append(dict(MinT=MinT[sl].contiguous(), taps8=ops.taps_rev8(taps[sl].contiguous()),
+                              hist=torch.zeros(B, dl, 2, Lh, dtype=dt, device=dev()),
+                              pos=torch.zeros(B, 2, dtype=torch.int32, device=dev()),
+                              hist_ref=torch.zeros(B, dl, 2, Lh, dtype=dt, device=dev()),
+                              pos_ref=torch.zeros(B, 2, dtype=torch.int32, device=dev()),
+                              Wd=Wd[:, r * il:(r + 1) * il].contiguous()))
+        for t in range(6):
+            xt = x[:, t].contiguous().to(dev())
+            h = (torch.randn(B, inter) / 2).to(dt).to(dev())
+            # ---- unfused: shard outputs gathered, partial products reduced (bf16 sums as a collective would form them)
+            ys = []
+            for rk in ranks:
+                y = torch.empty(B, dl, dtype=dt, device=dev())
+                ops.decode_approx_pipelined(xt, nwd, rk["MinT"], rk["hist_ref"], rk["taps8"], rk["pos_ref"], y,
+                                            add_residual=False)
+                ys.append(y)
+            x1 = (xt.float() + torch.cat(ys, 1).float()).to(dt)
+            n1 = ops.rmsnorm(x1, norm2)
+            parts = [ops.linear(h[:, r * il:(r + 1) * il].contiguous(), rk["Wd"]) for r, rk in enumerate(ranks)]
+            x2 = (x1.float() + torch.stack(parts).float().sum(0).to(dt).float()).to(dt)
+            # ---- fused: every rank's producers first, then every rank's combine
+            xs = [xt.clone() for _ in range(world)]
+            xn = [torch.empty_like(xt) for _ in range(world)]
+            for r, rk in enumerate(ranks):
+                ops.decode_approx_push(xs[r], nwd, rk["MinT"], rk["hist"], rk["taps8"], rk["pos"], exs[r].dest(0), d)
+            for r in range(world):
+                exs[r].combine(0, xs[r], norm_w=norm2, xn=xn[r])
+            for r, rk in enumerate(ranks):
+                ops.linear_push(h[:, r * il:(r + 1) * il].contiguous(), rk["Wd"], exs[r].dest(1), d)
+            for r in range(world):
+                x_mid = xs[r].clone()
+                exs[r].combine(1, xs[r])
+                assert torch.equal(x_mid, x1), (t, r)
+                close(xn[r], n1, 8e-3, what="next RMSNorm")   # the row sums are formed in another order
+                if world == 2:
+                    assert torch.equal(xs[r], x2), (t, r)    # two bf16 partials: one rounding either way
+                else:
+                    close(xs[r], x2, 8e-3)
+            ops.check_status()
+            for r in range(world):
+                for e in range(2):
+                    flags, epoch = exs[r].counters(e)
+                    assert flags == [t + 1] * world and epoch == t + 1
+        # a sender that never arrives: the bounded wait runs out, status 10, x untouched, the context stays usable
+        before = xs[0].clone()
+        ops.decode_approx_push(xs[0], nwd, ranks[0]["MinT"], ranks[0]["hist"], ranks[0]["taps8"], ranks[0]["pos"],
+                               exs[0].dest(0), d)
+        exs[0].combine(0, xs[0], wait_ms=50)
+        with pytest.raises(RuntimeError, match="status 10"):
+            ops.check_status()
+        assert torch.equal(xs[0], before)
+    finally:
+        for ex in exs:
+            ex.close()
+
+
 def test_decode_step_channel_shards_tile_the_layer():
     """Tensor-parallel form of the fused decode step: two ranks' channel shards (own history, own rows of
     M_inputs^T, own taps) give, concatenated and added to the input, exactly the whole-layer kernel's output."""

@@ -1,6 +1,8 @@
 """Tensor-parallel token loop on two GPUs (NCCL): every rank cuts its shard out of the fixture's full state dict,
 prefill logits are checked against the reference's (tests/golden/models.pt), a cached step against the
-reference's shorter-prefix logits, and both ranks must generate the same tokens as the single-GPU model."""
+reference's shorter-prefix logits, and both ranks must generate the same tokens as the single-GPU model.  In bf16 the
+cached steps run with the sub-layer exchanges fused into the kernels (stores into the other ranks' inboxes over
+NVLink); the same steps through the NCCL collectives must give the same logits and tokens."""
 import os
 import socket
 
@@ -47,6 +49,12 @@ def _worker(rank, world, port, name, q):
             tp.last_logits(ids[:, :T - 1].contiguous(), cache)
             short = tp.last_logits(ids[:, T - 1:T].contiguous(), cache).float().cpu()     # one cached step
             gen = tp.generate(ids[:, :9].contiguous(), max_length=21, do_sample=False).cpu()
+            fused = tp._exchange is not None
+            tp.fused_exchange = False                     # the same cached step and token loop through NCCL
+            cache = tp.new_cache(ids.shape[0])
+            tp.last_logits(ids[:, :T - 1].contiguous(), cache)
+            short_nccl = tp.last_logits(ids[:, T - 1:T].contiguous(), cache).float().cpu()
+            gen_nccl = tp.generate(ids[:, :9].contiguous(), max_length=21, do_sample=False).cpu()
         ops.check_status()
         single = None
         if rank == 0:   # the unsharded model on this GPU
@@ -57,7 +65,7 @@ def _worker(rank, world, port, name, q):
             m = m.to(dev).eval()
             single = m.generate(ids[:, :9].contiguous(), max_length=21, do_sample=False).cpu()
             os.remove(fp)
-        q.put((rank, full, short, gen, single))
+        q.put((rank, full, short, gen, single, fused, short_nccl, gen_nccl))
     finally:
         dist.destroy_process_group()
 
@@ -81,9 +89,15 @@ def test_two_gpu_tensor_parallel_model(name, world):
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
-    for rank, full, short, gen, single in res:
+    for rank, full, short, gen, single, fused, short_nccl, gen_nccl in res:
         close(full, r["logits_full"][:, -1].float(), tol)
         close(short, r["logits_short"][:, -1].float(), tol)
+        close(short_nccl, r["logits_short"][:, -1].float(), tol)
+        assert fused == (r["dtype"] == "bfloat16")           # bf16 token steps took the fused exchanges
+        if fused:
+            close(short, short_nccl, 1e-2, what="fused exchange vs NCCL")
+            # the same greedy tokens wherever the two largest logits are not within rounding of each other
+            assert (gen == gen_nccl).float().mean() > 0.9
     assert all(torch.equal(res[0][3], rr[3]) for rr in res[1:])   # every rank generates the same tokens
     if r["dtype"] == "float32":
         assert torch.equal(res[0][3], res[0][4])             # and, in fp32, the single-GPU model's
