@@ -752,6 +752,14 @@ def tp_object(a, dev, world, rank):
     ops.check_status()
     same = parallel.gather_token_ids(out[:1, T0:].contiguous(), world)
     dec_ms = parallel.max_over_ranks([tm["replay_ms"]], device=dev)[0] / tm["replayed_steps"]
+    fused = tp._exchange is not None
+    # the same token steps with the exchanges as NCCL collectives between the kernels
+    tp.fused_exchange = False
+    tm2 = {}
+    _, out2 = timed(ids, T0 + new, timings=tm2)
+    ops.check_status()
+    tp.fused_exchange = True
+    dec_ms_nccl = parallel.max_over_ranks([tm2["replay_ms"]], device=dev)[0] / tm2["replayed_steps"]
     pk = peaks()
     nbytes = _decode_bytes_per_step(cfg, B, T0 + new // 2) / world
     res = {"workload": f"FlashSTU.generate, 3B shapes: 32 layers d=3072 H=24 window 2048 K=32 L=32768 V=50257 bf16 "
@@ -762,7 +770,15 @@ def tp_object(a, dev, world, rank):
            "ranks_agree": bool((same == same[0]).all()),
            "roofline": {"bound": "hbm", "bytes_per_step_per_gpu": nbytes, "achieved": nbytes / (dec_ms * 1e-3) / 1e9,
                         "peak": pk["hbm_gbs"], "unit": "GB/s per GPU", "frac": nbytes / (dec_ms * 1e-3) / 1e9 / pk["hbm_gbs"]},
-           "collectives": "NCCL all-gather per STU layer, all-reduce per attention / MLP block, captured in the step graph"}
+           "decode_ms_per_token_step_nccl": dec_ms_nccl,
+           "tokens_equal_to_nccl_path": float((out[:, T0:] == out2[:, T0:]).float().mean()),
+           "collectives": ("token steps: the all-gather after every STU shard and the all-reduce after every attention / "
+                           "MLP block are stores into the other ranks' inboxes from inside the producing kernels "
+                           "(peer memory over NVLink) + one combine kernel each; logits all-gather and prefill: NCCL; "
+                           "`decode_ms_per_token_step_nccl` = the same steps with NCCL collectives between the kernels"
+                           if fused else
+                           "NCCL all-gather per STU layer, all-reduce per attention / MLP block, captured in the step "
+                           "graph")}
     del tp
     torch.cuda.empty_cache()
     # ---- parity of the sharded path on the reference's small hybrid fixtures (needs n_heads % ranks == 0)

@@ -74,6 +74,9 @@ _SIGNATURES = {
                                 _P], c_int),
     "stu_peer_combine": ([_P, _LL, _P, _LL, _LL, c_int, _P, c_int, _P, _P, _P, _LL, c_float, c_int, c_int, _P, c_int,
                           c_int, _P], c_int),
+    "stu_peer_xchg_bytes": ([], c_int),
+    "stu_peer_exchange": ([_P, _P, _LL, _P, _LL, c_int, c_int, _LL, _P, _P, _LL, c_float, c_int, c_int, _P, c_int,
+                           c_int, _P], c_int),
     "stu_sample": ([_P, _LL, c_int, c_int, c_float, c_int, c_float, c_int, _P, _P, _LL, _P, c_int, _P], c_int),
 }
 

@@ -140,7 +140,141 @@ __global__ void __launch_bounds__(256) peer_combine_kernel(bf16* __restrict__ x,
   }
 }
 
+// Push + wait + combine of one exchange in ONE launch, one CTA per row of the token batch:
+//   1. the CTA copies this rank's contribution of its row (`cols` values: the rank's channel slice for an all-gather,
+//      a full-width partial sum for an all-reduce) into EVERY rank's inbox with 16-byte stores (whole lines over
+//      NVLink), then raises this sender's counter of the row on every rank (one system-scope release);
+//   2. it waits (bounded) until the counters of all other senders of the row have reached the row's own epoch;
+//   3. x[row] = round(x[row] + round(sum of the inbox blocks' rows)), optionally followed by the next RMSNorm.
+// Rows are independent: no grid-wide step, and a row's exchange starts as soon as its CTA runs.
+template <int VPT>
+__global__ void __launch_bounds__(256) peer_exchange_kernel(const PeerXchg* __restrict__ xd, bf16* __restrict__ x,
+                                                            long long x_rs, const bf16* __restrict__ src,
+                                                            long long src_rs, int cols, int gather, long long slot_stride,
+                                                            int rows, const bf16* __restrict__ norm_w,
+                                                            bf16* __restrict__ xn, long long xn_rs, float eps, int d,
+                                                            int* status, unsigned long long wait_ns) {
+  __shared__ int s_ok;
+  __shared__ float s_red[8];
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const int n = xd->n, rank = xd->rank;
+  const unsigned target = xd->epoch[row] + 1u;
+  if (tid == 0) s_ok = 1;
+  // ---- 1. this rank's row into every inbox
+  {
+    const size_t off = (gather ? (size_t)rank * cols : (size_t)rank * slot_stride) + (size_t)row * d;
+    for (int c = tid * 8; c < cols; c += 256 * 8) {
+      const uint4 v = *reinterpret_cast<const uint4*>(src + (size_t)row * src_rs + c);
+      for (int p = 0; p < n; p++) *reinterpret_cast<uint4*>(xd->inbox[p] + off + c) = v;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence_system();
+    for (int p = 0; p < n; p++)
+      if (p != rank)
+        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(xd->flag[p] + (size_t)rank * rows + row) : "memory");
+  }
+  // ---- 2. the other senders of this row
+  if (tid < n && tid != rank) {
+    const unsigned* f = xd->flag[rank] + (size_t)tid * rows + row;
+    bool ok = false;
+    uint64_t start = 0;
+    for (unsigned it = 0; it < (1u << 26); ++it) {
+      if ((int)(ld_acquire_sys(f) - target) >= 0) { ok = true; break; }
+      if ((it & 63u) == 63u) {
+        const uint64_t now = global_ns();
+        if (start == 0) start = now;
+        else if (now - start > wait_ns) break;
+      }
+    }
+    if (!ok) s_ok = 0;
+  }
+  __syncthreads();
+  if (tid == 0) xd->epoch[row] = target;   // sent once more, whether or not the others arrived
+  if (!s_ok) {
+    if (tid == 0 && status) atomicExch(status, STATUS_PEER_WAIT);
+    return;
+  }
+  // ---- 3. combine
+  const bf16* inbox = xd->inbox[rank];
+  const int slots = gather ? 1 : n;
+  float v[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; k++) {
+    const int c = (tid + 256 * k) * 8;
+    if (c < d) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < slots; s++) {
+        float t[8];
+        load_vec(inbox + (size_t)s * slot_stride + (size_t)row * d + c, t);
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[j] += t[j];
+      }
+      float xv[8];
+      load_vec(x + (size_t)row * x_rs + c, xv);
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        v[k][j] = round_to<bf16>(xv[j] + round_to<bf16>(acc[j]));
+        ss += v[k][j] * v[k][j];
+      }
+      store_vec(x + (size_t)row * x_rs + c, v[k]);
+    }
+  }
+  if (!norm_w) return;
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) s_red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; w++) tot += s_red[w];
+  const float r = rsqrtf(tot / (float)d + eps);
+#pragma unroll
+  for (int k = 0; k < VPT; k++) {
+    const int c = (tid + 256 * k) * 8;
+    if (c < d) {
+      float w[8], o[8];
+      load_vec(norm_w + c, w);
+#pragma unroll
+      for (int j = 0; j < 8; j++) o[j] = v[k][j] * r * w[j];
+      store_vec(xn + (size_t)row * xn_rs + c, o);
+    }
+  }
+}
+
 }  // namespace
+
+extern "C" int stu_peer_xchg_bytes(void) { return (int)sizeof(PeerXchg); }
+
+// One exchange of the token step in one launch (see peer_exchange_kernel).  xchg = the exchange's PeerXchg record in
+// this rank's device memory; src [rows, cols] = this rank's contribution (gather != 0: its cols = d / n channels of every
+// row; gather == 0: a full-width partial sum, cols = d); the inbox blocks are slot_stride elements apart.
+extern "C" int stu_peer_exchange(const void* xchg, void* x, long long x_row_stride, const void* src,
+                                 long long src_row_stride, int cols, int gather, long long slot_stride,
+                                 const void* norm_w, void* xn, long long xn_row_stride, float eps, int rows, int d,
+                                 int* status, int wait_ms, int dtype, void* stream) {
+  if (!xchg || !x || !src || (norm_w && !xn)) return STU_ERR_NULL;
+  if (dtype != STU_BF16) return STU_ERR_DTYPE;
+  if (rows <= 0 || d <= 0 || d % 8 || d > 16384 || cols <= 0 || cols % 8 || cols > d) return STU_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(src) || (norm_w && (!aligned16(norm_w) || !aligned16(xn))) || x_row_stride % 8 ||
+      src_row_stride % 8 || slot_stride % 8 || (norm_w && xn_row_stride % 8))
+    return STU_ERR_ALIGN;
+  const unsigned long long wait_ns = (unsigned long long)(wait_ms > 0 ? wait_ms : 2000) * 1000000ull;
+  cudaStream_t st = (cudaStream_t)stream;
+#define LAUNCH_XCHG(V)                                                                                              \
+  peer_exchange_kernel<V><<<rows, 256, 0, st>>>((const PeerXchg*)xchg, (bf16*)x, x_row_stride, (const bf16*)src,   \
+                                                 src_row_stride, cols, gather, slot_stride, rows,                   \
+                                                 (const bf16*)norm_w, (bf16*)xn, xn_row_stride, eps, d, status,     \
+                                                 wait_ns)
+  if (d <= 2048) LAUNCH_XCHG(1);
+  else if (d <= 4096) LAUNCH_XCHG(2);
+  else if (d <= 8192) LAUNCH_XCHG(4);
+  else LAUNCH_XCHG(8);
+#undef LAUNCH_XCHG
+  STU_CHECK_LAUNCH();
+  return STU_OK;
+}
 
 // Receiving side of one exchange: see peer_combine_kernel.  inbox = this rank's inbox region of the exchange
 // ([slots] blocks slot_stride elements apart, rows in_row_stride apart), flags = this rank's n arrival counters of the

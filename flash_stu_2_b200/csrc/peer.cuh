@@ -30,3 +30,12 @@ __device__ __forceinline__ void peer_signal_when_last(const PeerDest* pd, unsign
       asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(pd->flag[p]) : "memory");
   }
 }
+
+// One exchange point as the exchange kernel (push + wait + combine in one launch, one CTA per row) sees it; lives in
+// the device memory of the rank that runs the kernel.
+struct PeerXchg {
+  int n, rank;
+  bf16* inbox[STU_MAX_PEERS];      // rank p's inbox of this exchange as mapped here: [slots][rows][d]
+  unsigned* flag[STU_MAX_PEERS];   // rank p's arrival counters of this exchange: [n senders][rows]
+  unsigned* epoch;                 // local [rows]: how many times each row has been exchanged
+};

@@ -322,6 +322,22 @@ def peer_combine(x, inbox: int, slot_stride: int, in_row_stride: int, slots: int
     _count()
 
 
+def peer_exchange(xchg: int, x, src, gather: bool, slot_stride: int, norm_w=None, xn=None, eps: float = RMS_EPS,
+                  wait_ms: int = 0):
+    """One exchange of a tensor-parallel token step in one launch: src (this rank's rows) into every rank's inbox,
+    wait for the other ranks' rows, x += their sum, optionally xn = RMSNorm(x) * norm_w (peer.PeerExchange.exchange)."""
+    _cuda(x, src)
+    rows, d = x.shape
+    assert src.shape[0] == rows and x.stride(1) == 1 and src.stride(1) == 1
+    assert norm_w is None or (xn is not None and xn.shape == x.shape and xn.stride(1) == 1)
+    rc = _lib.load().stu_peer_exchange(xchg, x.data_ptr(), x.stride(0), src.data_ptr(), src.stride(0), src.shape[1],
+                                       int(gather), slot_stride, _p(norm_w), _p(xn),
+                                       xn.stride(0) if xn is not None else 0, eps, rows, d,
+                                       status_word(x.device).data_ptr(), wait_ms, _dt(x), _stream())
+    _lib.check(rc, "stu_peer_exchange")
+    _count()
+
+
 def decode_approx_pipelined(x, norm_w, MinT, hist, taps8, pos, out, eps: float = RMS_EPS, add_residual: bool = True,
                             flags: int = 0):
     """The fused decode step of an approx STU layer (or of a channel shard: MinT [d_ch, d_in], add_residual=False) as

@@ -47,7 +47,14 @@ class PeerExchange:
         self.off_epoch = self.off_flags + _align(E * world * 4)
         self.off_ctr = self.off_epoch + _align(E * 4)
         self.off_desc = self.off_ctr + _align(E * 4)
-        self.bytes = self.off_desc + _align(E * self.desc_bytes)
+        # the single-launch exchange (push + wait + combine per row): counters per (exchange, sender, row), one epoch
+        # per (exchange, row), one record per exchange
+        self.xchg_bytes = _lib.load().stu_peer_xchg_bytes()
+        assert self.xchg_bytes == 8 + 16 * MAX_PEERS + 8
+        self.off_rflags = self.off_desc + _align(E * self.desc_bytes)
+        self.off_repoch = self.off_rflags + _align(E * world * rows * 4)
+        self.off_xdesc = self.off_repoch + _align(E * rows * 4)
+        self.bytes = self.off_xdesc + _align(E * self.xchg_bytes)
         self.base: Optional[int] = None          # own buffer
         self.bases: List[int] = []               # every rank's buffer as mapped here
         self._opened: List[int] = []
@@ -75,6 +82,15 @@ class PeerExchange:
                                 self.base + self.off_epoch + 4 * e, self.base + self.off_ctr + 4 * e)
         assert len(blob) == E * self.desc_bytes
         _lib.check(_lib.load().stu_peer_write(self.base + self.off_desc, blob, len(blob)), "stu_peer_write")
+        blob = b""
+        for e in range(E):
+            inbox = [b + self.off_inbox + e * w * self.rows * self.d * 2 for b in self.bases]
+            flag = [b + self.off_rflags + e * w * self.rows * 4 for b in self.bases]
+            pad = [0] * (MAX_PEERS - w)
+            blob += struct.pack(f"ii{MAX_PEERS}Q{MAX_PEERS}QQ", w, r, *inbox, *pad, *flag, *pad,
+                                self.base + self.off_repoch + e * self.rows * 4)
+        assert len(blob) == E * self.xchg_bytes
+        _lib.check(_lib.load().stu_peer_write(self.base + self.off_xdesc, blob, len(blob)), "stu_peer_write")
 
     @classmethod
     def connect(cls, kinds, rows, d, group=None) -> "PeerExchange":
@@ -133,6 +149,31 @@ class PeerExchange:
         ops.peer_combine(x, self.base + self.off_inbox + e * w * self.rows * self.d * 2, self.rows * self.d, self.d,
                          slots, self.base + self.off_flags + e * w * 4, w, self.base + self.off_epoch + 4 * e,
                          norm_w, xn, eps, wait_ms)
+
+    def exchange(self, e: int, x: torch.Tensor, src: torch.Tensor, norm_w: Optional[torch.Tensor] = None,
+                 xn: Optional[torch.Tensor] = None, eps: float = ops.RMS_EPS, wait_ms: int = 0):
+        """Exchange e in one launch: src [rows, d/world] (GATHER: this rank's channels) or [rows, d] (REDUCE: its
+        partial sum) goes to every rank, x [rows, d] += everybody's rows, optionally xn = RMSNorm(x) * norm_w."""
+        gather = self.kinds[e] == GATHER
+        assert src.shape[1] == (self.d // self.world if gather else self.d)
+        ops.peer_exchange(self.base + self.off_xdesc + e * self.xchg_bytes, x, src, gather, self.rows * self.d, norm_w,
+                          xn, eps, wait_ms)
+
+    def fake_arrival(self, e: int, sender: int, src: torch.Tensor, count: int):
+        """Test aid: make it look as if rank `sender` had delivered `src` for exchange e, `count` times so far (host
+        copies into this rank's inbox and counters).  Lets one GPU run a rank's exchange kernel without another
+        kernel it would have to wait for."""
+        w, rows, d = self.world, self.rows, self.d
+        src = src.detach().to("cpu").contiguous()
+        cols = src.shape[1]
+        col, slot = (sender * cols, 0) if self.kinds[e] == GATHER else (0, sender)
+        for row in range(rows):
+            dst = self.base + self.off_inbox + (((e * w + slot) * rows + row) * d + col) * 2
+            _lib.check(_lib.load().stu_peer_write(dst, src[row].view(torch.int16).numpy().tobytes(), cols * 2),
+                       "stu_peer_write")
+        blob = struct.pack(f"{rows}I", *([count] * rows))
+        _lib.check(_lib.load().stu_peer_write(self.base + self.off_rflags + ((e * w + sender) * rows) * 4, blob,
+                                              len(blob)), "stu_peer_write")
 
     def counters(self, e: int):
         """(arrival counters of exchange e, own send counter) read back from the device, for tests."""

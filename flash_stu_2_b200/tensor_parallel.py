@@ -11,11 +11,13 @@ Sharding (g ranks, rank r), one exchange per sub-layer:
     partial outputs all-reduced.  The KV ring of a rank holds its heads only.
   * LM head: vocabulary split; the logits shards are all-gathered (rank-major, padded rows cut off).
 Prefill: the collectives are torch.distributed calls (NCCL over NVLink on GPUs) between the same CUDA kernels the
-single-GPU path uses.  Token steps (bf16, all sequences at one position): the exchanges after the STU, attention and
-MLP sub-layers are fused into the kernels on either side of them (peer.PeerExchange): the channel-shard decode kernel
-and the down / c_proj kernels store their rows straight into every rank's inbox over NVLink and raise a flag, one
-combine kernel per exchange waits for all senders, adds the rows to the residual stream and applies the next
-sub-layer's RMSNorm.  Only the logits all-gather of a step stays a library collective.  Every rank ends a step with
+single-GPU path uses.  Token steps (bf16, all sequences at one position): each exchange after an STU, attention or
+MLP sub-layer is ONE kernel of this package (peer.PeerExchange.exchange, one CTA per sequence): it stores this rank's
+rows into every rank's inbox over NVLink (whole 16-byte vectors), raises a per-row flag, waits (bounded) for the
+other ranks' rows, adds them to the residual stream and applies the next sub-layer's RMSNorm - in place of a
+collective, an add and a norm kernel.  (A second mode, "push", stores from inside the producing kernels instead;
+measured slower: 2-byte stores over NVLink and a system-scope fence per CTA.)  Only the logits all-gather of a step
+stays a library collective.  Every rank ends a step with
 identical logits and, given the same uniforms, identical tokens.
 """
 from typing import Dict, Optional
@@ -150,7 +152,10 @@ class TensorParallelFlashSTU:
         self.window = int(ws[0] if isinstance(ws, (tuple, list)) else ws)
         self.eps = ops.RMS_EPS
         self.fused_decode = True
-        self.fused_exchange = True    # token steps: sub-layer exchanges inside the kernels (peer stores), not NCCL
+        # token steps: "exchange" = one kernel per sub-layer exchange pushes this rank's rows to the other ranks over
+        # peer memory, waits for theirs and folds them (and the next RMSNorm) into the residual stream; "push" = the
+        # producing kernels store into the inboxes themselves and a combine kernel waits; False = NCCL collectives
+        self.fused_exchange = "exchange"
         self._exchange = None
         self._derived = {}
         from .modules import Attention
@@ -266,13 +271,14 @@ class TensorParallelFlashSTU:
 
     def _token_step_fused(self, ids: torch.Tensor, cache, ex):
         """One new token per sequence: (residual stream [B,1,d], final-norm rows [B,d]).  Per layer the kernels are
-        [STU shard decode -> inboxes | c_attn, attention, c_proj -> inboxes], combine (+ MLP norm), gate/up,
-        down -> inboxes, combine (+ the next explicit norm)."""
+        [STU shard decode | c_attn, attention, c_proj], exchange (+ MLP norm), gate/up, down, exchange (+ the next
+        explicit norm); in "push" mode the producing kernels store into the inboxes and a combine kernel waits."""
         B = ids.shape[0]
         d, dl, n_layers = self.d, self.dl, self.cfg.n_layers
         x = ops.embed(ids, self.sd["tok_emb.weight"])
         x2 = x.view(B, d)
         xa, xb = self._xn
+        push = self.fused_exchange == "push"
         have_norm = False      # xa holds the attention norm of the current layer's input
         e = 0
         for i in range(n_layers):
@@ -286,28 +292,42 @@ class TensorParallelFlashSTU:
                 y = ops.swa_forward(qkv, k_ring, v_ring, pos, self.slopes, self.Hl, self.window, self.cfg.softcap,
                                     update_cache=True)
                 pos._host_t = t0 + 1
-                ops.linear_push(y.view(B, dl), self.sd[p + "attn.c_proj.weight"], ex.dest(e), d)
+                if push:
+                    ops.linear_push(y.view(B, dl), self.sd[p + "attn.c_proj.weight"], ex.dest(e), d)
+                else:
+                    src = ops.linear(y.view(B, dl), self.sd[p + "attn.c_proj.weight"])
             else:
                 hist, pos = cache[i]
                 t0 = host_pos(pos)
                 if t0 + 1 > self.capacity:
                     raise ValueError(f"sequence position {t0 + 1} exceeds the capacity {self.capacity}")
                 MinT, _, taps8 = self._stu_weights(i)
-                ops.decode_approx_push(x2, self.sd[p + "stu_norm.weight"], MinT, hist, taps8, pos, ex.dest(e), d,
-                                       self.eps)
+                if push:
+                    ops.decode_approx_push(x2, self.sd[p + "stu_norm.weight"], MinT, hist, taps8, pos, ex.dest(e), d,
+                                           self.eps)
+                else:
+                    src = torch.empty(B, dl, dtype=self.dtype, device=self.device)
+                    ops.decode_approx_shard(x2, self.sd[p + "stu_norm.weight"], MinT, hist, taps8, pos, src, self.eps)
                 pos._host_t = t0 + 1
-            ex.combine(e, x2, norm_w=self.sd[p + "mlp_norm.weight"], xn=xb, eps=self.eps)
+            if push:
+                ex.combine(e, x2, norm_w=self.sd[p + "mlp_norm.weight"], xn=xb, eps=self.eps)
+            else:
+                ex.exchange(e, x2, src, norm_w=self.sd[p + "mlp_norm.weight"], xn=xb, eps=self.eps)
             e += 1
             h = ops.linear(xb, self.sd[p + "mlp.gate_proj.weight"], W2=self.sd[p + "mlp.up_proj.weight"],
                            epilogue=ops.EPI_GELU_MUL)
-            ops.linear_push(h, self.sd[p + "mlp.down_proj.weight"], ex.dest(e), d)
             if i + 1 == n_layers:
                 nw = self.sd["norm.weight"]
             elif self._is_attn(i + 1):
                 nw = self.sd[f"layers.{i + 1}.attn_norm.weight"]
             else:
                 nw = None      # the STU shard kernel normalises its input itself
-            ex.combine(e, x2, norm_w=nw, xn=xa if nw is not None else None, eps=self.eps)
+            if push:
+                ops.linear_push(h, self.sd[p + "mlp.down_proj.weight"], ex.dest(e), d)
+                ex.combine(e, x2, norm_w=nw, xn=xa if nw is not None else None, eps=self.eps)
+            else:
+                ex.exchange(e, x2, ops.linear(h, self.sd[p + "mlp.down_proj.weight"]), norm_w=nw,
+                            xn=xa if nw is not None else None, eps=self.eps)
             have_norm = nw is not None
             e += 1
         return x, xa

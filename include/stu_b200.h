@@ -297,6 +297,21 @@ int stu_peer_combine(void* x, long long x_row_stride, const void* inbox, long lo
                      long long xn_row_stride, float eps, int rows, int d, int* status, int wait_ms, int dtype,
                      void* stream);
 
+/* One exchange of the token step in ONE launch, one CTA per row: the CTA copies this rank's contribution of its row
+ * (src [rows, cols]; gather != 0: the rank's cols = d / n channels, gather == 0: a full-width partial sum) into every
+ * rank's inbox with 16-byte stores, raises this sender's counter of the row on every rank, waits (bounded, wait_ms,
+ * 0: two seconds; status 10) for the other senders of the row, then x[row] = round(x[row] + round(sum)) and, with
+ * norm_w, xn[row] = RMSNorm(x[row]) * norm_w.  xchg = the exchange's record in this rank's device memory
+ * (stu_peer_xchg_bytes() bytes):
+ *   int n, rank;  void* inbox[8];  unsigned* flag[8];  unsigned* epoch;
+ * inbox[p] = rank p's inbox of the exchange ([slots][rows][d], blocks slot_stride elements apart), flag[p] = rank p's
+ * counters of the exchange ([n senders][rows]), epoch = this rank's [rows] exchange counts (all start at 0). */
+int stu_peer_xchg_bytes(void);
+int stu_peer_exchange(const void* xchg, void* x, long long x_row_stride, const void* src, long long src_row_stride,
+                      int cols, int gather, long long slot_stride, const void* norm_w, void* xn,
+                      long long xn_row_stride, float eps, int rows, int d, int* status, int wait_ms, int dtype,
+                      void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -463,6 +463,57 @@ def test_peer_exchange_of_the_token_step_with_all_ranks_emulated_on_one_gpu(worl
             ex.close()
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_single_launch_exchange_kernel_with_the_other_ranks_stood_in_by_host_copies(world):
+    """The exchange kernel (push + wait + combine + RMSNorm, one CTA per row) for every rank of a group on one GPU.
+    What the other ranks would have delivered is copied into the rank's inbox from the host before its kernel runs,
+    so the kernel never waits for another launch; its own rows must land in every other rank's inbox all the same."""
+    from flash_stu_2_b200 import ops
+    from flash_stu_2_b200.peer import GATHER, REDUCE, PeerExchange
+    dt = torch.bfloat16
+    B, d = 5, 128 * world
+    dl = d // world
+    torch.manual_seed(12)
+    exs = PeerExchange.emulate([GATHER, REDUCE], B, d, world)
+    norm = (1 + 0.1 * torch.randn(d)).to(dt).to(dev())
+    try:
+        for t in range(3):
+            x0 = torch.randn(B, d).to(dt).to(dev())
+            slices = [torch.randn(B, dl).to(dt).to(dev()) for _ in range(world)]
+            parts = [(torch.randn(B, d) / 2).to(dt).to(dev()) for _ in range(world)]
+            x1 = (x0.float() + torch.cat(slices, 1).float()).to(dt)
+            x2 = (x1.float() + torch.stack(parts).float().sum(0).to(dt).float()).to(dt)
+            for r in range(world):
+                for s_ in range(world):
+                    if s_ != r:
+                        exs[r].fake_arrival(0, s_, slices[s_], t + 1)
+                        exs[r].fake_arrival(1, s_, parts[s_], t + 1)
+            for r in range(world):
+                x = x0.clone()
+                xn = torch.empty_like(x)
+                exs[r].exchange(0, x, slices[r], norm_w=norm, xn=xn)
+                assert torch.equal(x, x1), (t, r)
+                close(xn, ops.rmsnorm(x1, norm), 8e-3)
+                exs[r].exchange(1, x, parts[r])
+                if world == 2:
+                    assert torch.equal(x, x2), (t, r)
+                else:
+                    close(x, x2, 8e-3)
+            ops.check_status()
+        # nobody else arrives for a further step (counters put back below the row's epoch): bounded wait, status 10,
+        # x untouched
+        for s_ in range(1, world):
+            exs[0].fake_arrival(0, s_, slices[s_], 0)
+        x = x0.clone()
+        exs[0].exchange(0, x, slices[0], wait_ms=50)
+        with pytest.raises(RuntimeError, match="status 10"):
+            ops.check_status()
+        assert torch.equal(x, x0)
+    finally:
+        for ex in exs:
+            ex.close()
+
+
 def test_decode_step_channel_shards_tile_the_layer():
     """Tensor-parallel form of the fused decode step: two ranks' channel shards (own history, own rows of
     M_inputs^T, own taps) give, concatenated and added to the input, exactly the whole-layer kernel's output."""
