@@ -962,31 +962,44 @@ def run_model_tp(a):
     samp = dict(spec["sampling"])
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
-    def timed(max_length):
+    def timed(max_length, timings=None):
         dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = ev(), ev()
         e0.record()
-        out = tp.generate(ids, max_length=max_length, uniforms=uniforms if samp.get("do_sample") else None, **samp)
+        out = tp.generate(ids, max_length=max_length, uniforms=uniforms if samp.get("do_sample") else None,
+                          timings=timings, **samp)
         e1.record()
         torch.cuda.synchronize()
         return parallel.max_over_ranks([e0.elapsed_time(e1)], device=dev)[0], out
 
-    timed(T0 + min(4, new))
+    timed(T0 + min(6, new))
     t_first = min(timed(T0 + 1)[0] for _ in range(2))
-    t_full, out = timed(T0 + new)
+    tm = {}
+    t_full, out = timed(T0 + new, tm)
     ops.check_status()
+    fused = tp._exchange is not None
+    step_ms = parallel.max_over_ranks([tm["replay_ms"]], device=dev)[0] / tm["replayed_steps"]
+    tp.fused_exchange = False          # the same token steps with NCCL collectives between the kernels
+    timed(T0 + min(6, new))
+    tm2 = {}
+    timed(T0 + new, tm2)
+    ops.check_status()
+    step_ms_nccl = parallel.max_over_ranks([tm2["replay_ms"]], device=dev)[0] / tm2["replayed_steps"]
     same = parallel.gather_token_ids(out[:1].contiguous(), world)
     if rank == 0:
         dec_ms = t_full - t_first
         print(json.dumps({
+            "token_step_ms": {"graph replays, device time": step_ms, "same with NCCL collectives": step_ms_nccl,
+                              "exchanges_in_kernels": fused},
             "metric": "decode tokens/s (aggregate over GPUs)", "value": B * (new - 1) / (dec_ms * 1e-3),
             "unit": "tokens/s", "n_gpus": world, "higher_is_better": True, "scaling": "strong", "dtype": spec["dtype"],
             "data": "synthetic",
             "config": {"workload": f"FlashSTU.generate {a.model}, tensor parallel over {world} GPUs: {cfg['n_layers']} layers "
                                    f"d={cfg['n_embd']} B={B} prompt {T0} +{new} tokens",
-                       "parallelism": f"tp{world} (all-gather per STU layer, all-reduce per attention / MLP block, NCCL)",
-                       "decode_launch": "one CUDA graph per token step (NCCL collectives captured), fused STU step on the rank's channels"},
+                       "parallelism": f"tp{world} (all-gather per STU layer, all-reduce per attention / MLP block: in token "
+                                      "steps one exchange kernel each over peer memory, in the prefill NCCL)",
+                       "decode_launch": "one CUDA graph per token step, fused STU step on the rank's channels"},
             "decode_ms_per_token_step": dec_ms / (new - 1),
             "prefill": {"value": B * T0 / (t_first * 1e-3), "unit": "tokens/s", "ms": t_first},
             "ranks_agree": bool((same == same[0]).all()),
