@@ -390,11 +390,17 @@ static int launch_skinny_bf16_mt(int MT, const void* A, long long lda, const voi
   return STU_ERR_SHAPE;
 }
 
+bool skinny_wide_takes(int M, int N, int K, int epi, bool norm);
+int skinny_wide_dispatch(const void* A, long long lda, const void* B, long long ldb, int M, int N, int K, int epi,
+                         const EpiArgs<bf16>& ep, cudaStream_t st);
+
 int skinny_dispatch(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N, int K,
                     int epi, const EpiArgsAny& ep, const void* norm_w, float eps, int dtype, int pdl, cudaStream_t st) {
   if (dtype == STU_BF16) {
     int MT = (M + 15) / 16;
     EpiArgs<bf16> e = ep.as<bf16>();
+    if (!B2 && skinny_wide_takes(M, N, K, epi, norm_w != nullptr))
+      return skinny_wide_dispatch(A, lda, B, ldb, M, N, K, epi, e, st);
     switch (epi) {
       case EPI_STORE: return launch_skinny_bf16_mt<EPI_STORE>(MT, A, lda, B, ldb, B2, M, N, K, e, norm_w, eps, pdl, st);
       case EPI_RESID: return launch_skinny_bf16_mt<EPI_RESID>(MT, A, lda, B, ldb, B2, M, N, K, e, norm_w, eps, pdl, st);

@@ -81,6 +81,24 @@ def test_linear_narrow_output_long_rows(dt):
 
 
 @pytest.mark.parametrize("epi", [0, 1])
+def test_linear_17_to_64_rows_32_features_per_cta(epi):
+    """Decode linears of 17..64 token rows (bf16): the kernel whose CTAs own 32 output features and split K over a
+    thread-block cluster (1, 2 or 4 CTAs), ragged N, K and M included."""
+    from flash_stu_2_b200 import ops
+    dt = torch.bfloat16
+    torch.manual_seed(8)
+    for (M, N, K) in [(32, 1536, 6144), (32, 1536, 1536), (32, 4608, 1536), (17, 72, 1024), (48, 1000, 2056),
+                      (64, 3072, 512), (33, 40, 264)]:
+        x = torch.randn(M, K).to(dt)
+        W = (torch.randn(N, K) / math.sqrt(K)).to(dt)
+        resid = torch.randn(M, N).to(dt)
+        ref = _lin_ref(x, W, None, resid, epi, dt)
+        y = ops.linear(x.to(dev()), W.to(dev()), resid=resid.to(dev()) if epi == 1 else None, epilogue=epi, backend=3)
+        ops.check_status()
+        close(y, ref, TOL[dt] / 2, what=f"{M}x{N}x{K}")
+
+
+@pytest.mark.parametrize("epi", [0, 1])
 def test_linear_wide_tensor_core_tiles(epi):
     """Outputs with at least two waves of 128 x 256 tiles take the wide-tile tcgen05 kernel; ragged M, N and K."""
     from flash_stu_2_b200 import ops
