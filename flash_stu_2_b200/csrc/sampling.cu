@@ -5,7 +5,9 @@
 // The reference draws with torch.multinomial; here one uniform u in [0,1) per sequence selects the
 // first kept vocabulary index whose running sum of exp(z - max) (vocabulary order) exceeds u * total,
 // which is reproducible across devices.
-// One CTA of 1024 threads per sequence.  top-k uses a 4-pass radix select over order-preserving keys;
+// One CTA of 1024 threads per sequence.  The scaled logits of the row are computed once, in the argmax pass, and kept
+// as order-preserving 32-bit keys in shared memory when the vocabulary fits (<= 52 k entries), so the later passes
+// neither re-read the logits nor repeat the division.  top-k uses a 4-pass radix select over those keys;
 // when top-k is given the (<= 1024) survivors are gathered, bitonic-sorted in shared memory and the
 // nucleus cut and the draw are made on that list, otherwise the draw scans the whole vocabulary.
 #include "common.cuh"
@@ -17,6 +19,10 @@ __device__ __forceinline__ uint32_t ord_key(float f) {
   uint32_t u = __float_as_uint(f);
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
+__device__ __forceinline__ float key_value(uint32_t k) {   // inverse of ord_key
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+constexpr int SP_CACHE_MAX = 52 * 1024;   // vocabulary entries whose keys fit beside the other shared arrays
 
 template <typename T> __device__ __forceinline__ float scaled_logit(const T* row, int i, float temperature) {
   float z = round_to<T>(__fdiv_rn(Elem<T>::to_f(row[i]), temperature));
@@ -27,7 +33,8 @@ template <typename T>
 __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logits, long long ld, int V,
                                                       float temperature, int top_k, float top_p, int do_sample,
                                                       const float* __restrict__ uniforms, long long* __restrict__ out,
-                                                      long long out_stride, int* __restrict__ status) {
+                                                      long long out_stride, int* __restrict__ status, int cache) {
+  extern __shared__ uint32_t s_key[];   // [V] when cache
   __shared__ float s_val[SP_CAND];
   __shared__ int s_idx[SP_CAND];
   __shared__ unsigned int s_hist[256];
@@ -43,8 +50,11 @@ __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logi
   int besti = V;
   for (int i = tid; i < V; i += SP_T) {
     float z = scaled_logit(row, i, temperature);
+    if (cache) s_key[i] = ord_key(z);
     if (z > best || (z == best && i < besti)) { best = z; besti = i; }
   }
+  // scaled logit of entry i for the later passes
+  auto zval = [&](int i) { return cache ? key_value(s_key[i]) : scaled_logit(row, i, temperature); };
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     float ob = __shfl_xor_sync(0xffffffffu, best, o);
@@ -87,7 +97,7 @@ __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logi
         const int i = base + tid;
         unsigned bin = 0xffffffffu;
         if (i < V) {
-          const unsigned key = ord_key(scaled_logit(row, i, temperature));
+          const unsigned key = cache ? s_key[i] : ord_key(scaled_logit(row, i, temperature));
           if ((key & mask) == prefix) bin = (key >> shift) & 255u;
         }
         const unsigned peers = __match_any_sync(0xffffffffu, bin);
@@ -111,7 +121,7 @@ __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logi
     if (tid == 0) s_count = 0;
     __syncthreads();
     for (int i = tid; i < V; i += SP_T) {
-      float z = scaled_logit(row, i, temperature);
+      float z = zval(i);
       if (ord_key(z) >= kth_key) {
         unsigned slot = atomicAdd(&s_count, 1u);
         if (slot < SP_CAND) { s_val[slot] = z; s_idx[slot] = i; }
@@ -204,7 +214,7 @@ __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logi
   const int chunk = (V + SP_T - 1) / SP_T;
   const int lo = tid * chunk, hi = min(V, lo + chunk);
   float part = 0.f;
-  for (int i = lo; i < hi; i++) part += __expf(scaled_logit(row, i, temperature) - zmax);
+  for (int i = lo; i < hi; i++) part += __expf(zval(i) - zmax);
   // block exclusive scan of the 1024 partial sums
   float incl = part;
 #pragma unroll
@@ -233,7 +243,7 @@ __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logi
     float cum = excl;
     int choice = hi - 1;
     for (int i = lo; i < hi; i++) {
-      cum += __expf(scaled_logit(row, i, temperature) - zmax);
+      cum += __expf(zval(i) - zmax);
       if (cum > target) { choice = i; break; }
     }
     atomicMin(&s_choice, choice);
@@ -252,14 +262,28 @@ extern "C" int stu_sample(const void* logits, long long ld, int B, int V, float 
   if (B <= 0 || V <= 0 || !(temperature > 0.f)) return STU_ERR_SHAPE;
   if (top_k > SP_CAND) return STU_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == STU_F32)
-    sample_kernel<float><<<B, SP_T, 0, st>>>((const float*)logits, ld, V, temperature, top_k, top_p, do_sample,
-                                             uniforms, out, out_stride, status);
-  else if (dtype == STU_BF16)
-    sample_kernel<bf16><<<B, SP_T, 0, st>>>((const bf16*)logits, ld, V, temperature, top_k, top_p, do_sample,
-                                            uniforms, out, out_stride, status);
-  else
+  // greedy selection makes one pass only: nothing to keep
+  const int cache = (do_sample && V <= SP_CACHE_MAX) ? 1 : 0;
+  const size_t smem = cache ? (size_t)V * sizeof(uint32_t) : 0;
+  if (dtype == STU_F32) {
+    if (cache) {
+      cudaError_t e = cudaFuncSetAttribute(sample_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           SP_CACHE_MAX * (int)sizeof(uint32_t));
+      if (e != cudaSuccess) return (int)e;
+    }
+    sample_kernel<float><<<B, SP_T, smem, st>>>((const float*)logits, ld, V, temperature, top_k, top_p, do_sample,
+                                                uniforms, out, out_stride, status, cache);
+  } else if (dtype == STU_BF16) {
+    if (cache) {
+      cudaError_t e = cudaFuncSetAttribute(sample_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           SP_CACHE_MAX * (int)sizeof(uint32_t));
+      if (e != cudaSuccess) return (int)e;
+    }
+    sample_kernel<bf16><<<B, SP_T, smem, st>>>((const bf16*)logits, ld, V, temperature, top_k, top_p, do_sample,
+                                               uniforms, out, out_stride, status, cache);
+  } else {
     return STU_ERR_DTYPE;
+  }
   STU_CHECK_LAUNCH();
   return STU_OK;
 }
