@@ -10,6 +10,8 @@
 // neither re-read the logits nor repeat the division.  top-k uses a 4-pass radix select over those keys;
 // when top-k is given the (<= 1024) survivors are gathered, bitonic-sorted in shared memory and the
 // nucleus cut and the draw are made on that list, otherwise the draw scans the whole vocabulary.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 constexpr int SP_T = 1024;
@@ -22,7 +24,8 @@ __device__ __forceinline__ uint32_t ord_key(float f) {
 __device__ __forceinline__ float key_value(uint32_t k) {   // inverse of ord_key
   return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
 }
-constexpr int SP_CACHE_MAX = 52 * 1024;   // vocabulary entries whose keys fit beside the other shared arrays
+constexpr int SP_CACHE_MAX = 50 * 1024 + 512;   // vocabulary entries whose keys fit beside the other shared arrays
+constexpr int SP_SUBH = 16;                     // radix histograms per CTA (one per pair of warps), two 16-bit bins per word
 
 template <typename T> __device__ __forceinline__ float scaled_logit(const T* row, int i, float temperature) {
   float z = round_to<T>(__fdiv_rn(Elem<T>::to_f(row[i]), temperature));
@@ -33,8 +36,10 @@ template <typename T>
 __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logits, long long ld, int V,
                                                       float temperature, int top_k, float top_p, int do_sample,
                                                       const float* __restrict__ uniforms, long long* __restrict__ out,
-                                                      long long out_stride, int* __restrict__ status, int cache) {
+                                                      long long out_stride, int* __restrict__ status, int cache,
+                                                      int variant) {
   extern __shared__ uint32_t s_key[];   // [V] when cache
+  __shared__ unsigned int s_sub[SP_SUBH][128];
   __shared__ float s_val[SP_CAND];
   __shared__ int s_idx[SP_CAND];
   __shared__ unsigned int s_hist[256];
@@ -88,11 +93,14 @@ __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logi
     for (int pass = 0; pass < 4; pass++) {
       const int shift = 24 - 8 * pass;
       if (tid < 256) s_hist[tid] = 0;
+      for (int i = tid; i < SP_SUBH * 128; i += SP_T) (&s_sub[0][0])[i] = 0;
       __syncthreads();
       const unsigned prefix = s_prefix;
       const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-      // logits share their sign and exponent bytes, so almost every key of a pass lands in one or two bins: lanes
-      // that hit the same bin are counted by one of them (match_any) instead of serialising on the shared counter
+      // logits share their sign and exponent bytes, so almost every key of a pass lands in one or two bins.  Each
+      // pair of warps counts into a histogram of its own (16-bit counters, two per word: a row has fewer than
+      // 65536 entries), which are summed afterwards; with one shared histogram the 32 warps queue on one counter.
+      unsigned int* sub = s_sub[warp >> 1];
       for (int base = 0; base < V; base += SP_T) {
         const int i = base + tid;
         unsigned bin = 0xffffffffu;
@@ -100,19 +108,50 @@ __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logi
           const unsigned key = cache ? s_key[i] : ord_key(scaled_logit(row, i, temperature));
           if ((key & mask) == prefix) bin = (key >> shift) & 255u;
         }
-        const unsigned peers = __match_any_sync(0xffffffffu, bin);
-        if (bin != 0xffffffffu && lane == __ffs(peers) - 1) atomicAdd(&s_hist[bin], (unsigned)__popc(peers));
+        if (variant == 0) {
+          const unsigned peers = __match_any_sync(0xffffffffu, bin);
+          if (bin != 0xffffffffu && lane == __ffs(peers) - 1) atomicAdd(&s_hist[bin], (unsigned)__popc(peers));
+        } else if (variant == 1) {
+          if (bin != 0xffffffffu) atomicAdd(&sub[bin >> 1], 1u << (16 * (bin & 1)));
+        } else {
+          const unsigned peers = __match_any_sync(0xffffffffu, bin);
+          if (bin != 0xffffffffu && lane == __ffs(peers) - 1)
+            atomicAdd(&sub[bin >> 1], (unsigned)__popc(peers) << (16 * (bin & 1)));
+        }
       }
       __syncthreads();
-      if (tid == 0) {
-        unsigned need = s_need, cum = 0;
-        int bin = 255;
-        for (; bin > 0; bin--) {
-          if (cum + s_hist[bin] >= need) break;
-          cum += s_hist[bin];
+      if (variant != 0 && tid < 256) {
+        unsigned c = 0;
+#pragma unroll
+        for (int h = 0; h < SP_SUBH; h++) c += (s_sub[h][tid >> 1] >> (16 * (tid & 1))) & 0xffffu;
+        s_hist[tid] = c;
+      }
+      __syncthreads();
+      // the bin that holds the need-th largest key: 8 bins per lane of warp 0, suffix sums across the lanes
+      if (warp == 0) {
+        const unsigned need = s_need;
+        unsigned t = 0;
+#pragma unroll
+        for (int j = 0; j < 8; j++) t += s_hist[8 * lane + j];
+        unsigned S = t;   // bins of this lane and of all higher lanes
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const unsigned n = __shfl_down_sync(0xffffffffu, S, o);
+          if (lane + o < 32) S += n;
         }
-        s_need = need - cum;
-        s_prefix = prefix | ((unsigned)bin << shift);
+        const unsigned reach = __ballot_sync(0xffffffffu, S >= need);
+        const int owner = reach ? 31 - __clz(reach) : 0;   // highest lane whose suffix reaches the need (else bin 0)
+        if (lane == owner) {
+          unsigned cum = S - t;
+          int bin = 8 * lane + 7;
+          for (; bin > 8 * lane; bin--) {
+            if (cum + s_hist[bin] >= need) break;
+            cum += s_hist[bin];
+          }
+          // (the lowest bin of the owner's range takes what is left, as bin 0 does in a sequential scan)
+          s_need = need - cum;
+          s_prefix = prefix | ((unsigned)bin << shift);
+        }
       }
       __syncthreads();
     }
@@ -264,6 +303,7 @@ extern "C" int stu_sample(const void* logits, long long ld, int B, int V, float 
   cudaStream_t st = (cudaStream_t)stream;
   // greedy selection makes one pass only: nothing to keep
   const int cache = (do_sample && V <= SP_CACHE_MAX) ? 1 : 0;
+  static const int variant = getenv("STU_SAMPLE_VARIANT") ? atoi(getenv("STU_SAMPLE_VARIANT")) : 2;
   const size_t smem = cache ? (size_t)V * sizeof(uint32_t) : 0;
   if (dtype == STU_F32) {
     if (cache) {
@@ -272,7 +312,7 @@ extern "C" int stu_sample(const void* logits, long long ld, int B, int V, float 
       if (e != cudaSuccess) return (int)e;
     }
     sample_kernel<float><<<B, SP_T, smem, st>>>((const float*)logits, ld, V, temperature, top_k, top_p, do_sample,
-                                                uniforms, out, out_stride, status, cache);
+                                                uniforms, out, out_stride, status, cache, (V < 65536) ? variant : 0);
   } else if (dtype == STU_BF16) {
     if (cache) {
       cudaError_t e = cudaFuncSetAttribute(sample_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -280,7 +320,7 @@ extern "C" int stu_sample(const void* logits, long long ld, int B, int V, float 
       if (e != cudaSuccess) return (int)e;
     }
     sample_kernel<bf16><<<B, SP_T, smem, st>>>((const bf16*)logits, ld, V, temperature, top_k, top_p, do_sample,
-                                               uniforms, out, out_stride, status, cache);
+                                               uniforms, out, out_stride, status, cache, (V < 65536) ? variant : 0);
   } else {
     return STU_ERR_DTYPE;
   }
