@@ -207,6 +207,19 @@ __global__ void __launch_bounds__(256) swa_decode_kernel(const T* __restrict__ q
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane % LPK, grp = lane / LPK;
   const int t0 = pos[2 * b];
+  if (update_cache) {
+    // Every CTA has read its position before it arrives here; the last one to arrive moves all positions on.  Doing
+    // this first (instead of after the output is stored) takes the fence, the atomic and the serial update off the
+    // end of the kernel, where nothing could hide them.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int total = gridDim.x * gridDim.y;
+      if (atomicAdd(&pos[1], 1) == total - 1) {
+        pos[1] = 0;
+        for (int i = 0; i < B; i++) pos[2 * i] += 1;
+      }
+    }
+  }
   const T* cur = qkv + (size_t)b * 3 * d + h * HD;   // q | k | v of the new token, this head
   float qv[VPL];
   {
@@ -299,18 +312,6 @@ __global__ void __launch_bounds__(256) swa_decode_kernel(const T* __restrict__ q
       }
     }
     out[(size_t)b * d + h * HD + threadIdx.x] = Elem<T>::from_f(num / den);
-  }
-  if (update_cache) {
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence();
-      const int total = gridDim.x * gridDim.y;
-      if (atomicAdd(&pos[1], 1) == total - 1) {
-        pos[1] = 0;
-        for (int i = 0; i < B; i++) pos[2 * i] += 1;
-        __threadfence();
-      }
-    }
   }
 }
 
