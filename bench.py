@@ -1009,8 +1009,8 @@ def run_model_tp(a):
 
 def run_model(a):
     """FlashSTU.generate() on a whole model with random-init weights (secondary workloads; the headline is the
-    block).  Decode tokens/s = B * (new - 1) / (time of a full generate - time of a generate that stops after the
-    first new token), CUDA events, one GPU."""
+    block).  Decode tokens/s = B / (device time per graph-replayed token step, CUDA events inside generate), one GPU;
+    the eager loop's figure is the difference of two whole-run times."""
     import tempfile
     import flash_stu_2_b200 as F
     from flash_stu_2_b200 import ops
@@ -1032,25 +1032,29 @@ def run_model(a):
     gen = torch.Generator(device=dev)
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
-    def timed(max_length, graph):
+    def timed(max_length, graph, timings=None):
         gen.manual_seed(0)
         e0, e1 = ev(), ev()
         torch.cuda.synchronize()
         e0.record()
-        out = model.generate(ids, max_length=max_length, generator=gen, cuda_graph=graph, **spec["sampling"])
+        out = model.generate(ids, max_length=max_length, generator=gen, cuda_graph=graph, timings=timings,
+                             **spec["sampling"])
         e1.record()
         torch.cuda.synchronize()
         return e0.elapsed_time(e1), out
 
     res = {}
+    tm = {}
     for graph in (True, False):
         timed(T0 + min(8, new), graph)                          # warm-up (derived weights, scratch)
         t_first = min(timed(T0 + 1, graph)[0] for _ in range(2))
-        t_full, out = timed(T0 + new, graph)
+        t_full, out = timed(T0 + new, graph, tm if graph else None)
         res[graph] = (t_first, t_full, out)
     ops.check_status()
     t_first, t_full, out = res[True]
-    dec_ms = t_full - t_first
+    # token steps: device time of the graph-replayed steps alone (the two eager steps and the capture before them are
+    # host work that varies by milliseconds from run to run, which makes differences of whole-run times useless)
+    dec_ms = tm["replay_ms"] / tm["replayed_steps"] * (new - 1) if tm.get("replayed_steps") else t_full - t_first
     n_param = sum(p.numel() for p in model.parameters())
     print(json.dumps({
         "metric": "decode tokens/s (aggregate over GPUs)", "value": B * (new - 1) / (dec_ms * 1e-3), "unit": "tokens/s",

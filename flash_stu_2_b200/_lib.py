@@ -61,6 +61,8 @@ _SIGNATURES = {
     "stu_lds_decode_features": ([_P, _LL, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P], c_int),
     "stu_swa_forward": ([_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                          _P], c_int),
+    "stu_decode_approx_projected": ([_P, _LL, _P, _LL, _P, _P, _P, _P, _LL, c_int, c_int, c_int, c_int, _P, c_int, _P],
+                                    c_int),
     "stu_peer_dest_bytes": ([], c_int),
     "stu_peer_alloc": ([_P, _LL], c_int),
     "stu_peer_free": ([_P], c_int),

@@ -230,6 +230,7 @@ __global__ void __launch_bounds__(256) swa_decode_kernel(const T* __restrict__ q
     for (int e = 0; e < VPL; e++) qv[e] *= scale;
   }
   const float slope = slopes[h];
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
   const int j_lo = max(0, t0 - window);
   const int nkeys = t0 - j_lo + 1;  // the new token included
   float m = -INFINITY, l = 0.f, acc[VPL];
@@ -255,29 +256,45 @@ __global__ void __launch_bounds__(256) swa_decode_kernel(const T* __restrict__ q
         }
       }
     }
+    // scores of the DEC_U keys of this group first, then ONE rescale of the running sums for all of them
+    float sc[DEC_U];
 #pragma unroll
     for (int u = 0; u < DEC_U; u++) {
       const int kk = base + u * 8 * KPW + grp;
-      float kf[VPL], vf[VPL];
+      float kf[VPL];
       kr[u].unpack(kf);
-      vr[u].unpack(vf);
       float dot = 0.f;
 #pragma unroll
       for (int e = 0; e < VPL; e++) dot = fmaf(qv[e], kf[e], dot);
 #pragma unroll
       for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      if (kk < nkeys) {
-        float sc = dot;
-        if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
-        sc -= slope * (float)(nkeys - 1 - kk);   // i - j
-        const float mnew = fmaxf(m, sc);
-        const float corr = __expf(m - mnew);     // 0 for the group's first key
-        const float pw = __expf(sc - mnew);
-        l = l * corr + pw;
-#pragma unroll
-        for (int e = 0; e < VPL; e++) acc[e] = fmaf(pw, vf[e], acc[e] * corr);
-        m = mnew;
+      if (softcap > 0.f) {
+        // bf16: hardware tanh, relative error 2^-11, below the bf16 rounding of the output (as in the prefill kernel)
+        float th;
+        if (sizeof(T) == 2) asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(dot * inv_cap));
+        else th = tanhf(dot * inv_cap);
+        dot = softcap * th;
       }
+      sc[u] = (kk < nkeys) ? dot - slope * (float)(nkeys - 1 - kk) : -INFINITY;   // ALiBi: i - j
+    }
+    float mnew = m;
+#pragma unroll
+    for (int u = 0; u < DEC_U; u++) mnew = fmaxf(mnew, sc[u]);
+    if (mnew > -INFINITY) {
+      const float corr = __expf(m - mnew);   // 0 while the group has seen no key yet
+      l *= corr;
+#pragma unroll
+      for (int e = 0; e < VPL; e++) acc[e] *= corr;
+#pragma unroll
+      for (int u = 0; u < DEC_U; u++) {
+        const float pw = __expf(sc[u] - mnew);   // 0 for a key past the end
+        float vf[VPL];
+        vr[u].unpack(vf);
+        l += pw;
+#pragma unroll
+        for (int e = 0; e < VPL; e++) acc[e] = fmaf(pw, vf[e], acc[e]);
+      }
+      m = mnew;
     }
   }
   const int gidx = warp * KPW + grp;

@@ -86,6 +86,8 @@ struct Params {
   int* status;
   int pdl;
   const PeerDest* peer;   // tensor parallelism: the output rows go to every rank's inbox instead of `out`
+  const bf16* xp_in;      // when set: the projected input of the new token, computed by the caller for the whole batch
+  long long xp_rstride;   //           (rows of d_ch values); norm_w, MinT and the projection warps' MMAs are not used
 };
 
 constexpr int NTHREADS = 13 * 32;   // 8 consumer warps, 1 producer warp, 4 projection warps
@@ -250,6 +252,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         const int b0 = bg * 8, c0 = cg * 8;
         const int nb = min(8, B - b0);
         // RMS statistics: warp gw takes sequences gw and gw + 4
+        if (!P.xp_in) {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
           const int bb = gw + 4 * h;
@@ -290,10 +293,12 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           s_red[gw][g * 8 + 2 * q + 1] = accp[1];
         }
         group_bar();
+        }   // !P.xp_in
         float term = 0.f, res = 0.f;
         const int bb = gt >> 3, cc = gt & 7;   // threads 0..63 of the group: (sequence, channel)
         if (gt < 64 && bb < nb) {
-          const float xp = round_to<bf16>((s_red[0][gt] + s_red[1][gt]) + (s_red[2][gt] + s_red[3][gt]));
+          const float xp = P.xp_in ? __bfloat162float(P.xp_in[(size_t)(b0 + bb) * P.xp_rstride + c0 + cc])
+                                   : round_to<bf16>((s_red[0][gt] + s_red[1][gt]) + (s_red[2][gt] + s_red[3][gt]));
           P.hist[((size_t)((size_t)(b0 + bb) * dch + c0 + cc) * 2 + p) * Lh + s] = __float2bfloat16_rn(xp);
           term = xp * __bfloat162float(P.taps8[(size_t)(c0 + cc) * LP + (Lh - 1)]);
           if (P.add_resid) res = __bfloat162float(P.x[(size_t)(b0 + bb) * P.x_rstride + c0 + cc]);
@@ -340,7 +345,12 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 static int launch_pipe(const void* x, long long x_row_stride, const void* norm_w, const void* MinT, void* hist,
                        const void* taps8, int* pos, void* out, long long out_row_stride, int B, int d_in, int d_ch,
                        int Lh, float eps, int add_residual, int* status, int dtype, void* stream,
-                       const PeerDest* peer) {
+                       const PeerDest* peer, const void* xp_in = nullptr, long long xp_row_stride = 0) {
+  if (xp_in) {   // projection done by the caller: x is only the residual, norm_w / MinT are not read
+    if ((add_residual && !x) || !hist || !taps8 || !pos || (!out && !peer)) return STU_ERR_NULL;
+    if (!x) x = xp_in;
+    norm_w = MinT = xp_in;
+  }
   if (!x || !norm_w || !MinT || !hist || !taps8 || !pos || (!out && !peer)) return STU_ERR_NULL;
   if (B <= 0 || d_in <= 0 || d_ch <= 0 || Lh <= 0 || d_in % 8 || d_ch % 8 || Lh % 8) return STU_ERR_SHAPE;
   if (add_residual && d_in != d_ch) return STU_ERR_SHAPE;
@@ -386,6 +396,8 @@ static int launch_pipe(const void* x, long long x_row_stride, const void* norm_w
   P.status = status;
   P.pdl = pdl;
   P.peer = peer;
+  P.xp_in = (const bf16*)xp_in;
+  P.xp_rstride = xp_row_stride;
 
   const size_t smem = (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * sizeof(uint64_t) + 1024;
   cudaError_t e = cudaFuncSetAttribute(stu_decode_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -418,4 +430,19 @@ extern "C" int stu_decode_approx_push(const void* x, long long x_row_stride, con
   if (!peer_dest) return STU_ERR_NULL;
   return launch_pipe(x, x_row_stride, norm_w, MinT, hist, taps8, pos, nullptr, dest_row_stride, B, d_in, d_ch, Lh, eps,
                      0, status, dtype, stream, (const PeerDest*)peer_dest);
+}
+
+// The decode step for a caller that has computed the projected input of the new token itself, as one GEMM over the
+// whole batch: xp [B, d_ch] = (rmsnorm(x) * norm_w) @ M_inputs (flash_stu/modules/stu.py:87), rounded to bf16.  The
+// kernel appends xp to hist, streams the history against the taps, advances pos and writes
+// out = (add_residual ? x : 0) + round(2 * taps . hist).  For batches of more than 8 sequences, where the per-row
+// projection inside stu_decode_approx_pipelined (48 KB of operands per 8 x 8 outputs) costs more than the row's stream.
+extern "C" int stu_decode_approx_projected(const void* x, long long x_row_stride, const void* xp,
+                                           long long xp_row_stride, void* hist, const void* taps8, int* pos, void* out,
+                                           long long out_row_stride, int B, int d_ch, int Lh, int add_residual,
+                                           int* status, int dtype, void* stream) {
+  if (!xp) return STU_ERR_NULL;
+  if (xp_row_stride % 8 || !aligned16(xp)) return STU_ERR_ALIGN;
+  return launch_pipe(x, x_row_stride, nullptr, nullptr, hist, taps8, pos, out, out_row_stride, B, d_ch, d_ch, Lh, 0.f,
+                     add_residual, status, dtype, stream, nullptr, xp, xp_row_stride);
 }

@@ -9,6 +9,8 @@ the cached decode defined here equals the reference's full-prefix forward row by
 import math
 from typing import Optional, Tuple
 
+import os
+
 import torch
 import torch.nn as nn
 
@@ -293,6 +295,8 @@ class STU(nn.Module):
     tensor_core_decode = True
     shared_tap_decode = True   # batches at one common position: the kernel with 8 channels x 8 sequences per CTA
     pipelined_decode = True    # ... and, of those, the persistent bulk-copy pipeline kernel
+    # from this batch size on, the token's projection is one GEMM of its own (STU_B200_PROJECTED_MIN_BATCH overrides)
+    projected_decode_min_batch = int(os.environ.get("STU_B200_PROJECTED_MIN_BATCH", "16"))
 
     def decode_step(self, x2d: torch.Tensor, norm_w: torch.Tensor, eps: float, entry, out2d: torch.Tensor):
         """out = x + STU(rmsnorm(x)) for one new token per sequence; appends to the cache."""
@@ -305,7 +309,14 @@ class STU(nn.Module):
         # rows of 8 sequences x 8 channels, slices of 256 cached positions per parity: the pipeline kernel pays a
         # per-row projection latency, which only long rows (or one row per SM) hide
         rows, nsl = (B + 7) // 8 * (d // 8), ((t >> 1) + 255) // 256
-        if (STU.pipelined_decode and STU.tensor_core_decode and STU.shared_tap_decode and taps8 is not None
+        if (B >= STU.projected_decode_min_batch and STU.pipelined_decode and STU.tensor_core_decode
+                and STU.shared_tap_decode and taps8 is not None and uniform_pos(pos) and d % 8 == 0
+                and x2d.shape[1] % 8 == 0):
+            # larger batches: the projection of the whole batch as one GEMM, then the pipeline kernel as a pure stream
+            xn = ops.rmsnorm(x2d, norm_w, eps)
+            xp = ops.linear(xn, MinT)
+            ops.decode_approx_projected(x2d, xp, hist, taps8, pos, out2d)
+        elif (STU.pipelined_decode and STU.tensor_core_decode and STU.shared_tap_decode and taps8 is not None
                 and uniform_pos(pos) and d % 8 == 0 and x2d.shape[1] % 8 == 0
                 and (nsl >= 8 or rows <= _sm_count(x2d.device))):
             # batch at one common position: the bulk-copy pipeline kernel

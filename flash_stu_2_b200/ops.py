@@ -282,6 +282,22 @@ def decode_approx_shard(x, norm_w, MinT, hist, taps8, pos, out, eps: float = RMS
     return out
 
 
+def decode_approx_projected(x, xp, hist, taps8, pos, out, add_residual: bool = True):
+    """Decode step of an approx STU sub-layer whose projected input xp [B, d_ch] the caller computed as one GEMM:
+    appends xp to the cache, out = (x +) taps . history."""
+    _cuda(xp, hist, taps8, pos, out)
+    B, dch, _, Lh = hist.shape
+    assert xp.shape == (B, dch) and out.shape == (B, dch) and xp.stride(1) == 1 and out.stride(1) == 1
+    assert hist.is_contiguous() and taps8.is_contiguous() and (x is not None or not add_residual)
+    rc = _lib.load().stu_decode_approx_projected(_p(x), x.stride(0) if x is not None else 0, xp.data_ptr(),
+                                                 xp.stride(0), hist.data_ptr(), taps8.data_ptr(), pos.data_ptr(),
+                                                 out.data_ptr(), out.stride(0), B, dch, Lh, int(add_residual),
+                                                 status_word(xp.device).data_ptr(), _dt(xp), _stream())
+    _lib.check(rc, "stu_decode_approx_projected")
+    _count()
+    return out
+
+
 def linear_push(x: torch.Tensor, W: torch.Tensor, dest: int, dest_row_stride: int):
     """x[M,K] @ W[N,K]^T stored into every tensor-parallel rank's inbox through the exchange descriptor at device
     address `dest` (peer.PeerExchange.dest); M <= 64, bf16."""

@@ -253,6 +253,15 @@ int stu_sample(const void* logits, long long ld, int B, int V, float temperature
                int do_sample, const float* uniforms, long long* out, long long out_stride, int* status, int dtype,
                void* stream);
 
+/* The same decode step for a caller that computed the projected input of the new token itself as one GEMM over the
+ * whole batch: xp [B, d_ch] = (rmsnorm(x) * norm_w) @ M_inputs (flash_stu/modules/stu.py:87), bf16.  Appends xp to
+ * hist, advances pos, out = (add_residual ? x : 0) + round(2 * taps . hist).  For batches of more than 8 sequences,
+ * where the per-row projection inside stu_decode_approx_pipelined costs more than the row's stream.  x may be NULL
+ * when add_residual = 0. */
+int stu_decode_approx_projected(const void* x, long long x_row_stride, const void* xp, long long xp_row_stride,
+                                void* hist, const void* taps8, int* pos, void* out, long long out_row_stride, int B,
+                                int d_ch, int Lh, int add_residual, int* status, int dtype, void* stream);
+
 /* ---- exchange between the GPUs of a tensor-parallel group, fused into the token loop's kernels ----------------
  * The reference is single-GPU (its sub-layers: flash_stu/layers/stu_layer.py:78-98,
  * flash_stu/layers/attention_layer.py); these calls replace the all-gather after a channel-sharded STU sub-layer and the

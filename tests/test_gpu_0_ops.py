@@ -532,6 +532,37 @@ def test_single_launch_exchange_kernel_with_the_other_ranks_stood_in_by_host_cop
             ex.close()
 
 
+@pytest.mark.parametrize("shape", [(17, 60, 256, 300), (32, 40, 128, 700), (9, 530, 64, 1100)])
+def test_decode_step_with_the_projection_done_by_the_caller(shape):
+    """Larger batches: rmsnorm + one GEMM give the projected input of the whole batch, the pipeline kernel only appends
+    it, streams the history and adds the residual.  Every step's row equals the full-prefix row, the cache equals the
+    projected inputs, positions advance."""
+    from flash_stu_2_b200 import ops
+    dt = torch.bfloat16
+    B, T, d, L = shape
+    Lh = ((L + 1) // 2 + 7) // 8 * 8
+    x, nw, Mi, fp, xp_ref, ref = _decode_fixture(dt, B, T, d, L)
+    hist = torch.full((B, d, 2, Lh), 3.0, dtype=dt, device=dev())   # stale values beyond the position must not matter
+    pos = torch.zeros(B, 2, dtype=torch.int32, device=dev())
+    taps8 = ops.taps_rev8(ops.taps_even(fp.to(dev()), Lh))
+    MinT = Mi.t().contiguous().to(dev())
+    xd, nwd = x.to(dev()), nw.to(dev())
+    outs = []
+    for t in range(T):
+        xt = xd[:, t].contiguous()
+        xp = ops.linear(ops.rmsnorm(xt, nwd), MinT)
+        out = torch.empty(B, d, dtype=dt, device=dev())
+        ops.decode_approx_projected(xt, xp, hist, taps8, pos, out)
+        outs.append(out)
+    ops.check_status()
+    assert pos[:, 0].tolist() == [T] * B and int(pos[0, 1]) == 0
+    close(torch.stack(outs, 1).cpu(), ref, 1.5e-2)
+    want = _hist_from(xp_ref, Lh)
+    for p_ in range(2):
+        n = (T - p_ + 1) // 2
+        close(hist[:, :, p_, :n], want[:, :, p_, :n], 1e-2)
+
+
 def test_decode_step_channel_shards_tile_the_layer():
     """Tensor-parallel form of the fused decode step: two ranks' channel shards (own history, own rows of
     M_inputs^T, own taps) give, concatenated and added to the input, exactly the whole-layer kernel's output."""
