@@ -36,14 +36,18 @@ __device__ __forceinline__ void mma_16816(float* c, uint32_t a0, uint32_t a1, ui
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int EPI, int MT, int KSPLIT>
+// NORM: x is RMS-normalised with the weight nw on the way in (statistics over the whole row in every CTA, the
+// normalised values rounded to bf16 as the reference's norm output is).
+template <int EPI, int MT, int KSPLIT, bool NORM>
 __global__ void __launch_bounds__(NW * 32) skinny_wide_kernel(const bf16* __restrict__ x, long long lda,
                                                               const bf16* __restrict__ W, long long ldb, int M, int N,
-                                                              int K, EpiArgs<bf16> ep) {
+                                                              int K, EpiArgs<bf16> ep, const bf16* __restrict__ nw,
+                                                              float eps) {
   constexpr int U = (MT <= 2) ? 2 : 1;   // chunks in flight per warp
   extern __shared__ float sm[];
   float* red = sm;                              // [NT][NW][MT][4][32]
   float* part = sm + NT * NW * MT * 128;        // [NT][MT][128], cluster partial (KSPLIT > 1)
+  __shared__ float s_r[MT * 16];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, q = lane & 3;
   const int n0 = blockIdx.x * (8 * NT);
@@ -60,6 +64,26 @@ __global__ void __launch_bounds__(NW * 32) skinny_wide_kernel(const bf16* __rest
   const int c_begin = KSPLIT > 1 ? (int)blockIdx.y * per : 0;
   const int c_end = KSPLIT > 1 ? min(nchunks_all, c_begin + per) : nchunks_all;
 
+  if (NORM) {
+    for (int m = warp; m < MT * 16; m += NW) {
+      float r = 0.f;
+      if (m < M) {
+        const bf16* src = x + (size_t)m * lda;
+        float ss = 0.f;
+        for (int k = lane * 8; k < K; k += 256) {
+          float v[8];
+          load_vec(src + k, v);
+#pragma unroll
+          for (int j = 0; j < 8; j++) ss += v[j] * v[j];
+        }
+        ss = warp_sum(ss);
+        r = rsqrtf(ss / (float)K + eps);
+      }
+      if (lane == 0) s_r[m] = r;
+    }
+    __syncthreads();
+  }
+
   float acc[NT][MT][4];
 #pragma unroll
   for (int j = 0; j < NT; j++)
@@ -69,7 +93,7 @@ __global__ void __launch_bounds__(NW * 32) skinny_wide_kernel(const bf16* __rest
       for (int i = 0; i < 4; i++) acc[j][t][i] = 0.f;
 
   for (int c0 = c_begin + warp; c0 < c_end; c0 += NW * U) {
-    uint4 wv[U][NT], xv[U][MT][2];
+    uint4 wv[U][NT], xv[U][MT][2], nwv[NORM ? U : 1];
 #pragma unroll
     for (int u = 0; u < U; u++) {
       const int ch = c0 + NW * u;
@@ -78,6 +102,7 @@ __global__ void __launch_bounds__(NW * 32) skinny_wide_kernel(const bf16* __rest
 #pragma unroll
       for (int j = 0; j < NT; j++)
         wv[u][j] = (kok && nvalid[j]) ? ldg_stream(wrow[j] + k) : make_uint4(0, 0, 0, 0);
+      if (NORM) nwv[u] = kok ? *reinterpret_cast<const uint4*>(nw + k) : make_uint4(0, 0, 0, 0);
 #pragma unroll
       for (int t = 0; t < MT; t++)
 #pragma unroll
@@ -91,12 +116,18 @@ __global__ void __launch_bounds__(NW * 32) skinny_wide_kernel(const bf16* __rest
     for (int u = 0; u < U; u++) {
       if (c0 + NW * u < c_end) {   // warp-uniform: mma.sync needs all 32 lanes
 #pragma unroll
-        for (int t = 0; t < MT; t++)
+        for (int t = 0; t < MT; t++) {
+          uint4 xa = xv[u][t][0], xb = xv[u][t][1];
+          if (NORM) {   // zero activations (rows past M, k past the row end) stay zero
+            xa = norm_pack(xa, s_r[t * 16 + g], nwv[u]);
+            xb = norm_pack(xb, s_r[t * 16 + 8 + g], nwv[u]);
+          }
 #pragma unroll
           for (int j = 0; j < NT; j++) {
-            mma_16816(acc[j][t], xv[u][t][0].x, xv[u][t][1].x, xv[u][t][0].y, xv[u][t][1].y, wv[u][j].x, wv[u][j].y);
-            mma_16816(acc[j][t], xv[u][t][0].z, xv[u][t][1].z, xv[u][t][0].w, xv[u][t][1].w, wv[u][j].z, wv[u][j].w);
+            mma_16816(acc[j][t], xa.x, xb.x, xa.y, xb.y, wv[u][j].x, wv[u][j].y);
+            mma_16816(acc[j][t], xa.z, xb.z, xa.w, xb.w, wv[u][j].z, wv[u][j].w);
           }
+        }
       }
     }
   }
@@ -145,11 +176,11 @@ __global__ void __launch_bounds__(NW * 32) skinny_wide_kernel(const bf16* __rest
   }
 }
 
-template <int EPI, int MT, int KSPLIT>
-int launch_wide(const void* A, long long lda, const void* B, long long ldb, int M, int N, int K,
-                const EpiArgs<bf16>& ep, cudaStream_t st) {
+template <int EPI, int MT, int KSPLIT, bool NORM>
+int launch_wide_n(const void* A, long long lda, const void* B, long long ldb, int M, int N, int K,
+                  const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st) {
   const size_t smem = (size_t)(NT * NW * MT * 128 + (KSPLIT > 1 ? NT * MT * 128 : 0)) * sizeof(float);
-  auto kern = skinny_wide_kernel<EPI, MT, KSPLIT>;
+  auto kern = skinny_wide_kernel<EPI, MT, KSPLIT, NORM>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   cudaLaunchConfig_t cfg = {};
@@ -164,29 +195,35 @@ int launch_wide(const void* A, long long lda, const void* B, long long ldb, int 
   at[0].val.clusterDim.z = 1;
   cfg.attrs = at;
   cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kern, (const bf16*)A, lda, (const bf16*)B, ldb, M, N, K, ep);
+  e = cudaLaunchKernelEx(&cfg, kern, (const bf16*)A, lda, (const bf16*)B, ldb, M, N, K, ep, (const bf16*)nw, eps);
   if (e != cudaSuccess) return (int)e;
   STU_CHECK_LAUNCH();
   return STU_OK;
 }
+template <int EPI, int MT, int KSPLIT>
+int launch_wide(const void* A, long long lda, const void* B, long long ldb, int M, int N, int K,
+                const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st) {
+  if (nw) return launch_wide_n<EPI, MT, KSPLIT, true>(A, lda, B, ldb, M, N, K, ep, nw, eps, st);
+  return launch_wide_n<EPI, MT, KSPLIT, false>(A, lda, B, ldb, M, N, K, ep, nw, eps, st);
+}
 
 template <int EPI, int MT>
 int launch_wide_split(int ks, const void* A, long long lda, const void* B, long long ldb, int M, int N, int K,
-                      const EpiArgs<bf16>& ep, cudaStream_t st) {
+                      const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st) {
   switch (ks) {
-    case 1: return launch_wide<EPI, MT, 1>(A, lda, B, ldb, M, N, K, ep, st);
-    case 2: return launch_wide<EPI, MT, 2>(A, lda, B, ldb, M, N, K, ep, st);
-    default: return launch_wide<EPI, MT, 4>(A, lda, B, ldb, M, N, K, ep, st);
+    case 1: return launch_wide<EPI, MT, 1>(A, lda, B, ldb, M, N, K, ep, nw, eps, st);
+    case 2: return launch_wide<EPI, MT, 2>(A, lda, B, ldb, M, N, K, ep, nw, eps, st);
+    default: return launch_wide<EPI, MT, 4>(A, lda, B, ldb, M, N, K, ep, nw, eps, st);
   }
 }
 
 template <int EPI>
 int launch_wide_mt(int ks, const void* A, long long lda, const void* B, long long ldb, int M, int N, int K,
-                   const EpiArgs<bf16>& ep, cudaStream_t st) {
+                   const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st) {
   switch ((M + 15) / 16) {
-    case 2: return launch_wide_split<EPI, 2>(ks, A, lda, B, ldb, M, N, K, ep, st);
-    case 3: return launch_wide_split<EPI, 3>(ks, A, lda, B, ldb, M, N, K, ep, st);
-    case 4: return launch_wide_split<EPI, 4>(ks, A, lda, B, ldb, M, N, K, ep, st);
+    case 2: return launch_wide_split<EPI, 2>(ks, A, lda, B, ldb, M, N, K, ep, nw, eps, st);
+    case 3: return launch_wide_split<EPI, 3>(ks, A, lda, B, ldb, M, N, K, ep, nw, eps, st);
+    case 4: return launch_wide_split<EPI, 4>(ks, A, lda, B, ldb, M, N, K, ep, nw, eps, st);
   }
   return STU_ERR_SHAPE;
 }
@@ -195,18 +232,19 @@ int launch_wide_mt(int ks, const void* A, long long lda, const void* B, long lon
 
 int device_sm_count();
 
-// 17..64 rows, store / residual epilogue, no fused norm.  STU_B200_DISABLE_WIDE_SKINNY=1 keeps the 8-feature kernel.
+// 17..64 rows, store / residual epilogue.  STU_B200_DISABLE_WIDE_SKINNY=1 keeps the 8-feature kernel.
 bool skinny_wide_takes(int M, int N, int K, int epi, bool norm) {
   static const bool off = getenv("STU_B200_DISABLE_WIDE_SKINNY") != nullptr;
-  return !off && !norm && M > 16 && M <= 64 && (epi == EPI_STORE || epi == EPI_RESID) && N >= 8 * NT && K >= 256;
+  (void)norm;
+  return !off && M > 16 && M <= 64 && (epi == EPI_STORE || epi == EPI_RESID) && N >= 8 * NT && K >= 256;
 }
 
 int skinny_wide_dispatch(const void* A, long long lda, const void* B, long long ldb, int M, int N, int K, int epi,
-                         const EpiArgs<bf16>& ep, cudaStream_t st) {
+                         const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st) {
   // split K over a cluster until there is about one CTA per SM, as long as every warp keeps at least one chunk
   const int ctas = (N + 8 * NT - 1) / (8 * NT), chunks = (K + 31) / 32, sms = device_sm_count();
   int ks = 1;
   while (ks < 4 && ctas * ks < sms && chunks / (2 * ks) >= NW) ks *= 2;
-  if (epi == EPI_STORE) return launch_wide_mt<EPI_STORE>(ks, A, lda, B, ldb, M, N, K, ep, st);
-  return launch_wide_mt<EPI_RESID>(ks, A, lda, B, ldb, M, N, K, ep, st);
+  if (epi == EPI_STORE) return launch_wide_mt<EPI_STORE>(ks, A, lda, B, ldb, M, N, K, ep, nw, eps, st);
+  return launch_wide_mt<EPI_RESID>(ks, A, lda, B, ldb, M, N, K, ep, nw, eps, st);
 }

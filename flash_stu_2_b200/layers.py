@@ -113,8 +113,12 @@ class AttentionLayer(nn.Module):
         xc = _inplace_target(x)
         B, T, d = xc.shape
         x2 = xc.view(B * T, d)
-        xn = ops.rmsnorm(xc, self.attn_norm.weight, self.attn_norm.eps)
-        y, entry = self.attn.attend(xn, past_key_value, use_cache)
+        if T == 1 and ops.can_fuse_norm(B, 3 * d, d, ops.EPI_STORE, x.dtype):
+            y, entry = self.attn.attend(xc, past_key_value, use_cache, norm_w=self.attn_norm.weight,
+                                        eps=self.attn_norm.eps)
+        else:
+            xn = ops.rmsnorm(xc, self.attn_norm.weight, self.attn_norm.eps)
+            y, entry = self.attn.attend(xn, past_key_value, use_cache)
         ops.linear(y.view(B * T, d), self.attn.c_proj.weight, resid=x2, out=x2, epilogue=ops.EPI_RESID)
         inter = self.mlp.intermediate_size
         if T == 1 and ops.can_fuse_norm(B, inter, d, ops.EPI_GELU_MUL, x.dtype):

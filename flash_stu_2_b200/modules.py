@@ -313,8 +313,10 @@ class STU(nn.Module):
                 and STU.shared_tap_decode and taps8 is not None and uniform_pos(pos) and d % 8 == 0
                 and x2d.shape[1] % 8 == 0):
             # larger batches: the projection of the whole batch as one GEMM, then the pipeline kernel as a pure stream
-            xn = ops.rmsnorm(x2d, norm_w, eps)
-            xp = ops.linear(xn, MinT)
+            if ops.can_fuse_norm(B, d, x2d.shape[1], ops.EPI_STORE, x2d.dtype):
+                xp = ops.linear(x2d, MinT, norm_w=norm_w, eps=eps)
+            else:
+                xp = ops.linear(ops.rmsnorm(x2d, norm_w, eps), MinT)
             ops.decode_approx_projected(x2d, xp, hist, taps8, pos, out2d)
         elif (STU.pipelined_decode and STU.tensor_core_decode and STU.shared_tap_decode and taps8 is not None
                 and uniform_pos(pos) and d % 8 == 0 and x2d.shape[1] % 8 == 0
@@ -387,10 +389,14 @@ class Attention(nn.Module):
         return (torch.zeros(batch, W, d, dtype=dt, device=device), torch.zeros(batch, W, d, dtype=dt, device=device),
                 new_pos(batch, device))
 
-    def attend(self, xn: torch.Tensor, entry=None, use_cache: bool = False):
-        """Heads merged, before c_proj: returns (y [B,T,d], entry)."""
+    def attend(self, xn: torch.Tensor, entry=None, use_cache: bool = False, norm_w=None, eps: float = 0.0):
+        """Heads merged, before c_proj: returns (y [B,T,d], entry).  With norm_w, xn is the un-normalised layer input
+        and the RMSNorm is applied inside the c_attn kernel (token steps)."""
         B, T, d = xn.shape
-        qkv = ops.linear(xn.reshape(B * T, d), self.c_attn.weight).view(B, T, 3 * d)
+        if norm_w is not None:
+            qkv = ops.linear(xn.reshape(B * T, d), self.c_attn.weight, norm_w=norm_w, eps=eps).view(B, T, 3 * d)
+        else:
+            qkv = ops.linear(xn.reshape(B * T, d), self.c_attn.weight).view(B, T, 3 * d)
         if entry is None and use_cache:
             entry = self.new_cache(B, xn.device)
         if entry is not None:

@@ -149,7 +149,8 @@ def test_bounded_wait_expiry_is_reported_and_the_context_survives():
 def test_linear_fused_norm_decode():
     from flash_stu_2_b200 import ops
     torch.manual_seed(2)
-    for (M, N, K, epi) in [(8, 4096, 1024, 2), (32, 1536, 1536, 0), (5, 104, 64, 1)]:
+    for (M, N, K, epi) in [(8, 4096, 1024, 2), (32, 1536, 1536, 0), (5, 104, 64, 1), (48, 4608, 1536, 0),
+                           (20, 1000, 520, 1), (64, 72, 2048, 0)]:
         dt = torch.bfloat16
         x = torch.randn(M, K).to(dt)
         nw = torch.randn(K).to(dt)
