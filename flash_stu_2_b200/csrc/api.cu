@@ -67,7 +67,10 @@ extern "C" int stu_linear(const void* x, long long x_row_stride, const void* W, 
   if (backend == BACKEND_AUTO) {
     // 17..64 rows: the weight-streaming kernel's time grows with M, the tcgen05 GEMM's does not but it needs enough
     // 128-wide column tiles to fill the machine (measured cross-over on a B200, weights from HBM)
-    if (sk_ok && tc_ok && prefers_tensor_gemm(M, N)) sk_ok = false;
+    // (gate/up at up to 32 rows stays on the weight-streaming side: its staged kernel keeps every SM pulling, while
+    // 32 rows are a quarter of one 128-row tile for the tensor-core GEMM)
+    if (sk_ok && tc_ok && prefers_tensor_gemm(M, N) && !(epilogue == EPI_GELU_MUL && M <= 32 && K % 32 == 0))
+      sk_ok = false;
     backend = sk_ok ? BACKEND_SKINNY : (tc_ok ? BACKEND_TCGEN05 : BACKEND_SIMT);
   }
   switch (backend) {

@@ -80,20 +80,28 @@ def test_linear_narrow_output_long_rows(dt):
         close(y, ref, TOL[dt] / 2)
 
 
-@pytest.mark.parametrize("epi", [0, 1])
-def test_linear_17_to_64_rows_32_features_per_cta(epi):
-    """Decode linears of 17..64 token rows (bf16): the kernel whose CTAs own 32 output features and split K over a
-    thread-block cluster (1, 2 or 4 CTAs), ragged N, K and M included."""
+@pytest.mark.parametrize("epi", [0, 1, 2])
+def test_linear_17_to_64_rows(epi):
+    """Decode linears of 17..64 token rows (bf16).  Store / residual: 32 output features per CTA, operands streamed
+    through registers, K over a cluster of up to 4 CTAs.  Gate/up at up to 32 rows: the kernel that stages the
+    activation rows in shared memory by bulk copies and has every weight load in flight at once (16 gate + 16 up rows
+    per CTA, K over a cluster of up to 8 CTAs).  Ragged N, K and M included (K not a multiple of 32 falls back to the
+    8-feature kernel)."""
     from flash_stu_2_b200 import ops
     dt = torch.bfloat16
     torch.manual_seed(8)
     for (M, N, K) in [(32, 1536, 6144), (32, 1536, 1536), (32, 4608, 1536), (17, 72, 1024), (48, 1000, 2056),
-                      (64, 3072, 512), (33, 40, 264)]:
+                      (64, 3072, 512), (33, 40, 264), (32, 6144, 1536), (25, 1000, 12288), (20, 40, 264),
+                      (32, 104, 8192)]:
+        if epi == 2 and M > 32 and N * K > 4e6:
+            continue
         x = torch.randn(M, K).to(dt)
         W = (torch.randn(N, K) / math.sqrt(K)).to(dt)
+        W2 = (torch.randn(N, K) / math.sqrt(K)).to(dt)
         resid = torch.randn(M, N).to(dt)
-        ref = _lin_ref(x, W, None, resid, epi, dt)
-        y = ops.linear(x.to(dev()), W.to(dev()), resid=resid.to(dev()) if epi == 1 else None, epilogue=epi, backend=3)
+        ref = _lin_ref(x, W, W2, resid, epi, dt)
+        y = ops.linear(x.to(dev()), W.to(dev()), W2=W2.to(dev()) if epi == 2 else None,
+                       resid=resid.to(dev()) if epi == 1 else None, epilogue=epi, backend=3)
         ops.check_status()
         close(y, ref, TOL[dt] / 2, what=f"{M}x{N}x{K}")
 
