@@ -29,6 +29,7 @@ _SIGNATURES = {
     "stu_set_status_word": ([_P], c_int),
     "stu_test_inject_wait_expiry": ([c_int], c_int),
     "stu_rmsnorm": ([_P, _P, _P, c_int, c_int, _LL, _LL, c_float, c_int, _P], c_int),
+    "stu_bias_act": ([_P, _P, _LL, c_int, _LL, c_int, c_int, _P], c_int),
     "stu_embed": ([_P, _P, _P, c_int, c_int, c_int, _P, c_int, _P], c_int),
     "stu_linear": ([_P, _LL, _P, _LL, _LL, _P, _P, _LL, _P, _LL, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                     _P, c_float, c_int, c_int, _P], c_int),

@@ -11,7 +11,7 @@ class FlashSTUConfig(PretrainedConfig):
 
     Same constructor signature and attribute names as the reference class.  Switches whose code
     path has no CUDA kernel here (use_flash_fft is ignored: there is a single convolution path;
-    tiling, the STU MLP sandwich and bias terms raise at module construction) are kept so that
+    tiling and bias terms raise at module construction) are kept so that
     existing configs load.
     """
     model_type = "FlashSTU"

@@ -97,3 +97,45 @@ extern "C" int stu_embed(const long long* ids, const void* table, void* out, int
   STU_CHECK_LAUNCH();
   return STU_OK;
 }
+
+// y[r, c] = act(y[r, c] + bias[c]) in place, one rounding after the bias and one after the activation (the reference's
+// nn.Linear bias followed by an activation module: mini_stu/stu.py:171-211 post-MLP; the SiLU between the STU
+// sandwich projections, flash_stu/layers/stu_layer.py:52,84).  act: 0 none, 1 ReLU, 2 GELU (erf), 3 tanh, 4 SiLU.
+template <typename T>
+__global__ void __launch_bounds__(256) bias_act_kernel(T* __restrict__ y, const T* __restrict__ bias, long long rows,
+                                                       int cols, long long y_rstride, int act) {
+  const long long total = rows * cols;
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
+    const long long r = i / cols;
+    const int c = (int)(i - r * cols);
+    T* p = y + r * y_rstride + c;
+    float v = Elem<T>::to_f(*p);
+    if (bias) v = round_to<T>(v + Elem<T>::to_f(bias[c]));
+    switch (act) {
+      case 1: v = fmaxf(v, 0.f); break;
+      case 2: v = 0.5f * v * (1.f + erff(v * 0.70710678118654752f)); break;
+      case 3: v = tanhf(v); break;
+      case 4: v = v / (1.f + expf(-v)); break;
+      default: break;
+    }
+    *p = Elem<T>::from_f(v);
+  }
+}
+
+extern "C" int stu_bias_act(void* y, const void* bias, long long rows, int cols, long long y_row_stride, int act,
+                            int dtype, void* stream) {
+  if (!y) return STU_ERR_NULL;
+  if (rows < 0 || cols <= 0 || act < 0 || act > 4) return STU_ERR_SHAPE;
+  if (rows == 0) return STU_OK;
+  const long long total = rows * cols;
+  const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == STU_F32)
+    bias_act_kernel<float><<<grid, 256, 0, st>>>((float*)y, (const float*)bias, rows, cols, y_row_stride, act);
+  else if (dtype == STU_BF16)
+    bias_act_kernel<bf16><<<grid, 256, 0, st>>>((bf16*)y, (const bf16*)bias, rows, cols, y_row_stride, act);
+  else
+    return STU_ERR_DTYPE;
+  STU_CHECK_LAUNCH();
+  return STU_OK;
+}

@@ -16,11 +16,23 @@ class STULayer(nn.Module):
     def __init__(self, config, phi, n):
         super().__init__()
         self.config = config
-        if config.stu_enable_mlp_sandwich:
-            raise NotImplementedError("stu_enable_mlp_sandwich has no kernel here")
         self.stu_norm = RMSNorm(config.n_embd, dtype=config.torch_dtype)
-        self.stu_mlp_enabled = False
-        self.stu = STU(config, phi, n)
+        # STU sandwich (flash_stu/layers/stu_layer.py:39-63,83-88): up-projection, SiLU, the STU on the hidden width,
+        # down-projection
+        self.stu_mlp_enabled = bool(config.stu_enable_mlp_sandwich)
+        if self.stu_mlp_enabled:
+            if config.bias:
+                raise NotImplementedError("bias=True has no kernel here (the reference default is bias=False)")
+            self.stu_mlp_hidden_size = (config.stu_mlp_hidden_size if config.stu_mlp_hidden_size is not None
+                                        else config.intermediate_size)
+            self.stu_mlp_in_proj = nn.Linear(config.n_embd, self.stu_mlp_hidden_size, bias=False,
+                                             dtype=config.torch_dtype)
+            self.stu_mlp_act = nn.SiLU()
+            self.stu = STU(config, phi, n, feature_dim=self.stu_mlp_hidden_size)
+            self.stu_mlp_out_proj = nn.Linear(self.stu_mlp_hidden_size, config.n_embd, bias=False,
+                                              dtype=config.torch_dtype)
+        else:
+            self.stu = STU(config, phi, n)
         self.mlp_norm = RMSNorm(config.n_embd, dtype=config.torch_dtype)
         self.mlp = MLP(config, dtype=config.torch_dtype)
         self._scratch = {}
@@ -51,6 +63,40 @@ class STULayer(nn.Module):
         ahead[1] = t + 1
         pos._host_t = t + 1
         return hist, pos
+
+    def _sandwich(self, xc, past_key_value, use_cache):
+        """x += out_proj(STU(silu(in_proj(norm(x))))) for any number of new positions; the cache holds the projected
+        history of the hidden width.  Token steps on a bf16 batch at one position read their position on the device
+        (the projection is a GEMM, the pipeline kernel appends and streams); other token steps are a one-position
+        prefill, whose position is a host argument."""
+        from .modules import host_pos, uniform_pos
+        B, T, d = xc.shape
+        Hs = self.stu_mlp_hidden_size
+        x2 = xc.view(B * T, d)
+        xn = ops.rmsnorm(x2, self.stu_norm.weight, self.stu_norm.eps)
+        h = ops.linear(xn, self.stu_mlp_in_proj.weight)
+        ops.bias_act(h, None, ops.ACT_SILU)
+        entry = past_key_value
+        taps8 = self.stu.prepared()[2] if self.stu.use_approx else None
+        if (T == 1 and entry is not None and taps8 is not None and uniform_pos(entry[1]) and Hs % 8 == 0
+                and STU.pipelined_decode):
+            hist, pos = entry
+            t = host_pos(pos)
+            if t + 1 > self.stu.capacity:
+                raise ValueError(f"sequence position {t + 1} exceeds the capacity {self.stu.capacity}")
+            xp = ops.linear(h, self.stu.prepared()[0])
+            y = torch.empty(B, Hs, dtype=xc.dtype, device=xc.device)
+            ops.decode_approx_projected(None, xp, hist, taps8, pos, y, add_residual=False)
+            pos._host_t = t + 1
+        else:
+            y3 = torch.zeros(B, T, Hs, dtype=xc.dtype, device=xc.device)
+            if self.stu.use_approx:
+                entry = self.stu.add_to_residual(h.view(B, T, Hs), y3, entry, use_cache)
+            else:
+                entry = self.stu.full_forward(h.view(B, T, Hs), None, y3, entry, use_cache)
+            y = y3.view(B * T, Hs)
+        ops.linear(y, self.stu_mlp_out_proj.weight, resid=x2, out=x2, epilogue=ops.EPI_RESID)
+        return entry
 
     def _can_fuse(self, x, entry):
         from .modules import uniform_pos
@@ -85,7 +131,11 @@ class STULayer(nn.Module):
     def forward(self, x: torch.Tensor, past_key_value=None, use_cache=False):
         xc = _inplace_target(x)
         B, T, d = xc.shape
-        if T == 1 and past_key_value is not None:
+        if self.stu_mlp_enabled:
+            entry = self._sandwich(xc, past_key_value, use_cache)
+            x2 = xc.view(B * T, d)
+            self.mlp.apply_residual(ops.rmsnorm(x2, self.mlp_norm.weight, self.mlp_norm.eps), x2, x2)
+        elif T == 1 and past_key_value is not None:
             entry = self._decode(xc, past_key_value)
         else:
             xn = ops.rmsnorm(xc, self.stu_norm.weight, self.stu_norm.eps)

@@ -64,8 +64,8 @@ class MiniSTU(nn.Module):
         super().__init__()
         if backend not in ("spectral", "lds"):
             raise ValueError(f"unknown backend {backend!r}")
-        if use_mlp:
-            raise NotImplementedError("MiniSTU(use_mlp=True) (plain post-MLP) is not part of this implementation")
+        if use_mlp and mlp_activation.lower() not in ("relu", "gelu", "tanh"):
+            raise ValueError(f"Unsupported activation: {mlp_activation}")
         self.seq_len, self.num_filters = seq_len, num_filters
         self.input_dim, self.output_dim = input_dim, output_dim
         self.use_hankel_L, self.use_mlp, self.dtype, self.backend = use_hankel_L, use_mlp, dtype, backend
@@ -97,7 +97,31 @@ class MiniSTU(nn.Module):
         if not use_hankel_L:
             self.M_phi_minus = nn.Parameter(
                 torch.randn(num_filters, input_dim, output_dim, dtype=dtype, device=self.device) * scale)
+        # optional post-MLP on the operator's output (mini_stu/stu.py:171-211): the same nn.Sequential of Linear (with
+        # bias), activation and dropout modules as the reference, so that state dicts carry over; only the Linear
+        # parameters are read here, the layers run as stu_linear + stu_bias_act
         self.mlp = None
+        self._mlp_plan = []
+        if use_mlp:
+            hid = mlp_hidden_dim if mlp_hidden_dim is not None else output_dim * 2
+            act_code = {"relu": ops.ACT_RELU, "gelu": ops.ACT_GELU, "tanh": ops.ACT_TANH}[mlp_activation.lower()]
+            act_mod = {"relu": nn.ReLU, "gelu": nn.GELU, "tanh": nn.Tanh}[mlp_activation.lower()]
+            layers = []
+            for i in range(mlp_num_layers):
+                if mlp_num_layers == 1:
+                    layers.append(nn.Linear(output_dim, output_dim, dtype=dtype, device=self.device))
+                    self._mlp_plan.append((len(layers) - 1, ops.ACT_NONE))
+                    break
+                d_i = output_dim if i == 0 else hid
+                d_o = output_dim if i == mlp_num_layers - 1 else hid
+                layers.append(nn.Linear(d_i, d_o, dtype=dtype, device=self.device))
+                last = i == mlp_num_layers - 1
+                self._mlp_plan.append((len(layers) - 1, ops.ACT_NONE if last else act_code))
+                if not last:
+                    layers.append(act_mod())
+                    if mlp_dropout > 0.0:
+                        layers.append(nn.Dropout(mlp_dropout))   # inference: identity
+            self.mlp = nn.Sequential(*layers)
         cfg = SimpleNamespace(num_eigh=num_filters, n_embd=input_dim, use_hankel_L=use_hankel_L, use_approx=False,
                               torch_dtype=dtype, d_in_tile=None, d_out_tile=None)
         inner = STU(cfg, phi, self.n)
@@ -233,7 +257,16 @@ class MiniSTU(nn.Module):
         op = self._op
         if op.phi.device != self.phi.device:
             op.phi = self.phi
-        return op(x)
+        y = op(x)
+        if self.mlp is not None:
+            B, T, _ = y.shape
+            h = y.view(B * T, -1)
+            for idx, act in self._mlp_plan:
+                lin = self.mlp[idx]
+                h = ops.linear(h, lin.weight)
+                ops.bias_act(h, lin.bias, act)
+            y = h.view(B, T, -1)
+        return y
 
     def get_num_params(self) -> int:
         return sum(p.numel() for p in self.parameters())

@@ -193,6 +193,12 @@ class FlashSTU(PreTrainedModel):
         # cannot issue as fast as the GPU retires them.  cuda_graph=False keeps the eager loop.
         capacity = min(self.config.seq_len, getattr(self.config, "cache_len", None) or self.config.seq_len)
         use_graph = bool(kwargs.get("cuda_graph", True)) and use_cache and steps > 3 and max_length - 1 <= capacity
+        # a sandwich layer's token step reads its position on the device only in the bf16 approx form
+        for layer in self.layers:
+            if getattr(layer, "stu_mlp_enabled", False) and not (
+                    layer.stu.use_approx and self.config.torch_dtype == torch.bfloat16
+                    and layer.stu_mlp_hidden_size % 8 == 0):
+                use_graph = False
         graph = None
         for step in range(steps):
             cur = T0 + step

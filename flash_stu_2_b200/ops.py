@@ -110,6 +110,21 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = RMS_EPS, out: Op
     return out.reshape(x.shape)
 
 
+ACT_NONE, ACT_RELU, ACT_GELU, ACT_TANH, ACT_SILU = 0, 1, 2, 3, 4
+
+
+def bias_act(y: torch.Tensor, bias: Optional[torch.Tensor], act: int = ACT_NONE):
+    """In place: y[..., c] = act(y[..., c] + bias[c]) (bias may be None)."""
+    _cuda(y, bias)
+    cols = y.shape[-1]
+    y2 = y.view(-1, cols)
+    assert y2.stride(1) == 1 and (bias is None or (bias.shape == (cols,) and bias.is_contiguous()))
+    rc = _lib.load().stu_bias_act(y2.data_ptr(), _p(bias), y2.shape[0], cols, y2.stride(0), act, _dt(y), _stream())
+    _lib.check(rc, "stu_bias_act")
+    _count()
+    return y
+
+
 def embed(ids: torch.Tensor, table: torch.Tensor):
     _cuda(ids, table)
     ids = ids.contiguous().to(torch.int64)

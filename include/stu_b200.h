@@ -48,6 +48,12 @@ int stu_test_inject_wait_expiry(int wait_ms);
 int stu_rmsnorm(const void* x, const void* w, void* y, int rows, int d, long long x_row_stride,
                 long long y_row_stride, float eps, int dtype, void* stream);
 
+/* y[r, c] = act(y[r, c] + bias[c]) in place (bias may be NULL); act: 0 none, 1 ReLU, 2 GELU (erf form), 3 tanh,
+ * 4 SiLU.  The nn.Linear bias + activation modules of the MiniSTU post-MLP (mini_stu/stu.py:171-211) and the SiLU
+ * between the projections of the STU sandwich (flash_stu/layers/stu_layer.py:52,84). */
+int stu_bias_act(void* y, const void* bias, long long rows, int cols, long long y_row_stride, int act, int dtype,
+                 void* stream);
+
 /* out[r,:] = table[ids[r],:] (int64 ids).  Replaces nn.Embedding at flash_stu/model.py:152. */
 int stu_embed(const long long* ids, const void* table, void* out, int rows, int d, int vocab, int* status,
               int dtype, void* stream);

@@ -214,6 +214,30 @@ def stu_layer(x: Tensor, p: Dict[str, Tensor], phi: Tensor, n: int, use_approx: 
     return x + mlp(rmsnorm(x, p["mlp_norm.weight"]), p)
 
 
+def stu_layer_sandwich(x: Tensor, p: Dict[str, Tensor], phi: Tensor, n: int, use_approx: bool) -> Tensor:
+    """STULayer._forward_impl with stu_enable_mlp_sandwich, flash_stu/layers/stu_layer.py:39-63,83-88:
+    up-projection, SiLU, the STU on the hidden width, down-projection; then the MLP half as in stu_layer."""
+    h = rmsnorm(x, p["stu_norm.weight"])
+    h = F.linear(h, p["stu_mlp_in_proj.weight"])
+    h = F.silu(h)
+    h = stu_forward(h, phi, _sub(p, "stu."), n, use_approx)
+    h = F.linear(h, p["stu_mlp_out_proj.weight"])
+    x = x + h
+    return x + mlp(rmsnorm(x, p["mlp_norm.weight"]), p)
+
+
+def post_mlp(y: Tensor, sd: Dict[str, Tensor], activation: str) -> Tensor:
+    """The nn.Sequential post-MLP of MiniSTU(use_mlp=True), mini_stu/stu.py:171-211,267: Linear layers (with bias)
+    at the indices present in the state dict, the activation after every layer but the last."""
+    act = {"relu": F.relu, "gelu": F.gelu, "tanh": torch.tanh}[activation]
+    idx = sorted({int(k.split(".")[1]) for k in sd if k.startswith("mlp.") and k.endswith(".weight")})
+    for n_, i in enumerate(idx):
+        y = F.linear(y, sd[f"mlp.{i}.weight"], sd[f"mlp.{i}.bias"])
+        if n_ + 1 < len(idx):
+            y = act(y)
+    return y
+
+
 def attention_layer(x: Tensor, p: Dict[str, Tensor], n_heads: int, window: int, softcap: float,
                     past=None):
     """AttentionLayer._forward_impl, flash_stu/layers/attention_layer.py:50-66."""

@@ -306,11 +306,59 @@ def golden_c1_full(tmp):
     save("c1_full", rec)
 
 
+def golden_variants(tmp):
+    """Inference variants next to the benchmark configurations: the STU layer with the MLP sandwich
+    (flash_stu/layers/stu_layer.py:39-63,83-88: in_proj -> SiLU -> STU on the hidden width -> out_proj), full-length
+    and shorter inputs, fp32 and bf16; MiniSTU with the post-MLP (mini_stu/stu.py:171-211) in its three shapes."""
+    from mini_stu import MiniSTU
+    out = {}
+    L, K, d, Hs = 128, 8, 64, 96
+    phi = make_phi(L, K)
+    for dt in (torch.float32, torch.bfloat16):
+        torch.manual_seed(21)
+        cfg = FlashSTUConfig(n_embd=d, seq_len=L, num_eigh=K, use_approx=True, use_attn=False, mlp_scale=4,
+                             use_flash_fft=False, torch_dtype=dt, n_layers=1, vocab_size=1, n_heads=1,
+                             stu_enable_mlp_sandwich=True, stu_mlp_hidden_size=Hs)
+        n = nearest_power_of_two(L * 2 - 1, round_up=True)
+        blk = FlashSTUBlock(config=cfg, phi=phi.to(dt), n=n)
+        for name, p in blk.named_parameters():
+            if ".stu.M_" in name:
+                nn.init.xavier_normal_(p)
+        full = full_sgn(blk)
+        x = torch.randn(3, L, d).to(dt)
+        T = 51
+        with torch.no_grad():
+            y = blk(x.clone()).clone()
+            set_len(blk, T, full)
+            y_short = blk(x[:, :T].clone()).clone()
+        out[f"sandwich_approx_{str(dt).split('.')[-1]}"] = {
+            "x": x, "y": y, "y_short": y_short, "T_short": T, "sd": sd_of(blk), "n": n, "L": L, "K": K, "d": d,
+            "hidden": Hs}
+    L, K, din, dout = 64, 8, 12, 20
+    phi = make_phi(L, K)
+    for name, kw in (("mini_mlp_relu2", dict(mlp_num_layers=2, mlp_activation="relu")),
+                     ("mini_mlp_gelu3", dict(mlp_num_layers=3, mlp_activation="gelu", mlp_hidden_dim=24)),
+                     ("mini_mlp_tanh2", dict(mlp_num_layers=2, mlp_activation="tanh", mlp_hidden_dim=16)),
+                     ("mini_mlp_single", dict(mlp_num_layers=1))):
+        torch.manual_seed(22)
+        m = MiniSTU(seq_len=L, num_filters=K, input_dim=din, output_dim=dout, use_flash_fft=False, use_mlp=True,
+                    dtype=torch.float32, precomputed_filters=phi, **kw)
+        x = torch.randn(2, L, din)
+        with torch.no_grad():
+            y = m(x)
+        out[name] = {"x": x, "y": y.clone(), "phi": phi, "kw": kw, "sd": sd_of(m)}
+    save("variants", out)
+
+
 if __name__ == "__main__":
     with tempfile.TemporaryDirectory() as tmp:
+        if len(sys.argv) > 1 and sys.argv[1] == "variants":
+            golden_variants(tmp)
+            raise SystemExit(0)
         golden_stu_modules(tmp)
         golden_models(tmp)
         golden_blocks(tmp)
         golden_mini(tmp)
         golden_slopes()
         golden_c1_full(tmp)
+        golden_variants(tmp)

@@ -230,3 +230,50 @@ def test_cache_laid_out_for_fewer_positions_than_the_filters(golden):
     ops.check_status()
     assert cache[0].shape[3] < (r["L"] + 1) // 2
     close(torch.cat(rows, 1).cpu(), r["y"][:, :cap], 2e-2)
+
+
+@pytest.mark.parametrize("name,tol", [("sandwich_approx_float32", 1e-3), ("sandwich_approx_bfloat16", 2e-2)])
+def test_stu_layer_with_the_mlp_sandwich_matches_reference_golden(golden, name, tol):
+    """stu_enable_mlp_sandwich (in_proj -> SiLU -> STU on the hidden width -> out_proj): the whole input, a shorter
+    input, and prefill + cached single-token steps (bf16: the steps read their position on the device) against the
+    reference's own outputs."""
+    import flash_stu_2_b200 as F
+    from flash_stu_2_b200 import ops
+    r = golden("variants")[name]
+    dt = r["x"].dtype
+    cfg = F.FlashSTUConfig(n_embd=r["d"], seq_len=r["L"], num_eigh=r["K"], use_approx=True, use_attn=False,
+                           mlp_scale=4, torch_dtype=dt, n_layers=1, vocab_size=1, n_heads=1,
+                           stu_enable_mlp_sandwich=True, stu_mlp_hidden_size=r["hidden"])
+    blk = F.FlashSTUBlock(config=cfg, phi=r["sd"]["phi"].clone(), n=r["n"])
+    blk.load_state_dict(r["sd"])
+    blk = blk.to(dev()).eval()
+    x = r["x"].to(dev())
+    T, Ts = x.shape[1], r["T_short"]
+    with torch.no_grad():
+        close(blk(x.clone()).cpu(), r["y"], tol)
+        close(blk(x[:, :Ts].clone()).cpu(), r["y_short"], tol)
+        T1 = T - 9
+        y1, cache = blk(x[:, :T1].clone(), use_cache=True)
+        rows = [y1]
+        for t in range(T1, T):
+            yt, cache = blk(x[:, t:t + 1].clone(), past_key_value=cache, use_cache=True)
+            rows.append(yt)
+    ops.check_status()
+    assert int(cache[1][0, 0]) == T
+    close(torch.cat(rows, 1).cpu(), r["y"], tol)
+
+
+@pytest.mark.parametrize("name", ["mini_mlp_relu2", "mini_mlp_gelu3", "mini_mlp_tanh2", "mini_mlp_single"])
+def test_mini_stu_with_post_mlp_matches_reference_golden(golden, name):
+    from flash_stu_2_b200 import MiniSTU, ops
+    r = golden("variants")[name]
+    L, din = r["x"].shape[1], r["x"].shape[2]
+    dout = r["y"].shape[2]
+    m = MiniSTU(seq_len=L, num_filters=r["phi"].shape[1], input_dim=din, output_dim=dout, use_mlp=True,
+                dtype=torch.float32, precomputed_filters=r["phi"], **r["kw"])
+    m.load_state_dict(r["sd"])
+    m = m.to(dev())
+    with torch.no_grad():
+        y = m(r["x"].to(dev()))
+    ops.check_status()
+    close(y.cpu(), r["y"], 1e-3)

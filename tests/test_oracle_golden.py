@@ -96,6 +96,23 @@ def test_mini_stu_matches_reference(golden):
     _close(Uc, U, 1e-9)
 
 
+def test_inference_variants_match_reference(golden):
+    """STU layer with the MLP sandwich (full-length and shorter input) and MiniSTU with the post-MLP."""
+    g = golden("variants")
+    for name in ("sandwich_approx_float32", "sandwich_approx_bfloat16"):
+        r = g[name]
+        sd = {k[len("layer."):]: v for k, v in r["sd"].items() if k.startswith("layer.")}
+        tol = 2e-5 if "float32" in name else 2e-2
+        _close(O.stu_layer_sandwich(r["x"], sd, r["sd"]["phi"], r["n"], True), r["y"], tol)
+        T = r["T_short"]
+        _close(O.stu_layer_sandwich(r["x"][:, :T], sd, r["sd"]["phi"], r["n"], True), r["y_short"], tol)
+    for name in ("mini_mlp_relu2", "mini_mlp_gelu3", "mini_mlp_tanh2", "mini_mlp_single"):
+        r = g[name]
+        n = O.fft_length(r["x"].shape[1])
+        y = O.stu_forward(r["x"], r["phi"], r["sd"], n, use_approx=False)
+        _close(O.post_mlp(y, r["sd"], r["kw"].get("mlp_activation", "relu")), r["y"], 1e-5)
+
+
 def test_alibi_slopes_match_reference(golden):
     for H, s in golden("alibi_slopes").items():
         assert torch.allclose(O.alibi_slopes(H).double(), s.double(), rtol=1e-6, atol=0)
