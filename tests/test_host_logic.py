@@ -57,9 +57,15 @@ def test_layer_alternation_and_alibi(tmp_path, golden):
 
 
 def test_unsupported_switches_fail_loudly(tmp_path):
-    for kw in (dict(use_hankel_L=True), dict(d_in_tile=16), dict(stu_enable_mlp_sandwich=True), dict(bias=True)):
+    for kw in (dict(use_hankel_L=True), dict(d_in_tile=16), dict(bias=True),
+               dict(stu_enable_mlp_sandwich=True, bias=True)):
         with pytest.raises(NotImplementedError):
             F.FlashSTU(_cfg(str(tmp_path), use_attn=False, **kw))
+    # the sandwich itself constructs, with the reference's parameter names
+    m = F.FlashSTU(_cfg(str(tmp_path), use_attn=False, stu_enable_mlp_sandwich=True, stu_mlp_hidden_size=24))
+    keys = set(m.state_dict())
+    assert {"layers.0.stu_mlp_in_proj.weight", "layers.0.stu_mlp_out_proj.weight"} <= keys
+    assert m.layers[0].stu.M_inputs.shape == (24, 24)
 
 
 def test_model_refuses_cpu(tmp_path):
