@@ -87,9 +87,9 @@ __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logi
   }
   const float u = uniforms[b];
 
-  if (top_k > 0 && top_k < V) {
-    // ---- radix select: key of the k-th largest
-    if (tid == 0) { s_prefix = 0; s_need = (unsigned)top_k; }
+  // ---- radix select: key of the need-th largest scaled logit (4 passes of 8 bits); all threads call it
+  auto select_kth = [&](unsigned need_total) -> unsigned {
+    if (tid == 0) { s_prefix = 0; s_need = need_total; }
     for (int pass = 0; pass < 4; pass++) {
       const int shift = 24 - 8 * pass;
       if (tid < 256) s_hist[tid] = 0;
@@ -155,7 +155,13 @@ __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logi
       }
       __syncthreads();
     }
-    const unsigned kth_key = s_prefix;
+    const unsigned r = s_prefix;
+    __syncthreads();
+    return r;
+  };
+  unsigned floor_from_list = 0;   // set when the candidate list overflows (ties): the full-vocabulary path takes over
+  if (top_k > 0 && top_k <= SP_CAND && top_k < V) {
+    const unsigned kth_key = select_kth((unsigned)top_k);
     // ---- gather survivors (key >= kth_key)
     if (tid == 0) s_count = 0;
     __syncthreads();
@@ -168,13 +174,16 @@ __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logi
     }
     __syncthreads();
     const int C = (int)s_count;
-    if (C > SP_CAND) {  // more ties than the candidate list holds: report and return the argmax
+    if (C > SP_CAND && !cache) {  // more ties than the candidate list holds: report and return the argmax
       if (tid == 0) {
         if (status) atomicExch(status, 4);
         out[(size_t)b * out_stride] = imax;
       }
       return;
     }
+    if (C > SP_CAND) {
+      floor_from_list = kth_key;   // (a key of a finite logit is never 0)
+    } else {
     if (tid >= C) { s_val[tid] = -INFINITY; s_idx[tid] = 0x7fffffff; }
     __syncthreads();
     int SN = 2;   // sort width: the power of two that holds the C survivors (the padding sorts to the end)
@@ -241,19 +250,130 @@ __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logi
       out[(size_t)b * out_stride] = choice;
     }
     return;
+    }   // candidate list
   }
-  if (top_p > 0.f && top_p < 1.f) {  // nucleus filtering without top-k is not implemented on the device
-    if (tid == 0) {
-      if (status) atomicExch(status, 5);
-      out[(size_t)b * out_stride] = imax;
+  // ---- full-vocabulary filters: nucleus without top-k, or a top-k wider than the candidate list (with or without a
+  //      nucleus cut inside it).  Needs the row's keys in shared memory.
+  const bool big_k = (top_k > SP_CAND && top_k < V) || floor_from_list != 0;
+  const bool nucleus = top_p > 0.f && top_p < 1.f;
+  unsigned keep_key = 0;          // entries with a key above this are kept ...
+  unsigned tie_key = 0xffffffffu; // ... and, of the entries equal to tie_key, the first tie_keep in vocabulary order
+  unsigned tie_keep = 0;
+  bool filtered = false;
+  if (big_k || nucleus) {
+    if (!cache) {   // the vocabulary does not fit in shared memory
+      if (tid == 0) {
+        if (status) atomicExch(status, nucleus ? 5 : 4);
+        out[(size_t)b * out_stride] = imax;
+      }
+      return;
     }
-    return;
+    filtered = true;
+    unsigned floor_key = 0;   // top-k: keys below this are out (ties with the k-th are kept, as in the reference)
+    if (big_k) floor_key = floor_from_list ? floor_from_list : select_kth((unsigned)top_k);
+    if (!nucleus) {
+      keep_key = floor_key > 0 ? floor_key - 1 : 0;
+      if (floor_key == 0) filtered = false;
+    } else {
+      // Probability mass as 40-bit fixed point of exp(z - zmax): integer sums do not depend on the order of the
+      // additions, so the cut is reproducible.  Sorted by (value descending, index ascending) an entry is kept while
+      // the mass ranked before it is <= top_p * total (flash_stu/model.py:284-291): find the key v* at which the mass
+      // from the top first exceeds that bound (4 passes of 8 bits over mass histograms); keys above v* are kept, of
+      // the entries equal to v* the first floor((bound - mass above) / mass of one) + 1 in vocabulary order.
+      unsigned long long* mh = reinterpret_cast<unsigned long long*>(&s_sub[0][0]);   // [4][256]
+      auto mass_of = [&](unsigned key) {
+        return (unsigned long long)(__expf(key_value(key) - zmax) * 1099511627776.f);   // 2^40
+      };
+      __shared__ unsigned long long s_total, s_bound, s_above;
+      if (tid == 0) s_total = 0;
+      __syncthreads();
+      {
+        unsigned long long part = 0;
+        for (int i = tid; i < V; i += SP_T)
+          if (s_key[i] >= floor_key) part += mass_of(s_key[i]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        if (lane == 0) atomicAdd(&s_total, part);
+      }
+      __syncthreads();
+      if (tid == 0) {
+        s_bound = (unsigned long long)((double)top_p * (double)s_total);
+        s_above = 0;
+        s_prefix = 0;
+      }
+      __syncthreads();
+      for (int pass = 0; pass < 4; pass++) {
+        const int shift = 24 - 8 * pass;
+        for (int i = tid; i < 4 * 256; i += SP_T) mh[i] = 0;
+        __syncthreads();
+        const unsigned prefix = s_prefix;
+        const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+        unsigned long long* sub = mh + (warp >> 3) * 256;
+        for (int i = tid; i < V; i += SP_T) {
+          const unsigned key = s_key[i];
+          if (key >= floor_key && (key & mask) == prefix) atomicAdd(&sub[(key >> shift) & 255u], mass_of(key));
+        }
+        __syncthreads();
+        if (tid == 0) {
+          // from the top bin down: the first bin whose mass pushes the running sum over the bound holds v*
+          unsigned long long cum = s_above;
+          const unsigned long long bound = s_bound;
+          int bin = 255;
+          for (; bin > 0; bin--) {
+            const unsigned long long hb = mh[bin] + mh[256 + bin] + mh[512 + bin] + mh[768 + bin];
+            if (cum + hb > bound) break;
+            cum += hb;
+          }
+          s_above = cum;
+          s_prefix = prefix | ((unsigned)bin << shift);
+        }
+        __syncthreads();
+      }
+      tie_key = s_prefix;
+      if (tie_key < floor_key) tie_key = floor_key;   // the bound was never exceeded: everything above the floor stays
+      keep_key = tie_key;
+      const unsigned long long one = mass_of(tie_key);
+      const unsigned long long room = s_bound >= s_above ? s_bound - s_above : 0;
+      tie_keep = one ? (unsigned)min((unsigned long long)V, room / one + 1ull) : (unsigned)V;
+      __syncthreads();
+    }
   }
+  // entry i survives the filters: above the cut, or one of the first tie_keep entries equal to the cut key (their
+  // rank among the ties in vocabulary order is supplied by the caller)
+  auto kept = [&](unsigned key, unsigned tie_rank) {
+    return !filtered || key > keep_key || (key == tie_key && tie_rank < tie_keep);
+  };
+
   // ---- plain temperature sampling over the whole vocabulary: chunked running sum in index order
   const int chunk = (V + SP_T - 1) / SP_T;
   const int lo = tid * chunk, hi = min(V, lo + chunk);
+  // ties with the cut key before this thread's chunk (vocabulary order): exclusive scan of the per-thread counts
+  unsigned tie_base = 0;
+  if (filtered && tie_key != 0xffffffffu) {
+    unsigned mine = 0;
+    for (int i = lo; i < hi; i++) mine += (s_key[i] == tie_key);
+    unsigned incl_t = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned n = __shfl_up_sync(0xffffffffu, incl_t, o);
+      if (lane >= o) incl_t += n;
+    }
+    if (lane == 31) s_redi[warp] = (int)incl_t;
+    __syncthreads();
+    unsigned before = 0;
+    for (int w = 0; w < warp; w++) before += (unsigned)s_redi[w];
+    tie_base = before + incl_t - mine;
+    __syncthreads();
+  }
   float part = 0.f;
-  for (int i = lo; i < hi; i++) part += __expf(zval(i) - zmax);
+  {
+    unsigned tr = tie_base;
+    for (int i = lo; i < hi; i++) {
+      const unsigned key = filtered ? s_key[i] : 0u;
+      if (kept(key, tr)) part += __expf(zval(i) - zmax);
+      if (filtered && key == tie_key) tr++;
+    }
+  }
   // block exclusive scan of the 1024 partial sums
   float incl = part;
 #pragma unroll
@@ -278,14 +398,20 @@ __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logi
   const float tot = __uint_as_float(s_hist[0]);
   const float target = u * tot;
   const float excl = s_red[warp] + incl - part;
-  if (lo < hi && excl <= target && target < excl + part) {
+  if (lo < hi && part > 0.f && excl <= target && target < excl + part) {
     float cum = excl;
-    int choice = hi - 1;
+    int choice = -1;
+    unsigned tr = tie_base;
     for (int i = lo; i < hi; i++) {
-      cum += __expf(zval(i) - zmax);
-      if (cum > target) { choice = i; break; }
+      const unsigned key = filtered ? s_key[i] : 0u;
+      if (kept(key, tr)) {
+        choice = i;   // the last kept entry of the chunk takes what rounding leaves over
+        cum += __expf(zval(i) - zmax);
+        if (cum > target) break;
+      }
+      if (filtered && key == tie_key) tr++;
     }
-    atomicMin(&s_choice, choice);
+    if (choice >= 0) atomicMin(&s_choice, choice);
   }
   __syncthreads();
   if (tid == 0) out[(size_t)b * out_stride] = (s_choice == 0x7fffffff) ? imax : s_choice;
@@ -299,7 +425,7 @@ extern "C" int stu_sample(const void* logits, long long ld, int B, int V, float 
   if (!logits || !out) return STU_ERR_NULL;
   if (do_sample && !uniforms) return STU_ERR_NULL;
   if (B <= 0 || V <= 0 || !(temperature > 0.f)) return STU_ERR_SHAPE;
-  if (top_k > SP_CAND) return STU_ERR_UNSUPPORTED;
+  if (top_k > SP_CAND && top_k < V && V > SP_CACHE_MAX) return STU_ERR_UNSUPPORTED;   // needs the row in shared memory
   cudaStream_t st = (cudaStream_t)stream;
   // greedy selection makes one pass only: nothing to keep
   const int cache = (do_sample && V <= SP_CACHE_MAX) ? 1 : 0;

@@ -181,8 +181,6 @@ class FlashSTU(PreTrainedModel):
         steps = max_length - T0
         if steps <= 0:
             return input_ids
-        if do_sample and top_p is not None and top_k is None:
-            raise NotImplementedError("top_p without top_k has no kernel here")
         dev = input_ids.device
         generated = torch.empty(B, max_length, dtype=torch.int64, device=dev)
         generated[:, :T0] = input_ids

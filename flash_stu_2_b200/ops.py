@@ -76,8 +76,8 @@ def status_word(device) -> torch.Tensor:
 
 
 STATUS_TEXT = {1: "token id outside the vocabulary", 2: "position outside the cache capacity (seq_len)",
-               3: "a bounded mbarrier wait ran out inside the tcgen05 GEMM", 4: "more top-k ties than the candidate list holds",
-               5: "top_p without top_k is not implemented on the device",
+               3: "a bounded mbarrier wait ran out inside the tcgen05 GEMM", 4: "more top-k ties than the candidate list holds and the vocabulary does not fit in shared memory",
+               5: "top_p without top_k (<= 1024) needs the vocabulary row in shared memory (at most 51712 entries)",
                6: "decode step told that all sequences share one position, but the cached positions differ",
                7: "a bounded pipeline wait ran out inside the decode kernel",
                8: "the fused token-step kernel found no partial sums for the current position in its workspace",

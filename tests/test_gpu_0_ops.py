@@ -707,7 +707,10 @@ def test_sampling_matches_oracle():
         out = torch.zeros(B, dtype=torch.int64, device=dev())
         ops.sample(logits.to(dev()), 1.0, None, None, False, None, out)
         assert torch.equal(out.cpu(), logits.float().argmax(-1))
-        for (temp, k, p) in [(0.8, 40, None), (0.8, 5, 0.9), (1.3, 1, None), (1.0, None, None)]:
+        # (temperature, top_k, top_p): candidate-list path (top_k <= 1024), and the full-vocabulary filters: nucleus
+        # without top-k, a top-k wider than the candidate list, and a nucleus inside such a top-k
+        for (temp, k, p) in [(0.8, 40, None), (0.8, 5, 0.9), (1.3, 1, None), (1.0, None, None), (0.9, None, 0.9),
+                             (1.0, None, 0.35), (0.7, 3000, None), (1.1, 5000, 0.8), (1.0, 1024, 0.95)]:
             u = torch.rand(B)
             z = O.filter_logits(logits, temp, k, p)
             want = O.pick_token(z, True, u).view(-1)
@@ -716,7 +719,7 @@ def test_sampling_matches_oracle():
             got = out.cpu()
             # the draw may differ only where u lands within rounding of a CDF boundary; require the
             # chosen token to be inside the filtered support and almost all draws identical
-            assert all(torch.isfinite(z[b, got[b]]) for b in range(B))
+            assert all(torch.isfinite(z[b, got[b]]) for b in range(B)), (temp, k, p, got.tolist())
             if dt == torch.float32:
                 frac = float((got == want).float().mean())
                 assert frac >= 0.8, f"{frac:.2f} of the fp32 draws equal the oracle's ({got.tolist()} vs {want.tolist()})"
