@@ -102,7 +102,7 @@ class STULayer(nn.Module):
         from .modules import uniform_pos
         B, _, d = x.shape
         # the kernel passes the MLP weights through 32 KB shared-memory slots: 16 rows of d and 8 rows of I values
-        return (ops.fused_step and self.stu.use_approx and x.dtype == torch.bfloat16 and B <= 8 and d % 8 == 0
+        return (ops.fused_step and self.stu.use_approx and not self.stu.use_hankel_L and x.dtype == torch.bfloat16 and B <= 8 and d % 8 == 0
                 and d <= 1024 and self.mlp.intermediate_size <= 4096
                 and self.mlp.intermediate_size % 8 == 0 and STU.pipelined_decode and STU.tensor_core_decode
                 and STU.shared_tap_decode and uniform_pos(entry[1]))

@@ -197,6 +197,8 @@ class FlashSTU(PreTrainedModel):
                     layer.stu.use_approx and self.config.torch_dtype == torch.bfloat16
                     and layer.stu_mlp_hidden_size % 8 == 0):
                 use_graph = False
+            if hasattr(layer, "stu") and layer.stu.use_approx and layer.stu.use_hankel_L:
+                use_graph = False   # the single-branch token step is a one-position prefill (host position)
         graph = None
         for step in range(steps):
             cur = T0 + step

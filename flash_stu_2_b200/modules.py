@@ -118,12 +118,16 @@ class STU(nn.Module):
         self.d_out = self.d_in
         self.use_hankel_L = config.use_hankel_L
         self.use_approx = config.use_approx
-        if config.d_in_tile is not None or config.d_out_tile is not None:
-            raise NotImplementedError("d_in_tile/d_out_tile (block-diagonal tiling) has no kernel here")
+        # block-diagonal tiling of the approx variant (flash_stu/modules/stu.py:123-191): only the diagonal
+        # tile x tile blocks of M_inputs take part; the full variant ignores the switch, as the reference does
+        self.tile = None
+        if self.use_approx and (getattr(config, "d_in_tile", None) is not None
+                                or getattr(config, "d_out_tile", None) is not None):
+            tile = min(config.d_in_tile or self.d_in, config.d_out_tile or self.d_out)
+            if tile < self.d_in:
+                self.tile = int(tile)
         dt = config.torch_dtype
         if self.use_approx:
-            if self.use_hankel_L:
-                raise NotImplementedError("use_hankel_L=True with use_approx=True (single branch) has no kernel here yet")
             self.M_inputs = nn.Parameter(torch.empty(self.d_in, self.d_out, dtype=dt))
             self.M_filters = nn.Parameter(torch.empty(self.K, self.d_in, dtype=dt))
         else:
@@ -159,11 +163,26 @@ class STU(nn.Module):
             with torch.no_grad():
                 # only the taps of positions a cache can hold are ever used
                 phi = self.phi[:self.capacity].to(self.M_filters.dtype).contiguous()
-                MinT = self.M_inputs.detach().t().contiguous()
+                Min = self.M_inputs.detach()
+                if self.tile is not None:
+                    # tiling: x_tile @ M_inputs[i:e, i:e] per diagonal block == x @ (M_inputs with the off-diagonal
+                    # blocks zeroed); the zeros add nothing to the fp32 sums
+                    blk = torch.arange(self.d_in, device=Min.device) // self.tile
+                    Min = Min * (blk[:, None] == blk[None, :]).to(Min.dtype)
+                MinT = Min.t().contiguous()
                 # fp = phi @ M_filters, rounded to the model dtype as in the reference (stu.py:88)
                 fp = ops.linear(phi, self.M_filters.detach(), transposed_weight=True, backend=ops.BACKEND_SIMT)
-                taps = ops.taps_even(fp, self.Lh)
-                taps8 = ops.taps_rev8(taps) if taps.dtype == torch.bfloat16 else None
+                if self.use_hankel_L:
+                    # single branch (stu_utils.py:229-246): y[t] = sum over ALL taps.  Even taps act on the same
+                    # time parity, odd taps on the other one a step earlier; the kernels return twice an even-tap
+                    # sum, so both tables are halved (exact) and the odd taps are stored at even positions.
+                    half = (fp.float() * 0.5).to(fp.dtype)
+                    taps = ops.taps_even(half, self.Lh)
+                    self._taps_odd = ops.taps_even(half[1:].contiguous(), self.Lh)
+                    taps8 = None
+                else:
+                    taps = ops.taps_even(fp, self.Lh)
+                    taps8 = ops.taps_rev8(taps) if taps.dtype == torch.bfloat16 else None
             self._prep, self._prep_key = (MinT, taps, taps8), key
         return self._prep
 
@@ -284,6 +303,13 @@ class STU(nn.Module):
         else:
             ops.conv_prefill_approx(hist, taps, yT, x, t0, t0 + T,
                                     use_tensor_cores=(xn.dtype == torch.bfloat16 and STU.tensor_core_conv))
+        if self.use_hankel_L:
+            # odd taps: the even-tap sum of the odd-tap table at time t - 1 goes to output row t
+            s0, s1 = max(t0 - 1, 0), t0 + T - 1
+            if s1 > s0:
+                r0 = s0 + 1 - t0
+                ops.conv_prefill_approx(hist, self._taps_odd, yT, x[:, r0:r0 + (s1 - s0)], s0, s1,
+                                        use_tensor_cores=(xn.dtype == torch.bfloat16 and STU.tensor_core_conv))
         if pos is not None:
             pos[:, 0] += T
             pos._host_t = t0 + T
@@ -306,6 +332,11 @@ class STU(nn.Module):
         if t + 1 > self.capacity:
             raise ValueError(f"sequence position {t + 1} exceeds the capacity {self.capacity} (seq_len={self.seq_len})")
         B, d, _, Lh = hist.shape
+        if self.use_hankel_L:
+            # single branch: a one-position prefill (its position is a host argument: not replayable from a graph)
+            out2d.copy_(x2d)
+            self.add_to_residual(ops.rmsnorm(x2d, norm_w, eps).view(B, 1, d), out2d.view(B, 1, d), entry, True)
+            return hist, pos
         # rows of 8 sequences x 8 channels, slices of 256 cached positions per parity: the pipeline kernel pays a
         # per-row projection latency, which only long rows (or one row per SM) hide
         rows, nsl = (B + 7) // 8 * (d // 8), ((t >> 1) + 255) // 256

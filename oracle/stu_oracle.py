@@ -137,6 +137,19 @@ def stu_forward(x: Tensor, phi: Tensor, p: Dict[str, Tensor], n: int,
     return sp if use_hankel_L else sp + sm
 
 
+def stu_forward_tiled(x: Tensor, phi: Tensor, p: Dict[str, Tensor], n: int, tile: int,
+                      use_hankel_L: bool = False) -> Tensor:
+    """STU._tile_diagonal_blocks, flash_stu/modules/stu.py:169-191: the approx operator on the diagonal
+    tile x tile blocks of M_inputs, tile by tile, results concatenated."""
+    outs = []
+    d = x.shape[-1]
+    for i in range(0, d, tile):
+        e = min(i + tile, d)
+        sub = {"M_inputs": p["M_inputs"][i:e, i:e], "M_filters": p["M_filters"][:, i:e]}
+        outs.append(stu_forward(x[..., i:e], phi, sub, n, True, use_hankel_L))
+    return torch.cat(outs, dim=-1)
+
+
 # --------------------------------------------------------------------------- S9 / S4 pointwise blocks
 RMS_EPS = float(torch.finfo(torch.float32).eps)
 

@@ -334,6 +334,24 @@ def golden_variants(tmp):
         out[f"sandwich_approx_{str(dt).split('.')[-1]}"] = {
             "x": x, "y": y, "y_short": y_short, "T_short": T, "sd": sd_of(blk), "n": n, "L": L, "K": K, "d": d,
             "hidden": Hs}
+    # block-diagonal tiling of the approx operator (flash_stu/modules/stu.py:123-191)
+    L, K, d = 64, 8, 48
+    phi32 = make_phi(L, K)
+    for dt in (torch.float32, torch.bfloat16):
+        for tile in (16, 20):
+            torch.manual_seed(23)
+            cfg = FlashSTUConfig(n_embd=d, seq_len=L, num_eigh=K, use_approx=True, use_flash_fft=False, torch_dtype=dt,
+                                 n_layers=1, vocab_size=1, d_in_tile=tile, d_out_tile=None if tile == 16 else 32)
+            n = nearest_power_of_two(L * 2 - 1, round_up=True)
+            m = STU(cfg, phi32.to(dt), n)
+            for p in m.parameters():
+                nn.init.xavier_normal_(p)
+            x = torch.randn(2, L, d).to(dt)
+            with torch.no_grad():
+                y = m(x).clone()
+            out[f"tiled{tile}_approx_{str(dt).split('.')[-1]}"] = {
+                "phi": phi32.to(dt), "x": x, "n": n, "y": y, "tile": (cfg.d_in_tile, cfg.d_out_tile),
+                "params": {k: v.detach().clone() for k, v in m.named_parameters()}}
     L, K, din, dout = 64, 8, 12, 20
     phi = make_phi(L, K)
     for name, kw in (("mini_mlp_relu2", dict(mlp_num_layers=2, mlp_activation="relu")),

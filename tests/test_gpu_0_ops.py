@@ -770,7 +770,8 @@ def test_full_variant_building_blocks(dt):
 
 @pytest.mark.parametrize("name,tol", [("std_full_float32", 1e-3), ("std_full_bfloat16", 2e-2),
                                        ("hankelL_full_float32", 1e-3), ("std_approx_float32", 1e-3),
-                                       ("std_approx_bfloat16", 2e-2)])
+                                       ("std_approx_bfloat16", 2e-2), ("hankelL_approx_float32", 1e-3),
+                                       ("hankelL_approx_bfloat16", 2e-2), ("hankelL_full_bfloat16", 2e-2)])
 def test_stu_operator_matches_reference_golden(golden, name, tol):
     """STU.forward (operator output, no residual) against the reference module's own outputs."""
     import flash_stu_2_b200 as F
@@ -793,6 +794,30 @@ def test_stu_operator_matches_reference_golden(golden, name, tol):
     ops.check_status()
     close(y, r["y_full"], tol)
     close(ys, r["y_short"], tol)
+
+
+@pytest.mark.parametrize("name,tol", [("tiled16_approx_float32", 1e-3), ("tiled20_approx_float32", 1e-3),
+                                       ("tiled16_approx_bfloat16", 2e-2), ("tiled20_approx_bfloat16", 2e-2)])
+def test_stu_operator_with_block_diagonal_tiling_matches_reference_golden(golden, name, tol):
+    """d_in_tile / d_out_tile (flash_stu/modules/stu.py:123-191): only the diagonal blocks of M_inputs take part
+    (tile 16 divides the width, tile 20 leaves a ragged last block)."""
+    import flash_stu_2_b200 as F
+    from flash_stu_2_b200 import ops
+    r = golden("variants")[name]
+    dt = r["x"].dtype
+    L, K = r["phi"].shape
+    d = r["x"].shape[2]
+    cfg = F.FlashSTUConfig(n_embd=d, seq_len=L, num_eigh=K, use_approx=True, torch_dtype=dt, n_layers=1, vocab_size=1,
+                           d_in_tile=r["tile"][0], d_out_tile=r["tile"][1])
+    m = F.STU(cfg, r["phi"].clone(), r["n"])
+    with torch.no_grad():
+        for k, v in r["params"].items():
+            getattr(m, k).copy_(v)
+    m = m.to(dev())
+    with torch.no_grad():
+        y = m(r["x"].to(dev()))
+    ops.check_status()
+    close(y, r["y"], tol)
 
 
 def test_mini_stu_spectral_matches_reference_golden(golden):

@@ -277,3 +277,38 @@ def test_mini_stu_with_post_mlp_matches_reference_golden(golden, name):
         y = m(r["x"].to(dev()))
     ops.check_status()
     close(y.cpu(), r["y"], 1e-3)
+
+
+@pytest.mark.parametrize("dt,tol", [(torch.float32, 1e-3), (torch.bfloat16, 2e-2)])
+def test_single_branch_approx_block_cached_steps_equal_prefill_rows(dt, tol):
+    """use_hankel_L with use_approx (one convolution branch over ALL taps: the even taps act on the same time parity,
+    the odd taps on the other one a step earlier): the layer's output against the oracle, and prefill + cached
+    single-token steps against the full forward."""
+    import flash_stu_2_b200 as F
+    from flash_stu_2_b200 import ops
+    torch.manual_seed(31)
+    L, K, d, B = 96, 8, 32, 3
+    phi = O.spectral_filters(L, K, use_hankel_L=True)
+    cfg = F.FlashSTUConfig(n_embd=d, seq_len=L, num_eigh=K, use_approx=True, use_hankel_L=True, use_attn=False,
+                           mlp_scale=4, torch_dtype=dt, n_layers=1, vocab_size=1, n_heads=1)
+    blk = F.FlashSTUBlock(config=cfg, phi=phi.to(dt), n=O.fft_length(L))
+    with torch.no_grad():
+        for name, p in blk.named_parameters():
+            if p.dim() >= 2:
+                torch.nn.init.xavier_normal_(p)
+    sd = {k[len("layer."):]: v.detach().clone() for k, v in blk.state_dict().items() if k.startswith("layer.")}
+    x = torch.randn(B, L, d).to(dt)
+    want = O.stu_layer(x, sd, phi.to(dt), O.fft_length(L), True, use_hankel_L=True)
+    blk = blk.to(dev()).eval()
+    xd = x.to(dev())
+    with torch.no_grad():
+        close(blk(xd.clone()).cpu(), want, tol)
+        T1 = L - 11
+        y1, cache = blk(xd[:, :T1].clone(), use_cache=True)
+        rows = [y1]
+        for t in range(T1, L):
+            yt, cache = blk(xd[:, t:t + 1].clone(), past_key_value=cache, use_cache=True)
+            rows.append(yt)
+    ops.check_status()
+    assert int(cache[1][0, 0]) == L
+    close(torch.cat(rows, 1).cpu(), want, tol)

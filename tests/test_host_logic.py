@@ -57,8 +57,7 @@ def test_layer_alternation_and_alibi(tmp_path, golden):
 
 
 def test_unsupported_switches_fail_loudly(tmp_path):
-    for kw in (dict(use_hankel_L=True), dict(d_in_tile=16), dict(bias=True),
-               dict(stu_enable_mlp_sandwich=True, bias=True)):
+    for kw in (dict(bias=True), dict(stu_enable_mlp_sandwich=True, bias=True)):
         with pytest.raises(NotImplementedError):
             F.FlashSTU(_cfg(str(tmp_path), use_attn=False, **kw))
     # the sandwich itself constructs, with the reference's parameter names

@@ -97,7 +97,8 @@ def test_mini_stu_matches_reference(golden):
 
 
 def test_inference_variants_match_reference(golden):
-    """STU layer with the MLP sandwich (full-length and shorter input) and MiniSTU with the post-MLP."""
+    """STU layer with the MLP sandwich (full-length and shorter input), block-diagonal tiling of the approx operator
+    and MiniSTU with the post-MLP."""
     g = golden("variants")
     for name in ("sandwich_approx_float32", "sandwich_approx_bfloat16"):
         r = g[name]
@@ -106,6 +107,11 @@ def test_inference_variants_match_reference(golden):
         _close(O.stu_layer_sandwich(r["x"], sd, r["sd"]["phi"], r["n"], True), r["y"], tol)
         T = r["T_short"]
         _close(O.stu_layer_sandwich(r["x"][:, :T], sd, r["sd"]["phi"], r["n"], True), r["y_short"], tol)
+    for name in ("tiled16_approx_float32", "tiled20_approx_float32", "tiled16_approx_bfloat16", "tiled20_approx_bfloat16"):
+        r = g[name]
+        tile = min(r["tile"][0] or 48, r["tile"][1] or 48)
+        _close(O.stu_forward_tiled(r["x"], r["phi"], r["params"], r["n"], tile), r["y"],
+               2e-5 if "float32" in name else 2e-2)
     for name in ("mini_mlp_relu2", "mini_mlp_gelu3", "mini_mlp_tanh2", "mini_mlp_single"):
         r = g[name]
         n = O.fft_length(r["x"].shape[1])
