@@ -53,11 +53,14 @@ __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logi
   // ---- argmax (lowest index among ties); also the fallback result
   float best = -INFINITY;
   int besti = V;
+  int saw_nan = 0;
   for (int i = tid; i < V; i += SP_T) {
     float z = scaled_logit(row, i, temperature);
+    saw_nan |= isnan(Elem<T>::to_f(row[i])) ? 1 : 0;   // (the clamp inside scaled_logit would hide it)
     if (cache) s_key[i] = ord_key(z);
     if (z > best || (z == best && i < besti)) { best = z; besti = i; }
   }
+  saw_nan = __syncthreads_or(saw_nan);
   // scaled logit of entry i for the later passes
   auto zval = [&](int i) { return cache ? key_value(s_key[i]) : scaled_logit(row, i, temperature); };
 #pragma unroll
@@ -86,6 +89,12 @@ __global__ void __launch_bounds__(SP_T) sample_kernel(const T* __restrict__ logi
     return;
   }
   const float u = uniforms[b];
+  if (saw_nan) {
+    // a NaN logit makes the reference's softmax NaN everywhere and it falls back to a uniformly random token
+    // (flash_stu/model.py:293-296); here the row's uniform picks it
+    if (tid == 0) out[(size_t)b * out_stride] = min(V - 1, (int)(u * (float)V));
+    return;
+  }
 
   // ---- radix select: key of the need-th largest scaled logit (4 passes of 8 bits); all threads call it
   auto select_kth = [&](unsigned need_total) -> unsigned {

@@ -725,6 +725,24 @@ def test_sampling_matches_oracle():
                 assert frac >= 0.8, f"{frac:.2f} of the fp32 draws equal the oracle's ({got.tolist()} vs {want.tolist()})"
 
 
+def test_sampling_row_with_a_nan_logit_draws_uniformly():
+    """The reference replaces the distribution of a row whose softmax is not finite by a uniform one
+    (flash_stu/model.py:293-296); the kernel takes the row's uniform for it and leaves the other rows alone."""
+    from flash_stu_2_b200 import ops
+    torch.manual_seed(9)
+    B, V = 4, 1000
+    logits = torch.randn(B, V)
+    logits[2, 17] = float("nan")
+    u = torch.tensor([0.3, 0.9, 0.25, 0.5])
+    out = torch.zeros(B, dtype=torch.int64, device=dev())
+    ops.sample(logits.to(dev()), 1.0, 50, None, True, u.to(dev()), out)
+    ops.check_status()
+    got = out.cpu()
+    assert int(got[2]) == int(0.25 * V)
+    z = O.filter_logits(logits[[0, 1, 3]], 1.0, 50, None)
+    assert all(torch.isfinite(z[i, got[b]]) for i, b in enumerate((0, 1, 3)))
+
+
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 def test_full_variant_building_blocks(dt):
     """to_history, the three Toeplitz matrices, the causal GEMM flag and the combine step against plain torch."""
