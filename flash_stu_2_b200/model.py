@@ -171,6 +171,19 @@ class FlashSTU(PreTrainedModel):
         use_cache: bool = True,
         **kwargs,
     ) -> torch.LongTensor:
+        """The reference's token loop (flash_stu/model.py:207-304) with a cache in every layer.
+
+        Differences from the reference a caller can observe: (1) a sampled token is drawn by inverse CDF from ONE
+        uniform number per sequence and step (`uniforms` [steps, B], else `generator`), walking the kept entries in
+        vocabulary order, where the reference calls torch.multinomial: same distribution, other random stream;
+        (2) the nucleus cut sums probability mass in 40-bit fixed point, so an entry whose cumulative mass lies
+        within 2^-40 of top_p may fall on the other side of the cut; (3) a row with a NaN logit gets the token
+        floor(u * vocab_size) from its uniform (the reference draws a uniformly random token there);
+        (4) prompts may be shorter than seq_len and steps read cached state (the reference recomputes the prefix);
+        (5) nucleus filtering without top_k, and top_k above 1024, need the vocabulary row in shared memory (at
+        most 51712 entries; status 5 / 4 otherwise).  kwargs: uniforms, generator, return_logits, cuda_graph (replay
+        the cached steps from one captured graph, default True), timings (dict filled with the device time of the
+        replayed steps)."""
         uniforms = kwargs.get("uniforms")
         generator = kwargs.get("generator")
         return_logits = kwargs.get("return_logits", False)
