@@ -80,6 +80,9 @@ _SIGNATURES = {
     "stu_peer_xchg_bytes": ([], c_int),
     "stu_peer_exchange": ([_P, _P, _LL, _P, _LL, c_int, c_int, _LL, _P, _P, _LL, c_float, c_int, c_int, _P, c_int,
                            c_int, _P], c_int),
+    "stu_swa_prefill_scratch_elems": ([c_int, c_int, c_int, c_int], c_longlong),
+    "stu_swa_prefill_tc5": ([_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P,
+                             c_int, _P], c_int),
     "stu_sample": ([_P, _LL, c_int, c_int, c_float, c_int, c_float, c_int, _P, _P, _LL, _P, c_int, _P], c_int),
 }
 

@@ -578,6 +578,15 @@ __global__ void __launch_bounds__(128) swa_flash_kernel(const bf16* __restrict__
 
 // qkv: [B, Tn, 3d] activations of this call (c_attn output); rings: [B, W, d]; pos: [B,2] int32 device
 // (column 0 = tokens already cached, column 1 of row 0 = arrival counter, must be 0); out: [B, Tn, d].
+// ring write + position advance after a prefill whose attention ran elsewhere (attention_umma.cu)
+int launch_kv_ring_write_bf16(const void* qkv, void* k_ring, void* v_ring, int* pos, int B, int Tn, int d, int W,
+                              cudaStream_t st) {
+  dim3 g2(Tn < W ? Tn : W, B);
+  kv_ring_write_kernel<bf16><<<g2, 256, 0, st>>>((const bf16*)qkv, (bf16*)k_ring, (bf16*)v_ring, pos, B, Tn, d, W);
+  STU_CHECK_LAUNCH();
+  return STU_OK;
+}
+
 extern "C" int stu_swa_forward(const void* qkv, void* k_ring, void* v_ring, int* pos, const float* slopes, void* out,
                                int B, int Tn, int H, int hd, int W, int window, float softcap, int update_cache,
                                int dtype, void* stream) {

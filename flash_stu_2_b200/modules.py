@@ -433,13 +433,15 @@ class Attention(nn.Module):
         if entry is not None:
             k_ring, v_ring, pos = entry
             t0 = host_pos(pos)
-            y = ops.swa_forward(qkv, k_ring, v_ring, pos, self.alibi_slopes, self.n_heads, self.window, self.softcap,
-                                update_cache=True)
+            attend = ops.swa_prefill_tc5 if ops.swa_prefill_tc5_supported(qkv, self.n_heads, t0) else ops.swa_forward
+            y = attend(qkv, k_ring, v_ring, pos, self.alibi_slopes, self.n_heads, self.window, self.softcap,
+                       update_cache=True)
             pos._host_t = t0 + T
             return y, entry
         dummy = torch.zeros(1, 1, 1, dtype=xn.dtype, device=xn.device)
-        y = ops.swa_forward(qkv, dummy, dummy, new_pos(B, xn.device), self.alibi_slopes, self.n_heads, self.window,
-                            self.softcap, update_cache=False)
+        attend = ops.swa_prefill_tc5 if ops.swa_prefill_tc5_supported(qkv, self.n_heads, 0) else ops.swa_forward
+        y = attend(qkv, dummy, dummy, new_pos(B, xn.device), self.alibi_slopes, self.n_heads, self.window,
+                   self.softcap, update_cache=False)
         return y, None
 
     def forward(self, x, past_key_value=None, use_cache=True):

@@ -82,7 +82,8 @@ STATUS_TEXT = {1: "token id outside the vocabulary", 2: "position outside the ca
                7: "a bounded pipeline wait ran out inside the decode kernel",
                8: "the fused token-step kernel found no partial sums for the current position in its workspace",
                9: "a bounded pipeline wait ran out inside the tcgen05 prefill convolution",
-               10: "a tensor-parallel rank waited in vain for another rank's sub-layer output"}
+               10: "a tensor-parallel rank waited in vain for another rank's sub-layer output",
+               11: "tcgen05 attention prefill: a bounded wait ran out, or a sequence was not at position 0"}
 
 
 def check_status(device=None):
@@ -539,6 +540,33 @@ def swa_forward(qkv, k_ring, v_ring, pos, slopes, H: int, window: int, softcap: 
                                      int(update_cache), _dt(qkv), _stream())
     _lib.check(rc, "stu_swa_forward")
     _count(2 if update_cache else 1)
+    return out
+
+
+swa_tc5 = True   # switch: prefills from position 0 with head dimension 128 (bf16) use the tcgen05 attention kernel
+
+
+def swa_prefill_tc5_supported(qkv, H: int, t0: int) -> bool:
+    d = qkv.shape[2] // 3
+    return swa_tc5 and qkv.dtype == torch.bfloat16 and d // H == 128 and t0 == 0 and qkv.shape[1] >= 128
+
+
+def swa_prefill_tc5(qkv, k_ring, v_ring, pos, slopes, H: int, window: int, softcap: float, update_cache: bool):
+    """swa_forward for a prefill that starts at position 0 (bf16, head dimension 128) on the tcgen05 tensor cores."""
+    _cuda(qkv, k_ring, v_ring, pos, slopes)
+    B, Tn, d3 = qkv.shape
+    d = d3 // 3
+    assert qkv.is_contiguous() and slopes.dtype == torch.float32 and pos.dtype == torch.int32 and d // H == 128
+    W = max(int(k_ring.shape[1]), window + 1)
+    assert not update_cache or (k_ring.shape == (B, W, d) and k_ring.is_contiguous() and v_ring.is_contiguous())
+    lib = _lib.load()
+    vt = torch.empty(lib.stu_swa_prefill_scratch_elems(B, Tn, H, 128), dtype=qkv.dtype, device=qkv.device)
+    out = torch.empty(B, Tn, d, dtype=qkv.dtype, device=qkv.device)
+    rc = lib.stu_swa_prefill_tc5(qkv.data_ptr(), vt.data_ptr(), k_ring.data_ptr(), v_ring.data_ptr(), pos.data_ptr(),
+                                 slopes.data_ptr(), out.data_ptr(), B, Tn, H, 128, W, window, float(softcap or 0.0),
+                                 int(update_cache), status_word(qkv.device).data_ptr(), _dt(qkv), _stream())
+    _lib.check(rc, "stu_swa_prefill_tc5")
+    _count(3 if update_cache else 2)
     return out
 
 

@@ -268,6 +268,18 @@ int stu_decode_approx_projected(const void* x, long long x_row_stride, const voi
                                 void* hist, const void* taps8, int* pos, void* out, long long out_row_stride, int B,
                                 int d_ch, int Lh, int add_residual, int* status, int dtype, void* stream);
 
+/* Attention of a prefill that starts at position 0 (every pos[2b] == 0, checked on the device: status 11 otherwise)
+ * on the tcgen05 tensor cores: bf16, head dimension 128.  Same semantics and outputs as stu_swa_forward for that
+ * case (flash_stu/modules/attention.py:72-101): 128 queries x one head per CTA, S = Q K^T and O += P V as
+ * tcgen05.mma with S, O in tensor memory, Q / K tiles / V^T tiles by cp.async.bulk.tensor, softmax by four warps
+ * against a lazily moved row maximum; update_cache stores the last W tokens in the rings and advances pos by Tn.
+ * vt_scratch: stu_swa_prefill_scratch_elems(B, Tn, H, 128) bf16 elements, 16-byte aligned (V transposed per head by
+ * a kernel of its own).  -4 for other head dimensions. */
+long long stu_swa_prefill_scratch_elems(int B, int Tn, int H, int hd);
+int stu_swa_prefill_tc5(const void* qkv, void* vt_scratch, void* k_ring, void* v_ring, int* pos, const float* slopes,
+                        void* out, int B, int Tn, int H, int hd, int W, int window, float softcap, int update_cache,
+                        int* status, int dtype, void* stream);
+
 /* ---- exchange between the GPUs of a tensor-parallel group, fused into the token loop's kernels ----------------
  * The reference is single-GPU (its sub-layers: flash_stu/layers/stu_layer.py:78-98,
  * flash_stu/layers/attention_layer.py); these calls replace the all-gather after a channel-sharded STU sub-layer and the

@@ -669,6 +669,45 @@ def test_attention_prefill_and_cached_decode(dt, cfg):
     close(y, ref, (1e-4 if dt == torch.float32 else 1.5e-2))
 
 
+@pytest.mark.parametrize("cfg", [(2, 300, 2, 100), (1, 700, 3, 256), (3, 260, 2, 1024), (2, 1031, 2, 77), (1, 128, 1, 16)])
+def test_attention_prefill_on_tcgen05_matches_oracle(cfg):
+    """Prefill from position 0, bf16, head dimension 128: the tcgen05 kernel (S and O in tensor memory, lazy row
+    maximum) against the fp32 oracle and against the mma.sync kernel; ragged last query tile, windows shorter and
+    longer than a key tile, the ring and the positions afterwards, then cached steps on top of it."""
+    from flash_stu_2_b200 import ops
+    B, T, H, w = cfg
+    hd, dt = 128, torch.bfloat16
+    d = H * hd
+    torch.manual_seed(13)
+    x = torch.randn(B, T, d).to(dt)
+    p = {"attn.c_attn.weight": (torch.randn(3 * d, d) / math.sqrt(d)).to(dt),
+         "attn.c_proj.weight": torch.eye(d).to(dt)}
+    ref, _ = O.attention(x, p, H, w, 50.0)
+    qkv = (x @ p["attn.c_attn.weight"].t()).to(dev())
+    slopes = O.alibi_slopes(H).float().to(dev())
+    W = w + 1
+    T1 = T - 3
+    q1 = qkv[:, :T1].contiguous()
+    assert ops.swa_prefill_tc5_supported(q1, H, 0) or T1 < 128
+    kr, vr = torch.zeros(B, W, d, dtype=dt, device=dev()), torch.zeros(B, W, d, dtype=dt, device=dev())
+    pos = torch.zeros(B, 2, dtype=torch.int32, device=dev())
+    kr2, vr2, pos2 = torch.zeros_like(kr), torch.zeros_like(vr), torch.zeros_like(pos)
+    y1 = ops.swa_prefill_tc5(q1, kr, vr, pos, slopes, H, w, 50.0, update_cache=True)
+    y2 = ops.swa_forward(q1, kr2, vr2, pos2, slopes, H, w, 50.0, update_cache=True)
+    ops.check_status()
+    close(y1, ref[:, :T1], 1.5e-2, what="tcgen05 vs oracle")
+    close(y1, y2, 1.5e-2, what="tcgen05 vs mma.sync")
+    assert torch.equal(kr, kr2) and torch.equal(vr, vr2) and torch.equal(pos, pos2)
+    ys = [y1]
+    for t in range(T1, T):
+        ys.append(ops.swa_forward(qkv[:, t:t + 1].contiguous(), kr, vr, pos, slopes, H, w, 50.0, update_cache=True))
+    close(torch.cat(ys, 1), ref, 1.5e-2)
+    # a sequence that is not at position 0 is refused on the device
+    ops.swa_prefill_tc5(q1, kr, vr, pos, slopes, H, w, 50.0, update_cache=False)
+    with pytest.raises(RuntimeError, match="status 11"):
+        ops.check_status()
+
+
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("cfg", [(2, 300, 2, 64, 100), (1, 700, 3, 128, 256), (3, 260, 2, 128, 1024)])
 def test_attention_chunked_prefill_across_many_key_tiles(dt, cfg):
