@@ -216,8 +216,9 @@ class TensorParallelFlashSTU:
                 t0 = host_pos(pos)
                 xn = ops.rmsnorm(x2, self.sd[p + "attn_norm.weight"], self.eps)
                 qkv = ops.linear(xn, self.sd[p + "attn.c_attn.weight"]).view(B, T, 3 * dl)
-                y = ops.swa_forward(qkv, k_ring, v_ring, pos, self.slopes, self.Hl, self.window, self.cfg.softcap,
-                                    update_cache=True)
+                attend = ops.swa_prefill_tc5 if ops.swa_prefill_tc5_supported(qkv, self.Hl, t0) else ops.swa_forward
+                y = attend(qkv, k_ring, v_ring, pos, self.slopes, self.Hl, self.window, self.cfg.softcap,
+                           update_cache=True)
                 pos._host_t = t0 + T
                 self._all_reduce_add(x2, ops.linear(y.view(B * T, dl), self.sd[p + "attn.c_proj.weight"]))
             else:
