@@ -48,11 +48,14 @@ __device__ __forceinline__ void mma_16816(float* c, uint32_t a0, uint32_t a1, ui
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// nw != NULL (KSPLIT == 1 only: the CTA holds whole rows): the staged rows are RMS-normalised in shared memory
+// before the MMAs, x * rsqrt(mean(x^2) + eps) * nw rounded to bf16 as the reference's norm output is.
 template <int EPI, int MT, int KSPLIT>
 __global__ void __launch_bounds__(NW * 32, 1) skinny_stage_kernel(const bf16* __restrict__ x, long long lda,
                                                                   const bf16* __restrict__ W, long long ldb,
                                                                   const bf16* __restrict__ W2, int M, int N, int K,
-                                                                  EpiArgs<bf16> ep) {
+                                                                  EpiArgs<bf16> ep, const bf16* __restrict__ nw,
+                                                                  float eps) {
   constexpr bool DUAL = (EPI == EPI_GELU_MUL);
   constexpr int NF = DUAL ? 16 : 32;   // output features per CTA
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -114,6 +117,27 @@ __global__ void __launch_bounds__(NW * 32, 1) skinny_stage_kernel(const bf16* __
   bool ok = true;
   if (nch > 0) ok = tma::mbar_wait_bounded(&s_bar, 0, &s_abort);
   ok = __all_sync(0xffffffffu, ok);
+  if (KSPLIT == 1 && nw) {
+    // fused RMSNorm: warp w normalises rows w, w + 16, ... in place (a row is 16-byte vectors of 8 values)
+    const int nvec = K >> 3;
+    for (int m = warp; m < M; m += NW) {
+      bf16* xr = xs + (size_t)m * pitch;
+      float ss = 0.f;
+      for (int v = lane; v < nvec; v += 32) {
+        float f[8];
+        load_vec(xr + v * 8, f);
+#pragma unroll
+        for (int j = 0; j < 8; j++) ss += f[j] * f[j];
+      }
+      ss = warp_sum(ss);
+      const float r = rsqrtf(ss / (float)K + eps);
+      for (int v = lane; v < nvec; v += 32) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(xr + v * 8);
+        *reinterpret_cast<uint4*>(xr + v * 8) = norm_pack(raw, r, *reinterpret_cast<const uint4*>(nw + v * 8));
+      }
+    }
+    __syncthreads();
+  }
   if (ok) {
 #pragma unroll
     for (int u = 0; u < U; u++) {
@@ -185,7 +209,7 @@ __global__ void __launch_bounds__(NW * 32, 1) skinny_stage_kernel(const bf16* __
 
 template <int EPI, int MT, int KSPLIT>
 int launch_stage(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N, int K,
-                 const EpiArgs<bf16>& ep, cudaStream_t st) {
+                 const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st) {
   constexpr int NF = (EPI == EPI_GELU_MUL) ? 16 : 32;
   const int per = ((K >> 5) + KSPLIT - 1) / KSPLIT;
   const size_t xs_bytes = (size_t)MT * 16 * (per * 32 + 32) * sizeof(bf16);
@@ -206,7 +230,8 @@ int launch_stage(const void* A, long long lda, const void* B, long long ldb, con
   at[0].val.clusterDim.z = 1;
   cfg.attrs = at;
   cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kern, (const bf16*)A, lda, (const bf16*)B, ldb, (const bf16*)B2, M, N, K, ep);
+  e = cudaLaunchKernelEx(&cfg, kern, (const bf16*)A, lda, (const bf16*)B, ldb, (const bf16*)B2, M, N, K, ep,
+                         (const bf16*)nw, eps);
   if (e != cudaSuccess) return (int)e;
   STU_CHECK_LAUNCH();
   return STU_OK;
@@ -214,12 +239,12 @@ int launch_stage(const void* A, long long lda, const void* B, long long ldb, con
 
 template <int EPI, int MT>
 int launch_stage_split(int ks, const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N,
-                       int K, const EpiArgs<bf16>& ep, cudaStream_t st) {
+                       int K, const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st) {
   switch (ks) {
-    case 1: return launch_stage<EPI, MT, 1>(A, lda, B, ldb, B2, M, N, K, ep, st);
-    case 2: return launch_stage<EPI, MT, 2>(A, lda, B, ldb, B2, M, N, K, ep, st);
-    case 4: return launch_stage<EPI, MT, 4>(A, lda, B, ldb, B2, M, N, K, ep, st);
-    case 8: return launch_stage<EPI, MT, 8>(A, lda, B, ldb, B2, M, N, K, ep, st);
+    case 1: return launch_stage<EPI, MT, 1>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+    case 2: return launch_stage<EPI, MT, 2>(A, lda, B, ldb, B2, M, N, K, ep, nullptr, eps, st);
+    case 4: return launch_stage<EPI, MT, 4>(A, lda, B, ldb, B2, M, N, K, ep, nullptr, eps, st);
+    case 8: return launch_stage<EPI, MT, 8>(A, lda, B, ldb, B2, M, N, K, ep, nullptr, eps, st);
   }
   return STU_ERR_UNSUPPORTED;
 }
@@ -235,20 +260,22 @@ bool skinny_stage_takes(int M, int N, int K, int epi, bool norm) {
   static const bool off = getenv("STU_B200_DISABLE_STAGE_SKINNY") != nullptr;
   static const bool all = getenv("STU_B200_STAGE_SKINNY") != nullptr;
   const bool epi_ok = epi == EPI_GELU_MUL || (all && (epi == EPI_STORE || epi == EPI_RESID));
-  return !off && !norm && M > 16 && M <= 32 && K % 32 == 0 && K >= 256 && (K >> 5) <= 8 * MAXC && N >= 32 && epi_ok;
+  // a fused norm needs whole rows in one CTA: K within 48 chunks (no split over a cluster)
+  if (norm && (K >> 5) > MAXC) return false;
+  return !off && M > 16 && M <= 32 && K % 32 == 0 && K >= 256 && (K >> 5) <= 8 * MAXC && N >= 32 && epi_ok;
 }
 
 int skinny_stage_dispatch(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N,
-                          int K, int epi, const EpiArgs<bf16>& ep, cudaStream_t st) {
+                          int K, int epi, const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st) {
   int ks = 1;
   while (ks < 8 && ((K >> 5) + ks - 1) / ks > MAXC) ks *= 2;
   // short K: split further while that still leaves every warp a chunk and the grid is below one CTA per SM
   const int ctas = (N + (epi == EPI_GELU_MUL ? 16 : 32) - 1) / (epi == EPI_GELU_MUL ? 16 : 32);
-  while (ks < 8 && ctas * ks < 148 && (K >> 5) / (2 * ks) >= NW) ks *= 2;
+  while (!nw && ks < 8 && ctas * ks < 148 && (K >> 5) / (2 * ks) >= NW) ks *= 2;
   switch (epi) {
-    case EPI_STORE: return launch_stage_split<EPI_STORE, 2>(ks, A, lda, B, ldb, B2, M, N, K, ep, st);
-    case EPI_RESID: return launch_stage_split<EPI_RESID, 2>(ks, A, lda, B, ldb, B2, M, N, K, ep, st);
-    case EPI_GELU_MUL: return launch_stage_split<EPI_GELU_MUL, 2>(ks, A, lda, B, ldb, B2, M, N, K, ep, st);
+    case EPI_STORE: return launch_stage_split<EPI_STORE, 2>(ks, A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+    case EPI_RESID: return launch_stage_split<EPI_RESID, 2>(ks, A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+    case EPI_GELU_MUL: return launch_stage_split<EPI_GELU_MUL, 2>(ks, A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
   }
   return STU_ERR_UNSUPPORTED;
 }

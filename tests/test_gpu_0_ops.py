@@ -158,7 +158,7 @@ def test_linear_fused_norm_decode():
     from flash_stu_2_b200 import ops
     torch.manual_seed(2)
     for (M, N, K, epi) in [(8, 4096, 1024, 2), (32, 1536, 1536, 0), (5, 104, 64, 1), (48, 4608, 1536, 0),
-                           (20, 1000, 520, 1), (64, 72, 2048, 0)]:
+                           (20, 1000, 520, 1), (64, 72, 2048, 0), (32, 6144, 1536, 2), (19, 200, 512, 2)]:
         dt = torch.bfloat16
         x = torch.randn(M, K).to(dt)
         nw = torch.randn(K).to(dt)
