@@ -752,14 +752,16 @@ def tp_object(a, dev, world, rank):
     ops.check_status()
     same = parallel.gather_token_ids(out[:1, T0:].contiguous(), world)
     dec_ms = parallel.max_over_ranks([tm["replay_ms"]], device=dev)[0] / tm["replayed_steps"]
-    fused = tp._exchange is not None
-    # the same token steps with the exchanges as NCCL collectives between the kernels
-    tp.fused_exchange = False
+    fused = tp._exchange is not None      # what the group-size default picked for the figure above
+    default_mode = tp.fused_exchange
+    # the same token steps with the other way of exchanging: NCCL collectives between the kernels / exchange kernels
+    tp.fused_exchange = False if fused else "force"
     tm2 = {}
     _, out2 = timed(ids, T0 + new, timings=tm2)
     ops.check_status()
-    tp.fused_exchange = True
-    dec_ms_nccl = parallel.max_over_ranks([tm2["replay_ms"]], device=dev)[0] / tm2["replayed_steps"]
+    tp.fused_exchange = default_mode
+    other_ms = parallel.max_over_ranks([tm2["replay_ms"]], device=dev)[0] / tm2["replayed_steps"]
+    dec_ms_nccl, dec_ms_xchg = (other_ms, dec_ms) if fused else (dec_ms, other_ms)
     pk = peaks()
     nbytes = _decode_bytes_per_step(cfg, B, T0 + new // 2) / world
     res = {"workload": f"FlashSTU.generate, 3B shapes: 32 layers d=3072 H=24 window 2048 K=32 L=32768 V=50257 bf16 "
@@ -770,7 +772,7 @@ def tp_object(a, dev, world, rank):
            "ranks_agree": bool((same == same[0]).all()),
            "roofline": {"bound": "hbm", "bytes_per_step_per_gpu": nbytes, "achieved": nbytes / (dec_ms * 1e-3) / 1e9,
                         "peak": pk["hbm_gbs"], "unit": "GB/s per GPU", "frac": nbytes / (dec_ms * 1e-3) / 1e9 / pk["hbm_gbs"]},
-           "decode_ms_per_token_step_nccl": dec_ms_nccl,
+           "decode_ms_per_token_step_nccl": dec_ms_nccl, "decode_ms_per_token_step_exchange_kernels": dec_ms_xchg,
            "tokens_equal_to_nccl_path": float((out[:, T0:] == out2[:, T0:]).float().mean()),
            "collectives": ("token steps: the all-gather after every STU shard and the all-reduce after every attention / "
                            "MLP block are stores into the other ranks' inboxes from inside the producing kernels "
@@ -778,7 +780,8 @@ def tp_object(a, dev, world, rank):
                            "`decode_ms_per_token_step_nccl` = the same steps with NCCL collectives between the kernels"
                            if fused else
                            "NCCL all-gather per STU layer, all-reduce per attention / MLP block, captured in the step "
-                           "graph")}
+                           "graph (the default above 4 ranks); `decode_ms_per_token_step_exchange_kernels` = the same "
+                           "steps with the peer-memory exchange kernels")}
     del tp
     torch.cuda.empty_cache()
     # ---- parity of the sharded path on the reference's small hybrid fixtures (needs n_heads % ranks == 0)

@@ -155,7 +155,12 @@ class TensorParallelFlashSTU:
         # token steps: "exchange" = one kernel per sub-layer exchange pushes this rank's rows to the other ranks over
         # peer memory, waits for theirs and folds them (and the next RMSNorm) into the residual stream; "push" = the
         # producing kernels store into the inboxes themselves and a combine kernel waits; False = NCCL collectives
-        self.fused_exchange = "exchange"
+        # Default by group size, from measurements on B200s (3B shapes, B = 64, ms per token step, exchange kernels
+        # against NCCL): 2 GPUs 10.67 / 11.13, 4 GPUs 6.80 / 6.72, 8 GPUs 6.15 / 5.76 (NCCL with in-switch reduction):
+        # every rank sends its full rows to every other rank, which is the cheapest pattern while latency dominates and
+        # loses to a reduce-scatter + all-gather once eight ranks' rows cross every link.  "force" keeps the exchange
+        # kernels at any group size.
+        self.fused_exchange = "exchange" if self.world <= 4 else False
         self._exchange = None
         self._derived = {}
         from .modules import Attention
