@@ -221,6 +221,7 @@ template <int EPI>
 int launch_wide_mt(int ks, const void* A, long long lda, const void* B, long long ldb, int M, int N, int K,
                    const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st) {
   switch ((M + 15) / 16) {
+    case 1: return launch_wide_split<EPI, 1>(ks, A, lda, B, ldb, M, N, K, ep, nw, eps, st);
     case 2: return launch_wide_split<EPI, 2>(ks, A, lda, B, ldb, M, N, K, ep, nw, eps, st);
     case 3: return launch_wide_split<EPI, 3>(ks, A, lda, B, ldb, M, N, K, ep, nw, eps, st);
     case 4: return launch_wide_split<EPI, 4>(ks, A, lda, B, ldb, M, N, K, ep, nw, eps, st);
@@ -235,6 +236,8 @@ int device_sm_count();
 // 17..64 rows, store / residual epilogue.  STU_B200_DISABLE_WIDE_SKINNY=1 keeps the 8-feature kernel.
 bool skinny_wide_takes(int M, int N, int K, int epi, bool norm) {
   static const bool off = getenv("STU_B200_DISABLE_WIDE_SKINNY") != nullptr;
+  // (9..16 rows stay with the 8-feature kernel: for the 16 x 1024 x 49152 contraction of the distilled-LDS features
+  // this kernel's 128 CTAs measured 1.48 ms per 12-layer token step against 1.12 ms)
   (void)norm;
   return !off && M > 16 && M <= 64 && (epi == EPI_STORE || epi == EPI_RESID) && N >= 8 * NT && K >= 256;
 }
