@@ -241,8 +241,10 @@ __global__ void __launch_bounds__(192, 2) swa_umma_kernel(const __grid_constant_
     const int row = quarter * 32 + lane;       // query row of this thread
     const int i = q0 + row;                    // absolute position (the sequence starts at 0)
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const float slope = slopes[h];
-    const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+    const float c2 = slopes[h] * LOG2E;
+    const float base_i = -c2 * (float)i;
+    const float k0 = softcap > 0.f ? scale / softcap : 0.f;
+    const float k1 = softcap > 0.f ? softcap * LOG2E : scale * LOG2E;
     unsigned char* prow = smem + P_OFF + (row >> 3) * 1024 + (row & 7) * 128;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
@@ -256,20 +258,24 @@ __global__ void __launch_bounds__(192, 2) swa_umma_kernel(const __grid_constant_
       tmem_ld32(tm_s + lane_base + (t & 1) * BN, sr);
       tmem_ld32(tm_s + lane_base + (t & 1) * BN + 32, sr + 32);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      // soft cap, ALiBi, mask; exp2 domain
+      // soft cap, ALiBi, mask; exp2 domain.  Constants folded so that a score costs one multiply, the hardware tanh
+      // and two fused multiply-adds: score2 = tanh(s * k0) * k1 + (c2 * j + base_i), with k0 = scale / softcap,
+      // k1 = softcap * log2(e), c2 = slope * log2(e), base_i = -c2 * i
       const bool interior = (jt + BN - 1 <= q0) && (jt >= q0 + BM - 1 - window) && (q0 + BM - 1 <= i_last);
+      const float base_t = fmaf(c2, (float)jt, base_i);
       float mx = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 64; c++) {
-        float sc = __uint_as_float(sr[c]) * scale;
+        float sc;
         if (softcap > 0.f) {   // hardware tanh: relative error 2^-11, below the bf16 rounding of P
           float th;
-          asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(sc * inv_cap));
-          sc = softcap * th;
+          asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(__uint_as_float(sr[c]) * k0));
+          sc = fmaf(th, k1, fmaf(c2, (float)c, base_t));
+        } else {
+          sc = fmaf(__uint_as_float(sr[c]), k1, fmaf(c2, (float)c, base_t));
         }
-        const int j = jt + c;
-        sc = (sc - slope * (float)(i - j)) * LOG2E;
         if (!interior) {
+          const int j = jt + c;
           const bool valid = (j <= i) && (j >= i - window) && (i <= i_last);
           sc = valid ? sc : -INFINITY;
         }
