@@ -71,6 +71,8 @@ def parse():
     ap.add_argument("--no-extra", action="store_true",
                     help="skip the extra objects of the default line (`generate`: the 24-layer model through "
                          "FlashSTU.generate(); `tp`, N > 1 only: the 3B shapes tensor-parallel over the N ranks)")
+    ap.add_argument("--cache-len", type=int, default=None,
+                    help="with --model: positions the layer caches hold (default: the config's seq_len)")
     ap.add_argument("--extra-new-tokens", type=int, default=64, help="tokens generated for the `generate` object")
     ap.add_argument("--tp-new-tokens", type=int, default=32, help="tokens generated for the `tp` object")
     ap.add_argument("--conv-timeline", action="store_true",
@@ -1029,7 +1031,8 @@ def run_model(a):
             fp = os.path.join(tmp, "phi.pt")
             F.save_spectral_filters(F.get_spectral_filters(L, K, device=dev, dtype=torch.float32), fp)
         torch.manual_seed(0)
-        model = F.FlashSTU(F.FlashSTUConfig(filter_path=fp, torch_dtype=dt, **cfg)).to(dev).eval()
+        extra = {"cache_len": a.cache_len} if a.cache_len else {}
+        model = F.FlashSTU(F.FlashSTUConfig(filter_path=fp, torch_dtype=dt, **extra, **cfg)).to(dev).eval()
     B, T0, new = spec["B"], spec["prompt"], (a.new_tokens or spec["new"])
     ids = torch.randint(0, cfg["vocab_size"], (B, T0), device=dev)
     gen = torch.Generator(device=dev)

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "stu_conv_prefill_approx_tc5": ([_P, _P, _P, _P, _LL, _LL, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int,
                                      _P], c_int),
     "stu_conv_prefill_set_timeline": ([_P], c_int),
+    "stu_set_programmatic_launch": ([c_int], c_int),
     "stu_conv_prefill_approx_static": ([_P, _P, _P, _LL, _LL, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
                                        c_int),
     "stu_taps_rev8": ([_P, _P, c_int, c_int, c_int, _P], c_int),

@@ -18,9 +18,17 @@ enum { BACKEND_AUTO = 0, BACKEND_SIMT = 1, BACKEND_TCGEN05 = 2, BACKEND_SKINNY =
 //               blocks resid_row_stride elements apart; resid itself is not read)
 // norm_w != NULL asks for x to be RMS-normalised (eps) on the way in; only the decode (skinny) path
 // fuses this, other shapes return STU_ERR_UNSUPPORTED so that the caller normalises separately.
+static int g_pdl = -1;   // -1: not decided yet (environment), 0 off, 1 on
 bool pdl_enabled() {
-  static const bool off = getenv("STU_B200_DISABLE_PDL") != nullptr;
-  return !off;
+  if (g_pdl < 0) g_pdl = getenv("STU_B200_DISABLE_PDL") ? 0 : 1;
+  return g_pdl != 0;
+}
+// Programmatic (overlapped) launches of the decode kernels on or off for the launches that follow; returns the
+// previous setting.  A captured CUDA graph keeps the setting it was captured with.
+extern "C" int stu_set_programmatic_launch(int on) {
+  const int prev = pdl_enabled() ? 1 : 0;
+  g_pdl = on ? 1 : 0;
+  return prev;
 }
 
 // Small-M shapes for which the tcgen05 GEMM beats the weight-streaming kernel.

@@ -206,6 +206,8 @@ __global__ void __launch_bounds__(256) swa_decode_kernel(const T* __restrict__ q
   const int d = H * HD;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane % LPK, grp = lane / LPK;
+  pdl_trigger();   // launched with the programmatic attribute: resident while the qkv projection drains
+  pdl_wait();
   const int t0 = pos[2 * b];
   if (update_cache) {
     // Every CTA has read its position before it arrives here; the last one to arrive moves all positions on.  Doing
@@ -340,8 +342,8 @@ static bool launch_swa_decode(const void* qkv, void* k_ring, void* v_ring, int* 
   if (hd % VPL || !aligned16(qkv) || !aligned16(k_ring) || !aligned16(v_ring) || !aligned16(out)) return false;
   dim3 grid(H, B);
 #define STU_SWA_DEC(LPK_)                                                                                        \
-  swa_decode_kernel<T, LPK_><<<grid, 256, 0, st>>>((const T*)qkv, (T*)k_ring, (T*)v_ring, pos, slopes, (T*)out, B, H, \
-                                                   W, window, scale, softcap, update_cache)
+  launch_maybe_overlapped(swa_decode_kernel<T, LPK_>, grid, dim3(256), 0, st, true, (const T*)qkv, (T*)k_ring,     \
+                          (T*)v_ring, pos, slopes, (T*)out, B, H, W, window, scale, softcap, update_cache)
   switch (hd / VPL) {
     case 4: STU_SWA_DEC(4); return true;
     case 8: STU_SWA_DEC(8); return true;

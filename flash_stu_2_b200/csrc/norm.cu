@@ -10,6 +10,10 @@ __global__ void __launch_bounds__(128) rmsnorm_kernel(const T* __restrict__ x, c
   constexpr int V = Elem<T>::VEC;
   const T* xr = x + (size_t)blockIdx.x * x_rstride;
   T* yr = y + (size_t)blockIdx.x * y_rstride;
+  // launched with the programmatic attribute: the CTAs are resident while the kernel before them drains, and the
+  // kernel after this one may bring its weights in meanwhile
+  pdl_trigger();
+  pdl_wait();
   float ss = 0.f;
   if (VECTOR) {
     for (int i = threadIdx.x * V; i < d; i += blockDim.x * V) {
@@ -50,10 +54,14 @@ static int launch_rmsnorm(const void* x, const void* w, void* y, int rows, int d
                           float eps, cudaStream_t st) {
   constexpr int V = Elem<T>::VEC;
   bool vec = (d % V == 0) && (xs % V == 0) && (ys % V == 0) && aligned16(x) && aligned16(w) && aligned16(y);
+  cudaError_t e;
   if (vec)
-    rmsnorm_kernel<T, true><<<rows, 128, 0, st>>>((const T*)x, (const T*)w, (T*)y, d, xs, ys, eps);
+    e = launch_maybe_overlapped(rmsnorm_kernel<T, true>, dim3(rows), dim3(128), 0, st, true, (const T*)x, (const T*)w,
+                                (T*)y, d, xs, ys, eps);
   else
-    rmsnorm_kernel<T, false><<<rows, 128, 0, st>>>((const T*)x, (const T*)w, (T*)y, d, xs, ys, eps);
+    e = launch_maybe_overlapped(rmsnorm_kernel<T, false>, dim3(rows), dim3(128), 0, st, true, (const T*)x,
+                                (const T*)w, (T*)y, d, xs, ys, eps);
+  if (e != cudaSuccess) return (int)e;
   STU_CHECK_LAUNCH();
   return STU_OK;
 }

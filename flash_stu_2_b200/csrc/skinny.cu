@@ -392,7 +392,7 @@ static int launch_skinny_bf16_mt(int MT, const void* A, long long lda, const voi
 
 bool skinny_stage_takes(int M, int N, int K, int epi, bool norm);
 int skinny_stage_dispatch(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N,
-                          int K, int epi, const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st);
+                          int K, int epi, const EpiArgs<bf16>& ep, const void* nw, float eps, int pdl, cudaStream_t st);
 bool skinny_wide_takes(int M, int N, int K, int epi, bool norm);
 int skinny_wide_dispatch(const void* A, long long lda, const void* B, long long ldb, int M, int N, int K, int epi,
                          const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st);
@@ -403,7 +403,7 @@ int skinny_dispatch(const void* A, long long lda, const void* B, long long ldb, 
     int MT = (M + 15) / 16;
     EpiArgs<bf16> e = ep.as<bf16>();
     if (skinny_stage_takes(M, N, K, epi, norm_w != nullptr))
-      return skinny_stage_dispatch(A, lda, B, ldb, B2, M, N, K, epi, e, norm_w, eps, st);
+      return skinny_stage_dispatch(A, lda, B, ldb, B2, M, N, K, epi, e, norm_w, eps, pdl, st);
     if (!B2 && skinny_wide_takes(M, N, K, epi, norm_w != nullptr))
       return skinny_wide_dispatch(A, lda, B, ldb, M, N, K, epi, e, norm_w, eps, st);
     switch (epi) {

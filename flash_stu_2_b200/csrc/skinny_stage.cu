@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(NW * 32, 1) skinny_stage_kernel(const bf16* __
                                                                   const bf16* __restrict__ W, long long ldb,
                                                                   const bf16* __restrict__ W2, int M, int N, int K,
                                                                   EpiArgs<bf16> ep, const bf16* __restrict__ nw,
-                                                                  float eps) {
+                                                                  float eps, int early_weights) {
   constexpr bool DUAL = (EPI == EPI_GELU_MUL);
   constexpr int NF = DUAL ? 16 : 32;   // output features per CTA
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -73,7 +73,29 @@ __global__ void __launch_bounds__(NW * 32, 1) skinny_stage_kernel(const bf16* __
   const int pitch = per * 32 + 32;   // elements
   bf16* xs = reinterpret_cast<bf16*>(smem_raw);
 
-  // ---- activations: one bulk copy per row, rows past M zero-filled by the threads
+  // ---- weights first: every chunk of this warp at once.  early_weights is the caller's promise that the kernel
+  // before this one in the stream does not write them; the loads then go out while that kernel is still running
+  // (programmatic launch), otherwise they wait for it like everything else.
+  const bf16* wrow[NT];
+  bool nvalid[NT];
+#pragma unroll
+  for (int j = 0; j < NT; j++) {
+    const int n = DUAL ? n0 + 8 * (j & 1) + g : n0 + 8 * j + g;
+    nvalid[j] = n < N;
+    wrow[j] = ((DUAL && j >= 2) ? W2 : W) + (size_t)(nvalid[j] ? n : 0) * ldb;
+  }
+  pdl_trigger();
+  if (!early_weights) pdl_wait();
+  uint4 wv[U][NT];
+#pragma unroll
+  for (int u = 0; u < U; u++) {
+    const int ch = c_begin + warp + NW * u;
+#pragma unroll
+    for (int j = 0; j < NT; j++)
+      wv[u][j] = (ch < c_end && nvalid[j]) ? ldg_stream(wrow[j] + (ch << 5) + q * 8) : make_uint4(0, 0, 0, 0);
+  }
+  // ---- activations: one bulk copy per row, rows past M zero-filled by the threads.  With the programmatic launch
+  // attribute everything above ran while the preceding kernel was still draining.
   if (threadIdx.x == 0) {
     tma::mbar_init(&s_bar, 1);
     s_abort = 0;
@@ -84,27 +106,11 @@ __global__ void __launch_bounds__(NW * 32, 1) skinny_stage_kernel(const bf16* __
     *reinterpret_cast<uint4*>(xs + (size_t)r * pitch + v * 8) = make_uint4(0, 0, 0, 0);
   }
   __syncthreads();
+  if (early_weights) pdl_wait();   // the activations are the output of the kernel before this one
   if (threadIdx.x == 0 && nch > 0) {
     tma::mbar_expect_tx(&s_bar, (uint32_t)M * nch * 64);
     for (int m = 0; m < M; m++)
       tma::bulk_load(xs + (size_t)m * pitch, x + (size_t)m * lda + c_begin * 32, nch * 64, &s_bar);
-  }
-  // ---- weights: every chunk of this warp at once
-  const bf16* wrow[NT];
-  bool nvalid[NT];
-#pragma unroll
-  for (int j = 0; j < NT; j++) {
-    const int n = DUAL ? n0 + 8 * (j & 1) + g : n0 + 8 * j + g;
-    nvalid[j] = n < N;
-    wrow[j] = ((DUAL && j >= 2) ? W2 : W) + (size_t)(nvalid[j] ? n : 0) * ldb;
-  }
-  uint4 wv[U][NT];
-#pragma unroll
-  for (int u = 0; u < U; u++) {
-    const int ch = c_begin + warp + NW * u;
-#pragma unroll
-    for (int j = 0; j < NT; j++)
-      wv[u][j] = (ch < c_end && nvalid[j]) ? ldg_stream(wrow[j] + (ch << 5) + q * 8) : make_uint4(0, 0, 0, 0);
   }
   float acc[NT][MT][4];
 #pragma unroll
@@ -209,7 +215,7 @@ __global__ void __launch_bounds__(NW * 32, 1) skinny_stage_kernel(const bf16* __
 
 template <int EPI, int MT, int KSPLIT>
 int launch_stage(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N, int K,
-                 const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st) {
+                 const EpiArgs<bf16>& ep, const void* nw, float eps, int early, cudaStream_t st) {
   constexpr int NF = (EPI == EPI_GELU_MUL) ? 16 : 32;
   const int per = ((K >> 5) + KSPLIT - 1) / KSPLIT;
   const size_t xs_bytes = (size_t)MT * 16 * (per * 32 + 32) * sizeof(bf16);
@@ -223,15 +229,17 @@ int launch_stage(const void* A, long long lda, const void* B, long long ldb, con
   cfg.blockDim = dim3(NW * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute at[1];
+  cudaLaunchAttribute at[2];
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = 1;
   at[0].val.clusterDim.y = KSPLIT;
   at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   e = cudaLaunchKernelEx(&cfg, kern, (const bf16*)A, lda, (const bf16*)B, ldb, (const bf16*)B2, M, N, K, ep,
-                         (const bf16*)nw, eps);
+                         (const bf16*)nw, eps, early);
   if (e != cudaSuccess) return (int)e;
   STU_CHECK_LAUNCH();
   return STU_OK;
@@ -239,12 +247,12 @@ int launch_stage(const void* A, long long lda, const void* B, long long ldb, con
 
 template <int EPI, int MT>
 int launch_stage_split(int ks, const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N,
-                       int K, const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st) {
+                       int K, const EpiArgs<bf16>& ep, const void* nw, float eps, int early, cudaStream_t st) {
   switch (ks) {
-    case 1: return launch_stage<EPI, MT, 1>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
-    case 2: return launch_stage<EPI, MT, 2>(A, lda, B, ldb, B2, M, N, K, ep, nullptr, eps, st);
-    case 4: return launch_stage<EPI, MT, 4>(A, lda, B, ldb, B2, M, N, K, ep, nullptr, eps, st);
-    case 8: return launch_stage<EPI, MT, 8>(A, lda, B, ldb, B2, M, N, K, ep, nullptr, eps, st);
+    case 1: return launch_stage<EPI, MT, 1>(A, lda, B, ldb, B2, M, N, K, ep, nw, eps, early, st);
+    case 2: return launch_stage<EPI, MT, 2>(A, lda, B, ldb, B2, M, N, K, ep, nullptr, eps, early, st);
+    case 4: return launch_stage<EPI, MT, 4>(A, lda, B, ldb, B2, M, N, K, ep, nullptr, eps, early, st);
+    case 8: return launch_stage<EPI, MT, 8>(A, lda, B, ldb, B2, M, N, K, ep, nullptr, eps, early, st);
   }
   return STU_ERR_UNSUPPORTED;
 }
@@ -266,16 +274,18 @@ bool skinny_stage_takes(int M, int N, int K, int epi, bool norm) {
 }
 
 int skinny_stage_dispatch(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N,
-                          int K, int epi, const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st) {
+                          int K, int epi, const EpiArgs<bf16>& ep, const void* nw, float eps, int pdl,
+                          cudaStream_t st) {
+  const int early = (pdl & STU_FLAG_OVERLAP) ? 1 : 0;
   int ks = 1;
   while (ks < 8 && ((K >> 5) + ks - 1) / ks > MAXC) ks *= 2;
   // short K: split further while that still leaves every warp a chunk and the grid is below one CTA per SM
   const int ctas = (N + (epi == EPI_GELU_MUL ? 16 : 32) - 1) / (epi == EPI_GELU_MUL ? 16 : 32);
   while (!nw && ks < 8 && ctas * ks < 148 && (K >> 5) / (2 * ks) >= NW) ks *= 2;
   switch (epi) {
-    case EPI_STORE: return launch_stage_split<EPI_STORE, 2>(ks, A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
-    case EPI_RESID: return launch_stage_split<EPI_RESID, 2>(ks, A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
-    case EPI_GELU_MUL: return launch_stage_split<EPI_GELU_MUL, 2>(ks, A, lda, B, ldb, B2, M, N, K, ep, nw, eps, st);
+    case EPI_STORE: return launch_stage_split<EPI_STORE, 2>(ks, A, lda, B, ldb, B2, M, N, K, ep, nw, eps, early, st);
+    case EPI_RESID: return launch_stage_split<EPI_RESID, 2>(ks, A, lda, B, ldb, B2, M, N, K, ep, nw, eps, early, st);
+    case EPI_GELU_MUL: return launch_stage_split<EPI_GELU_MUL, 2>(ks, A, lda, B, ldb, B2, M, N, K, ep, nw, eps, early, st);
   }
   return STU_ERR_UNSUPPORTED;
 }

@@ -64,6 +64,20 @@ __global__ void __launch_bounds__(NW * 32) skinny_wide_kernel(const bf16* __rest
   const int c_begin = KSPLIT > 1 ? (int)blockIdx.y * per : 0;
   const int c_end = KSPLIT > 1 ? min(nchunks_all, c_begin + per) : nchunks_all;
 
+  // The weights are nobody's output: the CTA asks for its whole slice (32 rows x its K range) towards L2 at once,
+  // and, launched with the programmatic attribute, does so while the kernel before it is still running.  Everything
+  // after the wait may read what that kernel wrote.
+  {
+    const int kb = c_begin << 5, ke = min(K, c_end << 5);
+    const int lines = (ke - kb + 63) >> 6;   // 128-byte lines per weight row
+    for (int i = threadIdx.x; i < 8 * NT * lines; i += NW * 32) {
+      const int r = i / lines, l = i - r * lines;
+      if (n0 + r < N) asm volatile("prefetch.global.L2 [%0];" ::"l"(W + (size_t)(n0 + r) * ldb + kb + l * 64));
+    }
+  }
+  pdl_trigger();
+  pdl_wait();
+
   if (NORM) {
     for (int m = warp; m < MT * 16; m += NW) {
       float r = 0.f;
@@ -188,13 +202,15 @@ int launch_wide_n(const void* A, long long lda, const void* B, long long ldb, in
   cfg.blockDim = dim3(NW * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute at[1];
+  cudaLaunchAttribute at[2];
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = 1;
   at[0].val.clusterDim.y = KSPLIT;
   at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   e = cudaLaunchKernelEx(&cfg, kern, (const bf16*)A, lda, (const bf16*)B, ldb, M, N, K, ep, (const bf16*)nw, eps);
   if (e != cudaSuccess) return (int)e;
   STU_CHECK_LAUNCH();

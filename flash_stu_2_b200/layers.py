@@ -125,7 +125,7 @@ class STULayer(nn.Module):
         if ops.can_fuse_norm(B, inter, d, ops.EPI_GELU_MUL, x.dtype):
             self.mlp.apply_residual(mid, mid, x2, norm_w=self.mlp_norm.weight, eps=self.mlp_norm.eps, overlap=True)
         else:
-            self.mlp.apply_residual(ops.rmsnorm(mid, self.mlp_norm.weight, self.mlp_norm.eps), mid, x2)
+            self.mlp.apply_residual(ops.rmsnorm(mid, self.mlp_norm.weight, self.mlp_norm.eps), mid, x2, overlap=True)
         return entry
 
     def forward(self, x: torch.Tensor, past_key_value=None, use_cache=False):
@@ -174,7 +174,7 @@ class AttentionLayer(nn.Module):
         if T == 1 and ops.can_fuse_norm(B, inter, d, ops.EPI_GELU_MUL, x.dtype):
             self.mlp.apply_residual(x2, x2, x2, norm_w=self.mlp_norm.weight, eps=self.mlp_norm.eps, overlap=True)
         else:
-            self.mlp.apply_residual(ops.rmsnorm(x2, self.mlp_norm.weight, self.mlp_norm.eps), x2, x2)
+            self.mlp.apply_residual(ops.rmsnorm(x2, self.mlp_norm.weight, self.mlp_norm.eps), x2, x2, overlap=(T == 1))
         if xc is not x:
             x.copy_(xc)
         if use_cache:

@@ -235,6 +235,12 @@ def conv_prefill_approx_tc5(hist, taps8, yT, x, t0: int, t_end: int):
     return x
 
 
+def set_programmatic_launch(on: bool) -> bool:
+    """Programmatic (overlapped) launches of the token-step kernels on or off for the launches that follow; returns the
+    previous setting.  A captured CUDA graph keeps the setting it was captured with."""
+    return bool(_lib.load().stu_set_programmatic_launch(int(bool(on))))
+
+
 def conv_prefill_timeline(words: Optional[torch.Tensor]):
     """Register (or, with None, remove) the int64 tensor of 128 words that receives the tcgen05 convolution's
     device-side time stamps; see stu_conv_prefill_set_timeline."""
@@ -300,15 +306,17 @@ def decode_approx_shard(x, norm_w, MinT, hist, taps8, pos, out, eps: float = RMS
 
 def decode_approx_projected(x, xp, hist, taps8, pos, out, add_residual: bool = True):
     """Decode step of an approx STU sub-layer whose projected input xp [B, d_ch] the caller computed as one GEMM:
-    appends xp to the cache, out = (x +) taps . history."""
+    appends xp to the cache, out = (x +) taps . history.  With overlap_decode the kernel starts its history stream
+    while the projection before it is still running and lets its own successor start at once."""
     _cuda(xp, hist, taps8, pos, out)
+    flags = (FLAG_OVERLAP | FLAG_EARLY_TRIGGER) if overlap_decode else 0
     B, dch, _, Lh = hist.shape
     assert xp.shape == (B, dch) and out.shape == (B, dch) and xp.stride(1) == 1 and out.stride(1) == 1
     assert hist.is_contiguous() and taps8.is_contiguous() and (x is not None or not add_residual)
     rc = _lib.load().stu_decode_approx_projected(_p(x), x.stride(0) if x is not None else 0, xp.data_ptr(),
                                                  xp.stride(0), hist.data_ptr(), taps8.data_ptr(), pos.data_ptr(),
                                                  out.data_ptr(), out.stride(0), B, dch, Lh, int(add_residual),
-                                                 status_word(xp.device).data_ptr(), _dt(xp), _stream())
+                                                 status_word(xp.device).data_ptr(), _dt(xp) | flags, _stream())
     _lib.check(rc, "stu_decode_approx_projected")
     _count()
     return out

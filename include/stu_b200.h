@@ -121,6 +121,14 @@ int stu_conv_prefill_approx_tc5(const void* hist, const void* taps8, void* yT, v
                                 long long x_tstride, int B, int d, int Lh, int y_Lh, int t0, int t_end, int* status,
                                 int dtype, void* stream);
 
+/* The token-step kernels (RMSNorm, the decode linears, the attention and STU decode kernels) are launched with the
+ * programmatic-stream-serialization attribute: each fetches its weights while the kernel before it drains and waits
+ * (griddepcontrol.wait) before it touches anything that kernel writes.  stu_set_programmatic_launch(0) turns the
+ * launches that follow back into plain stream-ordered ones (as STU_B200_DISABLE_PDL=1 does from the start) and
+ * returns the previous setting; a captured CUDA graph keeps what it was captured with.  No counterpart in the
+ * reference. */
+int stu_set_programmatic_launch(int on);
+
 /* Profiling aid of stu_conv_prefill_approx_tc5: while a device buffer of 128 64-bit words is registered, CTA 0 of
  * every launch writes nanosecond stamps of its first 8 units into it (16 words per unit: 0 accumulator free,
  * 1 first operands ready, 2 last MMA issued, 3 accumulator complete, 4 epilogue done; per phase: 5 stage free,
