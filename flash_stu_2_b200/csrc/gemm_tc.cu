@@ -11,6 +11,7 @@
 //
 // Every wait on an mbarrier is bounded: on expiry the waiter raises the status word, the CTA drains
 // its outstanding bulk copies (bounded as well), frees its TMEM and returns.
+#include <cooperative_groups.h>
 #include <cuda.h>
 #include <stdlib.h>
 
@@ -18,6 +19,8 @@
 #include "epilogue.cuh"
 
 int device_sm_count();   // SM count of the current device (cached per device)
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -444,6 +447,245 @@ int launch_tc(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& b2,
   return STU_OK;
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Token-step linear layers for 17..32 activation rows on the tensor cores, operands swapped: the WEIGHTS are the
+// 128-row operand (a tile = 128 output features, or 64 gate + 64 up rows of the same 64 features), the activation rows
+// the 32-column one, so every weight byte passes through shared memory exactly once and goes straight into
+// tcgen05.mma (M = 128, N = 32, K = 16); nothing is staged through registers and there is no cross-warp reduction.
+// The K range is split over the CTAs of a thread-block cluster (grid = tiles x KSPLIT, about one to two CTAs per SM,
+// 80 KB of operands in flight each); every CTA drains its 128 x 32 fp32 accumulator from tensor memory into its own
+// shared memory (token-major, conflict-free), the cluster synchronises, and every CTA sums the partial tiles of its
+// share of the tokens in a fixed order through distributed shared memory and runs their epilogue (coalesced along
+// the features).
+// Launched with the programmatic attribute: the successor is released once tensor memory has been allocated (a
+// co-resident successor that allocated first could otherwise block this kernel's allocation while waiting for it);
+// with early_weights (the caller's promise that the preceding kernel does not write the weights) the weight tiles of
+// the first stages are requested before griddepcontrol.wait, the activation tiles after it.
+constexpr int SU_BN = 32;
+constexpr int SU_B_BYTES = SU_BN * BK * 2;
+constexpr int SU_STAGE_BYTES = A_BYTES + SU_B_BYTES;
+
+// SU_STAGES: 4 (80 KB in flight, two CTAs per SM) for grids of more CTAs than SMs, 8 (160 KB) below that
+template <int EPI, int KSPLIT, int SU_STAGES>
+__global__ void __launch_bounds__(192, 1)
+    skinny_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmW2,
+                       const __grid_constant__ CUtensorMap tmX, int M, int N, int K, EpiArgs<bf16> ep, int* status,
+                       int early_weights, unsigned long long wait_ns) {
+  constexpr bool DUAL = (EPI == EPI_GELU_MUL);
+  constexpr int NF = DUAL ? 64 : 128;   // output features per tile
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  float* part = reinterpret_cast<float*>(smem + SU_STAGES * SU_STAGE_BYTES);   // [32 tokens][128 rows]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(part + SU_BN * BM);
+  uint64_t* empty_bar = full_bar + SU_STAGES;
+  uint64_t* tmem_full = empty_bar + SU_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* issued_ctr = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));
+  int* consumed_ctr = issued_ctr + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * NF;
+  const int num_kb = (K + BK - 1) / BK;
+  const int per = (num_kb + KSPLIT - 1) / KSPLIT;
+  const int kb0 = (int)blockIdx.y * per;
+  const int nkb = max(0, min(num_kb, kb0 + per) - kb0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < SU_STAGES; s++) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tmem_full, 1);
+    *abort_flag = 0;
+    *issued_ctr = 0;
+    *consumed_ctr = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(32));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();   // only now: this CTA holds its tensor memory
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer
+      auto load_w = [&](int s, int kb) {
+        unsigned char* sa = smem + s * SU_STAGE_BYTES;
+        if (DUAL) {   // 64 gate rows, then the 64 up rows of the same features
+          tma_load_2d(sa, &tmW, &full_bar[s], kb * BK, n0);
+          tma_load_2d(sa + A_BYTES / 2, &tmW2, &full_bar[s], kb * BK, n0);
+        } else {
+          tma_load_2d(sa, &tmW, &full_bar[s], kb * BK, n0);
+        }
+      };
+      auto load_x = [&](int s, int kb) {
+        tma_load_2d(smem + s * SU_STAGE_BYTES + A_BYTES, &tmX, &full_bar[s], kb * BK, 0);
+      };
+      const int pre = early_weights ? min(SU_STAGES, nkb) : 0;
+      for (int g = 0; g < pre; g++) {
+        mbar_expect_tx(&full_bar[g], SU_STAGE_BYTES);
+        load_w(g, kb0 + g);
+        *issued_ctr = g + 1;
+      }
+      pdl_wait();   // the activations are the output of the kernel before this one
+      for (int g = 0; g < pre; g++) load_x(g, kb0 + g);
+      for (int g = pre; g < nkb; g++) {
+        const int s = g % SU_STAGES;
+        const uint32_t ph = (uint32_t)(g / SU_STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, wait_ns)) break;
+        mbar_expect_tx(&full_bar[s], SU_STAGE_BYTES);
+        load_w(s, kb0 + g);
+        load_x(s, kb0 + g);
+        *issued_ctr = g + 1;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer
+      bool ok = true;
+      for (int g = 0; g < nkb; g++) {
+        const int s = g % SU_STAGES;
+        const uint32_t ph = (uint32_t)(g / SU_STAGES) & 1u;
+        if (!mbar_wait(&full_bar[s], ph, abort_flag, wait_ns)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t sa = smem_u32(smem + s * SU_STAGE_BYTES);
+        const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BK / 16; kk++) umma<SU_BN>(tmem_base, da + 2 * kk, db + 2 * kk, (g | kk) ? 1u : 0u);
+        umma_commit(&empty_bar[s]);
+        *consumed_ctr = g + 1;
+      }
+      if (ok && nkb > 0) umma_commit(tmem_full);
+    }
+  } else {
+    // ---------------- accumulator drain: TMEM lane quarter = warp % 4, one weight row per thread
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    uint32_t r[32];
+#pragma unroll
+    for (int c = 0; c < 32; c++) r[c] = 0u;
+    if (nkb > 0) {
+      bool ok = mbar_wait(tmem_full, 0, abort_flag, wait_ns);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 32; c++) part[c * BM + row] = __uint_as_float(r[c]);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
+  // ---- the partial tiles of the cluster meet in the first CTA (the role branches left the warps of the producer
+  // and of the MMA issuer diverged: they reconverge before the aligned cluster barrier)
+  __syncwarp();
+  __syncthreads();
+  cg::cluster_group cluster = cg::this_cluster();
+  if constexpr (KSPLIT > 1) cluster.sync();
+  {
+    // every CTA of the cluster sums and stores the tokens rank, rank + KSPLIT, ... of the tile (fixed order of the
+    // partial tiles, whoever sums them)
+    pdl_wait();   // returns at once (the producer waited before the first activation copy)
+    const int rank = KSPLIT > 1 ? (int)cluster.block_rank() : 0;
+    const float* parts[KSPLIT];
+#pragma unroll
+    for (int rk = 0; rk < KSPLIT; rk++) parts[rk] = KSPLIT > 1 ? cluster.map_shared_rank(part, rk) : part;
+    auto sum_at = [&](int idx) {
+      float v = parts[0][idx];
+#pragma unroll
+      for (int rk = 1; rk < KSPLIT; rk++) v += parts[rk][idx];
+      return v;
+    };
+    if (!*abort_flag) {
+      for (int e = threadIdx.x; e < (SU_BN / KSPLIT) * NF; e += 192) {
+        const int mi = e / NF, f = e - mi * NF, m = rank + mi * KSPLIT, n = n0 + f;
+        if (m < M && n < N)
+          epilogue_store<bf16, EPI>(ep, m, n, sum_at(m * BM + f), DUAL ? sum_at(m * BM + 64 + f) : 0.f);
+      }
+    }
+  }
+  if constexpr (KSPLIT > 1) cluster.sync(); else __syncthreads();   // the other CTAs' partial tiles stay alive until read
+  if (*abort_flag) {
+    if (threadIdx.x == 0) {
+      if (status) atomicExch(status, 3);
+      const int issued = *issued_ctr, consumed = *consumed_ctr;
+      const uint64_t drain_start = global_ns();
+      for (int g = consumed; g < issued; g++) {
+        const int s = g % SU_STAGES;
+        const uint32_t ph = (uint32_t)(g / SU_STAGES) & 1u;
+        for (uint32_t w = 0; w < WAIT_LIMIT; ++w) {
+          if (mbar_try_wait(&full_bar[s], ph)) break;
+          if ((w & 255u) == 255u && global_ns() - drain_start > wait_ns) break;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(32));
+  }
+}
+
+template <int EPI, int KSPLIT, int SU_STAGES>
+int launch_skinny_umma_st(const CUtensorMap& w, const CUtensorMap& w2, const CUtensorMap& x, int M, int N, int K,
+                       const EpiArgs<bf16>& ep, int early, int* status, cudaStream_t st) {
+  constexpr int NF = (EPI == EPI_GELU_MUL) ? 64 : 128;
+  const size_t smem = (size_t)SU_STAGES * SU_STAGE_BYTES + (size_t)SU_BN * BM * 4 + 1024 + 256;
+  auto kern = skinny_umma_kernel<EPI, KSPLIT, SU_STAGES>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((N + NF - 1) / NF, KSPLIT);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[2];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 1;
+  at[0].val.clusterDim.y = KSPLIT;
+  at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  e = cudaLaunchKernelEx(&cfg, kern, w, w2, x, M, N, K, ep, status, early, g_wait_ns);
+  if (e != cudaSuccess) return (int)e;
+  STU_CHECK_LAUNCH();
+  return STU_OK;
+}
+
+template <int EPI, int KSPLIT>
+int launch_skinny_umma(const CUtensorMap& w, const CUtensorMap& w2, const CUtensorMap& x, int M, int N, int K,
+                       const EpiArgs<bf16>& ep, int early, int* status, cudaStream_t st) {
+  constexpr int NF = (EPI == EPI_GELU_MUL) ? 64 : 128;
+  bool deep = 3 * ((N + NF - 1) / NF) * KSPLIT <= 2 * device_sm_count();
+  if (const char* sv = getenv("STU_B200_UMMA_STAGES")) deep = atoi(sv) == 8;   // tuning aid
+  if (!deep)
+    return launch_skinny_umma_st<EPI, KSPLIT, 4>(w, w2, x, M, N, K, ep, early, status, st);
+  return launch_skinny_umma_st<EPI, KSPLIT, 8>(w, w2, x, M, N, K, ep, early, status, st);
+}
+
+template <int EPI>
+int launch_skinny_umma_split(int ks, const CUtensorMap& w, const CUtensorMap& w2, const CUtensorMap& x, int M, int N,
+                             int K, const EpiArgs<bf16>& ep, int early, int* status, cudaStream_t st) {
+  switch (ks) {
+    case 1: return launch_skinny_umma<EPI, 1>(w, w2, x, M, N, K, ep, early, status, st);
+    case 2: return launch_skinny_umma<EPI, 2>(w, w2, x, M, N, K, ep, early, status, st);
+    case 4: return launch_skinny_umma<EPI, 4>(w, w2, x, M, N, K, ep, early, status, st);
+    default: return launch_skinny_umma<EPI, 8>(w, w2, x, M, N, K, ep, early, status, st);
+  }
+}
+
 }  // namespace
 
 // Per-device state of the library: the status word the host wrapper registered for the device that was current at
@@ -545,6 +787,41 @@ int gemm_tc_dispatch(const void* A, long long lda, const void* B, long long ldb,
     case EPI_RESID: return launch_tc<EPI_RESID, 6>(ma, mb, mb2, M, N, K, 0, causal, ep, device_status_word(), st);
     case EPI_GELU_MUL: return launch_tc<EPI_GELU_MUL, 4>(ma, mb, mb2, M, N, K, 0, 0, ep, device_status_word(), st);
     case EPI_BLOCKCOL: return launch_tc<EPI_BLOCKCOL, 6>(ma, mb, mb2, M, N, K, 0, causal, ep, device_status_word(), st);
+  }
+  return STU_ERR_UNSUPPORTED;
+}
+
+// Token-step linears of 17..32 rows on the tensor cores with swapped operands (skinny_umma_kernel).
+// STU_B200_DISABLE_UMMA_SKINNY=1 keeps them on the mma.sync weight-streaming kernels.
+bool skinny_umma_takes(int M, int N, int K, int epi, bool norm, bool peer) {
+  static const bool off = getenv("STU_B200_DISABLE_UMMA_SKINNY") != nullptr;
+  if (off || norm || peer) return false;
+  if (epi != EPI_STORE && epi != EPI_RESID && epi != EPI_GELU_MUL) return false;
+  return M > 16 && M <= 32 && K % 8 == 0 && K >= 128 && N >= 64;
+}
+
+int skinny_umma_dispatch(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N,
+                         int K, int epi, const EpiArgs<bf16>& ep, int pdl, cudaStream_t st) {
+  const bool dual = epi == EPI_GELU_MUL;
+  CUtensorMap mw, mw2, mx;
+  int rc = make_map(&mw, B, N, K, ldb, dual ? 64 : 128);
+  if (rc != STU_OK) return rc;
+  rc = make_map(&mw2, dual ? B2 : B, N, K, ldb, dual ? 64 : 128);
+  if (rc != STU_OK) return rc;
+  rc = make_map(&mx, A, M, K, lda, SU_BN);
+  if (rc != STU_OK) return rc;
+  // split K over a cluster until there is about one CTA per SM, every CTA keeping at least two 64-element blocks
+  const int tiles = (N + (dual ? 64 : 128) - 1) / (dual ? 64 : 128), num_kb = (K + BK - 1) / BK;
+  const int sms = device_sm_count();
+  int ks = 1;
+  while (ks < 8 && tiles * ks < sms - sms / 8 && num_kb / (2 * ks) >= 2) ks *= 2;
+  if (const char* kv = getenv("STU_B200_UMMA_KS")) ks = atoi(kv);   // tuning aid
+  const int early = (pdl & STU_FLAG_OVERLAP) ? 1 : 0;
+  int* status = device_status_word();
+  switch (epi) {
+    case EPI_STORE: return launch_skinny_umma_split<EPI_STORE>(ks, mw, mw2, mx, M, N, K, ep, early, status, st);
+    case EPI_RESID: return launch_skinny_umma_split<EPI_RESID>(ks, mw, mw2, mx, M, N, K, ep, early, status, st);
+    case EPI_GELU_MUL: return launch_skinny_umma_split<EPI_GELU_MUL>(ks, mw, mw2, mx, M, N, K, ep, early, status, st);
   }
   return STU_ERR_UNSUPPORTED;
 }

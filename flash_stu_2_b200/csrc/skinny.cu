@@ -393,6 +393,9 @@ static int launch_skinny_bf16_mt(int MT, const void* A, long long lda, const voi
 bool skinny_stage_takes(int M, int N, int K, int epi, bool norm);
 int skinny_stage_dispatch(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N,
                           int K, int epi, const EpiArgs<bf16>& ep, const void* nw, float eps, int pdl, cudaStream_t st);
+bool skinny_umma_takes(int M, int N, int K, int epi, bool norm, bool peer);
+int skinny_umma_dispatch(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N,
+                         int K, int epi, const EpiArgs<bf16>& ep, int pdl, cudaStream_t st);
 bool skinny_wide_takes(int M, int N, int K, int epi, bool norm);
 int skinny_wide_dispatch(const void* A, long long lda, const void* B, long long ldb, int M, int N, int K, int epi,
                          const EpiArgs<bf16>& ep, const void* nw, float eps, cudaStream_t st);
@@ -402,6 +405,8 @@ int skinny_dispatch(const void* A, long long lda, const void* B, long long ldb, 
   if (dtype == STU_BF16) {
     int MT = (M + 15) / 16;
     EpiArgs<bf16> e = ep.as<bf16>();
+    if (skinny_umma_takes(M, N, K, epi, norm_w != nullptr, e.peer != nullptr))
+      return skinny_umma_dispatch(A, lda, B, ldb, B2, M, N, K, epi, e, pdl, st);
     if (skinny_stage_takes(M, N, K, epi, norm_w != nullptr))
       return skinny_stage_dispatch(A, lda, B, ldb, B2, M, N, K, epi, e, norm_w, eps, pdl, st);
     if (!B2 && skinny_wide_takes(M, N, K, epi, norm_w != nullptr))

@@ -169,7 +169,8 @@ class AttentionLayer(nn.Module):
         else:
             xn = ops.rmsnorm(xc, self.attn_norm.weight, self.attn_norm.eps)
             y, entry = self.attn.attend(xn, past_key_value, use_cache)
-        ops.linear(y.view(B * T, d), self.attn.c_proj.weight, resid=x2, out=x2, epilogue=ops.EPI_RESID)
+        ov = ops.FLAG_OVERLAP if (T == 1 and ops.overlap_decode) else 0   # token step: weights fetched early
+        ops.linear(y.view(B * T, d), self.attn.c_proj.weight, resid=x2, out=x2, epilogue=ops.EPI_RESID | ov)
         inter = self.mlp.intermediate_size
         if T == 1 and ops.can_fuse_norm(B, inter, d, ops.EPI_GELU_MUL, x.dtype):
             self.mlp.apply_residual(x2, x2, x2, norm_w=self.mlp_norm.weight, eps=self.mlp_norm.eps, overlap=True)

@@ -347,7 +347,9 @@ class STU(nn.Module):
             if ops.can_fuse_norm(B, d, x2d.shape[1], ops.EPI_STORE, x2d.dtype):
                 xp = ops.linear(x2d, MinT, norm_w=norm_w, eps=eps)
             else:
-                xp = ops.linear(ops.rmsnorm(x2d, norm_w, eps), MinT)
+                # token step: MinT is nobody's output here, so its tiles may be requested while the norm kernel runs
+                xp = ops.linear(ops.rmsnorm(x2d, norm_w, eps), MinT,
+                                epilogue=ops.EPI_STORE | (ops.FLAG_OVERLAP if ops.overlap_decode else 0))
             ops.decode_approx_projected(x2d, xp, hist, taps8, pos, out2d)
         elif (STU.pipelined_decode and STU.tensor_core_decode and STU.shared_tap_decode and taps8 is not None
                 and uniform_pos(pos) and d % 8 == 0 and x2d.shape[1] % 8 == 0
@@ -427,7 +429,8 @@ class Attention(nn.Module):
         if norm_w is not None:
             qkv = ops.linear(xn.reshape(B * T, d), self.c_attn.weight, norm_w=norm_w, eps=eps).view(B, T, 3 * d)
         else:
-            qkv = ops.linear(xn.reshape(B * T, d), self.c_attn.weight).view(B, T, 3 * d)
+            ov = ops.FLAG_OVERLAP if (T == 1 and ops.overlap_decode) else 0   # token step: weights fetched early
+            qkv = ops.linear(xn.reshape(B * T, d), self.c_attn.weight, epilogue=ops.EPI_STORE | ov).view(B, T, 3 * d)
         if entry is None and use_cache:
             entry = self.new_cache(B, xn.device)
         if entry is not None:
