@@ -31,6 +31,8 @@ extern "C" int stu_set_programmatic_launch(int on) {
   return prev;
 }
 
+bool skinny_umma_takes(int M, int N, int K, int epi, bool norm, bool peer);   // gemm_tc.cu
+
 // Small-M shapes for which the tcgen05 GEMM beats the weight-streaming kernel.
 static bool prefers_tensor_gemm(int M, int N) { return (M >= 32 && N >= 5120) || (M >= 16 && N >= 32768); }
 
@@ -77,7 +79,9 @@ extern "C" int stu_linear(const void* x, long long x_row_stride, const void* W, 
     // 128-wide column tiles to fill the machine (measured cross-over on a B200, weights from HBM)
     // (gate/up at up to 32 rows stays on the weight-streaming side: its staged kernel keeps every SM pulling, while
     // 32 rows are a quarter of one 128-row tile for the tensor-core GEMM)
-    if (sk_ok && tc_ok && prefers_tensor_gemm(M, N) && !(epilogue == EPI_GELU_MUL && M <= 32 && K % 32 == 0))
+    // (17..64 rows stay on the weight-streaming side whatever N: there the weights are the tensor core's 128-row
+    // operand; LM head 32 x 200064 x 1536: 103.5 against 111.3 us)
+    if (sk_ok && tc_ok && prefers_tensor_gemm(M, N) && !skinny_umma_takes(M, N, K, epilogue, false, false))
       sk_ok = false;
     backend = sk_ok ? BACKEND_SKINNY : (tc_ok ? BACKEND_TCGEN05 : BACKEND_SIMT);
   }

@@ -449,9 +449,9 @@ int launch_tc(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& b2,
 
 
 // ------------------------------------------------------------------------------------------------
-// Token-step linear layers for 17..32 activation rows on the tensor cores, operands swapped: the WEIGHTS are the
+// Token-step linear layers for 17..64 activation rows on the tensor cores, operands swapped: the WEIGHTS are the
 // 128-row operand (a tile = 128 output features, or 64 gate + 64 up rows of the same 64 features), the activation rows
-// the 32-column one, so every weight byte passes through shared memory exactly once and goes straight into
+// the 32- or 64-column one, so every weight byte passes through shared memory exactly once and goes straight into
 // tcgen05.mma (M = 128, N = 32, K = 16); nothing is staged through registers and there is no cross-warp reduction.
 // The K range is split over the CTAs of a thread-block cluster (grid = tiles x KSPLIT, about one to two CTAs per SM,
 // 80 KB of operands in flight each); every CTA drains its 128 x 32 fp32 accumulator from tensor memory into its own
@@ -462,21 +462,21 @@ int launch_tc(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& b2,
 // co-resident successor that allocated first could otherwise block this kernel's allocation while waiting for it);
 // with early_weights (the caller's promise that the preceding kernel does not write the weights) the weight tiles of
 // the first stages are requested before griddepcontrol.wait, the activation tiles after it.
-constexpr int SU_BN = 32;
-constexpr int SU_B_BYTES = SU_BN * BK * 2;
-constexpr int SU_STAGE_BYTES = A_BYTES + SU_B_BYTES;
 
-// SU_STAGES: 4 (80 KB in flight, two CTAs per SM) for grids of more CTAs than SMs, 8 (160 KB) below that
-template <int EPI, int KSPLIT, int SU_STAGES>
+// SU_BN: activation rows per tile, 32 or 64 (the N of the MMA, the accumulator's columns).  SU_STAGES: ring depth;
+// the host picks a shallow ring (two CTAs per SM) for grids of more CTAs than SMs and a deep one below that.
+template <int EPI, int KSPLIT, int SU_STAGES, int SU_BN>
 __global__ void __launch_bounds__(192, 1)
     skinny_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmW2,
                        const __grid_constant__ CUtensorMap tmX, int M, int N, int K, EpiArgs<bf16> ep, int* status,
                        int early_weights, unsigned long long wait_ns) {
   constexpr bool DUAL = (EPI == EPI_GELU_MUL);
   constexpr int NF = DUAL ? 64 : 128;   // output features per tile
+  constexpr int SU_B_BYTES = SU_BN * BK * 2;
+  constexpr int SU_STAGE_BYTES = A_BYTES + SU_B_BYTES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  float* part = reinterpret_cast<float*>(smem + SU_STAGES * SU_STAGE_BYTES);   // [32 tokens][128 rows]
+  float* part = reinterpret_cast<float*>(smem + SU_STAGES * SU_STAGE_BYTES);   // [SU_BN tokens][128 rows]
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(part + SU_BN * BM);
   uint64_t* empty_bar = full_bar + SU_STAGES;
   uint64_t* tmem_full = empty_bar + SU_STAGES;
@@ -505,7 +505,7 @@ __global__ void __launch_bounds__(192, 1)
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"(32));
+                 "r"(SU_BN));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -569,20 +569,24 @@ __global__ void __launch_bounds__(192, 1)
     // ---------------- accumulator drain: TMEM lane quarter = warp % 4, one weight row per thread
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
-    uint32_t r[32];
-#pragma unroll
-    for (int c = 0; c < 32; c++) r[c] = 0u;
+    bool ok = true;
     if (nkb > 0) {
-      bool ok = mbar_wait(tmem_full, 0, abort_flag, wait_ns);
+      ok = mbar_wait(tmem_full, 0, abort_flag, wait_ns);
       ok = __all_sync(0xffffffffu, ok);
-      if (ok) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16), r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      }
+      if (ok) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
 #pragma unroll
-    for (int c = 0; c < 32; c++) part[c * BM + row] = __uint_as_float(r[c]);
+    for (int h = 0; h < SU_BN / 32; h++) {
+      uint32_t r[32];
+#pragma unroll
+      for (int c = 0; c < 32; c++) r[c] = 0u;
+      if (nkb > 0 && ok) {
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * 32), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      }
+#pragma unroll
+      for (int c = 0; c < 32; c++) part[(h * 32 + c) * BM + row] = __uint_as_float(r[c]);
+    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   }
   // ---- the partial tiles of the cluster meet in the first CTA (the role branches left the warps of the producer
@@ -632,16 +636,16 @@ __global__ void __launch_bounds__(192, 1)
   }
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(32));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(SU_BN));
   }
 }
 
-template <int EPI, int KSPLIT, int SU_STAGES>
+template <int EPI, int KSPLIT, int SU_STAGES, int SU_BN>
 int launch_skinny_umma_st(const CUtensorMap& w, const CUtensorMap& w2, const CUtensorMap& x, int M, int N, int K,
                        const EpiArgs<bf16>& ep, int early, int* status, cudaStream_t st) {
   constexpr int NF = (EPI == EPI_GELU_MUL) ? 64 : 128;
-  const size_t smem = (size_t)SU_STAGES * SU_STAGE_BYTES + (size_t)SU_BN * BM * 4 + 1024 + 256;
-  auto kern = skinny_umma_kernel<EPI, KSPLIT, SU_STAGES>;
+  const size_t smem = (size_t)SU_STAGES * (A_BYTES + SU_BN * BK * 2) + (size_t)SU_BN * BM * 4 + 1024 + 256;
+  auto kern = skinny_umma_kernel<EPI, KSPLIT, SU_STAGES, SU_BN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   cudaLaunchConfig_t cfg = {};
@@ -664,15 +668,19 @@ int launch_skinny_umma_st(const CUtensorMap& w, const CUtensorMap& w2, const CUt
   return STU_OK;
 }
 
+// ring depth: 32 rows: 4 stages of 20 KB (two CTAs per SM) or 8; 64 rows: 3 stages of 24 KB (two CTAs per SM) or 6
 template <int EPI, int KSPLIT>
 int launch_skinny_umma(const CUtensorMap& w, const CUtensorMap& w2, const CUtensorMap& x, int M, int N, int K,
                        const EpiArgs<bf16>& ep, int early, int* status, cudaStream_t st) {
   constexpr int NF = (EPI == EPI_GELU_MUL) ? 64 : 128;
   bool deep = 3 * ((N + NF - 1) / NF) * KSPLIT <= 2 * device_sm_count();
   if (const char* sv = getenv("STU_B200_UMMA_STAGES")) deep = atoi(sv) == 8;   // tuning aid
-  if (!deep)
-    return launch_skinny_umma_st<EPI, KSPLIT, 4>(w, w2, x, M, N, K, ep, early, status, st);
-  return launch_skinny_umma_st<EPI, KSPLIT, 8>(w, w2, x, M, N, K, ep, early, status, st);
+  if (M <= 32) {
+    if (!deep) return launch_skinny_umma_st<EPI, KSPLIT, 4, 32>(w, w2, x, M, N, K, ep, early, status, st);
+    return launch_skinny_umma_st<EPI, KSPLIT, 8, 32>(w, w2, x, M, N, K, ep, early, status, st);
+  }
+  if (!deep) return launch_skinny_umma_st<EPI, KSPLIT, 3, 64>(w, w2, x, M, N, K, ep, early, status, st);
+  return launch_skinny_umma_st<EPI, KSPLIT, 6, 64>(w, w2, x, M, N, K, ep, early, status, st);
 }
 
 template <int EPI>
@@ -791,13 +799,13 @@ int gemm_tc_dispatch(const void* A, long long lda, const void* B, long long ldb,
   return STU_ERR_UNSUPPORTED;
 }
 
-// Token-step linears of 17..32 rows on the tensor cores with swapped operands (skinny_umma_kernel).
+// Token-step linears of 17..64 rows on the tensor cores with swapped operands (skinny_umma_kernel).
 // STU_B200_DISABLE_UMMA_SKINNY=1 keeps them on the mma.sync weight-streaming kernels.
 bool skinny_umma_takes(int M, int N, int K, int epi, bool norm, bool peer) {
   static const bool off = getenv("STU_B200_DISABLE_UMMA_SKINNY") != nullptr;
   if (off || norm || peer) return false;
   if (epi != EPI_STORE && epi != EPI_RESID && epi != EPI_GELU_MUL) return false;
-  return M > 16 && M <= 32 && K % 8 == 0 && K >= 128 && N >= 64;
+  return M > 16 && M <= 64 && K % 8 == 0 && K >= 128 && N >= 64;
 }
 
 int skinny_umma_dispatch(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N,
@@ -808,7 +816,7 @@ int skinny_umma_dispatch(const void* A, long long lda, const void* B, long long 
   if (rc != STU_OK) return rc;
   rc = make_map(&mw2, dual ? B2 : B, N, K, ldb, dual ? 64 : 128);
   if (rc != STU_OK) return rc;
-  rc = make_map(&mx, A, M, K, lda, SU_BN);
+  rc = make_map(&mx, A, M, K, lda, M <= 32 ? 32 : 64);
   if (rc != STU_OK) return rc;
   // split K over a cluster until there is about one CTA per SM, every CTA keeping at least two 64-element blocks
   const int tiles = (N + (dual ? 64 : 128) - 1) / (dual ? 64 : 128), num_kb = (K + BK - 1) / BK;
