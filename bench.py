@@ -777,13 +777,15 @@ def tp_object(a, dev, world, rank):
            "decode_ms_per_token_step_nccl": dec_ms_nccl, "decode_ms_per_token_step_exchange_kernels": dec_ms_xchg,
            "tokens_equal_to_nccl_path": float((out[:, T0:] == out2[:, T0:]).float().mean()),
            "collectives": ("token steps: the all-gather after every STU shard and the all-reduce after every attention / "
-                           "MLP block are stores into the other ranks' inboxes from inside the producing kernels "
-                           "(peer memory over NVLink) + one combine kernel each; logits all-gather and prefill: NCCL; "
-                           "`decode_ms_per_token_step_nccl` = the same steps with NCCL collectives between the kernels"
+                           "MLP block are one exchange kernel each (rows stored into the other ranks' inboxes over "
+                           "NVLink peer memory, bounded wait, sum + residual + RMSNorm); logits all-gather and "
+                           "prefill: NCCL; `decode_ms_per_token_step_nccl` = the same steps with NCCL collectives "
+                           "between the kernels"
                            if fused else
                            "NCCL all-gather per STU layer, all-reduce per attention / MLP block, captured in the step "
-                           "graph (the default above 4 ranks); `decode_ms_per_token_step_exchange_kernels` = the same "
-                           "steps with the peer-memory exchange kernels")}
+                           "graph (the default above 4 ranks or above 256 KB per exchange); "
+                           "`decode_ms_per_token_step_exchange_kernels` = the same steps with the peer-memory "
+                           "exchange kernels")}
     del tp
     torch.cuda.empty_cache()
     # ---- parity of the sharded path on the reference's small hybrid fixtures (needs n_heads % ranks == 0)

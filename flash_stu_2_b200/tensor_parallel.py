@@ -261,6 +261,11 @@ class TensorParallelFlashSTU:
         """The peer buffers for token steps of B sequences (collective on first use; every rank makes the same calls)."""
         ok = (self.fused_exchange and self.world > 1 and self.device.type == "cuda" and self.dtype == torch.bfloat16
               and self.fused_decode and self.dl % 8 == 0 and B <= 64 and self.world <= 8)
+        # the default ("exchange") also follows the message size: above 256 KB per exchange (64 sequences of d=3072:
+        # 393 KB) NCCL between the kernels measured faster on two GPUs (8.90 against 9.26 ms per step), below it the
+        # exchange kernel does (32 sequences of d=1536, 98 KB: 2.16 against 2.39 ms)
+        if ok and self.fused_exchange == "exchange" and B * self.d * 2 > 256 * 1024:
+            ok = False
         if not ok:
             return None
         if self._exchange is None or self._exchange.rows != B:
