@@ -449,11 +449,11 @@ int launch_tc(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& b2,
 
 
 // ------------------------------------------------------------------------------------------------
-// Token-step linear layers for 17..64 activation rows on the tensor cores, operands swapped: the WEIGHTS are the
+// Token-step linear layers for 9..64 activation rows on the tensor cores, operands swapped: the WEIGHTS are the
 // 128-row operand (a tile = 128 output features, or 64 gate + 64 up rows of the same 64 features), the activation rows
-// the 32- or 64-column one, so every weight byte passes through shared memory exactly once and goes straight into
+// the 16-, 32- or 64-column one, so every weight byte passes through shared memory exactly once and goes straight into
 // tcgen05.mma (M = 128, N = 32, K = 16); nothing is staged through registers and there is no cross-warp reduction.
-// The K range is split over the CTAs of a thread-block cluster (grid = tiles x KSPLIT, about one to two CTAs per SM,
+// The K range is split over the CTAs of a thread-block cluster (up to 16; grid = tiles x KSPLIT, about one to two CTAs per SM,
 // 80 KB of operands in flight each); every CTA drains its 128 x 32 fp32 accumulator from tensor memory into its own
 // shared memory (token-major, conflict-free), the cluster synchronises, and every CTA sums the partial tiles of its
 // share of the tokens in a fixed order through distributed shared memory and runs their epilogue (coalesced along
@@ -463,7 +463,7 @@ int launch_tc(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& b2,
 // with early_weights (the caller's promise that the preceding kernel does not write the weights) the weight tiles of
 // the first stages are requested before griddepcontrol.wait, the activation tiles after it.
 
-// SU_BN: activation rows per tile, 32 or 64 (the N of the MMA, the accumulator's columns).  SU_STAGES: ring depth;
+// SU_BN: activation rows per tile, 16, 32 or 64 (the N of the MMA, the accumulator's columns).  SU_STAGES: ring depth;
 // the host picks a shallow ring (two CTAs per SM) for grids of more CTAs than SMs and a deep one below that.
 template <int EPI, int KSPLIT, int SU_STAGES, int SU_BN>
 __global__ void __launch_bounds__(192, 1)
@@ -505,7 +505,7 @@ __global__ void __launch_bounds__(192, 1)
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"(SU_BN));
+                 "r"(SU_BN < 32 ? 32 : SU_BN));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -576,7 +576,7 @@ __global__ void __launch_bounds__(192, 1)
       if (ok) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
 #pragma unroll
-    for (int h = 0; h < SU_BN / 32; h++) {
+    for (int h = 0; h < (SU_BN + 31) / 32; h++) {   // 16 rows: 32 columns are allocated, the upper 16 unused
       uint32_t r[32];
 #pragma unroll
       for (int c = 0; c < 32; c++) r[c] = 0u;
@@ -585,7 +585,7 @@ __global__ void __launch_bounds__(192, 1)
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       }
 #pragma unroll
-      for (int c = 0; c < 32; c++) part[(h * 32 + c) * BM + row] = __uint_as_float(r[c]);
+      for (int c = 0; c < (SU_BN < 32 ? SU_BN : 32); c++) part[(h * 32 + c) * BM + row] = __uint_as_float(r[c]);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   }
@@ -610,9 +610,9 @@ __global__ void __launch_bounds__(192, 1)
       return v;
     };
     if (!*abort_flag) {
-      for (int e = threadIdx.x; e < (SU_BN / KSPLIT) * NF; e += 192) {
+      for (int e = threadIdx.x; e < ((SU_BN + KSPLIT - 1) / KSPLIT) * NF; e += 192) {
         const int mi = e / NF, f = e - mi * NF, m = rank + mi * KSPLIT, n = n0 + f;
-        if (m < M && n < N)
+        if (m < M && m < SU_BN && n < N)
           epilogue_store<bf16, EPI>(ep, m, n, sum_at(m * BM + f), DUAL ? sum_at(m * BM + 64 + f) : 0.f);
       }
     }
@@ -636,7 +636,7 @@ __global__ void __launch_bounds__(192, 1)
   }
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(SU_BN));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(SU_BN < 32 ? 32 : SU_BN));
   }
 }
 
@@ -648,6 +648,10 @@ int launch_skinny_umma_st(const CUtensorMap& w, const CUtensorMap& w2, const CUt
   auto kern = skinny_umma_kernel<EPI, KSPLIT, SU_STAGES, SU_BN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
+  if (KSPLIT > 8) {   // clusters of 16 CTAs are outside the portable range
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return (int)e;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((N + NF - 1) / NF, KSPLIT);
   cfg.blockDim = dim3(192);
@@ -668,13 +672,18 @@ int launch_skinny_umma_st(const CUtensorMap& w, const CUtensorMap& w2, const CUt
   return STU_OK;
 }
 
-// ring depth: 32 rows: 4 stages of 20 KB (two CTAs per SM) or 8; 64 rows: 3 stages of 24 KB (two CTAs per SM) or 6
+// ring depth: 16 rows: 5 stages of 18 KB (two CTAs per SM) or 10; 32 rows: 4 stages of 20 KB or 8; 64 rows: 3 stages
+// of 24 KB or 6
 template <int EPI, int KSPLIT>
 int launch_skinny_umma(const CUtensorMap& w, const CUtensorMap& w2, const CUtensorMap& x, int M, int N, int K,
                        const EpiArgs<bf16>& ep, int early, int* status, cudaStream_t st) {
   constexpr int NF = (EPI == EPI_GELU_MUL) ? 64 : 128;
   bool deep = 3 * ((N + NF - 1) / NF) * KSPLIT <= 2 * device_sm_count();
   if (const char* sv = getenv("STU_B200_UMMA_STAGES")) deep = atoi(sv) == 8;   // tuning aid
+  if (M <= 16) {
+    if (!deep) return launch_skinny_umma_st<EPI, KSPLIT, 5, 16>(w, w2, x, M, N, K, ep, early, status, st);
+    return launch_skinny_umma_st<EPI, KSPLIT, 10, 16>(w, w2, x, M, N, K, ep, early, status, st);
+  }
   if (M <= 32) {
     if (!deep) return launch_skinny_umma_st<EPI, KSPLIT, 4, 32>(w, w2, x, M, N, K, ep, early, status, st);
     return launch_skinny_umma_st<EPI, KSPLIT, 8, 32>(w, w2, x, M, N, K, ep, early, status, st);
@@ -690,6 +699,7 @@ int launch_skinny_umma_split(int ks, const CUtensorMap& w, const CUtensorMap& w2
     case 1: return launch_skinny_umma<EPI, 1>(w, w2, x, M, N, K, ep, early, status, st);
     case 2: return launch_skinny_umma<EPI, 2>(w, w2, x, M, N, K, ep, early, status, st);
     case 4: return launch_skinny_umma<EPI, 4>(w, w2, x, M, N, K, ep, early, status, st);
+    case 16: return launch_skinny_umma<EPI, 16>(w, w2, x, M, N, K, ep, early, status, st);
     default: return launch_skinny_umma<EPI, 8>(w, w2, x, M, N, K, ep, early, status, st);
   }
 }
@@ -799,13 +809,16 @@ int gemm_tc_dispatch(const void* A, long long lda, const void* B, long long ldb,
   return STU_ERR_UNSUPPORTED;
 }
 
-// Token-step linears of 17..64 rows on the tensor cores with swapped operands (skinny_umma_kernel).
+// Token-step linears of 9..64 rows on the tensor cores with swapped operands (skinny_umma_kernel).
 // STU_B200_DISABLE_UMMA_SKINNY=1 keeps them on the mma.sync weight-streaming kernels.
 bool skinny_umma_takes(int M, int N, int K, int epi, bool norm, bool peer) {
   static const bool off = getenv("STU_B200_DISABLE_UMMA_SKINNY") != nullptr;
   if (off || norm || peer) return false;
   if (epi != EPI_STORE && epi != EPI_RESID && epi != EPI_GELU_MUL) return false;
-  return M > 16 && M <= 64 && K % 8 == 0 && K >= 128 && N >= 64;
+  // up to 8 rows the 8-feature mma.sync kernel is faster (8 x 4096 x 1024 gate/up 6.0 against 6.3 us, down 4.5 against
+  // 5.8 us); from 9 rows on this kernel is (16 rows: gate/up 6144 x 1536 14.2 -> 10.1 us, down 12.6 -> 7.9 us)
+  static const int min_rows = getenv("STU_B200_UMMA_MIN_ROWS") ? atoi(getenv("STU_B200_UMMA_MIN_ROWS")) : 9;   // tuning aid
+  return M >= min_rows && M <= 64 && K % 8 == 0 && K >= 128 && N >= 64;
 }
 
 int skinny_umma_dispatch(const void* A, long long lda, const void* B, long long ldb, const void* B2, int M, int N,
@@ -816,13 +829,15 @@ int skinny_umma_dispatch(const void* A, long long lda, const void* B, long long 
   if (rc != STU_OK) return rc;
   rc = make_map(&mw2, dual ? B2 : B, N, K, ldb, dual ? 64 : 128);
   if (rc != STU_OK) return rc;
-  rc = make_map(&mx, A, M, K, lda, M <= 32 ? 32 : 64);
+  rc = make_map(&mx, A, M, K, lda, M <= 16 ? 16 : (M <= 32 ? 32 : 64));
   if (rc != STU_OK) return rc;
   // split K over a cluster until there is about one CTA per SM, every CTA keeping at least two 64-element blocks
+  // (six for the step from 8 to 16 CTAs per cluster: down 1536 x 6144 at 32 rows 8.4 -> 7.8 us, the 16 x 1024 x 49152
+  // contraction of the distilled-LDS features 31.9 -> 21.8 us, but c_proj 1536 x 1536 5.2 -> 5.6 us)
   const int tiles = (N + (dual ? 64 : 128) - 1) / (dual ? 64 : 128), num_kb = (K + BK - 1) / BK;
   const int sms = device_sm_count();
   int ks = 1;
-  while (ks < 8 && tiles * ks < sms - sms / 8 && num_kb / (2 * ks) >= 2) ks *= 2;
+  while (ks < 16 && tiles * ks < sms - sms / 8 && num_kb / (2 * ks) >= (ks >= 8 ? 6 : 2)) ks *= 2;
   if (const char* kv = getenv("STU_B200_UMMA_KS")) ks = atoi(kv);   // tuning aid
   const int early = (pdl & STU_FLAG_OVERLAP) ? 1 : 0;
   int* status = device_status_word();

@@ -252,8 +252,7 @@ int device_sm_count();
 // 17..64 rows, store / residual epilogue.  STU_B200_DISABLE_WIDE_SKINNY=1 keeps the 8-feature kernel.
 bool skinny_wide_takes(int M, int N, int K, int epi, bool norm) {
   static const bool off = getenv("STU_B200_DISABLE_WIDE_SKINNY") != nullptr;
-  // (9..16 rows stay with the 8-feature kernel: for the 16 x 1024 x 49152 contraction of the distilled-LDS features
-  // this kernel's 128 CTAs measured 1.48 ms per 12-layer token step against 1.12 ms)
+  // (asked only for shapes the tcgen05 kernel of gemm_tc.cu does not take: fused norm, peer stores, odd strides)
   (void)norm;
   return !off && M > 16 && M <= 64 && (epi == EPI_STORE || epi == EPI_RESID) && N >= 8 * NT && K >= 256;
 }
