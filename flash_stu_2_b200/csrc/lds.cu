@@ -64,44 +64,75 @@ __global__ void __launch_bounds__(256) lds_final_state_kernel(const T* __restric
 }
 
 // One recurrent step: h <- A (.) h + B (.) x_t, then U[b][f*d + i] = round(sum_n h[n] C[n,f]).
-// One warp per (b,i).  The state update is spread over the lanes by mode (lane, lane+32, ...); for the contraction
-// the warp puts its new state into shared memory and the lanes switch to features: lane f walks the D modes with
-// the state as a broadcast read and C[n][f] as a conflict-free row read, so no cross-lane reduction is needed.
+// Over the B*d channels the contraction is a [rows x D] . [D x F] product in float64: it runs on the float64 tensor
+// path (mma.sync m8n8k4), a warp owning 8 consecutive channels.  Lane (r = lane / 4, c = lane % 4) updates the modes
+// 4s + c of channel r - exactly the element of the A fragment it has to supply for K step s - so the new state goes
+// from the update straight into the MMA without passing through shared memory; C sits in shared memory as float64
+// with a row pitch of F + 4 (the four rows of a B fragment then fall on distinct banks).  One K step: 32 bytes of
+// state per channel read and written (whole sectors), 6 MMAs for 48 features.  (The first form of this kernel gave a
+// warp one channel and its lanes the features: 2 * D float64 FMAs per lane, each with a shared-memory read of C and a
+// float -> double conversion; the 12-layer stack spent most of its token step there.)
+constexpr int LDS_NTF = LDS_MAXF / 8;   // n-tiles of 8 features
+
+__device__ __forceinline__ void dmma_884(double& c0, double& c1, double a, double b) {
+  asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+               : "+d"(c0), "+d"(c1)
+               : "d"(a), "d"(b));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) lds_decode_kernel(const T* __restrict__ x, long long x_rstride,
                                                          double* __restrict__ h, const double* __restrict__ A,
                                                          const double* __restrict__ Bv, const T* __restrict__ C,
                                                          T* __restrict__ U, int B, int d, int D, int F) {
   extern __shared__ __align__(16) unsigned char lds_smem[];
-  double* st_s = reinterpret_cast<double*>(lds_smem);            // [8 warps][D]
-  float* Cs = reinterpret_cast<float*>(st_s + 8 * D);            // [D][F]
-  for (int e = threadIdx.x; e < D * F; e += 256) Cs[e] = Elem<T>::to_f(C[e]);
-  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const bool rok = row < B * d;
-  const int b = rok ? row / d : 0, i = rok ? row - b * d : 0;
-  if (rok) {
-    const double xv = (double)Elem<T>::to_f(x[(size_t)b * x_rstride + i]);
-    for (int n = lane; n < D; n += 32) {
-      const double v = fma(A[n], h[(size_t)row * D + n], Bv[n] * xv);
-      h[(size_t)row * D + n] = v;
-      st_s[warp * D + n] = v;
-    }
+  const int Dp = (D + 3) & ~3, Fp = 8 * ((F + 7) / 8) + 4;
+  double* Cs = reinterpret_cast<double*>(lds_smem);   // [Dp][Fp], zero outside [D][F]
+  double* As = Cs + (size_t)Dp * Fp;                  // [Dp]
+  double* Bs = As + Dp;                               // [Dp]
+  for (int e = threadIdx.x; e < Dp * Fp; e += 256) {
+    const int n = e / Fp, f = e - n * Fp;
+    Cs[e] = (n < D && f < F) ? (double)Elem<T>::to_f(C[n * F + f]) : 0.0;
+  }
+  for (int n = threadIdx.x; n < Dp; n += 256) {
+    As[n] = n < D ? A[n] : 0.0;
+    Bs[n] = n < D ? Bv[n] : 0.0;
   }
   __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r = lane >> 2, c = lane & 3;
+  const int rows = B * d;
+  const int row = (blockIdx.x * 8 + warp) * 8 + r;
+  const bool rok = row < rows;
+  const int b = rok ? row / d : 0, i = rok ? row - b * d : 0;
+  const double xv = rok ? (double)Elem<T>::to_f(x[(size_t)b * x_rstride + i]) : 0.0;
+  double* hr = h + (size_t)(rok ? row : 0) * D;
+  const int ntf = (F + 7) >> 3;
+  double acc[LDS_NTF][2];
+#pragma unroll
+  for (int j = 0; j < LDS_NTF; j++) acc[j][0] = acc[j][1] = 0.0;
+#pragma unroll 4
+  for (int k0 = 0; k0 < Dp; k0 += 4) {
+    const int n = k0 + c;
+    double v = 0.0;
+    if (rok && n < D) {
+      v = fma(As[n], hr[n], Bs[n] * xv);
+      hr[n] = v;
+    }
+    const double* crow = Cs + (size_t)n * Fp + r;   // B fragment: C[k0 + c][8j + r]
+#pragma unroll
+    for (int j = 0; j < LDS_NTF; j++)
+      if (j < ntf) dmma_884(acc[j][0], acc[j][1], v, crow[8 * j]);
+  }
+  // accumulator: channel r, features 8j + 2c and 8j + 2c + 1
   if (rok) {
-    const double* sw = st_s + warp * D;
-    for (int f = lane; f < F; f += 32) {
-      double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
-      int n = 0;
-      for (; n + 4 <= D; n += 4) {
-        a0 = fma(sw[n], (double)Cs[n * F + f], a0);
-        a1 = fma(sw[n + 1], (double)Cs[(n + 1) * F + f], a1);
-        a2 = fma(sw[n + 2], (double)Cs[(n + 2) * F + f], a2);
-        a3 = fma(sw[n + 3], (double)Cs[(n + 3) * F + f], a3);
+#pragma unroll
+    for (int j = 0; j < LDS_NTF; j++) {
+#pragma unroll
+      for (int q = 0; q < 2; q++) {
+        const int f = 8 * j + 2 * c + q;
+        if (j < ntf && f < F) U[(size_t)b * F * d + (size_t)f * d + i] = Elem<T>::from_f((float)acc[j][q]);
       }
-      for (; n < D; n++) a0 = fma(sw[n], (double)Cs[n * F + f], a0);
-      U[(size_t)b * F * d + (size_t)f * d + i] = Elem<T>::from_f((float)((a0 + a1) + (a2 + a3)));
     }
   }
 }
@@ -287,18 +318,19 @@ extern "C" int stu_lds_decode_features(const void* x, long long x_row_stride, do
   if (!x || !h || !A || !Bv || !C || !U) return STU_ERR_NULL;
   if (B <= 0 || d <= 0 || D <= 0 || D > LDS_MAXD || F <= 0 || F > LDS_MAXF) return STU_ERR_SHAPE;
   const int rows = B * d;
-  const size_t smem = (size_t)D * F * sizeof(float) + (size_t)8 * D * sizeof(double);
+  const int Dp = (D + 3) & ~3, Fp = 8 * ((F + 7) / 8) + 4;
+  const size_t smem = ((size_t)Dp * Fp + 2 * (size_t)Dp) * sizeof(double);
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
   if (dtype == STU_F32) {
     e = cudaFuncSetAttribute(lds_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    lds_decode_kernel<float><<<(rows + 7) / 8, 256, smem, st>>>((const float*)x, x_row_stride, h, A, Bv,
+    lds_decode_kernel<float><<<(rows + 63) / 64, 256, smem, st>>>((const float*)x, x_row_stride, h, A, Bv,
                                                                 (const float*)C, (float*)U, B, d, D, F);
   } else if (dtype == STU_BF16) {
     e = cudaFuncSetAttribute(lds_decode_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    lds_decode_kernel<bf16><<<(rows + 7) / 8, 256, smem, st>>>((const bf16*)x, x_row_stride, h, A, Bv, (const bf16*)C,
+    lds_decode_kernel<bf16><<<(rows + 63) / 64, 256, smem, st>>>((const bf16*)x, x_row_stride, h, A, Bv, (const bf16*)C,
                                                                (bf16*)U, B, d, D, F);
   } else {
     return STU_ERR_DTYPE;
