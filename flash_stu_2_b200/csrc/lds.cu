@@ -111,18 +111,29 @@ __global__ void __launch_bounds__(256) lds_decode_kernel(const T* __restrict__ x
   double acc[LDS_NTF][2];
 #pragma unroll
   for (int j = 0; j < LDS_NTF; j++) acc[j][0] = acc[j][1] = 0.0;
-#pragma unroll 4
-  for (int k0 = 0; k0 < Dp; k0 += 4) {
-    const int n = k0 + c;
-    double v = 0.0;
-    if (rok && n < D) {
-      v = fma(As[n], hr[n], Bs[n] * xv);
-      hr[n] = v;
-    }
-    const double* crow = Cs + (size_t)n * Fp + r;   // B fragment: C[k0 + c][8j + r]
+  // 16 K steps at a time: all their state loads go out before the first is used (64 bytes x 16 in flight per lane)
+  for (int kc = 0; kc < Dp; kc += 64) {
+    double hv[16];
 #pragma unroll
-    for (int j = 0; j < LDS_NTF; j++)
-      if (j < ntf) dmma_884(acc[j][0], acc[j][1], v, crow[8 * j]);
+    for (int u = 0; u < 16; u++) {
+      const int n = kc + 4 * u + c;
+      hv[u] = (rok && n < D) ? hr[n] : 0.0;
+    }
+#pragma unroll
+    for (int u = 0; u < 16; u++) {
+      const int n = kc + 4 * u + c;
+      if (kc + 4 * u < Dp) {   // warp-uniform
+        double v = 0.0;
+        if (rok && n < D) {
+          v = fma(As[n], hv[u], Bs[n] * xv);
+          hr[n] = v;
+        }
+        const double* crow = Cs + (size_t)n * Fp + r;   // B fragment: C[4s + c][8j + r]
+#pragma unroll
+        for (int j = 0; j < LDS_NTF; j++)
+          if (j < ntf) dmma_884(acc[j][0], acc[j][1], v, crow[8 * j]);
+      }
+    }
   }
   // accumulator: channel r, features 8j + 2c and 8j + 2c + 1
   if (rok) {
