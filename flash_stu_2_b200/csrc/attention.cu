@@ -172,7 +172,8 @@ __global__ void __launch_bounds__(256) kv_ring_write_kernel(const T* __restrict_
 // 8 * 32/LPK groups of the CTA are merged once at the end through shared memory.  The new token's key and
 // value come from the qkv activations; the CTA then stores them into ring slot t % W for its head (no one reads
 // that slot in this launch: it held key t-W, outside the window), and the last CTA advances the positions.
-constexpr int DEC_U = 4;  // warp-wide key loads (and as many value loads) in flight per warp
+constexpr int DEC_U = 4;  // warp-wide key copies (and as many value copies) per round; two rounds in flight
+constexpr int DEC_RING_BYTES = 2 * DEC_U * 2 * 256 * 16;
 
 template <typename T> struct Vec16 {
   uint4 raw;
@@ -239,25 +240,50 @@ __global__ void __launch_bounds__(256) swa_decode_kernel(const T* __restrict__ q
 #pragma unroll
   for (int e = 0; e < VPL; e++) acc[e] = 0.f;
   const size_t ring_b = (size_t)b * W;
-  for (int base = warp * KPW; base < nkeys; base += 8 * KPW * DEC_U) {  // warp-uniform
+  // Keys and values travel global -> shared memory by 16-byte asynchronous copies, two rounds of DEC_U keys (and
+  // values) in flight per thread: every thread copies into slots of its own and reads them back itself, so the ring
+  // needs no barrier, and the bytes in flight are bounded by shared memory (64 KB per CTA), not by registers.
+  extern __shared__ uint4 dec_ring[];   // [2 stages][DEC_U][key | value][256 threads]
+  const int first = warp * KPW;
+  const int niter = first < nkeys ? (nkeys - first + 8 * KPW * DEC_U - 1) / (8 * KPW * DEC_U) : 0;   // warp-uniform
+  auto issue = [&](int it, int stage) {
+    if (it < niter) {
+#pragma unroll
+      for (int u = 0; u < DEC_U; u++) {
+        const int kk = first + it * 8 * KPW * DEC_U + u * 8 * KPW + grp;
+        const bool ok = kk < nkeys;
+        const int j = j_lo + kk;
+        const T *ks, *vs;
+        if (ok && j == t0) {   // the new token's key and value come from the qkv activations
+          ks = cur + d + sub * VPL;
+          vs = cur + 2 * d + sub * VPL;
+        } else {
+          const size_t off = (ring_b + (size_t)(ok ? j % W : 0)) * d + h * HD + sub * VPL;
+          ks = k_ring + off;
+          vs = v_ring + off;
+        }
+        const unsigned nbytes = ok ? 16u : 0u;   // 0: the slot is filled with zeros
+        const unsigned kd = (unsigned)__cvta_generic_to_shared(&dec_ring[((stage * DEC_U + u) * 2 + 0) * 256 + threadIdx.x]);
+        const unsigned vd = (unsigned)__cvta_generic_to_shared(&dec_ring[((stage * DEC_U + u) * 2 + 1) * 256 + threadIdx.x]);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kd), "l"(ks), "r"(nbytes) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vd), "l"(vs), "r"(nbytes) : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");   // one group per call, empty past the end
+  };
+  issue(0, 0);
+  issue(1, 1);
+  for (int it = 0; it < niter; it++) {  // warp-uniform
+    const int base = first + it * 8 * KPW * DEC_U;
+    const int stage = it & 1;
+    asm volatile("cp.async.wait_group 1;" ::: "memory");   // round `it` has landed, round it + 1 may be in flight
     Vec16<T> kr[DEC_U], vr[DEC_U];
 #pragma unroll
     for (int u = 0; u < DEC_U; u++) {
-      const int kk = base + u * 8 * KPW + grp;
-      kr[u].raw = make_uint4(0, 0, 0, 0);
-      vr[u].raw = make_uint4(0, 0, 0, 0);
-      if (kk < nkeys) {
-        const int j = j_lo + kk;
-        if (j == t0) {
-          kr[u].raw = *reinterpret_cast<const uint4*>(cur + d + sub * VPL);
-          vr[u].raw = *reinterpret_cast<const uint4*>(cur + 2 * d + sub * VPL);
-        } else {
-          const size_t off = (ring_b + (size_t)(j % W)) * d + h * HD + sub * VPL;
-          kr[u].raw = *reinterpret_cast<const uint4*>(k_ring + off);
-          vr[u].raw = *reinterpret_cast<const uint4*>(v_ring + off);
-        }
-      }
+      kr[u].raw = dec_ring[((stage * DEC_U + u) * 2 + 0) * 256 + threadIdx.x];
+      vr[u].raw = dec_ring[((stage * DEC_U + u) * 2 + 1) * 256 + threadIdx.x];
     }
+    issue(it + 2, stage);   // refill the slots just read
     // scores of the DEC_U keys of this group first, then ONE rescale of the running sums for all of them
     float sc[DEC_U];
 #pragma unroll
@@ -342,8 +368,10 @@ static bool launch_swa_decode(const void* qkv, void* k_ring, void* v_ring, int* 
   if (hd % VPL || !aligned16(qkv) || !aligned16(k_ring) || !aligned16(v_ring) || !aligned16(out)) return false;
   dim3 grid(H, B);
 #define STU_SWA_DEC(LPK_)                                                                                        \
-  launch_maybe_overlapped(swa_decode_kernel<T, LPK_>, grid, dim3(256), 0, st, true, (const T*)qkv, (T*)k_ring,     \
-                          (T*)v_ring, pos, slopes, (T*)out, B, H, W, window, scale, softcap, update_cache)
+  cudaFuncSetAttribute(swa_decode_kernel<T, LPK_>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_RING_BYTES);    \
+  launch_maybe_overlapped(swa_decode_kernel<T, LPK_>, grid, dim3(256), DEC_RING_BYTES, st, true, (const T*)qkv,     \
+                          (T*)k_ring, (T*)v_ring, pos, slopes, (T*)out, B, H, W, window, scale, softcap,            \
+                          update_cache)
   switch (hd / VPL) {
     case 4: STU_SWA_DEC(4); return true;
     case 8: STU_SWA_DEC(8); return true;
