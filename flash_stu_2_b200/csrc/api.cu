@@ -127,6 +127,7 @@ extern "C" int stu_linear_can_fuse_norm(int M, int N, int K, int epilogue, int d
   // 17..64 rows: every CTA would recompute the statistics of all rows (the 32-feature kernel from L2, the staged
   // gate/up kernel from its shared-memory copy); a separate norm kernel measured faster both times (24-layer model,
   // B = 32: 2.17 against 2.27 ms per token step, and 2.19 against 2.30 ms).  The kernels accept norm_w all the same.
+  // (a fused norm inside the tcgen05 token-step kernel measured slower as well: 2.12-2.25 against 1.71-1.85 ms)
   if (M > 16) return 0;
   return 1;
 }

@@ -463,37 +463,43 @@ int launch_tc(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& b2,
 // with early_weights (the caller's promise that the preceding kernel does not write the weights) the weight tiles of
 // the first stages are requested before griddepcontrol.wait, the activation tiles after it.
 
-// SU_BN: activation rows per tile, 16, 32 or 64 (the N of the MMA, the accumulator's columns).  SU_STAGES: ring depth;
-// the host picks a shallow ring (two CTAs per SM) for grids of more CTAs than SMs and a deep one below that.
-template <int EPI, int KSPLIT, int SU_STAGES, int SU_BN>
+// SU_BN: activation rows per tile, 16, 32 or 64 (the N of the MMA, the accumulator's columns).  nstages: ring depth,
+// chosen by the host: shallow (two CTAs per SM) for grids of more CTAs than SMs, deep below that.
+// (A fused RMSNorm - the drain warps normalising the rows into swizzled shared-memory tiles while the weight stream
+// runs, bit-identical to the norm kernel - was built and measured: the 24-layer token step went from 1.71-1.85 ms
+// to 2.12-2.25 ms, the MMAs waiting for 32 rows of statistics that a separate, overlapped norm kernel has long
+// finished.  Callers keep the separate norm kernel.)
+constexpr int SU_MAXST = 10;
+template <int EPI, int KSPLIT, int SU_BN>
 __global__ void __launch_bounds__(192, 1)
     skinny_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmW2,
                        const __grid_constant__ CUtensorMap tmX, int M, int N, int K, EpiArgs<bf16> ep, int* status,
-                       int early_weights, unsigned long long wait_ns) {
+                       int early_weights, unsigned long long wait_ns, int nstages) {
   constexpr bool DUAL = (EPI == EPI_GELU_MUL);
   constexpr int NF = DUAL ? 64 : 128;   // output features per tile
   constexpr int SU_B_BYTES = SU_BN * BK * 2;
-  constexpr int SU_STAGE_BYTES = A_BYTES + SU_B_BYTES;
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  float* part = reinterpret_cast<float*>(smem + SU_STAGES * SU_STAGE_BYTES);   // [SU_BN tokens][128 rows]
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(part + SU_BN * BM);
-  uint64_t* empty_bar = full_bar + SU_STAGES;
-  uint64_t* tmem_full = empty_bar + SU_STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* issued_ctr = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));
-  int* consumed_ctr = issued_ctr + 1;
-
+  constexpr int PART_BYTES = SU_BN * BM * 4;
+  constexpr int stage_bytes = A_BYTES + SU_B_BYTES;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * NF;
   const int num_kb = (K + BK - 1) / BK;
   const int per = (num_kb + KSPLIT - 1) / KSPLIT;
   const int kb0 = (int)blockIdx.y * per;
   const int nkb = max(0, min(num_kb, kb0 + per) - kb0);
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  // ring | partial tile | barriers
+  float* part = reinterpret_cast<float*>(smem + nstages * stage_bytes);   // [SU_BN tokens][128 rows]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + nstages * stage_bytes + PART_BYTES);
+  uint64_t* empty_bar = full_bar + SU_MAXST;
+  uint64_t* tmem_full = empty_bar + SU_MAXST;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* issued_ctr = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));
+  int* consumed_ctr = issued_ctr + 1;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < SU_STAGES; s++) {
+    for (int s = 0; s < nstages; s++) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -518,7 +524,7 @@ __global__ void __launch_bounds__(192, 1)
     if (lane == 0) {
       // ---------------- TMA producer
       auto load_w = [&](int s, int kb) {
-        unsigned char* sa = smem + s * SU_STAGE_BYTES;
+        unsigned char* sa = smem + s * stage_bytes;
         if (DUAL) {   // 64 gate rows, then the 64 up rows of the same features
           tma_load_2d(sa, &tmW, &full_bar[s], kb * BK, n0);
           tma_load_2d(sa + A_BYTES / 2, &tmW2, &full_bar[s], kb * BK, n0);
@@ -527,21 +533,21 @@ __global__ void __launch_bounds__(192, 1)
         }
       };
       auto load_x = [&](int s, int kb) {
-        tma_load_2d(smem + s * SU_STAGE_BYTES + A_BYTES, &tmX, &full_bar[s], kb * BK, 0);
+        tma_load_2d(smem + s * stage_bytes + A_BYTES, &tmX, &full_bar[s], kb * BK, 0);
       };
-      const int pre = early_weights ? min(SU_STAGES, nkb) : 0;
+      const int pre = early_weights ? min(nstages, nkb) : 0;
       for (int g = 0; g < pre; g++) {
-        mbar_expect_tx(&full_bar[g], SU_STAGE_BYTES);
+        mbar_expect_tx(&full_bar[g], stage_bytes);
         load_w(g, kb0 + g);
         *issued_ctr = g + 1;
       }
       pdl_wait();   // the activations are the output of the kernel before this one
       for (int g = 0; g < pre; g++) load_x(g, kb0 + g);
       for (int g = pre; g < nkb; g++) {
-        const int s = g % SU_STAGES;
-        const uint32_t ph = (uint32_t)(g / SU_STAGES) & 1u;
+        const int s = g % nstages;
+        const uint32_t ph = (uint32_t)(g / nstages) & 1u;
         if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, wait_ns)) break;
-        mbar_expect_tx(&full_bar[s], SU_STAGE_BYTES);
+        mbar_expect_tx(&full_bar[s], stage_bytes);
         load_w(s, kb0 + g);
         load_x(s, kb0 + g);
         *issued_ctr = g + 1;
@@ -551,12 +557,12 @@ __global__ void __launch_bounds__(192, 1)
     if (lane == 0) {
       // ---------------- MMA issuer
       bool ok = true;
-      for (int g = 0; g < nkb; g++) {
-        const int s = g % SU_STAGES;
-        const uint32_t ph = (uint32_t)(g / SU_STAGES) & 1u;
+      for (int g = 0; ok && g < nkb; g++) {
+        const int s = g % nstages;
+        const uint32_t ph = (uint32_t)(g / nstages) & 1u;
         if (!mbar_wait(&full_bar[s], ph, abort_flag, wait_ns)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t sa = smem_u32(smem + s * SU_STAGE_BYTES);
+        const uint32_t sa = smem_u32(smem + s * stage_bytes);
         const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
 #pragma unroll
         for (int kk = 0; kk < BK / 16; kk++) umma<SU_BN>(tmem_base, da + 2 * kk, db + 2 * kk, (g | kk) ? 1u : 0u);
@@ -589,8 +595,8 @@ __global__ void __launch_bounds__(192, 1)
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   }
-  // ---- the partial tiles of the cluster meet in the first CTA (the role branches left the warps of the producer
-  // and of the MMA issuer diverged: they reconverge before the aligned cluster barrier)
+  // ---- the partial tiles of the cluster meet (the role branches left the warps of the producer and of the MMA
+  // issuer diverged: they reconverge before the aligned cluster barrier)
   __syncwarp();
   __syncthreads();
   cg::cluster_group cluster = cg::this_cluster();
@@ -624,8 +630,8 @@ __global__ void __launch_bounds__(192, 1)
       const int issued = *issued_ctr, consumed = *consumed_ctr;
       const uint64_t drain_start = global_ns();
       for (int g = consumed; g < issued; g++) {
-        const int s = g % SU_STAGES;
-        const uint32_t ph = (uint32_t)(g / SU_STAGES) & 1u;
+        const int s = g % nstages;
+        const uint32_t ph = (uint32_t)(g / nstages) & 1u;
         for (uint32_t w = 0; w < WAIT_LIMIT; ++w) {
           if (mbar_try_wait(&full_bar[s], ph)) break;
           if ((w & 255u) == 255u && global_ns() - drain_start > wait_ns) break;
@@ -640,12 +646,30 @@ __global__ void __launch_bounds__(192, 1)
   }
 }
 
-template <int EPI, int KSPLIT, int SU_STAGES, int SU_BN>
-int launch_skinny_umma_st(const CUtensorMap& w, const CUtensorMap& w2, const CUtensorMap& x, int M, int N, int K,
+// Shared memory of one CTA: ring, partial tile, barriers and bookkeeping, alignment slack.
+template <int SU_BN>
+size_t su_smem_bytes(int nstages) {
+  return (size_t)nstages * (A_BYTES + SU_BN * BK * 2) + (size_t)SU_BN * BM * 4 + (2 * SU_MAXST + 1) * 8 + 64 + 1024;
+}
+
+template <int EPI, int KSPLIT, int SU_BN>
+int launch_skinny_umma(const CUtensorMap& w, const CUtensorMap& w2, const CUtensorMap& x, int M, int N, int K,
                        const EpiArgs<bf16>& ep, int early, int* status, cudaStream_t st) {
   constexpr int NF = (EPI == EPI_GELU_MUL) ? 64 : 128;
-  const size_t smem = (size_t)SU_STAGES * (A_BYTES + SU_BN * BK * 2) + (size_t)SU_BN * BM * 4 + 1024 + 256;
-  auto kern = skinny_umma_kernel<EPI, KSPLIT, SU_STAGES, SU_BN>;
+  const int tiles = (N + NF - 1) / NF;
+  // ring depth: deep (about 160 KB of weights in flight, one CTA per SM) for grids that leave a third of the SMs
+  // empty anyway, else as deep as lets two CTAs share an SM
+  bool deep = 3 * tiles * KSPLIT <= 2 * device_sm_count();
+  if (const char* sv = getenv("STU_B200_UMMA_STAGES")) deep = atoi(sv) == 8;   // tuning aid
+  const size_t two_per_sm = (233472 / 2) - 1024;   // per-SM shared memory, per-CTA reservation
+  int nstages = deep ? (SU_BN == 16 ? 10 : (SU_BN == 32 ? 8 : 6)) : 2;
+  if (!deep)
+    while (nstages < SU_MAXST && su_smem_bytes<SU_BN>(nstages + 1) <= two_per_sm) nstages++;
+  while (nstages > 2 && su_smem_bytes<SU_BN>(nstages) > 227 * 1024) nstages--;
+  if (su_smem_bytes<SU_BN>(nstages) > 227 * 1024) return STU_ERR_UNSUPPORTED;
+  if (!deep && nstages > 5) nstages = 5;
+  const size_t smem = su_smem_bytes<SU_BN>(nstages);
+  auto kern = skinny_umma_kernel<EPI, KSPLIT, SU_BN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   if (KSPLIT > 8) {   // clusters of 16 CTAs are outside the portable range
@@ -653,7 +677,7 @@ int launch_skinny_umma_st(const CUtensorMap& w, const CUtensorMap& w2, const CUt
     if (e != cudaSuccess) return (int)e;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((N + NF - 1) / NF, KSPLIT);
+  cfg.gridDim = dim3(tiles, KSPLIT);
   cfg.blockDim = dim3(192);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
@@ -666,41 +690,30 @@ int launch_skinny_umma_st(const CUtensorMap& w, const CUtensorMap& w2, const CUt
   at[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
-  e = cudaLaunchKernelEx(&cfg, kern, w, w2, x, M, N, K, ep, status, early, g_wait_ns);
+  e = cudaLaunchKernelEx(&cfg, kern, w, w2, x, M, N, K, ep, status, early, g_wait_ns, nstages);
   if (e != cudaSuccess) return (int)e;
   STU_CHECK_LAUNCH();
   return STU_OK;
 }
 
-// ring depth: 16 rows: 5 stages of 18 KB (two CTAs per SM) or 10; 32 rows: 4 stages of 20 KB or 8; 64 rows: 3 stages
-// of 24 KB or 6
 template <int EPI, int KSPLIT>
-int launch_skinny_umma(const CUtensorMap& w, const CUtensorMap& w2, const CUtensorMap& x, int M, int N, int K,
-                       const EpiArgs<bf16>& ep, int early, int* status, cudaStream_t st) {
-  constexpr int NF = (EPI == EPI_GELU_MUL) ? 64 : 128;
-  bool deep = 3 * ((N + NF - 1) / NF) * KSPLIT <= 2 * device_sm_count();
-  if (const char* sv = getenv("STU_B200_UMMA_STAGES")) deep = atoi(sv) == 8;   // tuning aid
-  if (M <= 16) {
-    if (!deep) return launch_skinny_umma_st<EPI, KSPLIT, 5, 16>(w, w2, x, M, N, K, ep, early, status, st);
-    return launch_skinny_umma_st<EPI, KSPLIT, 10, 16>(w, w2, x, M, N, K, ep, early, status, st);
-  }
-  if (M <= 32) {
-    if (!deep) return launch_skinny_umma_st<EPI, KSPLIT, 4, 32>(w, w2, x, M, N, K, ep, early, status, st);
-    return launch_skinny_umma_st<EPI, KSPLIT, 8, 32>(w, w2, x, M, N, K, ep, early, status, st);
-  }
-  if (!deep) return launch_skinny_umma_st<EPI, KSPLIT, 3, 64>(w, w2, x, M, N, K, ep, early, status, st);
-  return launch_skinny_umma_st<EPI, KSPLIT, 6, 64>(w, w2, x, M, N, K, ep, early, status, st);
+int launch_skinny_umma_bn(const CUtensorMap& w, const CUtensorMap& w2, const CUtensorMap& x, int M, int N, int K,
+                          const EpiArgs<bf16>& ep, int early, int* status, cudaStream_t st) {
+  if (M <= 16) return launch_skinny_umma<EPI, KSPLIT, 16>(w, w2, x, M, N, K, ep, early, status, st);
+  if (M <= 32) return launch_skinny_umma<EPI, KSPLIT, 32>(w, w2, x, M, N, K, ep, early, status, st);
+  return launch_skinny_umma<EPI, KSPLIT, 64>(w, w2, x, M, N, K, ep, early, status, st);
 }
 
 template <int EPI>
 int launch_skinny_umma_split(int ks, const CUtensorMap& w, const CUtensorMap& w2, const CUtensorMap& x, int M, int N,
-                             int K, const EpiArgs<bf16>& ep, int early, int* status, cudaStream_t st) {
+                             int K, const EpiArgs<bf16>& ep, int early, int* status,
+                             cudaStream_t st) {
   switch (ks) {
-    case 1: return launch_skinny_umma<EPI, 1>(w, w2, x, M, N, K, ep, early, status, st);
-    case 2: return launch_skinny_umma<EPI, 2>(w, w2, x, M, N, K, ep, early, status, st);
-    case 4: return launch_skinny_umma<EPI, 4>(w, w2, x, M, N, K, ep, early, status, st);
-    case 16: return launch_skinny_umma<EPI, 16>(w, w2, x, M, N, K, ep, early, status, st);
-    default: return launch_skinny_umma<EPI, 8>(w, w2, x, M, N, K, ep, early, status, st);
+    case 1: return launch_skinny_umma_bn<EPI, 1>(w, w2, x, M, N, K, ep, early, status, st);
+    case 2: return launch_skinny_umma_bn<EPI, 2>(w, w2, x, M, N, K, ep, early, status, st);
+    case 4: return launch_skinny_umma_bn<EPI, 4>(w, w2, x, M, N, K, ep, early, status, st);
+    case 16: return launch_skinny_umma_bn<EPI, 16>(w, w2, x, M, N, K, ep, early, status, st);
+    default: return launch_skinny_umma_bn<EPI, 8>(w, w2, x, M, N, K, ep, early, status, st);
   }
 }
 
@@ -813,7 +826,7 @@ int gemm_tc_dispatch(const void* A, long long lda, const void* B, long long ldb,
 // STU_B200_DISABLE_UMMA_SKINNY=1 keeps them on the mma.sync weight-streaming kernels.
 bool skinny_umma_takes(int M, int N, int K, int epi, bool norm, bool peer) {
   static const bool off = getenv("STU_B200_DISABLE_UMMA_SKINNY") != nullptr;
-  if (off || norm || peer) return false;
+  if (off || peer || norm) return false;
   if (epi != EPI_STORE && epi != EPI_RESID && epi != EPI_GELU_MUL) return false;
   // up to 8 rows the 8-feature mma.sync kernel is faster (8 x 4096 x 1024 gate/up 6.0 against 6.3 us, down 4.5 against
   // 5.8 us); from 9 rows on this kernel is (16 rows: gate/up 6144 x 1536 14.2 -> 10.1 us, down 12.6 -> 7.9 us)
@@ -844,7 +857,8 @@ int skinny_umma_dispatch(const void* A, long long lda, const void* B, long long 
   switch (epi) {
     case EPI_STORE: return launch_skinny_umma_split<EPI_STORE>(ks, mw, mw2, mx, M, N, K, ep, early, status, st);
     case EPI_RESID: return launch_skinny_umma_split<EPI_RESID>(ks, mw, mw2, mx, M, N, K, ep, early, status, st);
-    case EPI_GELU_MUL: return launch_skinny_umma_split<EPI_GELU_MUL>(ks, mw, mw2, mx, M, N, K, ep, early, status, st);
+    case EPI_GELU_MUL:
+      return launch_skinny_umma_split<EPI_GELU_MUL>(ks, mw, mw2, mx, M, N, K, ep, early, status, st);
   }
   return STU_ERR_UNSUPPORTED;
 }
