@@ -23,6 +23,9 @@ import sys
 import threading
 import time
 
+# stdout carries the one JSON line: whatever NCCL logs (its version banner, NCCL_DEBUG output) goes to stderr
+os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+
 import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))

@@ -689,6 +689,14 @@ int launch_skinny_umma(const CUtensorMap& w, const CUtensorMap& w2, const CUtens
   at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
+  cfg.numAttrs = 1;
+  if (KSPLIT > 8) {   // can the GPU co-schedule a cluster of this size and footprint at all?  (the caller falls back)
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess || clusters < 1) {
+      (void)cudaGetLastError();
+      return STU_ERR_UNSUPPORTED;
+    }
+  }
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
   e = cudaLaunchKernelEx(&cfg, kern, w, w2, x, M, N, K, ep, status, early, g_wait_ns, nstages);
   if (e != cudaSuccess) return (int)e;
@@ -712,7 +720,10 @@ int launch_skinny_umma_split(int ks, const CUtensorMap& w, const CUtensorMap& w2
     case 1: return launch_skinny_umma_bn<EPI, 1>(w, w2, x, M, N, K, ep, early, status, st);
     case 2: return launch_skinny_umma_bn<EPI, 2>(w, w2, x, M, N, K, ep, early, status, st);
     case 4: return launch_skinny_umma_bn<EPI, 4>(w, w2, x, M, N, K, ep, early, status, st);
-    case 16: return launch_skinny_umma_bn<EPI, 16>(w, w2, x, M, N, K, ep, early, status, st);
+    case 16: {
+      const int rc = launch_skinny_umma_bn<EPI, 16>(w, w2, x, M, N, K, ep, early, status, st);
+      if (rc != STU_ERR_UNSUPPORTED) return rc;   // no room for clusters of 16 on this GPU: clusters of 8
+    }
     default: return launch_skinny_umma_bn<EPI, 8>(w, w2, x, M, N, K, ep, early, status, st);
   }
 }
