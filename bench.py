@@ -23,9 +23,6 @@ import sys
 import threading
 import time
 
-# stdout carries the one JSON line: whatever NCCL logs (its version banner, NCCL_DEBUG output) goes to stderr
-os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-
 import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -1081,6 +1078,11 @@ def run_model(a):
 
 
 if __name__ == "__main__":
+    # stdout carries the one JSON line: Python's prints keep the original stream, while whatever native libraries write
+    # to file descriptor 1 (NCCL's version banner) is sent to stderr
+    sys.stdout.flush()
+    sys.stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     args = parse()
     if args.impl != "reference":
         from flash_stu_2_b200 import ops as _ops
