@@ -50,6 +50,26 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert lib.stu_conv_prefill_approx_tc5(a, a, a, a, 333 * 8, 8, 1, 8, 256, 168, 0, 333, None, 0, None) == -1
 
 
+def test_programmatic_launch_switch_round_trips_without_a_gpu():
+    """stu_set_programmatic_launch returns the previous setting; the token-step kernels read it at launch time."""
+    from flash_stu_2_b200 import ops
+    prev = ops.set_programmatic_launch(False)
+    try:
+        assert ops.set_programmatic_launch(True) is False
+        assert ops.set_programmatic_launch(True) is True
+    finally:
+        ops.set_programmatic_launch(prev)
+
+
+def test_linear_bench_module_imports_without_a_gpu():
+    import torch
+    import flash_stu_2_b200.linear_bench as lb
+    if torch.cuda.is_available():
+        pytest.skip("with a GPU the module would run its measurement")
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        lb.main([])
+
+
 def test_ops_refuse_cpu_tensors():
     import torch
     from flash_stu_2_b200 import ops
