@@ -70,8 +70,10 @@ int stu_embed(const long long* ids, const void* table, void* out, int rows, int 
  *               [tokens, F*d] operand of the contraction with M (stu_lds.py:389-393)
  *   norm_w     when non-NULL, x is RMS-normalised with this weight (eps) inside the kernel; only fused for
  *              decode shapes (see stu_linear_can_fuse_norm), otherwise -4.
- *   backend    0 auto (M<=64: weight-streaming mma.sync/FMA kernel; bf16 aligned: tcgen05+TMA GEMM; else
- *              CUDA-core GEMM), 1 CUDA-core, 2 tcgen05, 3 decode kernel. */
+ *   backend    0 auto (M<=64: the token-step kernels - bf16 with 9..64 rows: tcgen05 with the weights as the 128-row
+ *              operand and K split over a thread-block cluster; up to 8 rows, fp32 or a fused norm: weight-streaming
+ *              mma.sync/FMA kernels; larger M, bf16 aligned: tcgen05+TMA GEMM; else CUDA-core GEMM),
+ *              1 CUDA-core, 2 tcgen05 GEMM, 3 token-step kernels. */
 /* epilogue flags: 0x100 = W is lower triangular (k-blocks above the diagonal are skipped); 0x200 = launch with
  * programmatic stream serialization: the kernel fetches W (which the preceding kernel must not write) while that
  * kernel drains, and reads x only after it has completed (skinny shapes, M <= 64; ignored otherwise);
