@@ -408,7 +408,45 @@ EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D map over a row-major bf16 matrix [rows, cols] with row stride ld (elements); box 64 x box_rows, 128B swizzle.
+// A map depends on nothing but these arguments, so the encoded maps are kept in a small per-thread table keyed by
+// them (a token step asks for the same few dozen maps over and over; an entry never goes stale, it is just an address
+// and a shape).
+struct MapKey {
+  const void* base;
+  long long rows, cols, ld;
+  int box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int MAP_SLOTS = 1024;   // direct-mapped
+int make_map_uncached(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows);
 int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows = BM) {
+  static thread_local MapSlot* table = nullptr;
+  if (!table) table = new MapSlot[MAP_SLOTS]();
+  const MapKey key{base, rows, cols, ld, box_rows};
+  unsigned long long h = (unsigned long long)(uintptr_t)base * 0x9E3779B97F4A7C15ull;
+  h ^= (unsigned long long)rows * 0xC2B2AE3D27D4EB4Full + (unsigned long long)cols * 0x165667B19E3779F9ull +
+       (unsigned long long)ld * 0x27D4EB2F165667C5ull + (unsigned long long)box_rows;
+  MapSlot& slot = table[(h >> 20) % MAP_SLOTS];
+  if (slot.used && slot.key == key) {
+    *map = slot.map;
+    return STU_OK;
+  }
+  const int rc = make_map_uncached(map, base, rows, cols, ld, box_rows);
+  if (rc == STU_OK) {
+    slot.key = key;
+    slot.map = *map;
+    slot.used = true;
+  }
+  return rc;
+}
+int make_map_uncached(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return STU_ERR_UNSUPPORTED;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
