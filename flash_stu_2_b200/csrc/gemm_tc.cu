@@ -762,6 +762,7 @@ int launch_skinny_umma_split(int ks, const CUtensorMap& w, const CUtensorMap& w2
       const int rc = launch_skinny_umma_bn<EPI, 16>(w, w2, x, M, N, K, ep, early, status, st);
       if (rc != STU_ERR_UNSUPPORTED) return rc;   // no room for clusters of 16 on this GPU: clusters of 8
     }
+      [[fallthrough]];
     default: return launch_skinny_umma_bn<EPI, 8>(w, w2, x, M, N, K, ep, early, status, st);
   }
 }
